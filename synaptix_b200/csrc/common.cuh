@@ -1,0 +1,77 @@
+// Shared helpers of the sm_100a kernels: dtype codes, loads/stores with 32-bit math,
+// reductions with a fixed order, launch-error reporting.
+//
+// Every exported function is `extern "C" int sx_*(..., cudaStream_t stream)` and returns
+// 0 or a cudaError_t of the launch (never of the kernel's execution: nothing synchronises).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define SX_F32 0
+#define SX_BF16 1
+
+// error codes of argument checks (outside cudaError_t's range)
+#define SX_ERR_DTYPE 10001
+#define SX_ERR_SIZE 10002
+#define SX_ERR_ALIGN 10003
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> struct sx_type;
+template <> struct sx_type<float> { static constexpr int code = SX_F32; };
+template <> struct sx_type<bf16> { static constexpr int code = SX_BF16; };
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum with a fixed order (lanes by butterfly, then warps in index order).
+// `red` is shared memory of at least 33 floats. All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int i = 0; i < nwarp; ++i) s += red[i];
+    red[32] = s;
+  }
+  __syncthreads();
+  return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarp = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = red[0];
+    for (int i = 1; i < nwarp; ++i) s = fmaxf(s, red[i]);
+    red[32] = s;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+static inline int sx_launch_status() { return (int)cudaGetLastError(); }
+
+#define SX_PAGE 64

@@ -1,0 +1,427 @@
+// Plain kernels for every operation of a decoder step, for float32 and bfloat16 storage,
+// all arithmetic in 32-bit (FFMA only: no tensor cores, no TF32).  They take every size;
+// they are the whole of the float32 path, and the fallback of the bfloat16 path for sizes
+// that the fast kernels refuse.
+//
+// What they compute follows the reference's formulas:
+//   embedding   crates/synaptix-kernels-cuda/src/cu/embed/embed.cu:18-46
+//   RMSNorm     crates/synaptix-kernels-cuda/src/cu/reduction/rms_norm.cu:26-98 (plain gain w)
+//   residual    crates/synaptix-kernels-cuda/src/cu/fused/norm/rmsnorm_residual.cu:97-159
+//   rotary      crates/synaptix-kernels-cuda/src/cu/elementwise/rope.cu:27-118 (rotate-half)
+//   KV append   crates/synaptix-kernels-cuda/src/cu/elementwise/kv_append.cu:53-78
+//   attention   crates/synaptix-kernels-cuda/src/cu/fused/attention/flash_decode.cu:92-205
+//   SiLU*mul    crates/synaptix-kernels-cuda/src/cu/fused/mlp/silu_and_mul.cu:11-52
+//   f32 GEMM    crates/synaptix-kernels-cuda/src/best_cu/gemm/gemm_f32.cu:1-69
+// but not how: the residual stream is kept in 32-bit, the cache is paged, tokens of
+// sequences with unequal lengths are packed into one stream.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------
+// embedding gather: out[t, :] = float(table[ids[t], :]); an id outside the table gives zeros
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ out, int H, int V) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool ok = id >= 0 && id < V;
+  const T* row = table + (size_t)(ok ? id : 0) * H;
+  float* o = out + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ok ? to_f32(row[i]) : 0.f;
+}
+
+extern "C" int sx_embed_gather(const void* table, int dt, const int* ids, float* out,
+                               int n_tokens, int H, int V, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (dt == SX_F32)
+    embed_gather_kernel<float><<<n_tokens, 256, 0, stream>>>((const float*)table, ids, out, H, V);
+  else if (dt == SX_BF16)
+    embed_gather_kernel<bf16><<<n_tokens, 256, 0, stream>>>((const bf16*)table, ids, out, H, V);
+  else
+    return SX_ERR_DTYPE;
+  return sx_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// residual add + RMSNorm.
+//   v = h[t] (+ delta[t]);  if write_h: h[t] = v;  y[r] = v * rsqrt(mean(v^2) + eps) * w
+// Rows: r = 0..R-1, t = rows ? rows[r] : r.  h and the sum of squares are 32-bit.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta,
+                                   const float* __restrict__ w, float eps, T* __restrict__ y,
+                                   const int* __restrict__ rows, int H, int write_h) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const int t = rows ? rows[r] : r;
+  float* hr = h + (size_t)t * H;
+  const T* dr = delta ? delta + (size_t)t * H : nullptr;
+  T* yr = y + (size_t)r * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = hr[i];
+    if (dr) {
+      v += to_f32(dr[i]);
+      if (write_h) hr[i] = v;
+    }
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = hr[i];
+    if (dr && !write_h) v += to_f32(dr[i]);
+    yr[i] = from_f32<T>(v * inv * w[i]);
+  }
+}
+
+extern "C" int sx_add_rmsnorm(float* h, const void* delta, const float* w, float eps, void* y,
+                              const int* rows, int R, int H, int dt, int write_h,
+                              cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (dt == SX_F32)
+    add_rmsnorm_kernel<float><<<R, 256, 0, stream>>>(h, (const float*)delta, w, eps, (float*)y, rows, H, write_h);
+  else if (dt == SX_BF16)
+    add_rmsnorm_kernel<bf16><<<R, 256, 0, stream>>>(h, (const bf16*)delta, w, eps, (bf16*)y, rows, H, write_h);
+  else
+    return SX_ERR_DTYPE;
+  return sx_launch_status();
+}
+
+// h[t] += delta[t] (32-bit residual sum), for the places where no norm follows
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ h, const T* __restrict__ delta, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) h[i] += to_f32(delta[i]);
+}
+extern "C" int sx_residual_add(float* h, const void* delta, long long n, int dt, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  if (dt == SX_F32) residual_add_kernel<float><<<grid, 256, 0, stream>>>(h, (const float*)delta, (size_t)n);
+  else if (dt == SX_BF16) residual_add_kernel<bf16><<<grid, 256, 0, stream>>>(h, (const bf16*)delta, (size_t)n);
+  else return SX_ERR_DTYPE;
+  return sx_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// C[M,N] = A[M,K] * W[N,K]^T, 32-bit accumulation in k order.  Two kernels:
+//   gemm_tile: 64x64x16 tiles, 4x4 outputs per thread (any M);
+//   gemm_rows: one warp per output column, up to 8 rows of A at a time (M <= 16).
+// ---------------------------------------------------------------------------------------
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(256) gemm_tile_kernel(const TA* __restrict__ A, const TW* __restrict__ W,
+                                                        TC* __restrict__ C, int M, int N, int K) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Ws[BK][BN + 4];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * 256;
+      const int r = idx >> 4, c = idx & 15;
+      const int k = k0 + c;
+      const int m = m0 + r, n = n0 + r;
+      As[c][r] = (m < M && k < K) ? to_f32(A[(size_t)m * K + k]) : 0.f;
+      Ws[c][r] = (n < N && k < K) ? to_f32(W[(size_t)n * K + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) C[(size_t)m * N + n] = from_f32<TC>(acc[i][j]);
+    }
+  }
+}
+
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(128) gemm_rows_kernel(const TA* __restrict__ A, const TW* __restrict__ W,
+                                                        TC* __restrict__ C, int M, int N, int K) {
+  const int lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (n >= N) return;
+  const TW* wr = W + (size_t)n * K;
+  for (int m0 = 0; m0 < M; m0 += 8) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      const float w = to_f32(wr[k]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (m0 + i < M) acc[i] = fmaf(to_f32(A[(size_t)(m0 + i) * K + k]), w, acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float s = warp_sum(acc[i]);
+      if (lane == 0 && m0 + i < M) C[(size_t)(m0 + i) * N + n] = from_f32<TC>(s);
+    }
+  }
+}
+
+template <typename TA, typename TW, typename TC>
+static int gemm_generic_launch(const void* A, const void* W, void* C, int M, int N, int K,
+                               cudaStream_t stream) {
+  if (M <= 16) {
+    gemm_rows_kernel<TA, TW, TC><<<(N + 3) / 4, 128, 0, stream>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K);
+  } else {
+    dim3 grid((N + 63) / 64, (M + 63) / 64);
+    gemm_tile_kernel<TA, TW, TC><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K);
+  }
+  return sx_launch_status();
+}
+
+extern "C" int sx_gemm_generic(const void* A, int a_dt, const void* W, int w_dt, void* C, int c_dt,
+                               int M, int N, int K, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) return SX_ERR_SIZE;
+  if ((size_t)((M + 63) / 64) > 65535) return SX_ERR_SIZE;
+  if (a_dt == SX_F32 && w_dt == SX_F32 && c_dt == SX_F32)
+    return gemm_generic_launch<float, float, float>(A, W, C, M, N, K, stream);
+  if (a_dt == SX_BF16 && w_dt == SX_BF16 && c_dt == SX_BF16)
+    return gemm_generic_launch<bf16, bf16, bf16>(A, W, C, M, N, K, stream);
+  if (a_dt == SX_BF16 && w_dt == SX_BF16 && c_dt == SX_F32)
+    return gemm_generic_launch<bf16, bf16, float>(A, W, C, M, N, K, stream);
+  if (a_dt == SX_F32 && w_dt == SX_BF16 && c_dt == SX_F32)
+    return gemm_generic_launch<float, bf16, float>(A, W, C, M, N, K, stream);
+  return SX_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------
+// head preparation and cache write, one block per (token, head of the fused projection):
+//   q heads: optional RMSNorm over the head (gain wq), optional rotate-half rotation of the
+//            first rotary_dim elements by angle pos * inv_freq[i], written to q_out[t, head, :];
+//   k heads: the same with wk, written into the sequence's page at the token's position;
+//   v heads: copied into the page.
+// qkv is [T, (nh + 2 nkv) * hd]: q heads, then k heads, then v heads.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) qkv_prepare_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
+    const float* __restrict__ wq, const float* __restrict__ wk, const float* __restrict__ inv_freq,
+    int rotary_dim, float eps, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+    const int* __restrict__ block_table, int maxp, int nh, int nkv, int hd, int n_pages) {
+  extern __shared__ float xs[];          // hd floats
+  __shared__ float red[33];
+  const int t = blockIdx.x, head = blockIdx.y;
+  const int row = (nh + 2 * nkv) * hd;
+  const T* src = qkv + (size_t)t * row + (size_t)head * hd;
+  const int pos = positions[t];
+
+  const bool is_q = head < nh;
+  const bool is_k = !is_q && head < nh + nkv;
+  const int kvh = is_q ? 0 : (is_k ? head - nh : head - nh - nkv);
+
+  T* dst;
+  if (is_q) {
+    dst = q_out + ((size_t)t * nh + head) * hd;
+  } else {
+    const int s = seq_of_token[t];
+    const int page = block_table[(size_t)s * maxp + (pos >> 6)];
+    if (page < 0 || page >= n_pages) return;   // host guarantees a page; never write outside
+    T* base = is_k ? k_pages : v_pages;
+    if (!base) return;                           // a layer that reads another layer's cache writes nothing
+    dst = base + (((size_t)page * nkv + kvh) * SX_PAGE + (pos & 63)) * hd;
+  }
+
+  if (!is_q && !is_k) {                      // v: copy
+    for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = src[i];
+    return;
+  }
+
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+    const float v = to_f32(src[i]);
+    xs[i] = v;
+    ss += v * v;
+  }
+  const float* w = is_q ? wq : wk;
+  float inv = 1.f;
+  if (w) {
+    ss = block_sum(ss, red);
+    inv = rsqrtf(ss / (float)hd + eps);
+  } else {
+    __syncthreads();
+  }
+  // normalised values stay in 32-bit until the rotation is done
+  for (int i = threadIdx.x; i < hd; i += blockDim.x)
+    if (w) xs[i] = xs[i] * inv * w[i];
+  __syncthreads();
+
+  const int half = inv_freq ? rotary_dim / 2 : 0;
+  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+    float o;
+    if (i < 2 * half) {
+      const int j = i < half ? i : i - half;
+      float sn, cs;
+      sincosf((float)pos * inv_freq[j], &sn, &cs);
+      const float x1 = xs[j], x2 = xs[j + half];
+      o = i < half ? x1 * cs - x2 * sn : x1 * sn + x2 * cs;
+    } else {
+      o = xs[i];
+    }
+    dst[i] = from_f32<T>(o);
+  }
+}
+
+extern "C" int sx_qkv_prepare(const void* qkv, void* q_out, void* k_pages, void* v_pages,
+                              const float* wq, const float* wk, const float* inv_freq, int rotary_dim,
+                              float eps, const int* positions, const int* seq_of_token,
+                              const int* block_table, int maxp, int n_tokens, int nh, int nkv, int hd,
+                              int n_pages, int dt, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (hd <= 0 || (rotary_dim & 1) || rotary_dim > hd || nh + 2 * nkv > 65535) return SX_ERR_SIZE;
+  dim3 grid(n_tokens, nh + 2 * nkv);
+  const size_t smem = (size_t)hd * sizeof(float);
+  if (smem > 48 * 1024) return SX_ERR_SIZE;
+  if (dt == SX_F32)
+    qkv_prepare_kernel<float><<<grid, 128, smem, stream>>>(
+        (const float*)qkv, (float*)q_out, (float*)k_pages, (float*)v_pages, wq, wk, inv_freq, rotary_dim, eps,
+        positions, seq_of_token, block_table, maxp, nh, nkv, hd, n_pages);
+  else if (dt == SX_BF16)
+    qkv_prepare_kernel<bf16><<<grid, 128, smem, stream>>>(
+        (const bf16*)qkv, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, wq, wk, inv_freq, rotary_dim, eps,
+        positions, seq_of_token, block_table, maxp, nh, nkv, hd, n_pages);
+  else
+    return SX_ERR_DTYPE;
+  return sx_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// attention over the paged cache, one block per (token, query head): scores of the keys
+// lo..pos in tiles of 128, running maximum and sum (online softmax), all in 32-bit.
+//   lo = window > 0 ? max(0, pos - window + 1) : 0;  query head h reads kv head h / (nh/nkv).
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) attn_generic_kernel(
+    const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+    T* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+    const int* __restrict__ block_table, int maxp, int nh, int nkv, int hd, float scale, int window) {
+  extern __shared__ float smem[];
+  float* qs = smem;            // hd
+  float* ps = smem + hd;       // 128
+  __shared__ float red[33];
+  const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int pos = positions[t];
+  const int* bt = block_table + (size_t)seq_of_token[t] * maxp;
+  const int kvh = h / (nh / nkv);
+  const T* qr = q + ((size_t)t * nh + h) * hd;
+  for (int i = tid; i < hd; i += 128) qs[i] = to_f32(qr[i]);
+  __syncthreads();
+
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  float m = -INFINITY, l = 0.f;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};     // hd <= 512
+
+  for (int j0 = lo; j0 <= pos; j0 += 128) {
+    const int j = j0 + tid;
+    float s = -INFINITY;
+    if (j <= pos) {
+      const int page = bt[j >> 6];
+      const T* kr = k_pages + (((size_t)page * nkv + kvh) * SX_PAGE + (j & 63)) * hd;
+      float d = 0.f;
+      for (int i = 0; i < hd; ++i) d = fmaf(qs[i], to_f32(kr[i]), d);
+      s = d * scale;
+    }
+    const float tmax = block_max(s, red);
+    const float m_new = fmaxf(m, tmax);
+    const float p = (j <= pos) ? expf(s - m_new) : 0.f;
+    const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+    ps[tid] = p;
+    const float psum = block_sum(p, red);   // also orders the writes to ps before the reads below
+    l = l * corr + psum;
+    const int ntile = min(128, pos - j0 + 1);
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const int d = tid + a * 128;
+      if (d < hd) {
+        float v = acc[a] * corr;
+        for (int jj = 0; jj < ntile; ++jj) {
+          const int jk = j0 + jj;
+          const int page = bt[jk >> 6];
+          v = fmaf(ps[jj], to_f32(v_pages[(((size_t)page * nkv + kvh) * SX_PAGE + (jk & 63)) * hd + d]), v);
+        }
+        acc[a] = v;
+      }
+    }
+    m = m_new;
+    __syncthreads();
+  }
+  T* o = out + ((size_t)t * nh + h) * hd;
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    const int d = tid + a * 128;
+    if (d < hd) o[d] = from_f32<T>(acc[a] / l);
+  }
+}
+
+extern "C" int sx_attn_generic(const void* q, const void* k_pages, const void* v_pages, void* out,
+                               const int* positions, const int* seq_of_token, const int* block_table,
+                               int maxp, int n_tokens, int nh, int nkv, int hd, float scale, int window,
+                               int dt, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (hd <= 0 || hd > 512 || nkv <= 0 || nh % nkv != 0 || nh > 65535) return SX_ERR_SIZE;
+  dim3 grid(n_tokens, nh);
+  const size_t smem = (size_t)(hd + 128) * sizeof(float);
+  if (dt == SX_F32)
+    attn_generic_kernel<float><<<grid, 128, smem, stream>>>(
+        (const float*)q, (const float*)k_pages, (const float*)v_pages, (float*)out, positions, seq_of_token,
+        block_table, maxp, nh, nkv, hd, scale, window);
+  else if (dt == SX_BF16)
+    attn_generic_kernel<bf16><<<grid, 128, smem, stream>>>(
+        (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, positions, seq_of_token,
+        block_table, maxp, nh, nkv, hd, scale, window);
+  else
+    return SX_ERR_DTYPE;
+  return sx_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i],  silu(x) = x / (1 + exp(-x)), in 32-bit
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t n) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n) return;
+  const size_t t = idx / I;
+  const int i = (int)(idx - t * I);
+  const float g = to_f32(gu[t * 2 * I + i]);
+  const float u = to_f32(gu[t * 2 * I + I + i]);
+  out[idx] = from_f32<T>(g / (1.f + expf(-g)) * u);
+}
+
+extern "C" int sx_silu_mul(const void* gu, void* out, int n_tokens, int I, int dt, cudaStream_t stream) {
+  const size_t n = (size_t)n_tokens * I;
+  if (n == 0) return 0;
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  if (dt == SX_F32) silu_mul_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, I, n);
+  else if (dt == SX_BF16) silu_mul_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, I, n);
+  else return SX_ERR_DTYPE;
+  return sx_launch_status();
+}

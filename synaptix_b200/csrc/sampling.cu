@@ -1,0 +1,305 @@
+// Sampling on the device: one block per row of logits [R, V] (float32).
+//
+// What is computed follows the reference's host-side pipeline
+// (crates/synaptix-models/llm/common/src/generate.rs:304-340):
+//   repetition penalty -> presence/frequency penalty -> temperature -> top-k -> top-p -> min-p
+//   -> argmax if temperature <= 0, else a multinomial draw
+// with the processors of crates/synaptix-infer/src/sampling/{repetition,logit_processor,top_k,
+// top_p,min_p,greedy,multinomial}.rs and the Philox4x32-10 generator of
+// crates/synaptix-ops/src/rng.rs:1-97.  The reference sorts on the host; here the top-k and
+// top-p cut-offs are found by bisection on the values' bit patterns, with block-wide
+// reductions in a fixed order, so a row's result depends on nothing but the row.
+#include "common.cuh"
+
+#define SAMPLE_THREADS 1024
+
+// order-preserving map float -> uint32 (larger float, larger key); NaN is treated as -inf
+__device__ __forceinline__ uint32_t order_key(float x) {
+  if (x != x) x = -INFINITY;
+  const uint32_t b = __float_as_uint(x);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__device__ __forceinline__ int block_sum_int(int v, int* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int s = 0;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) s += red[i];
+    red[32] = s;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// ---------------------------------------------------------------------------------------
+// argmax per row; among equal maxima the LAST index wins, as Rust's Iterator::max_by does
+// (crates/synaptix-infer/src/sampling/greedy.rs:8-12)
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void argmax_combine(float& bv, int& bi, float v, int i) {
+  if (v > bv || (v == bv && i > bi)) { bv = v; bi = i; }
+}
+
+__device__ int block_argmax(const float* __restrict__ row, int V, float inv_t_div, bool divide,
+                            float* red_v, int* red_i) {
+  float bv = -INFINITY;
+  int bi = -1;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float v = row[i];
+    if (divide) v = v / inv_t_div;
+    if (v != v) v = -INFINITY;
+    argmax_combine(bv, bi, v, i);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    argmax_combine(bv, bi, ov, oi);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float v = red_v[0];
+    int i = red_i[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) argmax_combine(v, i, red_v[w], red_i[w]);
+    red_i[32] = i < 0 ? V - 1 : i;
+    red_v[32] = v;
+  }
+  __syncthreads();
+  return red_i[32];
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS) argmax_rows_kernel(const float* __restrict__ logits,
+                                                                     int* __restrict__ out, int V) {
+  __shared__ float red_v[33];
+  __shared__ int red_i[33];
+  const int r = blockIdx.x;
+  const int i = block_argmax(logits + (size_t)r * V, V, 1.f, false, red_v, red_i);
+  if (threadIdx.x == 0) out[r] = i;
+}
+
+extern "C" int sx_argmax_rows(const float* logits, int* out, int R, int V, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (V <= 0) return SX_ERR_SIZE;
+  argmax_rows_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, out, V);
+  return sx_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// penalties over a window of each row's context (crates/synaptix-infer/src/sampling/
+// repetition.rs:7-77).  hist is [R, hist_stride]; row r's context is hist[r, 0..hist_len[r]);
+// the window is its last `last_n` tokens (0 = all).  Repetition: once per OCCURRENCE,
+// logit > 0 ? logit / p : logit * p.  Presence/frequency: once per distinct token,
+// logit -= presence + frequency * count.  counts is scratch [R, V] int32.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(SAMPLE_THREADS) penalties_kernel(
+    float* __restrict__ logits, int* __restrict__ counts, const int* __restrict__ hist,
+    const int* __restrict__ hist_len, int hist_stride, int last_n, float rep, float presence,
+    float frequency, int V) {
+  const int r = blockIdx.x;
+  float* row = logits + (size_t)r * V;
+  int* cnt = counts + (size_t)r * V;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) cnt[i] = 0;
+  __syncthreads();
+  const int n = hist_len[r];
+  const int start = (last_n > 0 && last_n < n) ? n - last_n : 0;
+  const int* hr = hist + (size_t)r * hist_stride;
+  for (int i = start + threadIdx.x; i < n; i += blockDim.x) {
+    const int t = hr[i];
+    if (t >= 0 && t < V) atomicAdd(&cnt[t], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const int c = cnt[i];
+    if (c == 0) continue;
+    float x = row[i];
+    if (rep != 1.0f)
+      for (int k = 0; k < c; ++k) x = x > 0.f ? x / rep : x * rep;
+    if (presence != 0.f || frequency != 0.f) x -= presence + frequency * (float)c;
+    row[i] = x;
+  }
+}
+
+extern "C" int sx_penalties(float* logits, int* counts, const int* hist, const int* hist_len,
+                            int hist_stride, int last_n, float rep, float presence, float frequency,
+                            int R, int V, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  penalties_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, counts, hist, hist_len, hist_stride, last_n,
+                                                      rep, presence, frequency, V);
+  return sx_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// Philox4x32-10 (crates/synaptix-ops/src/rng.rs:1-97): key = (seed lo, seed hi); the
+// reference draws word number `step` of one stream per request, i.e. block step/4, word
+// step%4 with counter (block, 0, 0, 0).  Here counter[1] carries the request's index in its
+// call, so rows of a batch have independent streams and request 0 equals the reference's.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t philox_word(uint32_t k0, uint32_t k1, uint32_t c0, uint32_t c1, int word) {
+  uint32_t c[4] = {c0, c1, 0u, 0u};
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+    const uint32_t n0 = hi1 ^ c[1] ^ k0, n1 = lo1, n2 = hi0 ^ c[3] ^ k1, n3 = lo0;
+    c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return c[word & 3];
+}
+
+// ---------------------------------------------------------------------------------------
+// temperature / top-k / top-p / min-p / multinomial, one block per row
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_rows_kernel(
+    const float* __restrict__ logits, int* __restrict__ out, int V, float temperature, int top_k,
+    float top_p, float min_p, uint32_t seed_lo, uint32_t seed_hi, const int* __restrict__ seq_index,
+    const int* __restrict__ step, float* __restrict__ u_out) {
+  __shared__ float red[33];
+  __shared__ float red_v[33];
+  __shared__ int red_i[33];
+  __shared__ float chunk_excl[SAMPLE_THREADS];
+  __shared__ int found;
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const float* row = logits + (size_t)r * V;
+
+  if (!(temperature > 0.f)) {       // greedy
+    const int i = block_argmax(row, V, 1.f, false, red_v, red_i);
+    if (tid == 0) out[r] = i;
+    return;
+  }
+  const bool divide = temperature != 1.0f;
+#define XVAL(i) (divide ? row[i] / temperature : row[i])
+
+  // maximum
+  float mx = -INFINITY;
+  for (int i = tid; i < V; i += SAMPLE_THREADS) {
+    float v = XVAL(i);
+    if (v == v) mx = fmaxf(mx, v);
+  }
+  mx = block_max(mx, red);
+
+  // top-k: largest key tk with count(key >= tk) >= k
+  uint32_t tk = 0u;
+  if (top_k > 0 && top_k < V) {
+    for (int bit = 31; bit >= 0; --bit) {
+      const uint32_t cand = tk | (1u << bit);
+      int c = 0;
+      for (int i = tid; i < V; i += SAMPLE_THREADS) c += order_key(XVAL(i)) >= cand;
+      c = block_sum_int(c, red_i);
+      if (c >= top_k) tk = cand;
+    }
+  }
+  // top-p: largest key tp with mass(key > tp) > top_p * mass(all kept by top-k); keep key > tp
+  bool use_tp = false;
+  uint32_t tp = 0u;
+  if (top_p < 1.0f) {
+    float s = 0.f;
+    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+      const float v = XVAL(i);
+      if (order_key(v) >= tk && v > -INFINITY) s += expf(v - mx);
+    }
+    s = block_sum(s, red);
+    const float thresh = top_p * s;
+    // mass(key > 0) is everything except keys equal to 0 (never a finite value)
+    float g0 = 0.f;
+    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+      const float v = XVAL(i);
+      const uint32_t k = order_key(v);
+      if (k >= tk && k > 0u && v > -INFINITY) g0 += expf(v - mx);
+    }
+    g0 = block_sum(g0, red);
+    if (g0 > thresh) {
+      use_tp = true;
+      for (int bit = 31; bit >= 0; --bit) {
+        const uint32_t cand = tp | (1u << bit);
+        float g = 0.f;
+        for (int i = tid; i < V; i += SAMPLE_THREADS) {
+          const float v = XVAL(i);
+          const uint32_t k = order_key(v);
+          if (k >= tk && k > cand && v > -INFINITY) g += expf(v - mx);
+        }
+        g = block_sum(g, red);
+        if (g > thresh) tp = cand;
+      }
+    }
+  }
+  // min-p: with the maximum's probability as reference, keep exp(x - max) >= min_p
+#define KEPT(v) (order_key(v) >= tk && (!use_tp || order_key(v) > tp) && (v) > -INFINITY && \
+                 (!(min_p > 0.f) || expf((v) - mx) >= min_p))
+
+  // multinomial over the kept values: contiguous chunks per thread, exclusive scan of chunk sums
+  const int chunk = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+  const int b = tid * chunk, e = min(V, b + chunk);
+  float cs = 0.f;
+  for (int i = b; i < e; ++i) {
+    const float v = XVAL(i);
+    if (KEPT(v)) cs += expf(v - mx);
+  }
+  chunk_excl[tid] = cs;
+  if (tid == 0) found = -1;
+  __syncthreads();
+  if (tid == 0) {
+    float run = 0.f;
+    for (int t = 0; t < SAMPLE_THREADS; ++t) {
+      const float c = chunk_excl[t];
+      chunk_excl[t] = run;
+      run += c;
+    }
+    red[32] = run;
+  }
+  __syncthreads();
+  const float total = red[32];
+  const uint32_t word = philox_word(seed_lo, seed_hi, (uint32_t)(step[r] >> 2), (uint32_t)seq_index[r], step[r] & 3);
+  // u = (word as f64 as f32) / (u32::MAX as f32)   (multinomial.rs:30-32)
+  const float u = (float)(double)word / 4294967296.0f;
+  if (tid == 0 && u_out) u_out[r] = u;
+  const float target = u * total;
+  const float lo = chunk_excl[tid];
+  if (cs > 0.f && target >= lo && target < lo + cs) {
+    float run = lo;
+    int pick = -1, last = -1;
+    for (int i = b; i < e; ++i) {
+      const float v = XVAL(i);
+      if (!KEPT(v)) continue;
+      last = i;
+      run += expf(v - mx);
+      if (target < run) { pick = i; break; }
+    }
+    if (pick < 0) pick = last;        // rounding at the chunk's end
+    atomicMax(&found, pick);          // at most one thread gets here with target in its range
+  }
+  __syncthreads();
+  const int first_try = found;
+  __syncthreads();
+  if (first_try < 0) {                // u == 1 or rounding past the end: last kept index
+    int last = -1;
+    for (int i = b; i < e; ++i) {
+      const float v = XVAL(i);
+      if (KEPT(v)) last = i;
+    }
+    if (last >= 0) atomicMax(&found, last);
+    __syncthreads();
+  }
+  if (tid == 0) out[r] = found < 0 ? V - 1 : found;
+#undef XVAL
+#undef KEPT
+}
+
+extern "C" int sx_sample_rows(const float* logits, int* out, int R, int V, float temperature, int top_k,
+                              float top_p, float min_p, unsigned long long seed, const int* seq_index,
+                              const int* step, float* u_out, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (V <= 0) return SX_ERR_SIZE;
+  sample_rows_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(
+      logits, out, V, temperature, top_k, top_p, min_p, (uint32_t)(seed & 0xffffffffull),
+      (uint32_t)(seed >> 32), seq_index, step, u_out);
+  return sx_launch_status();
+}

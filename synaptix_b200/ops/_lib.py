@@ -1,0 +1,72 @@
+"""Calling the compiled kernels: pointers, dtype codes, streams, error codes."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc.build import KernelsUnavailable, load_library
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+_ERRORS = {10001: "unsupported dtype combination", 10002: "unsupported size", 10003: "misaligned pointer or stride",
+           10004: "a bounded wait inside the kernel ran out (see the kernel's status word)"}
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or its launch failed."""
+
+
+def dt_code(dtype: torch.dtype) -> int:
+    try:
+        return _DT[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 and bfloat16 tensors, not {dtype}") from None
+
+
+def require_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise KernelsUnavailable(
+                "this operation runs only as a CUDA kernel on an sm_100a device; it was given a "
+                f"{t.device} tensor (there is no CPU path)")
+        if not t.is_contiguous():
+            raise KernelError("kernels take contiguous tensors")
+
+
+def ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code in _ERRORS:
+        raise KernelError(f"{what}: {_ERRORS[code]}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+_FN_CACHE = {}
+
+
+def fn(lib: str, name: str):
+    key = (lib, name)
+    f = _FN_CACHE.get(key)
+    if f is None:
+        f = getattr(load_library(lib), name)
+        f.restype = ctypes.c_int
+        _FN_CACHE[key] = f
+    return f
+
+
+c_int = ctypes.c_int
+c_float = ctypes.c_float
+c_longlong = ctypes.c_longlong
+c_ulonglong = ctypes.c_ulonglong

@@ -1,0 +1,132 @@
+"""What every part of a layer is, and what a step hands to the parts.
+
+A model is put together from parts; each part has its sizes and constants as
+constructor parameters, names the tensors it needs, and is chosen by the
+architecture's builder layer by layer.  No part knows which model it is in:
+the tensor-name prefix it is given is data like any other.
+
+Interfaces (a new part of any kind implements the one of its kind):
+
+``Part``           ``tensor_specs() -> {name: TensorSpec}``; ``bind(tensors, runtime)``.
+``Norm``           ``forward(h)`` and ``add_forward(h, delta, rows=None)``: ``h`` is the
+                   float32 residual stream ``[T, width]``; ``add_forward`` first adds
+                   ``delta`` into it; both return the normalised rows in the compute dtype.
+``PositionEncoding`` ``rotation() -> (inv_freq float32 [rotary_dim/2], rotary_dim) | None``:
+                   rotate-half rotation by ``position * inv_freq[i]``, applied to queries and
+                   keys inside the fused head-preparation kernel.
+``Mixer``          ``cache_request() -> KVRequest | StateRequest | None``;
+                   ``forward(x, ctx, cache_view, write_cache=True) -> [T, width]``.
+``FeedForward``    ``forward(x, ctx) -> [T, width]``.
+``Block``          ``forward(h, pending, ctx, cache_view, write_cache) -> (h, pending)`` where
+                   ``pending`` is a branch output not yet added into ``h`` (so that the sum can
+                   be fused with the next norm).
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Dict, List, Mapping, Optional
+
+import torch
+
+from ..weights.loader import TensorSpec
+
+
+@dataclasses.dataclass
+class Runtime:
+    """Where and in which precision a model runs."""
+    device: torch.device
+    dtype: torch.dtype          # compute and cache dtype: torch.bfloat16 or torch.float32
+
+    @property
+    def is_fp32(self) -> bool:
+        return self.dtype == torch.float32
+
+
+class StepContext:
+    """One step's batch, packed: the tokens of all sequences in one stream.
+
+    Device tensors (int32): ``token_ids [T]``, ``positions [T]`` (absolute position of each
+    token in its sequence), ``seq_of_token [T]`` (row of the per-sequence arrays),
+    ``cu_seqlens [S+1]`` (first packed token of each sequence), ``seq_past [S]`` (tokens
+    held before the step), ``seq_lens [S]`` (held after it), ``seq_slots [S]`` (cache slot),
+    ``block_tables[g] [S, max_pages]`` (pages of each sequence in storage group ``g``),
+    ``want_rows [R]`` (packed indices whose logits are wanted).
+
+    Host values: ``n_tokens``, ``n_seqs``, ``n_want``, ``max_new`` (longest run of new
+    tokens), ``max_len`` (longest sequence after the step), ``all_single`` (every sequence
+    brings exactly one token).  Inside a captured graph the host values are upper bounds.
+    """
+    __slots__ = ("token_ids", "positions", "seq_of_token", "cu_seqlens", "seq_past", "seq_lens",
+                 "seq_slots", "block_tables", "want_rows", "n_tokens", "n_seqs", "n_want",
+                 "max_new", "max_len", "all_single", "runtime", "scratch")
+
+    def __init__(self, **kw):
+        self.scratch = {}
+        for k, v in kw.items():
+            setattr(self, k, v)
+
+
+class Part:
+    """Anything that owns tensors."""
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        pass
+
+    def children(self) -> List["Part"]:
+        return []
+
+    # helpers -------------------------------------------------------------
+    def all_tensor_specs(self) -> Dict[str, TensorSpec]:
+        out = dict(self.tensor_specs())
+        for c in self.children():
+            for n, s in c.all_tensor_specs().items():
+                if n in out and out[n] != s:
+                    raise ValueError(f"tensor {n!r} is asked for twice with different shapes")
+                out[n] = s
+        return out
+
+    def bind_all(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        self.bind(tensors, rt)
+        for c in self.children():
+            c.bind_all(tensors, rt)
+
+
+class Norm(Part):
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_forward(self, h: torch.Tensor, delta: Optional[torch.Tensor],
+                    rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def rotation(self):
+        return None
+
+
+class Mixer(Part):
+    def cache_request(self):
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache_view, write_cache: bool = True) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+def to_device_matrix(t: torch.Tensor, rt: Runtime) -> torch.Tensor:
+    """A matrix in the compute dtype on the device (a 32-bit matrix is rounded once, to
+    nearest even, when the compute dtype is bfloat16)."""
+    return t.to(device=rt.device, dtype=rt.dtype).contiguous()
+
+
+def to_device_f32(t: torch.Tensor, rt: Runtime) -> torch.Tensor:
+    """A gain vector in 32-bit on the device (widening bfloat16 loses nothing)."""
+    return t.to(device=rt.device, dtype=torch.float32).contiguous()

@@ -1,0 +1,33 @@
+"""The arrangement of parts in a layer.
+
+``PreNormBlock`` (crates/synaptix-models/llm/common/src/model.rs:1179-1199):
+``h += mixer(norm1(h)); h += ffn(norm2(h))``.  The residual stream ``h`` is
+float32; each branch output is handed on as ``pending`` and added by the next
+norm's kernel, so a sum and a norm are one pass over memory.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+
+from .base import FeedForward, Mixer, Norm, Part, StepContext
+
+
+class PreNormBlock(Part):
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward):
+        self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+
+    def children(self) -> List[Part]:
+        return [self.norm1, self.mixer, self.norm2, self.ffn]
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                cache_view, write_cache: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+        x = self.norm1.add_forward(h, pending)
+        a = self.mixer.forward(x, ctx, cache_view, write_cache)
+        y = self.norm2.add_forward(h, a)
+        m = self.ffn.forward(y, ctx)
+        return h, m

@@ -1,0 +1,39 @@
+"""RMSNorm with a plain gain, fused with the residual sum.
+
+Formula (crates/synaptix-ops/src/norm/rms_norm.rs:17-26; CUDA
+crates/synaptix-kernels-cuda/src/cu/reduction/rms_norm.cu:84-96):
+``y = x * rsqrt(mean(x^2) + eps) * w`` in 32-bit, gain ``w`` (not ``1 + w``).
+The residual stream itself is float32 here, so the sum ``h + delta`` is never
+rounded to the compute dtype (the reference rounds it, rmsnorm_residual.cu:97-159).
+"""
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from .. import ops
+from ..weights.loader import TensorSpec
+from .base import Norm, Runtime, to_device_f32
+
+
+class RMSNorm(Norm):
+    def __init__(self, weight_name: str, width: int, eps: float):
+        self.weight_name = weight_name
+        self.width = width
+        self.eps = float(eps)
+        self.weight: Optional[torch.Tensor] = None
+        self._dtype = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.weight_name: TensorSpec((self.width,), "gain")}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
+        self.weight = to_device_f32(tensors[self.weight_name], rt)
+        self._dtype = rt.dtype
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return ops.add_rmsnorm(h, None, self.weight, self.eps, self._dtype)
+
+    def add_forward(self, h, delta, rows=None):
+        return ops.add_rmsnorm(h, delta, self.weight, self.eps, self._dtype, rows=rows)
