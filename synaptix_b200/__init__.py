@@ -8,8 +8,9 @@ and hand-written CUDA kernels with a true 32-bit path beside the bfloat16 one.
 """
 from .config import ConfigError, Qwen3Config, load_config, register_architecture
 from .weights import WeightError, write_model_folder
+from .api import LLM, generate, load_llm
 
 __version__ = "0.1.0"
 
 __all__ = ["ConfigError", "Qwen3Config", "load_config", "register_architecture", "WeightError",
-           "write_model_folder", "__version__"]
+           "write_model_folder", "LLM", "generate", "load_llm", "__version__"]

@@ -1,0 +1,90 @@
+"""The Python entry point: load a model once, generate for lists of token ids.
+
+The reference's facade is ``load_llm(...) -> Llm`` with ``generate_streaming`` and
+``GenerationOptions`` (crates/synaptix/src/facade/llm.rs:297-310,933-1006); option
+names and defaults are those of its ``GenerationConfig``
+(crates/synaptix-models/llm/common/src/generate.rs:16-57).  Prompts are token ids:
+tokenizers are outside this library.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+
+from .engine.generate import GenerationOptions, GenerationResult, GenerationStats, run_generation
+from .engine.step import Engine
+from .models import load_model
+from .sampling import Sampler, SamplingParams
+
+
+class LLM:
+    """A loaded model with its cache.
+
+    ``max_tokens`` sizes the cache: the most tokens live sequences hold at any time, each
+    sequence's count rounded up to a multiple of 64.  ``max_seq`` (the reference's name for
+    the per-sequence capacity) is a shorthand: with ``max_batch`` it gives
+    ``max_tokens = max_batch * max_seq``.
+    """
+
+    def __init__(self, model_dir: str, compute_dtype="bf16", device: str = "cuda:0",
+                 max_tokens: Optional[int] = None, max_seq: Optional[int] = None, max_batch: int = 8,
+                 graph: bool = True, source=None):
+        self.model = load_model(model_dir, dtype=compute_dtype, device=device, source=source)
+        cfg = self.model.config
+        if max_tokens is None:
+            per_seq = max_seq or getattr(cfg, "max_position_embeddings", None) or 4096
+            max_tokens = max_batch * per_seq
+        self.engine = Engine(self.model, max_tokens=max_tokens, use_graphs=graph)
+        self.last_stats: Optional[GenerationStats] = None
+
+    @property
+    def config(self):
+        return self.model.config
+
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64, temperature: float = 0.0,
+                 top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, repetition_penalty: float = 1.0,
+                 repeat_last_n: int = 0, presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
+                 seed: int = 0, eos_token_id: Optional[int] = None, eos_token_ids: Optional[Sequence[int]] = None,
+                 max_batch_size: Optional[int] = None,
+                 on_token: Optional[Callable[[int, int], None]] = None,
+                 return_details: bool = False):
+        """Generate for each prompt (a list of token ids); returns the new tokens of each.
+
+        Stop tokens: ``eos_token_ids`` together with ``eos_token_id``; if neither is given,
+        the model configuration's.  A stop token ends its sequence and is part of the output.
+        """
+        single = len(prompts) > 0 and isinstance(prompts[0], int)
+        if single:
+            prompts = [prompts]
+        if eos_token_id is None and eos_token_ids is None:
+            stop: Tuple[int, ...] = tuple(self.model.stop_token_ids)
+        else:
+            stop = tuple(eos_token_ids or ()) + ((eos_token_id,) if eos_token_id is not None else ())
+        params = SamplingParams(temperature=temperature, top_k=top_k, top_p=top_p, min_p=min_p,
+                                repetition_penalty=repetition_penalty, repeat_last_n=repeat_last_n,
+                                presence_penalty=presence_penalty, frequency_penalty=frequency_penalty,
+                                seed=seed)
+        sampler = Sampler(params, self.engine.device)
+        opts = GenerationOptions(max_new_tokens=max_new_tokens, stop_token_ids=stop, sampling=params,
+                                 max_batch_size=max_batch_size)
+        results, stats = run_generation(self.engine, sampler.sample_to_host, prompts, opts, on_token=on_token)
+        self.last_stats = stats
+        if return_details:
+            return results[0] if single else results
+        out = [r.tokens for r in results]
+        return out[0] if single else out
+
+
+def load_llm(model_dir: str, **kw) -> LLM:
+    return LLM(model_dir, **kw)
+
+
+def generate(model_dir: str, prompts: Sequence[Sequence[int]], compute_dtype="bf16", device="cuda:0",
+             max_tokens: Optional[int] = None, **gen_kw) -> List[List[int]]:
+    """One-shot: load ``model_dir`` and generate for ``prompts`` (lists of token ids)."""
+    if max_tokens is None:
+        new = gen_kw.get("max_new_tokens", 64)
+        max_tokens = sum(((len(p) + new + 63) // 64) * 64 for p in prompts)
+    return LLM(model_dir, compute_dtype=compute_dtype, device=device, max_tokens=max_tokens).generate(
+        prompts, **gen_kw)

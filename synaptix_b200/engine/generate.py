@@ -1,0 +1,153 @@
+"""The generation loop above the step function.
+
+For each batch: all prompts in one step (unequal lengths), one token sampled per
+sequence from the logits at its last prompt token, then steps of one token for
+every sequence still running.  A sequence ends when it emits a stop token (which
+is part of its output), when it has ``max_new_tokens`` tokens (the first sampled
+token counts), or when the cache cannot hold another token; its slot is given
+back at once and the later steps shrink.  Requests beyond one batch run as
+further batches, one after another, in the slots the earlier ones gave back.
+
+Single-sequence semantics follow the reference's loop
+(crates/synaptix-models/llm/common/src/generate.rs:237-302: the stop check is on
+the last emitted token before the next model call, :281-285; ``eos_set`` :202-208).
+The loop knows the engine only as ``open() / close(slot) / step(entries) ->
+logits`` and the sampler only as a function of logits, so its decisions are
+tested on the CPU with a fake of both.
+"""
+from __future__ import annotations
+
+import dataclasses
+import time
+from typing import Callable, List, Optional, Sequence, Tuple
+
+from ..cache.pages import PAGE_TOKENS, CacheFull, pages_for
+from ..sampling.params import SamplingParams
+from .step import Entry
+
+
+@dataclasses.dataclass(frozen=True)
+class GenerationOptions:
+    max_new_tokens: int = 64
+    stop_token_ids: Tuple[int, ...] = ()
+    sampling: SamplingParams = SamplingParams()
+    max_batch_size: Optional[int] = None      # None: as many as the cache holds
+
+
+@dataclasses.dataclass
+class GenerationResult:
+    tokens: List[int]
+    finish_reason: str          # "stop", "length" or "capacity"
+    prompt_tokens: int
+
+
+@dataclasses.dataclass
+class GenerationStats:
+    """As the reference's GenerationStats (generate.rs:59-65), summed over batches."""
+    prompt_tokens: int = 0
+    new_tokens: int = 0
+    prefill_ms: float = 0.0
+    decode_ms: float = 0.0
+    batches: int = 0
+    decode_steps: int = 0
+
+
+class _Live:
+    __slots__ = ("request", "slot", "prompt", "out")
+
+    def __init__(self, request, slot, prompt):
+        self.request, self.slot, self.prompt, self.out = request, slot, prompt, []
+
+
+def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, max_tokens: int, max_seqs: int,
+                 max_batch_size: Optional[int]) -> List[List[int]]:
+    """Cut the request list, in order, into batches that fit the cache when every
+    request runs to ``max_new_tokens`` (each request's tokens rounded up to whole pages).
+    A request that does not fit even alone still gets a batch of its own if its prompt
+    fits; it then ends by capacity."""
+    total_pages = pages_for(max_tokens)
+    limit = max_seqs if max_batch_size is None else min(max_seqs, max_batch_size)
+    batches: List[List[int]] = []
+    cur: List[int] = []
+    used = 0
+    for i, n in enumerate(prompt_lens):
+        if pages_for(n) > total_pages:
+            raise CacheFull(f"request {i}: its prompt of {n} tokens does not fit a cache of "
+                            f"{total_pages * PAGE_TOKENS} tokens")
+        # the last sampled token is never fed back, so n + max_new - 1 tokens reach the cache
+        need = min(pages_for(n + max(0, max_new_tokens - 1)), total_pages)
+        if cur and (used + need > total_pages or len(cur) >= limit):
+            batches.append(cur)
+            cur, used = [], 0
+        cur.append(i)
+        used += need
+    if cur:
+        batches.append(cur)
+    return batches
+
+
+def run_generation(engine, sample: Callable, prompts: Sequence[Sequence[int]], options: GenerationOptions,
+                   on_token: Optional[Callable[[int, int], None]] = None,
+                   clock: Callable[[], float] = time.perf_counter):
+    """Generate for every prompt; returns ``(results, stats)`` in the prompts' order.
+
+    ``sample(logits, request_index, step, contexts) -> list of ints`` draws one token per row.
+    ``on_token(request_index, token)`` is called for every token as it is produced.
+    """
+    prompts = [list(p) for p in prompts]
+    for i, p in enumerate(prompts):
+        if not p:
+            raise ValueError(f"request {i}: the prompt is empty")
+    results: List[Optional[GenerationResult]] = [None] * len(prompts)
+    stats = GenerationStats()
+    if options.max_new_tokens <= 0:
+        return [GenerationResult([], "length", len(p)) for p in prompts], stats
+    stop = set(options.stop_token_ids)
+    need_ctx = options.sampling.penalties_on
+
+    def finish(seq: _Live, reason: str) -> None:
+        engine.close(seq.slot)
+        results[seq.request] = GenerationResult(seq.out, reason, len(seq.prompt))
+
+    def take(seq: _Live, token: int) -> bool:
+        """Record a token; True if the sequence goes on."""
+        seq.out.append(token)
+        stats.new_tokens += 1
+        if on_token is not None:
+            on_token(seq.request, token)
+        if token in stop:
+            finish(seq, "stop")
+            return False
+        if len(seq.out) >= options.max_new_tokens:
+            finish(seq, "length")
+            return False
+        return True
+
+    for batch in plan_batches([len(p) for p in prompts], options.max_new_tokens, engine.max_tokens,
+                              engine.max_seqs, options.max_batch_size):
+        stats.batches += 1
+        live = [_Live(i, engine.open(), prompts[i]) for i in batch]
+        t0 = clock()
+        logits = engine.step([Entry(s.slot, s.prompt, [len(s.prompt) - 1]) for s in live])
+        toks = sample(logits, [s.request for s in live], [0] * len(live),
+                      [s.prompt for s in live] if need_ctx else None)
+        stats.prefill_ms += (clock() - t0) * 1e3
+        stats.prompt_tokens += sum(len(s.prompt) for s in live)
+        live = [s for s, t in zip(live, toks) if take(s, int(t))]
+
+        t0 = clock()
+        while live:
+            try:
+                logits = engine.step([Entry(s.slot, [s.out[-1]], [0]) for s in live])
+            except CacheFull:
+                # no page for everyone: the longest sequence ends, the others go on
+                victim = max(live, key=lambda s: len(s.prompt) + len(s.out))
+                finish(victim, "capacity")
+                live = [s for s in live if s is not victim]
+                continue
+            stats.decode_steps += 1
+            toks = sample(logits, [s.request for s in live], [len(s.out) for s in live],
+                          [s.prompt + s.out for s in live] if need_ctx else None)
+            live = [s for s, t in zip(live, toks) if take(s, int(t))]
+        stats.decode_ms += (clock() - t0) * 1e3
+    return results, stats

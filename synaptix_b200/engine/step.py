@@ -73,7 +73,7 @@ class _Staging:
 class Engine:
     """A loaded model with its cache: slots are opened, stepped and closed here."""
 
-    def __init__(self, model, *, max_tokens: int, max_seqs: Optional[int] = None):
+    def __init__(self, model, *, max_tokens: int, max_seqs: Optional[int] = None, use_graphs: bool = True):
         if model.runtime is None:
             raise ValueError("the model has no weights bound")
         rt = model.runtime
@@ -86,6 +86,15 @@ class Engine:
         self.cache = Cache(model.cache_requests(), max_tokens=max_tokens, max_seqs=max_seqs,
                            dtype=rt.dtype, device=rt.device)
         self._staging = _Staging(rt.device)
+        self.use_graphs = use_graphs
+
+    @property
+    def max_tokens(self) -> int:
+        return self.cache.max_tokens
+
+    @property
+    def max_seqs(self) -> int:
+        return self.cache.max_seqs
 
     # -- slots -----------------------------------------------------------------
     def open(self) -> int:
