@@ -1,0 +1,316 @@
+"""Each kernel alone against a plain float32 reference of the same operation, at sizes other
+than the engine tests use.  Inputs are made so that faults show: pages in scrambled order,
+unused cache filled with NaN, one far key whose score stands out, keys at a window's edge."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+
+DT = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+def dev(t, dtype=None):
+    t = t.to("cuda")
+    return t.to(dtype) if dtype is not None else t
+
+
+def make_paged(seqs_k, seqs_v, nkv, hd, dtype, seed=0):
+    """Dense per-sequence K/V [len, nkv, hd] -> NaN-filled pages in scrambled order + block table."""
+    g = torch.Generator().manual_seed(seed)
+    need = [(k.shape[0] + 63) // 64 for k in seqs_k]
+    n_pages = sum(need) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    kp = torch.full((n_pages, nkv, 64, hd), float("nan"), dtype=dtype)
+    vp = torch.full((n_pages, nkv, 64, hd), float("nan"), dtype=dtype)
+    maxp = max(need)
+    bt = torch.zeros((len(seqs_k), maxp), dtype=torch.int32)
+    for s, (k, v) in enumerate(zip(seqs_k, seqs_v)):
+        for i in range(need[s]):
+            page = perm.pop()
+            bt[s, i] = page
+            n = min(64, k.shape[0] - 64 * i)
+            kp[page, :, :n] = k[64 * i:64 * i + n].transpose(0, 1).to(dtype)
+            vp[page, :, :n] = v[64 * i:64 * i + n].transpose(0, 1).to(dtype)
+    return kp.cuda(), vp.cuda(), bt.cuda()
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_embed_gather(dtype):
+    from synaptix_b200 import ops
+    table = torch.randn(1000, 200).to(dtype)
+    ids = torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32)
+    out = ops.embed_gather(dev(table), dev(ids))
+    assert out.dtype == torch.float32
+    assert torch.equal(out.cpu(), table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("H", [7, 300, 2560])
+def test_add_rmsnorm(dtype, H):
+    from synaptix_b200 import ops
+    T = 9
+    h = torch.randn(T, H) * 3
+    d = torch.randn(T, H).to(dtype)
+    w = 1 + 0.2 * torch.randn(H)
+    eps = 1e-5
+    hd = dev(h.clone())
+    y = ops.add_rmsnorm(hd, dev(d), dev(w), eps, dtype)
+    s = h + d.float()
+    assert torch.allclose(hd.cpu(), s, atol=1e-6)                       # the sum is kept in 32-bit
+    assert torch.allclose(y.float().cpu(), P.rms_norm(s, w, eps), **tol(dtype))
+    # without delta; and gathered rows leave h alone
+    hd = dev(h.clone())
+    y = ops.add_rmsnorm(hd, None, dev(w), eps, dtype)
+    assert torch.allclose(y.float().cpu(), P.rms_norm(h, w, eps), **tol(dtype))
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32)
+    y = ops.add_rmsnorm(hd, dev(d), dev(w), eps, dtype, rows=dev(rows))
+    assert torch.equal(hd.cpu(), h)
+    assert torch.allclose(y.float().cpu(), P.rms_norm(s[rows.long()], w, eps), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("M,N,K", [(1, 389, 77), (5, 64, 96), (16, 130, 33), (17, 200, 160), (100, 389, 250), (130, 70, 1)])
+def test_gemm_generic(dtype, M, N, K):
+    from synaptix_b200 import ops
+    a = torch.randn(M, K).to(dtype)
+    w = torch.randn(N, K).to(dtype)
+    ref = a.double() @ w.double().T
+    out = ops.gemm_generic(dev(a), dev(w), out_dtype=torch.float32)
+    assert torch.allclose(out.cpu().double(), ref, atol=1e-4 * math.sqrt(K), rtol=1e-5)
+    out = ops.gemm_generic(dev(a), dev(w))
+    assert out.dtype == dtype
+    assert torch.allclose(out.float().cpu().double(), ref, atol=(1e-4 if dtype == torch.float32 else 0.08) * math.sqrt(K), rtol=tol(dtype)["rtol"])
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_silu_mul(dtype):
+    from synaptix_b200 import ops
+    gu = (torch.randn(5, 2 * 37) * 4).to(dtype)
+    g, u = gu.float()[:, :37], gu.float()[:, 37:]
+    out = ops.silu_mul(dev(gu))
+    assert torch.allclose(out.float().cpu(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd,rot,norm", [(4, 2, 16, 16, True), (6, 2, 32, 32, True), (5, 1, 48, 24, True),
+                                                 (3, 3, 80, 80, False), (2, 1, 256, 0, True)])
+def test_qkv_prepare_norm_rotation_and_cache_write(dtype, nh, nkv, hd, rot, norm):
+    from synaptix_b200 import ops
+    from synaptix_b200.parts import rotary_inv_freq
+    lens_past, lens_new = [0, 70, 63], [5, 1, 66]
+    eps, theta = 1e-5, 5000.0
+    S = len(lens_new)
+    T = sum(lens_new)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd).to(dtype)
+    wq, wk = 1 + 0.3 * torch.randn(hd), 1 + 0.3 * torch.randn(hd)
+    pos = torch.cat([torch.arange(p, p + n) for p, n in zip(lens_past, lens_new)]).to(torch.int32)
+    sot = torch.cat([torch.full((n,), i) for i, n in enumerate(lens_new)]).to(torch.int32)
+    # pages: empty sequences of the final lengths, NaN everywhere
+    zeros = [torch.zeros(p + n, nkv, hd) for p, n in zip(lens_past, lens_new)]
+    kp, vp, bt = make_paged(zeros, zeros, nkv, hd, dtype, seed=1)
+    kp.fill_(float("nan")); vp.fill_(float("nan"))
+    q_out = torch.empty(T, nh * hd, dtype=dtype, device="cuda")
+    inv = torch.from_numpy(rotary_inv_freq(theta, rot)).cuda() if rot else None
+    ops.qkv_prepare(dev(qkv), q_out, kp, vp, dev(wq) if norm else None, dev(wk) if norm else None, inv, rot, eps,
+                    dev(pos), dev(sot), bt, nh, nkv, hd)
+    x = qkv.float()
+    q = x[:, :nh * hd].view(T, nh, hd)
+    k = x[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd)
+    v = x[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    if norm:
+        q, k = P.rms_norm(q, wq, eps), P.rms_norm(k, wk, eps)
+    if rot:
+        f = P.rotary_freqs(theta, rot)
+        q = torch.cat([P.rope_rotate_half(q[..., :rot], pos, f), q[..., rot:]], -1)
+        k = torch.cat([P.rope_rotate_half(k[..., :rot], pos, f), k[..., rot:]], -1)
+    assert torch.allclose(q_out.float().cpu().view(T, nh, hd), q, **tol(dtype))
+    kpc, vpc, btc = kp.float().cpu(), vp.float().cpu(), bt.cpu()
+    written = torch.zeros(kpc.shape[0], 64, dtype=torch.bool)
+    for t in range(T):
+        s, p = int(sot[t]), int(pos[t])
+        page = int(btc[s, p // 64])
+        assert torch.allclose(kpc[page, :, p % 64], k[t], **tol(dtype))
+        assert torch.allclose(vpc[page, :, p % 64], v[t], **tol(dtype))
+        written[page, p % 64] = True
+    # nothing else was touched
+    assert torch.isnan(kpc.permute(0, 2, 1, 3)[~written]).all() and torch.isnan(vpc.permute(0, 2, 1, 3)[~written]).all()
+    # a layer that reads another layer's cache writes nothing
+    q2 = torch.empty_like(q_out)
+    ops.qkv_prepare(dev(qkv), q2, None, None, dev(wq) if norm else None, dev(wk) if norm else None, inv, rot, eps,
+                    dev(pos), dev(sot), bt, nh, nkv, hd)
+    assert torch.equal(q2, q_out)
+
+
+def attention_reference(q, ks, vs, positions, sot, scale, window):
+    """q [T, nh, hd]; ks/vs dense per sequence; each token attends within its own sequence."""
+    T, nh, hd = q.shape
+    out = torch.empty(T, nh, hd, dtype=torch.float64)
+    for t in range(T):
+        s, p = int(sot[t]), int(positions[t])
+        lo = 0 if window is None else max(0, p - window + 1)
+        k, v = ks[s][lo:p + 1].double(), vs[s][lo:p + 1].double()
+        g = nh // k.shape[1]
+        for h in range(nh):
+            sc = (k[:, h // g] @ q[t, h].double()) * scale
+            pr = torch.softmax(sc, 0)
+            out[t, h] = pr @ v[:, h // g]
+    return out.float()
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, None), (6, 2, 32, None), (5, 1, 48, 24), (8, 8, 64, None),
+                                               (8, 2, 128, 100), (2, 1, 256, None), (3, 1, 80, None)])
+def test_attention_generic(dtype, nh, nkv, hd, window):
+    from synaptix_b200 import ops
+    past, new = [0, 130, 200, 64], [67, 1, 3, 1]
+    ks = [torch.randn(p + n, nkv, hd).to(dtype).float() for p, n in zip(past, new)]
+    vs = [torch.randn(p + n, nkv, hd).to(dtype).float() for p, n in zip(past, new)]
+    kp, vp, bt = make_paged(ks, vs, nkv, hd, dtype, seed=2)
+    T = sum(new)
+    q = torch.randn(T, nh, hd).to(dtype)
+    pos = torch.cat([torch.arange(p, p + n) for p, n in zip(past, new)]).to(torch.int32)
+    sot = torch.cat([torch.full((n,), i) for i, n in enumerate(new)]).to(torch.int32)
+    scale = 1 / math.sqrt(hd)
+    out = ops.attn_generic(dev(q.view(T, nh * hd)), kp, vp, dev(pos), dev(sot), bt, nh, nkv, hd, scale, window)
+    ref = attention_reference(q.float(), ks, vs, pos, sot, scale, window)
+    assert torch.allclose(out.float().cpu().view(T, nh, hd), ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    """One key, far back, is scaled so that its score stands out: the output must be its value."""
+    from synaptix_b200 import ops
+    nh, nkv, hd, L = 4, 2, 64, 700
+    for far in (0, 1, 63, 64, 333, 698, 699):
+        k = torch.randn(L, nkv, hd) * 0.1
+        v = torch.randn(L, nkv, hd)
+        q = torch.randn(1, nh, hd)
+        # make key `far` of each kv head parallel to the mean query of its group, and long
+        for kh in range(nkv):
+            k[far, kh] = q[0, kh * 2] / q[0, kh * 2].norm() * 40.0
+        q[0, 1], q[0, 3] = q[0, 0].clone(), q[0, 2].clone()
+        kp, vp, bt = make_paged([k], [v], nkv, hd, dtype, seed=far)
+        pos = torch.tensor([L - 1], dtype=torch.int32)
+        sot = torch.zeros(1, dtype=torch.int32)
+        out = ops.attn_generic(dev(q.view(1, nh * hd), dtype), kp, vp, dev(pos), dev(sot), bt, nh, nkv, hd, 1.0, None)
+        out = out.float().cpu().view(nh, hd)
+        for h in range(nh):
+            assert torch.allclose(out[h], v[far, h // 2].to(dtype).float(), atol=2e-2), f"far key {far}, head {h}"
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_attention_window_edge(dtype):
+    """The key just outside the window has a huge score and a huge value: it must not count;
+    the key just inside is the one that stands out."""
+    from synaptix_b200 import ops
+    nh, nkv, hd, W = 2, 1, 32, 70
+    for p in (69, 70, 71, 133, 134, 200):
+        L = p + 1
+        k = torch.randn(L, nkv, hd) * 0.05
+        v = torch.randn(L, nkv, hd)
+        q = torch.randn(1, nh, hd)
+        q[0, 1] = q[0, 0]
+        unit = q[0, 0] / q[0, 0].norm()
+        inside, outside = p - W + 1, p - W
+        if inside >= 0:
+            k[inside, 0] = unit * 30.0
+        if outside >= 0:
+            k[outside, 0] = unit * 60.0
+            v[outside, 0] = 1000.0
+        kp, vp, bt = make_paged([k], [v], nkv, hd, dtype, seed=p)
+        out = ops.attn_generic(dev(q.view(1, nh * hd), dtype), kp, vp, dev(torch.tensor([p], dtype=torch.int32)),
+                               dev(torch.zeros(1, dtype=torch.int32)), bt, nh, nkv, hd, 1.0, W)
+        out = out.float().cpu().view(nh, hd)
+        if inside >= 0:
+            assert torch.allclose(out[0], v[inside, 0].to(dtype).float(), atol=2e-2), f"position {p}"
+        assert out.abs().max() < 50, f"position {p}: a key outside the window was used"
+
+
+def test_argmax_last_of_equal_maxima():
+    from synaptix_b200.ops import sampling as K
+    x = torch.randn(5, 3001)
+    x[0, 17] = 50.0
+    x[1, 5] = x[1, 2999] = 40.0
+    x[2, :] = 1.0
+    x[3, 3000] = 60.0
+    x[4, 0] = 70.0
+    got = K.argmax_rows(x.cuda()).tolist()
+    assert got == [17, 2999, 3000, 3000, 0]
+    assert got == [P.greedy(r) for r in x]
+
+
+def test_penalties_match_the_plain_processors():
+    from synaptix_b200.ops import sampling as K
+    V = 500
+    x = torch.randn(3, V) * 3
+    ctxs = [[1, 2, 2, 2, 7, 499], [3] * 10 + [4], [5, 6, 7, 8, 9, 5, 5]]
+    for last_n in (0, 4):
+        hist = torch.zeros(3, 11, dtype=torch.int32)
+        lens = torch.tensor([len(c) for c in ctxs], dtype=torch.int32)
+        for r, c in enumerate(ctxs):
+            hist[r, :len(c)] = torch.tensor(c)
+        y = x.clone().cuda()
+        K.apply_penalties(y, hist.cuda(), lens.cuda(), last_n, 1.3, 0.5, 0.25)
+        for r in range(3):
+            ref = P.processed_logits(x[r].numpy(), ctxs[r], repetition_penalty=1.3, repeat_last_n=last_n,
+                                     presence_penalty=0.5, frequency_penalty=0.25)
+            assert np.allclose(y[r].cpu().numpy(), ref, atol=1e-5)
+
+
+@pytest.mark.parametrize("kw", [dict(temperature=1.0), dict(temperature=0.7), dict(temperature=0.8, top_k=5),
+                                dict(temperature=1.2, top_p=0.6), dict(temperature=1.0, min_p=0.2),
+                                dict(temperature=0.9, top_k=40, top_p=0.8, min_p=0.05)])
+def test_sample_rows_draws_from_the_filtered_distribution(kw):
+    from synaptix_b200.ops import sampling as K
+    V, R, seed = 3001, 64, 1234
+    x = torch.randn(R, V) * 2.5
+    seq = torch.arange(R, dtype=torch.int32) % 7
+    step = torch.arange(R, dtype=torch.int32)
+    u_out = torch.empty(R, device="cuda")
+    got = K.sample_rows(x.cuda(), kw.get("temperature", 1.0), kw.get("top_k", 0), kw.get("top_p", 1.0),
+                        kw.get("min_p", 0.0), seed, seq.cuda(), step.cuda(), u_out=u_out).tolist()
+    us = u_out.cpu().tolist()
+    for r in range(R):
+        u_ref = float(P.uniform_from_u32(P.philox_u32(seed, int(step[r]), int(seq[r]))))
+        assert us[r] == u_ref
+        v = P.processed_logits(x[r].numpy(), **kw)
+        kept = np.isfinite(v)
+        assert kept[got[r]], f"row {r}: token {got[r]} was filtered out"
+        cum = P.multinomial_intervals(v)
+        lo = cum[got[r] - 1] if got[r] > 0 else 0.0
+        assert lo - 1e-4 <= u_ref <= cum[got[r]] + 1e-4, f"row {r}: u={u_ref} outside [{lo}, {cum[got[r]]}]"
+
+
+def test_sample_rows_kept_sets_match_exactly():
+    """With a point mass the draw is forced; with top_k=1 it is the argmax, whatever u is."""
+    from synaptix_b200.ops import sampling as K
+    x = torch.randn(8, 777)
+    z = torch.zeros(8, dtype=torch.int32).cuda()
+    got = K.sample_rows(x.cuda(), 1.0, 1, 1.0, 0.0, 5, z, z).tolist()
+    assert got == x.argmax(dim=1).tolist()
+    got = K.sample_rows(x.cuda(), 1.0, 0, 1e-6, 0.0, 5, z, z).tolist()
+    assert got == x.argmax(dim=1).tolist()
+    got = K.sample_rows(x.cuda(), 1.0, 0, 1.0, 1.0, 5, z, z).tolist()
+    assert got == x.argmax(dim=1).tolist()
+    got = K.sample_rows(x.cuda(), 0.0, 0, 1.0, 0.0, 5, z, z).tolist()       # temperature 0: greedy
+    assert got == x.argmax(dim=1).tolist()
+
+
+def test_sampling_does_not_depend_on_batch_composition():
+    from synaptix_b200.ops import sampling as K
+    x = torch.randn(6, 1000) * 2
+    seq = torch.tensor([3, 1, 4, 1, 5, 9], dtype=torch.int32)
+    step = torch.tensor([2, 7, 1, 8, 2, 8], dtype=torch.int32)
+    whole = K.sample_rows(x.cuda(), 0.8, 50, 0.9, 0.0, 99, seq.cuda(), step.cuda()).tolist()
+    for r in range(6):
+        one = K.sample_rows(x[r:r + 1].cuda(), 0.8, 50, 0.9, 0.0, 99, seq[r:r + 1].cuda(), step[r:r + 1].cuda()).tolist()
+        assert one[0] == whole[r]
