@@ -182,7 +182,9 @@ class Engine:
             seq_past=cut(4, S), seq_lens=cut(5, S), seq_slots=cut(6, S), want_rows=cut(7, R),
             block_tables=[cut(8 + g, S * maxp, (S, maxp)) for g in range(ngroups)],
             n_tokens=T, n_seqs=S, n_want=R, max_new=max(new), max_len=max(p + n for p, n in zip(past, new)),
-            all_single=all(n == 1 for n in new), runtime=self.runtime)
+            all_single=all(n == 1 for n in new), runtime=self.runtime,
+            host={"cu_seqlens": cu.tolist(), "seq_past": list(past), "seq_lens": [p + n for p, n in zip(past, new)],
+                  "seq_slots": [e.slot for e in entries]})
 
     def step(self, entries: Sequence[Entry]) -> torch.Tensor:
         """Run one step; returns float32 logits ``[n_wanted, vocab]`` on the device."""

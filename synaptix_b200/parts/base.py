@@ -54,20 +54,26 @@ class StepContext:
 
     Host values: ``n_tokens``, ``n_seqs``, ``n_want``, ``max_new`` (longest run of new
     tokens), ``max_len`` (longest sequence after the step), ``all_single`` (every sequence
-    brings exactly one token).  Inside a captured graph the host values are upper bounds.
+    brings exactly one token), and ``host``: a dict of Python lists ``cu_seqlens``, ``seq_past``,
+    ``seq_lens``, ``seq_slots`` for parts that loop over sequences on the host.  Inside a
+    captured graph the host values are upper bounds and ``host`` is ``None``: a part that needs
+    it sets ``graph_safe = False`` and the engine then runs every step eagerly.
     """
     __slots__ = ("token_ids", "positions", "seq_of_token", "cu_seqlens", "seq_past", "seq_lens",
                  "seq_slots", "block_tables", "want_rows", "n_tokens", "n_seqs", "n_want",
-                 "max_new", "max_len", "all_single", "runtime", "scratch")
+                 "max_new", "max_len", "all_single", "runtime", "scratch", "host")
 
     def __init__(self, **kw):
         self.scratch = {}
+        self.host = None
         for k, v in kw.items():
             setattr(self, k, v)
 
 
 class Part:
     """Anything that owns tensors."""
+
+    graph_safe = True      # False: forward depends on host values of the step (no CUDA graph)
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         return {}
@@ -87,6 +93,9 @@ class Part:
                     raise ValueError(f"tensor {n!r} is asked for twice with different shapes")
                 out[n] = s
         return out
+
+    def all_graph_safe(self) -> bool:
+        return self.graph_safe and all(c.all_graph_safe() for c in self.children())
 
     def bind_all(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
         self.bind(tensors, rt)
