@@ -61,8 +61,10 @@ class Cache:
                  max_seqs: Optional[int], dtype: torch.dtype, device):
         self.device = torch.device(device)
         self.dtype = dtype
-        self.n_pages = max(1, pages_for(max_tokens))
-        self.max_tokens = self.n_pages * PAGE_TOKENS
+        # page 0 of every group is never handed out: rows that pad a batch up to a captured
+        # graph's size write there, and released or unused block-table entries point there
+        self.n_pages = max(1, pages_for(max_tokens)) + 1
+        self.max_tokens = (self.n_pages - 1) * PAGE_TOKENS
         self.max_seqs = int(max_seqs) if max_seqs is not None else self.n_pages
         if self.max_seqs <= 0:
             raise ValueError("max_seqs must be > 0")
@@ -106,9 +108,9 @@ class Cache:
             self._state.append(torch.zeros((n, self.max_seqs) + tuple(r.shape),
                                            dtype=r.dtype, device=self.device))
 
-        pools = [PagePool(self.n_pages) for _ in kv_keys]
+        pools = [PagePool(self.n_pages - 1, first=1) for _ in kv_keys]
         if not pools:                       # a model without keys still has lengths to keep
-            pools = [PagePool(self.n_pages)]
+            pools = [PagePool(self.n_pages - 1, first=1)]
             windows: List[Optional[int]] = [None]
         else:
             windows = [r.window for r in kv_keys]

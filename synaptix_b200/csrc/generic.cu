@@ -425,3 +425,24 @@ extern "C" int sx_silu_mul(const void* gu, void* out, int n_tokens, int I, int d
   else return SX_ERR_DTYPE;
   return sx_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------
+// after a decode step, on the device: every sequence takes its sampled token as the next
+// input and moves one position on (used by decode runs that never come back to the host)
+// ---------------------------------------------------------------------------------------
+__global__ void decode_advance_kernel(int* __restrict__ token_ids, const int* __restrict__ sampled,
+                                      int* __restrict__ positions, int* __restrict__ seq_past,
+                                      int* __restrict__ seq_lens, int S) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= S) return;
+  token_ids[i] = sampled[i];
+  positions[i] += 1;
+  seq_past[i] += 1;
+  seq_lens[i] += 1;
+}
+extern "C" int sx_decode_advance(int* token_ids, const int* sampled, int* positions, int* seq_past,
+                                 int* seq_lens, int S, cudaStream_t stream) {
+  if (S <= 0) return 0;
+  decode_advance_kernel<<<(S + 127) / 128, 128, 0, stream>>>(token_ids, sampled, positions, seq_past, seq_lens, S);
+  return sx_launch_status();
+}

@@ -128,7 +128,7 @@ def run_generation(engine, sample: Callable, prompts: Sequence[Sequence[int]], o
         stats.batches += 1
         live = [_Live(i, engine.open(), prompts[i]) for i in batch]
         t0 = clock()
-        logits = engine.step([Entry(s.slot, s.prompt, [len(s.prompt) - 1]) for s in live])
+        logits = engine.step([Entry(s.slot, s.prompt, [len(s.prompt) - 1]) for s in live], keep=False)
         toks = sample(logits, [s.request for s in live], [0] * len(live),
                       [s.prompt for s in live] if need_ctx else None)
         stats.prefill_ms += (clock() - t0) * 1e3
@@ -138,7 +138,7 @@ def run_generation(engine, sample: Callable, prompts: Sequence[Sequence[int]], o
         t0 = clock()
         while live:
             try:
-                logits = engine.step([Entry(s.slot, [s.out[-1]], [0]) for s in live])
+                logits = engine.step([Entry(s.slot, [s.out[-1]], [0]) for s in live], keep=False)
             except CacheFull:
                 # no page for everyone: the longest sequence ends, the others go on
                 victim = max(live, key=lambda s: len(s.prompt) + len(s.out))

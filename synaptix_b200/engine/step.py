@@ -7,20 +7,25 @@ attention and the cache write use each token's sequence and position, and the
 final norm and output head run only on the wanted rows.  It runs only the
 tokens it is given, from the cache earlier steps left, and returns float32
 logits ``[n_wanted, vocab]`` in the order of the entries and of ``want``.
-There is no padding, so padding cannot change a result.
+Prompts are never padded.  A step of single tokens may be replayed as a CUDA
+graph captured for a fixed number of rows; rows beyond the live ones then run a
+dummy token that writes to a cache page no sequence owns, and their logits are
+dropped, so this padding changes no result either.
 
 The reference's nearest equivalents are rectangular: ``DecoderModel::forward``
 with one shared past length (crates/synaptix-models/llm/common/src/model.rs:
 1052-1055,1107-1117) and ``forward_decode_dev`` for B rows of one token with
-per-row positions (:1489-1549).
+per-row positions, replayed as a CUDA graph
+(:1489-1549; crates/synaptix-infer/src/graph_capture/capture.rs:24-122).
 """
 from __future__ import annotations
 
-from typing import List, NamedTuple, Optional, Sequence
+from typing import Dict, List, NamedTuple, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache import PAGE_TOKENS, Cache, CacheFull, SlotError, pages_for
 from ..csrc.build import KernelsUnavailable
 from ..parts.base import StepContext
@@ -41,6 +46,29 @@ def _align4(n: int) -> int:
     return (n + 3) & ~3
 
 
+class _Layout:
+    """Where each index array of a step lies in the one int32 buffer that is uploaded."""
+    NAMES = ("token_ids", "positions", "seq_of_token", "cu_seqlens", "seq_past", "seq_lens", "seq_slots",
+             "want_rows")
+
+    def __init__(self, T: int, S: int, R: int, maxp: int, ngroups: int):
+        self.T, self.S, self.R, self.maxp, self.ngroups = T, S, R, maxp, ngroups
+        sizes = [T, T, T, S + 1, S, S, S, R] + [S * maxp] * ngroups
+        self.sizes = sizes
+        self.offs = [0]
+        for s in sizes:
+            self.offs.append(self.offs[-1] + _align4(s))
+        self.total = self.offs[-1]
+
+    def views(self, flat):
+        """name -> view of ``flat`` (numpy or torch), block tables as a list under 'block_tables'."""
+        out = {n: flat[self.offs[i]:self.offs[i] + self.sizes[i]] for i, n in enumerate(self.NAMES)}
+        out["block_tables"] = [
+            flat[self.offs[8 + g]:self.offs[8 + g] + self.S * self.maxp].reshape(self.S, self.maxp)
+            for g in range(self.ngroups)]
+        return out
+
+
 class _Staging:
     """Pinned host buffers for a step's index arrays, reused round-robin; a buffer is
     written again only after the copy that last read it has finished."""
@@ -50,8 +78,9 @@ class _Staging:
         self.bufs: List[Optional[torch.Tensor]] = [None] * depth
         self.events: List[Optional[torch.cuda.Event]] = [None] * depth
         self.i = 0
+        self.bytes_uploaded = 0
 
-    def upload(self, flat: np.ndarray) -> torch.Tensor:
+    def upload(self, flat: np.ndarray, into: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = flat.shape[0]
         i = self.i
         self.i = (i + 1) % len(self.bufs)
@@ -62,12 +91,67 @@ class _Staging:
             buf = torch.empty(max(n, 4096), dtype=torch.int32, pin_memory=True)
             self.bufs[i] = buf
         buf[:n].numpy()[:] = flat
-        dev = torch.empty(n, dtype=torch.int32, device=self.device)
-        dev.copy_(buf[:n], non_blocking=True)
+        dev = into if into is not None else torch.empty(n, dtype=torch.int32, device=self.device)
+        dev[:n].copy_(buf[:n], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev
+        self.bytes_uploaded += n * 4
         return dev
+
+
+def _bucket_rows(n: int) -> int:
+    """Rows of a captured single-token step: 1, 2, 4, 8, then multiples of 8 up to 64, of 32 beyond."""
+    if n <= 8:
+        b = 1
+        while b < n:
+            b *= 2
+        return b
+    if n <= 64:
+        return (n + 7) // 8 * 8
+    return (n + 31) // 32 * 32
+
+
+def _bucket_pages(n: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b
+
+
+class _CapturedStep:
+    """A single-token step of ``S`` rows with block tables ``maxp`` pages wide, with its index
+    arrays at fixed addresses, run eagerly the first time and replayed as a graph afterwards."""
+
+    def __init__(self, engine: "Engine", S: int, maxp: int):
+        self.engine = engine
+        self.layout = _Layout(S, S, S, maxp, engine.cache.n_block_tables)
+        self.flat = torch.zeros(self.layout.total, dtype=torch.int32, device=engine.device)
+        v = self.layout.views(self.flat)
+        self.ctx = StepContext(
+            token_ids=v["token_ids"], positions=v["positions"], seq_of_token=v["seq_of_token"],
+            cu_seqlens=v["cu_seqlens"], seq_past=v["seq_past"], seq_lens=v["seq_lens"], seq_slots=v["seq_slots"],
+            want_rows=v["want_rows"], block_tables=v["block_tables"], n_tokens=S, n_seqs=S, n_want=S, max_new=1,
+            max_len=maxp * PAGE_TOKENS, all_single=True, runtime=engine.runtime)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.launches = 0
+
+    def run(self) -> torch.Tensor:
+        eng = self.engine
+        if self.graph is not None:
+            self.graph.replay()
+            eng.kernel_launches += self.launches
+            return self.logits
+        before = eng.kernel_launches
+        out = eng._forward(self.ctx)                    # eager: the real result of this step
+        self.launches = eng.kernel_launches - before
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):                       # recorded, not run: the cache is untouched
+            self.logits = eng._forward(self.ctx)
+        eng.kernel_launches = before + self.launches
+        self.graph = g
+        return out
 
 
 class Engine:
@@ -86,7 +170,10 @@ class Engine:
         self.cache = Cache(model.cache_requests(), max_tokens=max_tokens, max_seqs=max_seqs,
                            dtype=rt.dtype, device=rt.device)
         self._staging = _Staging(rt.device)
-        self.use_graphs = use_graphs
+        self.use_graphs = bool(use_graphs) and model.all_graph_safe()
+        self._captured: Dict[Tuple[int, int], _CapturedStep] = {}
+        self.kernel_launches = 0         # kernels of this package launched (graph replays counted by content)
+        ops.set_launch_counter(self)
 
     @property
     def max_tokens(self) -> int:
@@ -107,8 +194,11 @@ class Engine:
         return self.cache.slots.length(slot)
 
     # -- a step ------------------------------------------------------------------
-    def plan(self, entries: Sequence[Entry]) -> StepContext:
-        """Check the entries, reserve pages and upload the step's index arrays."""
+    def _forward(self, ctx: StepContext) -> torch.Tensor:
+        ops.set_launch_counter(self)
+        return self.model.forward(ctx, self.cache)
+
+    def _check(self, entries: Sequence[Entry]) -> Tuple[List[int], List[int]]:
         slots = self.cache.slots
         vocab = self.model.embedding.vocab
         if not entries:
@@ -118,79 +208,149 @@ class Engine:
             if e.slot in seen:
                 raise StepError(f"slot {e.slot} appears twice in one step")
             seen.add(e.slot)
-            if len(e.tokens) == 0:
+            n = len(e.tokens)
+            if n == 0:
                 raise StepError(f"slot {e.slot}: an entry brings at least one token")
             slots.length(e.slot)            # raises SlotError if the slot is not open
-        new = [len(e.tokens) for e in entries]
-        slots.reserve_many([e.slot for e in entries], new)
-
-        S, T = len(entries), sum(new)
-        past = [slots.length(e.slot) for e in entries]
-        ngroups = self.cache.n_block_tables
-        maxp = max(pages_for(p + n) for p, n in zip(past, new))
-        R = sum(len(e.want) for e in entries)
-
-        sizes = [T, T, T, S + 1, S, S, S, R] + [S * maxp] * ngroups
-        offs = [0]
-        for s in sizes:
-            offs.append(offs[-1] + _align4(s))
-        flat = np.zeros(offs[-1], dtype=np.int32)
-        tok = flat[offs[0]:offs[0] + T]
-        pos = flat[offs[1]:offs[1] + T]
-        sot = flat[offs[2]:offs[2] + T]
-        cu = flat[offs[3]:offs[3] + S + 1]
-        sp = flat[offs[4]:offs[4] + S]
-        sl = flat[offs[5]:offs[5] + S]
-        ss = flat[offs[6]:offs[6] + S]
-        wr = flat[offs[7]:offs[7] + R]
-        t0 = 0
-        r0 = 0
-        for i, e in enumerate(entries):
-            n = new[i]
-            arr = np.asarray(e.tokens, dtype=np.int64)
-            if arr.ndim != 1 or (arr < 0).any() or (arr >= vocab).any():
+            lo, hi = min(e.tokens), max(e.tokens)
+            if lo < 0 or hi >= vocab:
                 raise StepError(f"slot {e.slot}: token ids must lie in [0, {vocab})")
-            tok[t0:t0 + n] = arr
-            pos[t0:t0 + n] = np.arange(past[i], past[i] + n)
-            sot[t0:t0 + n] = i
-            cu[i] = t0
-            sp[i] = past[i]
-            sl[i] = past[i] + n
-            ss[i] = e.slot
             for w in e.want:
                 if not (0 <= w < n):
                     raise StepError(f"slot {e.slot}: wanted place {w} is outside its {n} tokens")
-                wr[r0] = t0 + w
+        new = [len(e.tokens) for e in entries]
+        slots.reserve_many([e.slot for e in entries], new)
+        past = [slots.length(e.slot) for e in entries]
+        return past, new
+
+    def _fill(self, lay: _Layout, entries: Sequence[Entry], past: List[int], new: List[int]) -> np.ndarray:
+        """The step's index arrays; rows of ``lay`` beyond the entries are dummy single tokens."""
+        slots = self.cache.slots
+        flat = np.zeros(lay.total, dtype=np.int32)
+        v = lay.views(flat)
+        tok, pos, sot, cu = v["token_ids"], v["positions"], v["seq_of_token"], v["cu_seqlens"]
+        t0 = r0 = 0
+        for i, e in enumerate(entries):
+            n = new[i]
+            tok[t0:t0 + n] = e.tokens
+            pos[t0:t0 + n] = np.arange(past[i], past[i] + n)
+            sot[t0:t0 + n] = i
+            cu[i] = t0
+            v["seq_past"][i] = past[i]
+            v["seq_lens"][i] = past[i] + n
+            v["seq_slots"][i] = e.slot
+            for w in e.want:
+                v["want_rows"][r0] = t0 + w
                 r0 += 1
             t0 += n
-        cu[S] = T
-        for g in range(ngroups):
-            bt = flat[offs[8 + g]:offs[8 + g] + S * maxp].reshape(S, maxp)
+        for i in range(len(entries), lay.S):          # dummy rows: token 0 at position 0 of the unowned page 0
+            sot[t0] = i
+            cu[i] = t0
+            v["seq_lens"][i] = 1
+            v["seq_slots"][i] = 0
+            v["want_rows"][r0] = t0
+            r0 += 1
+            t0 += 1
+        cu[lay.S] = t0
+        for g in range(lay.ngroups):
+            bt = v["block_tables"][g]
             for i, e in enumerate(entries):
-                tb = slots.table(e.slot, g)
-                row = np.asarray(tb[:maxp], dtype=np.int32)
+                row = np.asarray(slots.table(e.slot, g)[:lay.maxp], dtype=np.int32)
                 bt[i, :row.shape[0]] = np.maximum(row, 0)
+        return flat
 
-        dev = self._staging.upload(flat)
-
-        def cut(k, n, shape=None):
-            t = dev[offs[k]:offs[k] + n]
-            return t if shape is None else t.view(shape)
-
+    def plan(self, entries: Sequence[Entry], past: List[int], new: List[int]) -> StepContext:
+        """Upload the step's index arrays and wrap them."""
+        S, T = len(entries), sum(new)
+        R = sum(len(e.want) for e in entries)
+        maxp = max(pages_for(p + n) for p, n in zip(past, new))
+        lay = _Layout(T, S, R, maxp, self.cache.n_block_tables)
+        flat = self._fill(lay, entries, past, new)
+        v = lay.views(self._staging.upload(flat))
         return StepContext(
-            token_ids=cut(0, T), positions=cut(1, T), seq_of_token=cut(2, T), cu_seqlens=cut(3, S + 1),
-            seq_past=cut(4, S), seq_lens=cut(5, S), seq_slots=cut(6, S), want_rows=cut(7, R),
-            block_tables=[cut(8 + g, S * maxp, (S, maxp)) for g in range(ngroups)],
+            token_ids=v["token_ids"], positions=v["positions"], seq_of_token=v["seq_of_token"],
+            cu_seqlens=v["cu_seqlens"], seq_past=v["seq_past"], seq_lens=v["seq_lens"], seq_slots=v["seq_slots"],
+            want_rows=v["want_rows"], block_tables=v["block_tables"],
             n_tokens=T, n_seqs=S, n_want=R, max_new=max(new), max_len=max(p + n for p, n in zip(past, new)),
             all_single=all(n == 1 for n in new), runtime=self.runtime,
-            host={"cu_seqlens": cu.tolist(), "seq_past": list(past), "seq_lens": [p + n for p, n in zip(past, new)],
-                  "seq_slots": [e.slot for e in entries]})
+            host={"cu_seqlens": lay.views(flat)["cu_seqlens"].tolist(), "seq_past": list(past),
+                  "seq_lens": [p + n for p, n in zip(past, new)], "seq_slots": [e.slot for e in entries]})
 
-    def step(self, entries: Sequence[Entry]) -> torch.Tensor:
-        """Run one step; returns float32 logits ``[n_wanted, vocab]`` on the device."""
+    def step(self, entries: Sequence[Entry], keep: bool = True) -> torch.Tensor:
+        """Run one step; returns float32 logits ``[n_wanted, vocab]`` on the device.
+
+        With ``keep=False`` the result may be a buffer that the next step overwrites
+        (the generation loop samples from it at once and needs no copy)."""
         entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
-        ctx = self.plan(entries)
-        logits = self.model.forward(ctx, self.cache)
+        past, new = self._check(entries)
+        single = all(n == 1 and tuple(e.want) == (0,) for n, e in zip(new, entries))
+        if single and self.use_graphs:
+            S = _bucket_rows(len(entries))
+            maxp = _bucket_pages(max(pages_for(p + 1) for p in past))
+            cap = self._captured.get((S, maxp))
+            if cap is None:
+                cap = self._captured[(S, maxp)] = _CapturedStep(self, S, maxp)
+            self._staging.upload(self._fill(cap.layout, entries, past, new), into=cap.flat)
+            logits = cap.run()[:len(entries)]
+            if keep:
+                logits = logits.clone()
+        else:
+            ctx = self.plan(entries, past, new)
+            logits = self._forward(ctx)
         for e in entries:
             self.cache.slots.advance(e.slot, len(e.tokens))
         return logits
+
+    # -- decoding without coming back to the host ------------------------------------
+    def decode_run(self, slots: Sequence[int], tokens: Sequence[int], n_steps: int, sampler=None) -> torch.Tensor:
+        """``n_steps`` single-token steps for ``slots`` starting from ``tokens``, each step's
+        sampled token fed to the next on the device; returns the sampled tokens int32
+        ``[n_steps, len(slots)]`` (on the device).  ``sampler(logits) -> int32 [rows]`` runs on
+        the device inside the captured step (default: argmax).  Stop tokens are not looked at."""
+        from ..ops import sampling as K
+        if n_steps <= 0:
+            return torch.empty((0, len(slots)), dtype=torch.int32, device=self.device)
+        entries = [Entry(s, [t], [0]) for s, t in zip(slots, tokens)]
+        past, _ = self._check(entries)
+        self.cache.slots.reserve_many(list(slots), [n_steps] * len(slots))
+        S = len(entries)
+        maxp = max(pages_for(p + n_steps) for p in past)
+        lay = _Layout(S, S, S, maxp, self.cache.n_block_tables)
+        flat = self._staging.upload(self._fill(lay, entries, past, [1] * S)).clone()
+        v = lay.views(flat)
+        ctx = StepContext(
+            token_ids=v["token_ids"], positions=v["positions"], seq_of_token=v["seq_of_token"],
+            cu_seqlens=v["cu_seqlens"], seq_past=v["seq_past"], seq_lens=v["seq_lens"], seq_slots=v["seq_slots"],
+            want_rows=v["want_rows"], block_tables=v["block_tables"], n_tokens=S, n_seqs=S, n_want=S, max_new=1,
+            max_len=maxp * PAGE_TOKENS, all_single=True, runtime=self.runtime)
+        out = torch.empty((n_steps, S), dtype=torch.int32, device=self.device)
+        sampled = torch.empty(S, dtype=torch.int32, device=self.device)
+
+        def one():
+            logits = self._forward(ctx)
+            tok = K.argmax_rows(logits, out=sampled) if sampler is None else sampler(logits)
+            if tok is not sampled:
+                sampled.copy_(tok)
+            ops.decode_advance(ctx.token_ids, sampled, ctx.positions, ctx.seq_past, ctx.seq_lens)
+
+        before = self.kernel_launches
+        one()
+        per_step = self.kernel_launches - before
+        out[0].copy_(sampled)
+        if n_steps > 1:
+            if self.use_graphs:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    one()
+                self.kernel_launches = before + per_step
+                for k in range(1, n_steps):
+                    g.replay()
+                    out[k].copy_(sampled)
+                self.kernel_launches += per_step * (n_steps - 1)
+            else:
+                for k in range(1, n_steps):
+                    one()
+                    out[k].copy_(sampled)
+        for s in slots:
+            self.cache.slots.advance(s, n_steps)
+        return out

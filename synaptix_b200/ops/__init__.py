@@ -12,11 +12,12 @@ from typing import Optional
 import torch
 
 from ..csrc.build import KernelsUnavailable
-from ._lib import KernelError
-from .generic import (add_rmsnorm, attn_generic, embed_gather, gemm_generic, qkv_prepare, residual_add,
+from ._lib import KernelError, set_launch_counter
+from .generic import (add_rmsnorm, attn_generic, decode_advance, embed_gather, gemm_generic, qkv_prepare,
+                      residual_add,
                       silu_mul)
 
-__all__ = ["KernelsUnavailable", "KernelError", "add_rmsnorm", "attn_generic", "embed_gather",
+__all__ = ["KernelsUnavailable", "KernelError", "set_launch_counter", "decode_advance", "add_rmsnorm", "attn_generic", "embed_gather",
            "gemm_generic", "qkv_prepare", "residual_add", "silu_mul", "linear", "attention"]
 
 

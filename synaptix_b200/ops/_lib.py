@@ -45,8 +45,23 @@ def stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def check(code: int, what: str) -> None:
+_COUNTER = [None]
+
+
+def set_launch_counter(obj) -> None:
+    """``obj.kernel_launches`` is incremented for every kernel launched from here on."""
+    _COUNTER[0] = obj
+
+
+def count_launches(n: int) -> None:
+    if _COUNTER[0] is not None:
+        _COUNTER[0].kernel_launches += n
+
+
+def check(code: int, what: str, launches: int = 1) -> None:
     if code == 0:
+        if _COUNTER[0] is not None:
+            _COUNTER[0].kernel_launches += launches
         return
     if code in _ERRORS:
         raise KernelError(f"{what}: {_ERRORS[code]}")

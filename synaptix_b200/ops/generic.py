@@ -139,3 +139,11 @@ def silu_mul(gu: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tens
     check(fn("generic", "sx_silu_mul")(ptr(gu), ptr(out), c_int(T), c_int(I), c_int(dt_code(gu.dtype)), stream()),
           "silu_mul")
     return out
+
+
+def decode_advance(token_ids: torch.Tensor, sampled: torch.Tensor, positions: torch.Tensor,
+                   seq_past: torch.Tensor, seq_lens: torch.Tensor) -> None:
+    """On the device: ``token_ids = sampled`` and every position and length grows by one."""
+    require_cuda(token_ids, sampled, positions, seq_past, seq_lens)
+    check(fn("generic", "sx_decode_advance")(ptr(token_ids), ptr(sampled), ptr(positions), ptr(seq_past),
+                                             ptr(seq_lens), c_int(token_ids.numel()), stream()), "decode_advance")

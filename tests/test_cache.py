@@ -127,11 +127,12 @@ def test_windowed_group_gives_pages_back_while_running():
 def test_cache_groups_requests_and_resets_state():
     reqs = [KVRequest(2, 16), KVRequest(2, 16, window=8), KVRequest(2, 16), StateRequest((3, 4)), None]
     c = Cache(reqs, max_tokens=200, max_seqs=3, dtype=torch.float32, device="cpu")
-    assert c.n_pages == 4 and c.max_tokens == 256
+    assert c.n_pages == 5 and c.max_tokens == 256      # 4 pages to hand out + the never-used page 0
     assert len(c.kv_groups) == 2 and c.n_block_tables == 2
     v0, v1, v2 = c.view(0), c.view(1), c.view(2)
     assert v0.group == v2.group == 0 and v1.group == 1 and v1.window == 8
-    assert v0.k.shape == (4, 2, PAGE_TOKENS, 16)
+    assert v0.k.shape == (5, 2, PAGE_TOKENS, 16)
+    assert all(0 not in c.slots.pools[g].alloc(4) for g in range(2))
     assert v0.k.data_ptr() != v2.k.data_ptr() and v0.k.data_ptr() != v1.k.data_ptr()
     assert c.view(4) is None
     st = c.view(3)

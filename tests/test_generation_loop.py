@@ -26,7 +26,7 @@ class CounterEngine:
         self.slots.close(slot)
         self.closed.append(slot)
 
-    def step(self, entries):
+    def step(self, entries, keep=True):
         self.slots.reserve_many([e.slot for e in entries], [len(e.tokens) for e in entries])
         for e in entries:
             self.slots.advance(e.slot, len(e.tokens))
