@@ -1,0 +1,268 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the Qwen3-4B shape with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W]
+
+A step is one decode step of the whole batch (default batch 8, context 4,096: every
+sequence holds a prompt and decodes up to 4,096 tokens, the timed steps being the last K).
+One JSON line is printed: ``value`` = decoded tokens per second timed on the device over K
+graph-replayed steps whose sampled tokens feed the next step on the device; ``e2e`` = the same
+through the Python entry point (``LLM.generate``), host tokens in and out every step;
+``prefill`` = one 2,048-token prompt; ``points`` = decoding at batch 1 and 64; ``roofline`` =
+bytes a decode step has to read (every weight once, the cache of the live sequences) over
+its time, against the measured copy bandwidth.  Inputs are larger than L2 (a step streams
+all weights, ~8 GB), so L2 is not flushed between steps.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Qwen3-4B shape (the benchmark configuration): every size named here goes into "config"
+QWEN3_4B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, hidden_size=2560,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=9728, vocab_size=151936,
+    rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=40960,
+    hidden_act="silu", attention_bias=False, use_sliding_window=False)
+FULL_LAYERS = 36
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = dict(FALLBACK_PEAKS, source="fallback")
+    if os.path.isfile(p):
+        try:
+            d = json.load(open(p))
+            for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+                if isinstance(d.get(k), (int, float)):
+                    out[k] = float(d[k])
+            out["source"] = "measured"
+        except (OSError, ValueError):
+            pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        mhz, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                mhz.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def decode_bytes(cfg, layers, batch, mean_context):
+    """Bytes one decode step has to read: every matrix once, the embedding rows of the batch,
+    and the keys and values of the live sequences (bfloat16)."""
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = ((nh + 2 * nkv) * hd * H + nh * hd * H + 3 * I * H + 2 * H + 2 * hd) * 2
+    head = V * H * 2
+    kv = 2 * nkv * hd * 2 * layers * mean_context * batch
+    return layers * per_layer + head + batch * H * 2 + kv
+
+
+def prefill_flops(cfg, layers, T):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    mat = ((nh + 2 * nkv) * hd * H + nh * hd * H + 3 * I * H) * 2 * T
+    att = 2 * 2 * nh * hd * T * (T + 1) / 2
+    return layers * (mat + att) + 2 * V * H
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration has (named in config)")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch-1/64 points, the prefill and the e2e run")
+    a = ap.parse_args()
+
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "VitaminDB/synaptix is a Rust workspace (no Python package, no Rust toolchain offline) whose "
+                          "kernels are NVRTC sources for sm_80/sm_120a with no sm_100 path; it cannot be installed or run here"}))
+        return 0
+    if a.gpus != 1:
+        print(f"bench.py measures one GPU: this library runs on a single B200 (asked for --gpus {a.gpus})")
+        return 2
+    a.warmup = max(a.warmup, 3)
+
+    import torch
+    from synaptix_b200.api import LLM
+    from synaptix_b200.config import Qwen3Config
+    from synaptix_b200.engine import DecodeRun, Engine, Entry
+    from synaptix_b200.models import model_skeleton
+    from synaptix_b200.parts import Runtime
+    from synaptix_b200.weights import RandomSource
+
+    cfgd = dict(QWEN3_4B, num_hidden_layers=a.layers)
+    cfg = Qwen3Config.from_dict(cfgd)
+    dev = torch.device("cuda:0")
+    model = model_skeleton(cfg)
+    src = RandomSource(model.all_tensor_specs(), seed=0, std_matrix=0.02, std_gain=0.05, device="cuda:0")
+    model.load(src, Runtime(dev, torch.bfloat16), where="random weights")
+    pk = peaks()
+
+    batches = [a.batch] if a.no_points else sorted({a.batch, 1, 64})
+    K, W = a.steps, a.warmup
+    start_len = a.context - (K + W) - 1          # the timed steps end at the context length
+    if start_len < 1:
+        raise SystemExit("--context is too short for --steps + --warmup")
+    engine = Engine(model, max_tokens=max(batches) * (a.context + 64))
+    g = torch.Generator().manual_seed(1)
+
+    def fill(B):
+        """Open B sequences and run their prompts (a few sequences a step)."""
+        slots = [engine.open() for _ in range(B)]
+        first = []
+        for i in range(0, B, 4):
+            part = slots[i:i + 4]
+            prompts = [torch.randint(0, cfg.vocab_size, (start_len,), generator=g).tolist() for _ in part]
+            lg = engine.step([Entry(s, p, [start_len - 1]) for s, p in zip(part, prompts)], keep=False)
+            first += lg.argmax(-1).tolist()
+        return slots, first
+
+    results = {}
+    clocks = None
+    launches = 0
+    for B in batches:
+        slots, first = fill(B)
+        run = DecodeRun(engine, slots, first, W + K)
+        run.steps(W)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = engine.kernel_launches
+        with ClockSampler() as cs:
+            torch.cuda.synchronize()
+            e0.record()
+            run.steps(K)
+            e1.record()
+            torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        results[B] = {"ms_per_step": ms / K, "tok_s": B * K / (ms / 1e3)}
+        if B == a.batch:
+            clocks = cs.summary()
+            launches = engine.kernel_launches - l0
+        for s in slots:
+            engine.close(s)
+
+    main_r = results[a.batch]
+    mean_ctx = a.context - K / 2.0
+    nbytes = decode_bytes(cfgd, a.layers, a.batch, mean_ctx)
+    achieved = nbytes / (main_r["ms_per_step"] / 1e3) / 1e9
+    line = {
+        "metric": "decode tok/s (Qwen3-4B shape, bf16, random weights)", "value": round(main_r["tok_s"], 2),
+        "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(main_r["ms_per_step"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "Qwen3-4B shape, random weights", "global_batch": a.batch, "seq_len": a.context,
+                   "parallelism": "1 GPU", "layers": a.layers, "layers_of_config": FULL_LAYERS,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_norm_eps, "tied_head": True,
+                   "prefill_tokens": 2048, "l2": "inputs larger than L2 (a step streams ~8 GB of weights)"},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"], "bytes_per_step": int(nbytes)},
+    }
+
+    if not a.no_points:
+        line["points"] = {f"decode_b{B}": round(r["tok_s"], 2) for B, r in results.items() if B != a.batch}
+        line["points"][f"decode_b{a.batch}"] = round(main_r["tok_s"], 2)
+        # prefill of 2,048 tokens, one sequence, fresh slot each time
+        T = 2048
+        toks = torch.randint(0, cfg.vocab_size, (T,), generator=g).tolist()
+        times = []
+        for it in range(3 + 5):
+            s = engine.open()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            engine.step([Entry(s, toks, [T - 1])], keep=False)
+            e1.record()
+            torch.cuda.synchronize()
+            engine.close(s)
+            if it >= 3:
+                times.append(e0.elapsed_time(e1))
+        pms = sorted(times)[len(times) // 2]
+        fl = prefill_flops(cfgd, a.layers, T)
+        line["prefill"] = {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
+                           "frac": round(fl / (pms / 1e3) / 1e12 / pk["bf16_tflops"], 4), "of": pk["source"],
+                           "tflops": round(fl / (pms / 1e3) / 1e12, 1)}
+        # end to end through the Python entry point: host tokens in and out every step
+        del engine
+        torch.cuda.empty_cache()
+        llm = LLM.__new__(LLM)
+        llm.model = model
+        llm.engine = Engine(model, max_tokens=a.batch * (a.context + 64))
+        llm.last_stats = None
+        e2e_steps = K
+        prompts = [torch.randint(0, cfg.vocab_size, (a.context - e2e_steps - 1,), generator=g).tolist()
+                   for _ in range(a.batch)]
+        llm.generate(prompts[:1], max_new_tokens=W + 1, eos_token_ids=[])          # warm-up, captures nothing reused
+        llm.generate(prompts, max_new_tokens=W + 1, eos_token_ids=[], max_batch_size=a.batch)
+        llm.generate(prompts, max_new_tokens=e2e_steps + 1, eos_token_ids=[], max_batch_size=a.batch)
+        st = llm.last_stats
+        line["e2e"] = {"value": round(a.batch * st.decode_steps / (st.decode_ms / 1e3), 2), "unit": "tokens/s",
+                       "h2d_bytes_per_step": st.decode_h2d_bytes // max(st.decode_steps, 1),
+                       "d2h_bytes_per_step": st.decode_d2h_bytes // max(st.decode_steps, 1),
+                       "steps": st.decode_steps}
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -59,20 +59,26 @@ def find_nvcc() -> str:
                              "/usr/local/cuda/bin); the kernels of this package must be compiled for sm_100a")
 
 
+_BUILD_DIR: Optional[str] = None
+_BUILD_DIR_LOCK = threading.Lock()
+
+
 def _build_dir() -> str:
-    d = os.path.join(PKG_DIR, "_build")
-    try:
-        os.makedirs(d, exist_ok=True)
-        probe = os.path.join(d, f".w{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.remove(probe)
-        return d
-    except OSError:
-        uid = os.getuid() if hasattr(os, "getuid") else 0
-        d = os.path.join(tempfile.gettempdir(), f"synaptix_b200-build-{uid}")
-        os.makedirs(d, exist_ok=True)
-        return d
+    global _BUILD_DIR
+    with _BUILD_DIR_LOCK:
+        if _BUILD_DIR is None:
+            d = os.path.join(PKG_DIR, "_build")
+            try:
+                os.makedirs(d, exist_ok=True)
+                fd, probe = tempfile.mkstemp(prefix=".w", dir=d)
+                os.close(fd)
+                os.remove(probe)
+            except OSError:
+                uid = os.getuid() if hasattr(os, "getuid") else 0
+                d = os.path.join(tempfile.gettempdir(), f"synaptix_b200-build-{uid}")
+                os.makedirs(d, exist_ok=True)
+            _BUILD_DIR = d
+        return _BUILD_DIR
 
 
 def _source_hash(name: str) -> str:

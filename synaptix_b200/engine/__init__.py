@@ -1,6 +1,6 @@
 from .generate import (GenerationOptions, GenerationResult, GenerationStats, plan_batches,
                        run_generation)
-from .step import Engine, Entry, StepError
+from .step import DecodeRun, Engine, Entry, StepError
 
-__all__ = ["Engine", "Entry", "StepError", "GenerationOptions", "GenerationResult", "GenerationStats",
+__all__ = ["DecodeRun", "Engine", "Entry", "StepError", "GenerationOptions", "GenerationResult", "GenerationStats",
            "plan_batches", "run_generation"]

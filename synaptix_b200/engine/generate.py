@@ -50,6 +50,8 @@ class GenerationStats:
     decode_ms: float = 0.0
     batches: int = 0
     decode_steps: int = 0
+    decode_h2d_bytes: int = 0     # bytes of index arrays uploaded from pinned memory during decode steps
+    decode_d2h_bytes: int = 0     # bytes of sampled tokens read back during decode steps
 
 
 class _Live:
@@ -136,7 +138,9 @@ def run_generation(engine, sample: Callable, prompts: Sequence[Sequence[int]], o
         live = [s for s, t in zip(live, toks) if take(s, int(t))]
 
         t0 = clock()
+        up0 = getattr(engine, "h2d_bytes", 0)
         while live:
+            stats.decode_d2h_bytes += 4 * len(live)
             try:
                 logits = engine.step([Entry(s.slot, [s.out[-1]], [0]) for s in live], keep=False)
             except CacheFull:
@@ -150,4 +154,5 @@ def run_generation(engine, sample: Callable, prompts: Sequence[Sequence[int]], o
                           [s.prompt + s.out for s in live] if need_ctx else None)
             live = [s for s, t in zip(live, toks) if take(s, int(t))]
         stats.decode_ms += (clock() - t0) * 1e3
+        stats.decode_h2d_bytes += getattr(engine, "h2d_bytes", 0) - up0
     return results, stats

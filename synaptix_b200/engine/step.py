@@ -183,6 +183,11 @@ class Engine:
     def max_seqs(self) -> int:
         return self.cache.max_seqs
 
+    @property
+    def h2d_bytes(self) -> int:
+        """Bytes of step index arrays uploaded from pinned host memory so far."""
+        return self._staging.bytes_uploaded
+
     # -- slots -----------------------------------------------------------------
     def open(self) -> int:
         return self.cache.open()
@@ -305,52 +310,76 @@ class Engine:
     def decode_run(self, slots: Sequence[int], tokens: Sequence[int], n_steps: int, sampler=None) -> torch.Tensor:
         """``n_steps`` single-token steps for ``slots`` starting from ``tokens``, each step's
         sampled token fed to the next on the device; returns the sampled tokens int32
-        ``[n_steps, len(slots)]`` (on the device).  ``sampler(logits) -> int32 [rows]`` runs on
-        the device inside the captured step (default: argmax).  Stop tokens are not looked at."""
-        from ..ops import sampling as K
+        ``[n_steps, len(slots)]`` (on the device).  See ``DecodeRun``."""
         if n_steps <= 0:
             return torch.empty((0, len(slots)), dtype=torch.int32, device=self.device)
+        return DecodeRun(self, slots, tokens, n_steps, sampler).steps(n_steps)
+
+
+class DecodeRun:
+    """Single-token steps of a fixed set of sequences that never come back to the host: each
+    step's sampled token is the next step's input, positions advance on the device, and the
+    whole step (model, sampling, advance) is one CUDA graph after its first, eager run.
+
+    Pages for ``max_steps`` more tokens are reserved up front, so block tables do not change.
+    ``sampler(logits) -> int32 [rows]`` runs on the device inside the step (default: argmax).
+    Stop tokens are not looked at; the generation loop is the place for that.
+    """
+
+    def __init__(self, engine: Engine, slots: Sequence[int], tokens: Sequence[int], max_steps: int, sampler=None):
+        from ..ops import sampling as K
+        self.engine = engine
+        self.slots = list(slots)
+        self.max_steps = max_steps
+        self.done = 0
         entries = [Entry(s, [t], [0]) for s, t in zip(slots, tokens)]
-        past, _ = self._check(entries)
-        self.cache.slots.reserve_many(list(slots), [n_steps] * len(slots))
+        past, _ = engine._check(entries)
+        engine.cache.slots.reserve_many(self.slots, [max_steps] * len(self.slots))
         S = len(entries)
-        maxp = max(pages_for(p + n_steps) for p in past)
-        lay = _Layout(S, S, S, maxp, self.cache.n_block_tables)
-        flat = self._staging.upload(self._fill(lay, entries, past, [1] * S)).clone()
+        maxp = max(pages_for(p + max_steps) for p in past)
+        lay = _Layout(S, S, S, maxp, engine.cache.n_block_tables)
+        flat = engine._staging.upload(engine._fill(lay, entries, past, [1] * S)).clone()
         v = lay.views(flat)
-        ctx = StepContext(
+        self.ctx = ctx = StepContext(
             token_ids=v["token_ids"], positions=v["positions"], seq_of_token=v["seq_of_token"],
             cu_seqlens=v["cu_seqlens"], seq_past=v["seq_past"], seq_lens=v["seq_lens"], seq_slots=v["seq_slots"],
             want_rows=v["want_rows"], block_tables=v["block_tables"], n_tokens=S, n_seqs=S, n_want=S, max_new=1,
-            max_len=maxp * PAGE_TOKENS, all_single=True, runtime=self.runtime)
-        out = torch.empty((n_steps, S), dtype=torch.int32, device=self.device)
-        sampled = torch.empty(S, dtype=torch.int32, device=self.device)
+            max_len=maxp * PAGE_TOKENS, all_single=True, runtime=engine.runtime)
+        self.sampled = sampled = torch.empty(S, dtype=torch.int32, device=engine.device)
 
         def one():
-            logits = self._forward(ctx)
+            logits = engine._forward(ctx)
             tok = K.argmax_rows(logits, out=sampled) if sampler is None else sampler(logits)
             if tok is not sampled:
                 sampled.copy_(tok)
             ops.decode_advance(ctx.token_ids, sampled, ctx.positions, ctx.seq_past, ctx.seq_lens)
 
-        before = self.kernel_launches
-        one()
-        per_step = self.kernel_launches - before
-        out[0].copy_(sampled)
-        if n_steps > 1:
-            if self.use_graphs:
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
-                    one()
-                self.kernel_launches = before + per_step
-                for k in range(1, n_steps):
-                    g.replay()
-                    out[k].copy_(sampled)
-                self.kernel_launches += per_step * (n_steps - 1)
-            else:
-                for k in range(1, n_steps):
-                    one()
-                    out[k].copy_(sampled)
-        for s in slots:
-            self.cache.slots.advance(s, n_steps)
+        self._one = one
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.launches_per_step = 0
+
+    def steps(self, n: int) -> torch.Tensor:
+        """Run ``n`` more steps; returns their sampled tokens int32 ``[n, rows]`` on the device."""
+        eng = self.engine
+        if self.done + n > self.max_steps:
+            raise StepError(f"this run reserved {self.max_steps} steps, {self.done} are done, {n} more asked")
+        out = torch.empty((n, len(self.slots)), dtype=torch.int32, device=eng.device)
+        for k in range(n):
+            if self.graph is None:
+                before = eng.kernel_launches
+                self._one()                                   # eager: the real step
+                self.launches_per_step = eng.kernel_launches - before
+                if eng.use_graphs:
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        self._one()                           # recorded, not run
+                    eng.kernel_launches = before + self.launches_per_step
+                    self.graph = g
+            elif self.graph is not None:
+                self.graph.replay()
+                eng.kernel_launches += self.launches_per_step
+            out[k].copy_(self.sampled)
+        self.done += n
+        for s in self.slots:
+            eng.cache.slots.advance(s, n)
         return out
