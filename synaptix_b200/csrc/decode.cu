@@ -1,0 +1,581 @@
+// Weight-streaming matrix products for decode steps (few rows of activations, bfloat16).
+//
+//   y[b, n] = sum_k x[b, k] * W[n, k]      b < M <= 64,  W [N, K] row-major,  32-bit accumulation
+//
+// A decode step reads every weight once, so these kernels are bound by HBM, not by math.
+// The reference has a warp-per-row GEMV for one row of activations only and falls to a 32x32
+// GEMM tile for more (crates/synaptix-kernels-cuda/src/best_cu/gemv/mma_gemv.cu:19-133,
+// crates/synaptix-kernels-cuda/src/cuda_backend.rs:738-754); here one kernel serves 1..64 rows
+// and reads W once for all of them.
+//
+// Shape of the kernel.  The roles of the operands are swapped: 16 rows of W are the M side of
+// mma.sync.m16n8k16 and 8 rows of activations its N side, so a warp owns 16 output columns for
+// all M activation rows.  Every thread loads 16 contiguous bytes of a W row (8 k-values) straight
+// from global memory into the registers of two MMAs: since a dot product does not care in which
+// order k is visited, the k-values that thread (g, t) holds are declared to be "its" fragment
+// columns, and the activation fragment is loaded with the same map.  No shared-memory staging,
+// no ldmatrix: the only traffic is W once from HBM and x from L1/L2.
+//   warp tile   16 rows of W x (K / KS) of k, KS warps of a block split K and add up through
+//               shared memory in warp order (fixed order, no atomics)
+//   epilogues   bf16 or f32 store;  SiLU(gate)*up for a stacked [gate; up] matrix, where a
+//               warp's 16 rows are 8 gate rows and the 8 matching up rows;
+//               optional RMSNorm prologue: x = rmsnorm(h + delta) * gain computed per block
+//               (h float32), so that the norm needs no kernel and no round trip of x.
+#include "common.cuh"
+
+#define SK_WARPS 8
+#define SK_THREADS (SK_WARPS * 32)
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2 };
+
+// NT: activation rows in tiles of 8 (M <= 8 NT);  KS: warps that split K;  RT = SK_WARPS / KS row tiles per block
+// XS: activations are read from shared memory (filled by the norm prologue) instead of global memory
+template <int NT, int KS, int EPI, bool XS>
+__global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(
+    const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int M, int N, int K,
+    // norm prologue (XS only): x = rmsnorm(h_in + delta) * gain; block 0 writes h_in + delta to h_out
+    const float* __restrict__ h_in, const bf16* __restrict__ delta, float* __restrict__ h_out,
+    const float* __restrict__ gain, float eps) {
+  constexpr int RT = SK_WARPS / KS;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* red = reinterpret_cast<float*>(smem_raw);                        // [SK_WARPS][NT][4][32]
+  bf16* xs = reinterpret_cast<bf16*>(smem_raw + (KS > 1 ? SK_WARPS * NT * 4 * 32 * sizeof(float) : 0));  // [NT*8][K]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int rt = warp / KS, ks = warp % KS;
+
+  if (XS) {
+    // RMSNorm prologue, one warp per activation row, 32-bit throughout
+    for (int b = warp; b < NT * 8; b += SK_WARPS) {
+      bf16* xr = xs + (size_t)b * K;
+      if (b < M) {
+        const float* hr = h_in + (size_t)b * K;
+        const bf16* dr = delta ? delta + (size_t)b * K : nullptr;
+        float ss = 0.f;
+        for (int k = lane; k < K; k += 32) {
+          const float v = hr[k] + (dr ? __bfloat162float(dr[k]) : 0.f);
+          ss += v * v;
+        }
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)K + eps);
+        for (int k = lane; k < K; k += 32) {
+          const float v = hr[k] + (dr ? __bfloat162float(dr[k]) : 0.f);
+          if (blockIdx.x == 0 && h_out) h_out[(size_t)b * K + k] = v;
+          xr[k] = __float2bfloat16_rn(v * inv * gain[k]);
+        }
+      } else {
+        for (int k = lane; k < K; k += 32) xr[k] = __float2bfloat16_rn(0.f);
+      }
+    }
+    __syncthreads();
+  }
+
+  // rows of W this warp owns
+  const int tile = blockIdx.x * RT + rt;
+  int row_lo, row_hi;          // W rows behind fragment rows g and g + 8
+  bool tile_ok;
+  if (EPI == EPI_SILU_MUL) {   // N = 2 I stacked [gate; up]; the tile is 8 gate rows and their up rows
+    const int I = N / 2;
+    const int i = tile * 8 + g;
+    tile_ok = tile * 8 < I;
+    row_lo = min(i, I - 1);
+    row_hi = I + min(i, I - 1);
+  } else {
+    tile_ok = tile * 16 < N;
+    row_lo = min(tile * 16 + g, N - 1);
+    row_hi = min(tile * 16 + g + 8, N - 1);
+  }
+
+  float acc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  const int nsteps = K >> 5;                       // 32 k-values a step
+  const int per = (nsteps + KS - 1) / KS;
+  const int s_begin = ks * per, s_end = min(nsteps, s_begin + per);
+
+  if (tile_ok) {
+    const bf16* wlo = W + (size_t)row_lo * K + t * 8;
+    const bf16* whi = W + (size_t)row_hi * K + t * 8;
+    constexpr int U = 4;
+    int s = s_begin;
+    for (; s + U <= s_end; s += U) {
+      uint4 va[U], vb[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        va[u] = ld_stream16(wlo + (size_t)(s + u) * 32);
+        vb[u] = ld_stream16(whi + (size_t)(s + u) * 32);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const int b = nt * 8 + g;
+          uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+          if (XS) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + (s + u) * 32 + t * 8);
+          else if (b < M) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + (s + u) * 32 + t * 8));
+          mma_bf16_16816(acc[nt], va[u].x, vb[u].x, va[u].y, vb[u].y, xv.x, xv.y);
+          mma_bf16_16816(acc[nt], va[u].z, vb[u].z, va[u].w, vb[u].w, xv.z, xv.w);
+        }
+      }
+    }
+    for (; s < s_end; ++s) {
+      const uint4 va = ld_stream16(wlo + (size_t)s * 32);
+      const uint4 vb = ld_stream16(whi + (size_t)s * 32);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int b = nt * 8 + g;
+        uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+        if (XS) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + s * 32 + t * 8);
+        else if (b < M) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + s * 32 + t * 8));
+        mma_bf16_16816(acc[nt], va.x, vb.x, va.y, vb.y, xv.x, xv.y);
+        mma_bf16_16816(acc[nt], va.z, vb.z, va.w, vb.w, xv.z, xv.w);
+      }
+    }
+  }
+
+  // add up the KS partial sums of a row tile in warp order
+  if (KS > 1) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) red[((warp * NT + nt) * 4 + j) * 32 + lane] = acc[nt][j];
+    __syncthreads();
+    if (ks != 0) return;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float v = acc[nt][j];
+        for (int w = 1; w < KS; ++w) v += red[(((warp + w) * NT + nt) * 4 + j) * 32 + lane];
+        acc[nt][j] = v;
+      }
+  }
+  if (!tile_ok) return;
+
+  // fragment element (j): row g (j < 2) or g + 8 of the tile, activation row nt*8 + t*2 + (j & 1)
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int b = nt * 8 + t * 2 + j;
+      if (b >= M) continue;
+      if (EPI == EPI_SILU_MUL) {
+        const int I = N / 2;
+        const int i = tile * 8 + g;
+        if (i < I) {
+          const float gate = acc[nt][j], up = acc[nt][2 + j];
+          reinterpret_cast<bf16*>(out)[(size_t)b * I + i] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+        }
+      } else {
+        const int n0 = tile * 16 + g, n1 = n0 + 8;
+        if (EPI == EPI_F32) {
+          if (n0 < N) reinterpret_cast<float*>(out)[(size_t)b * N + n0] = acc[nt][j];
+          if (n1 < N) reinterpret_cast<float*>(out)[(size_t)b * N + n1] = acc[nt][2 + j];
+        } else {
+          if (n0 < N) reinterpret_cast<bf16*>(out)[(size_t)b * N + n0] = __float2bfloat16_rn(acc[nt][j]);
+          if (n1 < N) reinterpret_cast<bf16*>(out)[(size_t)b * N + n1] = __float2bfloat16_rn(acc[nt][2 + j]);
+        }
+      }
+    }
+  }
+}
+
+template <int NT, int KS, int EPI, bool XS>
+static int skinny_launch(const bf16* x, const bf16* W, void* out, int M, int N, int K, const float* h_in,
+                         const bf16* delta, float* h_out, const float* gain, float eps, cudaStream_t stream) {
+  constexpr int RT = SK_WARPS / KS;
+  const int tiles = (EPI == EPI_SILU_MUL) ? (N / 2 + 7) / 8 : (N + 15) / 16;
+  const int grid = (tiles + RT - 1) / RT;
+  size_t smem = (KS > 1 ? (size_t)SK_WARPS * NT * 4 * 32 * sizeof(float) : 0) + (XS ? (size_t)NT * 8 * K * sizeof(bf16) : 0);
+  auto kern = skinny_gemm_kernel<NT, KS, EPI, XS>;
+  if (smem > 48 * 1024) {
+    if (smem > 200 * 1024) return SX_ERR_SIZE;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  kern<<<grid, SK_THREADS, smem, stream>>>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps);
+  return sx_launch_status();
+}
+
+template <int NT, int EPI, bool XS>
+static int skinny_pick_ks(int ks, const bf16* x, const bf16* W, void* out, int M, int N, int K, const float* h_in,
+                          const bf16* delta, float* h_out, const float* gain, float eps, cudaStream_t stream) {
+  switch (ks) {
+    case 8: return skinny_launch<NT, 8, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
+    case 4: return skinny_launch<NT, 4, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
+    case 2: return skinny_launch<NT, 2, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
+    default: return skinny_launch<NT, 1, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
+  }
+}
+
+template <int EPI, bool XS>
+static int skinny_pick_nt(int ks, const bf16* x, const bf16* W, void* out, int M, int N, int K, const float* h_in,
+                          const bf16* delta, float* h_out, const float* gain, float eps, cudaStream_t stream) {
+  if (M <= 8) return skinny_pick_ks<1, EPI, XS>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
+  if (M <= 16) return skinny_pick_ks<2, EPI, XS>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
+  if (XS) return SX_ERR_SIZE;   // the norm prologue keeps all rows in shared memory: up to 16 rows
+  if (M <= 32) return skinny_pick_ks<4, EPI, false>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
+  if (M <= 64) return skinny_pick_ks<8, EPI, false>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
+  return SX_ERR_SIZE;
+}
+
+// x [M, K] bf16 (or, with h_in, computed as rmsnorm(h_in + delta) * gain), W [N, K] bf16.
+// epi 0: out bf16 [M, N];  1: out f32 [M, N];  2: W is [gate; up] stacked, out bf16 [M, N/2] = silu(gate) * up.
+// ks: warps that split K (1, 2, 4, 8).  Requires K % 32 == 0, 16-byte aligned x and W, M <= 64
+// (M <= 16 with the norm prologue).
+extern "C" int sx_skinny_gemm(const void* x, const void* W, void* out, int M, int N, int K, int epi, int ks,
+                              const float* h_in, const void* delta, float* h_out, const float* gain, float eps,
+                              cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 31) || M > 64) return SX_ERR_SIZE;
+  if (epi == EPI_SILU_MUL && (N & 1)) return SX_ERR_SIZE;
+  if (((uintptr_t)W & 15) || (x && ((uintptr_t)x & 15))) return SX_ERR_ALIGN;
+  const bf16* xb = (const bf16*)x;
+  const bf16* wb = (const bf16*)W;
+  const bf16* db = (const bf16*)delta;
+  if (h_in) {
+    switch (epi) {
+      case EPI_BF16: return skinny_pick_nt<EPI_BF16, true>(ks, xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, stream);
+      case EPI_SILU_MUL: return skinny_pick_nt<EPI_SILU_MUL, true>(ks, xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, stream);
+      default: return SX_ERR_DTYPE;
+    }
+  }
+  switch (epi) {
+    case EPI_BF16: return skinny_pick_nt<EPI_BF16, false>(ks, xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, stream);
+    case EPI_F32: return skinny_pick_nt<EPI_F32, false>(ks, xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, stream);
+    case EPI_SILU_MUL: return skinny_pick_nt<EPI_SILU_MUL, false>(ks, xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, stream);
+    default: return SX_ERR_DTYPE;
+  }
+}
+
+// =======================================================================================
+// The same product with W brought in by bulk asynchronous copies through a ring of
+// shared-memory stages (cp.async.bulk + mbarrier), persistent over row tiles.
+//
+// The direct-load kernel above has only a few 16-byte loads per thread in flight, which is
+// too little for the small matrices of a layer (the 31 MB of a fused q/k/v matrix need
+// several MB in flight to run at HBM speed).  Here a producer warp keeps STAGES x 16 KB per
+// block in flight whatever the consumers do: a stage is 16 rows of W x 512 k-values, each row
+// one 1 KB bulk copy; 8 consumer warps split a stage's k between them (two 32-k steps each),
+// read their fragments from shared memory with the same "16 bytes of k per thread" map as
+// above, and add up through shared memory at the end of a row tile.  A block walks over row
+// tiles blockIdx.x, blockIdx.x + gridDim.x, ... with the ring running ahead across tiles.
+// Every wait on an mbarrier is bounded; a wait that runs out sets *status and the block ends.
+// =======================================================================================
+#define RG_CONSUMERS 8
+#define RG_THREADS (RG_CONSUMERS * 32 + 32)
+#define RG_STAGE_K 512
+#define RG_ROW_BYTES (RG_STAGE_K * 2 + 16)        // padded: rows land in different banks
+#define RG_STAGE_BYTES (16 * RG_ROW_BYTES)
+#define RG_SPIN_LIMIT (1u << 26)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+// bounded wait: false if the phase did not complete within the limit
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < RG_SPIN_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+template <int NT, int EPI, bool XS, int STAGES>
+__global__ void __launch_bounds__(RG_THREADS) ring_gemm_kernel(
+    const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int M, int N, int K,
+    const float* __restrict__ h_in, const bf16* __restrict__ delta, float* __restrict__ h_out,
+    const float* __restrict__ gain, float eps, int* __restrict__ status) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned char* stages = smem_raw;                                                   // STAGES * RG_STAGE_BYTES
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + STAGES * RG_STAGE_BYTES);   // full[STAGES], empty[STAGES]
+  float* red = reinterpret_cast<float*>(bars + 2 * STAGES);                           // [2][8][NT][4][32]
+  bf16* xs = reinterpret_cast<bf16*>(red + 2 * RG_CONSUMERS * NT * 4 * 32);           // [NT*8][K] (XS only)
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, RG_CONSUMERS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+
+  const int n_rows_out = (EPI == EPI_SILU_MUL) ? N / 2 : N;
+  const int rows_per_tile = (EPI == EPI_SILU_MUL) ? 8 : 16;
+  const int tiles = (n_rows_out + rows_per_tile - 1) / rows_per_tile;
+  const int nk = (K + RG_STAGE_K - 1) / RG_STAGE_K;
+
+  if (warp == RG_CONSUMERS) {
+    // ------------------------------ producer ------------------------------
+    uint32_t it = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
+      int row = 0;
+      if (lane < 16) {
+        if (EPI == EPI_SILU_MUL) {
+          const int i = min(tile * 8 + (lane & 7), N / 2 - 1);
+          row = (lane < 8) ? i : N / 2 + i;
+        } else {
+          row = min(tile * 16 + lane, N - 1);
+        }
+      }
+      const bf16* wrow = W + (size_t)row * K;
+      for (int kb = 0; kb < nk; ++kb, ++it) {
+        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait(empty0 + 8 * s, ph ^ 1);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {
+          if (lane == 0) atomicExch(status, 1);
+          alive = false;
+          break;
+        }
+        const int k0 = kb * RG_STAGE_K;
+        const uint32_t row_bytes = (uint32_t)min(RG_STAGE_K, K - k0) * 2u;
+        if (lane == 0) mbar_expect_tx(full0 + 8 * s, row_bytes * 16u);
+        __syncwarp();
+        if (lane < 16)
+          bulk_copy_g2s(smem_u32(stages + (size_t)s * RG_STAGE_BYTES + lane * RG_ROW_BYTES), wrow + k0, row_bytes,
+                        full0 + 8 * s);
+      }
+    }
+    // copies in flight are waited for by the consumers; if they gave up, wait here (bounded)
+    return;
+  }
+
+  // ------------------------------ consumers ------------------------------
+  if (XS) {
+    for (int b = warp; b < NT * 8; b += RG_CONSUMERS) {
+      bf16* xr = xs + (size_t)b * K;
+      if (b < M) {
+        const float* hr = h_in + (size_t)b * K;
+        const bf16* dr = delta ? delta + (size_t)b * K : nullptr;
+        float ss = 0.f;
+        for (int k = lane; k < K; k += 32) {
+          const float v = hr[k] + (dr ? __bfloat162float(dr[k]) : 0.f);
+          ss += v * v;
+        }
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)K + eps);
+        for (int k = lane; k < K; k += 32) {
+          const float v = hr[k] + (dr ? __bfloat162float(dr[k]) : 0.f);
+          if (blockIdx.x == 0 && h_out) h_out[(size_t)b * K + k] = v;
+          xr[k] = __float2bfloat16_rn(v * inv * gain[k]);
+        }
+      } else {
+        for (int k = lane; k < K; k += 32) xr[k] = __float2bfloat16_rn(0.f);
+      }
+    }
+    asm volatile("bar.sync 1, %0;\n" ::"n"(RG_CONSUMERS * 32) : "memory");
+  }
+
+  uint32_t it = 0;
+  int buf = 0;
+  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, buf ^= 1) {
+    float acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+    for (int kb = 0; kb < nk; ++kb, ++it) {
+      const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+      if (!mbar_wait(full0 + 8 * s, ph)) {
+        if (lane == 0) atomicExch(status, 2);
+        return;
+      }
+      const int k0 = kb * RG_STAGE_K;
+      const int steps = min(RG_STAGE_K, K - k0) >> 5;
+      const uint32_t base = smem_u32(stages + (size_t)s * RG_STAGE_BYTES) + t * 16;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int st = warp + h * RG_CONSUMERS;
+        if (st < steps) {
+          const uint4 va = lds16(base + g * RG_ROW_BYTES + st * 64);
+          const uint4 vb = lds16(base + (g + 8) * RG_ROW_BYTES + st * 64);
+          const int kk = k0 + st * 32 + t * 8;
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const int b = nt * 8 + g;
+            uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+            if (XS) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + kk);
+            else if (b < M) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + kk));
+            mma_bf16_16816(acc[nt], va.x, vb.x, va.y, vb.y, xv.x, xv.y);
+            mma_bf16_16816(acc[nt], va.z, vb.z, va.w, vb.w, xv.z, xv.w);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * s);
+    }
+
+    // add up the 8 warps' partial sums in warp order
+    float* rb = red + (size_t)buf * RG_CONSUMERS * NT * 4 * 32;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) rb[((warp * NT + nt) * 4 + j) * 32 + lane] = acc[nt][j];
+    asm volatile("bar.sync 1, %0;\n" ::"n"(RG_CONSUMERS * 32) : "memory");
+    if (warp != 0) continue;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float v = acc[nt][j];
+        for (int w = 1; w < RG_CONSUMERS; ++w) v += rb[((w * NT + nt) * 4 + j) * 32 + lane];
+        acc[nt][j] = v;
+      }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int b = nt * 8 + t * 2 + j;
+        if (b >= M) continue;
+        if (EPI == EPI_SILU_MUL) {
+          const int I = N / 2;
+          const int i = tile * 8 + g;
+          if (i < I) {
+            const float gate = acc[nt][j], up = acc[nt][2 + j];
+            reinterpret_cast<bf16*>(out)[(size_t)b * I + i] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+          }
+        } else {
+          const int n0 = tile * 16 + g, n1 = n0 + 8;
+          if (EPI == EPI_F32) {
+            if (n0 < N) reinterpret_cast<float*>(out)[(size_t)b * N + n0] = acc[nt][j];
+            if (n1 < N) reinterpret_cast<float*>(out)[(size_t)b * N + n1] = acc[nt][2 + j];
+          } else {
+            if (n0 < N) reinterpret_cast<bf16*>(out)[(size_t)b * N + n0] = __float2bfloat16_rn(acc[nt][j]);
+            if (n1 < N) reinterpret_cast<bf16*>(out)[(size_t)b * N + n1] = __float2bfloat16_rn(acc[nt][2 + j]);
+          }
+        }
+      }
+    }
+  }
+}
+
+static int* rg_status_word() {
+  static int* p = nullptr;           // one word per process and device 0..; allocated at first use
+  static int dev_of = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (p == nullptr || dev_of != dev) {
+    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, sizeof(int));
+    dev_of = dev;
+  }
+  return p;
+}
+
+template <int NT, int EPI, bool XS>
+static int ring_launch(const bf16* x, const bf16* W, void* out, int M, int N, int K, const float* h_in,
+                       const bf16* delta, float* h_out, const float* gain, float eps, int max_blocks,
+                       cudaStream_t stream) {
+  constexpr int STAGES = 6;
+  int* status = rg_status_word();
+  if (!status) return (int)cudaErrorMemoryAllocation;
+  const int rows_per_tile = (EPI == EPI_SILU_MUL) ? 8 : 16;
+  const int n_rows_out = (EPI == EPI_SILU_MUL) ? N / 2 : N;
+  const int tiles = (n_rows_out + rows_per_tile - 1) / rows_per_tile;
+  const int grid = tiles < max_blocks ? tiles : max_blocks;
+  const size_t smem = (size_t)STAGES * RG_STAGE_BYTES + 2 * STAGES * sizeof(uint64_t) +
+                      2 * (size_t)RG_CONSUMERS * NT * 4 * 32 * sizeof(float) + (XS ? (size_t)NT * 8 * K * sizeof(bf16) : 0);
+  if (smem > 227 * 1024) return SX_ERR_SIZE;
+  auto kern = ring_gemm_kernel<NT, EPI, XS, STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  kern<<<grid, RG_THREADS, smem, stream>>>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, status);
+  return sx_launch_status();
+}
+
+template <int EPI, bool XS>
+static int ring_pick_nt(const bf16* x, const bf16* W, void* out, int M, int N, int K, const float* h_in,
+                        const bf16* delta, float* h_out, const float* gain, float eps, int max_blocks,
+                        cudaStream_t stream) {
+  if (M <= 8) return ring_launch<1, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, max_blocks, stream);
+  if (M <= 16) return ring_launch<2, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, max_blocks, stream);
+  if (XS) return SX_ERR_SIZE;
+  if (M <= 32) return ring_launch<4, EPI, false>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, max_blocks, stream);
+  if (M <= 64) return ring_launch<8, EPI, false>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, max_blocks, stream);
+  return SX_ERR_SIZE;
+}
+
+// Same contract as sx_skinny_gemm; max_blocks bounds the persistent grid (2 blocks per SM fit).
+extern "C" int sx_ring_gemm(const void* x, const void* W, void* out, int M, int N, int K, int epi, int max_blocks,
+                            const float* h_in, const void* delta, float* h_out, const float* gain, float eps,
+                            cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 31) || M > 64 || max_blocks <= 0) return SX_ERR_SIZE;
+  if (epi == EPI_SILU_MUL && (N & 1)) return SX_ERR_SIZE;
+  if (((uintptr_t)W & 15) || (x && ((uintptr_t)x & 15))) return SX_ERR_ALIGN;
+  const bf16* xb = (const bf16*)x;
+  const bf16* wb = (const bf16*)W;
+  const bf16* db = (const bf16*)delta;
+  if (h_in) {
+    switch (epi) {
+      case EPI_BF16: return ring_pick_nt<EPI_BF16, true>(xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, max_blocks, stream);
+      case EPI_SILU_MUL: return ring_pick_nt<EPI_SILU_MUL, true>(xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, max_blocks, stream);
+      default: return SX_ERR_DTYPE;
+    }
+  }
+  switch (epi) {
+    case EPI_BF16: return ring_pick_nt<EPI_BF16, false>(xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, max_blocks, stream);
+    case EPI_F32: return ring_pick_nt<EPI_F32, false>(xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, max_blocks, stream);
+    case EPI_SILU_MUL: return ring_pick_nt<EPI_SILU_MUL, false>(xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, max_blocks, stream);
+    default: return SX_ERR_DTYPE;
+  }
+}
+
+// the status word of the ring kernels: 0, or which wait ran out (1 producer, 2 consumer)
+extern "C" int sx_ring_status(int* host_value) {
+  int* p = rg_status_word();
+  if (!p) return (int)cudaErrorMemoryAllocation;
+  return (int)cudaMemcpy(host_value, p, sizeof(int), cudaMemcpyDeviceToHost);
+}

@@ -13,6 +13,7 @@ import torch
 
 from ..csrc.build import KernelsUnavailable
 from ._lib import KernelError, set_launch_counter
+from .decode import skinny_gemm, skinny_supported
 from .generic import (add_rmsnorm, attn_generic, decode_advance, embed_gather, gemm_generic, qkv_prepare,
                       residual_add,
                       silu_mul)
@@ -21,9 +22,25 @@ __all__ = ["KernelsUnavailable", "KernelError", "set_launch_counter", "decode_ad
            "gemm_generic", "qkv_prepare", "residual_add", "silu_mul", "linear", "attention"]
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """``x[M, K] @ w[N, K].T`` with 32-bit accumulation; output in ``out_dtype`` (default ``x``'s)."""
-    return gemm_generic(x, w, out_dtype=out_dtype)
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           epilogue: Optional[str] = None) -> torch.Tensor:
+    """``x[M, K] @ w[N, K].T`` with 32-bit accumulation; output in ``out_dtype`` (default ``x``'s).
+    ``epilogue="silu_mul"``: ``w`` is ``[gate; up]`` stacked and the result is
+    ``silu(x gate^T) * (x up^T)``, ``[M, N/2]``."""
+    M, K = x.shape
+    N = w.shape[0]
+    if out_dtype is None:
+        out_dtype = x.dtype
+    if skinny_supported(M, N, K, x.dtype, w.dtype) and out_dtype in (torch.bfloat16, torch.float32):
+        if epilogue == "silu_mul":
+            if out_dtype == torch.bfloat16:
+                return skinny_gemm(x, w, epilogue="silu_mul")
+        else:
+            return skinny_gemm(x, w, epilogue="f32" if out_dtype == torch.float32 else None)
+    y = gemm_generic(x, w, out_dtype=out_dtype if epilogue is None else x.dtype)
+    if epilogue == "silu_mul":
+        y = silu_mul(y)
+    return y
 
 
 def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx, block_table: torch.Tensor,

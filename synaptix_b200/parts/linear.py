@@ -45,5 +45,6 @@ class Linear(Part):
         """Use an already bound matrix (a tied output head uses the embedding table)."""
         self.weight = weight
 
-    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        return ops.linear(x, self.weight, out_dtype=out_dtype)
+    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                epilogue: Optional[str] = None) -> torch.Tensor:
+        return ops.linear(x, self.weight, out_dtype=out_dtype, epilogue=epilogue)

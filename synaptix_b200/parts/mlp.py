@@ -25,6 +25,5 @@ class SwiGLU(FeedForward):
         return [self.gate_up, self.down]
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gu = self.gate_up.forward(x)
-        z = ops.silu_mul(gu)
+        z = self.gate_up.forward(x, epilogue="silu_mul")
         return self.down.forward(z)

@@ -314,3 +314,113 @@ def test_sampling_does_not_depend_on_batch_composition():
     for r in range(6):
         one = K.sample_rows(x[r:r + 1].cuda(), 0.8, 50, 0.9, 0.0, 99, seq[r:r + 1].cuda(), step[r:r + 1].cuda()).tolist()
         assert one[0] == whole[r]
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("N,K", [(389, 32), (100, 256), (2560, 2560), (48, 9728), (16, 64)])
+def test_skinny_gemm(M, N, K):
+    from synaptix_b200.ops.decode import skinny_gemm
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    for ks in (1, 2, 4, 8):
+        out = skinny_gemm(x.cuda(), w.cuda(), epilogue="f32", ks=ks)
+        assert out.shape == (M, N)
+        assert torch.allclose(out.cpu().double(), ref, atol=2e-5 * math.sqrt(K), rtol=1e-5), f"ks={ks}"
+    out = skinny_gemm(x.cuda(), w.cuda())
+    assert out.dtype == torch.bfloat16 and torch.allclose(out.float().cpu().double(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M", [1, 8, 13, 64])
+@pytest.mark.parametrize("I,K", [(9, 64), (160, 96), (1000, 2560)])
+def test_skinny_gemm_silu_mul_epilogue(M, I, K):
+    from synaptix_b200.ops.decode import skinny_gemm
+    x = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K) * 2 / math.sqrt(K)).to(torch.bfloat16)
+    y = x.double() @ w.double().T
+    gate, up = y[:, :I], y[:, I:]
+    ref = gate / (1 + torch.exp(-gate)) * up
+    for ks in (1, 4, 8):
+        out = skinny_gemm(x.cuda(), w.cuda(), epilogue="silu_mul", ks=ks)
+        assert out.shape == (M, I)
+        assert torch.allclose(out.float().cpu().double(), ref, atol=3e-2, rtol=2e-2), f"ks={ks}"
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 16])
+@pytest.mark.parametrize("epilogue,N", [(None, 200), ("silu_mul", 144)])
+def test_skinny_gemm_with_norm_prologue(M, epilogue, N):
+    from synaptix_b200.ops.decode import skinny_gemm
+    K = 320
+    h = torch.randn(M, K) * 2
+    d = torch.randn(M, K).to(torch.bfloat16)
+    gain = 1 + 0.2 * torch.randn(K)
+    w = (torch.randn(N, K) / math.sqrt(K)).to(torch.bfloat16)
+    s = h + d.float()
+    xn = P.rms_norm(s, gain, 1e-5).to(torch.bfloat16)
+    y = xn.double() @ w.double().T
+    if epilogue == "silu_mul":
+        gate, up = y[:, :N // 2], y[:, N // 2:]
+        y = gate / (1 + torch.exp(-gate)) * up
+    h_out = torch.full((M, K), float("nan"), device="cuda")
+    out = skinny_gemm(None, w.cuda(), epilogue=epilogue, norm_h=h.cuda(), norm_delta=d.cuda(), norm_h_out=h_out,
+                      norm_gain=gain.cuda(), norm_eps=1e-5)
+    assert torch.allclose(h_out.cpu(), s, atol=1e-6)
+    assert torch.allclose(out.float().cpu().double(), y, atol=3e-2, rtol=2e-2)
+    out = skinny_gemm(None, w.cuda(), epilogue=epilogue, norm_h=h.cuda(), norm_delta=None, norm_h_out=None,
+                      norm_gain=gain.cuda(), norm_eps=1e-5)
+    y2 = P.rms_norm(h, gain, 1e-5).to(torch.bfloat16).double() @ w.double().T
+    if epilogue == "silu_mul":
+        y2 = y2[:, :N // 2] / (1 + torch.exp(-y2[:, :N // 2])) * y2[:, N // 2:]
+    assert torch.allclose(out.float().cpu().double(), y2, atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M", [1, 8, 9, 16, 40, 64])
+@pytest.mark.parametrize("N,K", [(389, 32), (100, 544), (2560, 2560), (48, 9728), (16, 512), (700, 1056)])
+def test_ring_gemm(M, N, K):
+    from synaptix_b200.ops.decode import ring_gemm, ring_status
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    for max_blocks in (None, 3):              # 3 blocks: every block walks over many row tiles
+        out = ring_gemm(x.cuda(), w.cuda(), epilogue="f32", max_blocks=max_blocks)
+        assert torch.allclose(out.cpu().double(), ref, atol=2e-5 * math.sqrt(K), rtol=1e-5), f"max_blocks={max_blocks}"
+    out = ring_gemm(x.cuda(), w.cuda())
+    assert out.dtype == torch.bfloat16 and torch.allclose(out.float().cpu().double(), ref, atol=2e-2, rtol=2e-2)
+    assert ring_status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 13, 64])
+@pytest.mark.parametrize("I,K", [(9, 64), (160, 96), (1000, 2560)])
+def test_ring_gemm_silu_mul_epilogue(M, I, K):
+    from synaptix_b200.ops.decode import ring_gemm, ring_status
+    x = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K) * 2 / math.sqrt(K)).to(torch.bfloat16)
+    y = x.double() @ w.double().T
+    ref = y[:, :I] / (1 + torch.exp(-y[:, :I])) * y[:, I:]
+    for max_blocks in (None, 2):
+        out = ring_gemm(x.cuda(), w.cuda(), epilogue="silu_mul", max_blocks=max_blocks)
+        assert out.shape == (M, I) and torch.allclose(out.float().cpu().double(), ref, atol=3e-2, rtol=2e-2)
+    assert ring_status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 5, 16])
+@pytest.mark.parametrize("epilogue,N", [(None, 200), ("silu_mul", 144)])
+def test_ring_gemm_with_norm_prologue(M, epilogue, N):
+    from synaptix_b200.ops.decode import ring_gemm, ring_status
+    K = 1056
+    h = torch.randn(M, K) * 2
+    d = torch.randn(M, K).to(torch.bfloat16)
+    gain = 1 + 0.2 * torch.randn(K)
+    w = (torch.randn(N, K) / math.sqrt(K)).to(torch.bfloat16)
+    s = h + d.float()
+    y = P.rms_norm(s, gain, 1e-5).to(torch.bfloat16).double() @ w.double().T
+    if epilogue == "silu_mul":
+        y = y[:, :N // 2] / (1 + torch.exp(-y[:, :N // 2])) * y[:, N // 2:]
+    h_out = torch.full((M, K), float("nan"), device="cuda")
+    out = ring_gemm(None, w.cuda(), epilogue=epilogue, norm_h=h.cuda(), norm_delta=d.cuda(), norm_h_out=h_out,
+                    norm_gain=gain.cuda(), norm_eps=1e-5)
+    assert torch.allclose(h_out.cpu(), s, atol=1e-6)
+    assert torch.allclose(out.float().cpu().double(), y, atol=3e-2, rtol=2e-2)
+    assert ring_status() == 0
