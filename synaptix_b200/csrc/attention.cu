@@ -1,0 +1,448 @@
+// Attention over the paged cache for bfloat16, on tensor cores: scores and P*V as
+// mma.sync.m16n8k16 with 32-bit accumulation, softmax in 32-bit in the exp2 domain,
+// keys and values brought page by page (64 keys) into shared memory by cp.async.
+//
+//   prefill  one block per (64 query rows of one sequence, query head); each of 4 warps owns
+//            16 query rows and walks over the sequence's pages up to its diagonal.
+//   decode   one block per (split of a sequence's pages, kv head, sequence): the G = nh/nkv
+//            query heads that share the kv head are the rows of ONE fragment, so every key and
+//            value byte is read once for all of them; the 4 warps split the 64 keys of a page,
+//            keep their own running maximum and sum, and are merged at the end.  With more than
+//            one split, un-normalised partial results go to scratch memory and a second kernel
+//            merges them.
+//
+// The reference's prefill kernel has the same FA-2 scheme for contiguous caches
+// (crates/synaptix-kernels-cuda/src/cu/fused/attention/flash_splitq.cu:49-52,187-600); its decode
+// kernel is scalar and re-reads K/V for every query head
+// (crates/synaptix-kernels-cuda/src/cu/fused/attention/flash_decode.cu:92-205,340-387).
+//
+// Masking: key j is visible to the query at position p iff j <= p and (window == 0 or
+// j > p - window).  Rows of a page at or beyond the sequence's length are zero-filled in shared
+// memory (never read from the cache), so stale or non-finite cache contents cannot leak.
+#include "common.cuh"
+
+#define AT_THREADS 128
+#define AT_STAGES 3
+
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;      // src-size 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+template <int HD> struct AtLayout {
+  static constexpr int ROW = HD * 2 + 16;              // bytes of a padded row: ldmatrix rows hit distinct banks
+  static constexpr int TILE = 64 * ROW;                // one page of K (or V)
+  static constexpr int STAGE = 2 * TILE;               // K then V
+  static constexpr int SMEM = AT_STAGES * STAGE;
+};
+
+// one page (64 keys) of K and V of (page, kvh) -> stage; rows >= valid_rows are zero-filled
+template <int HD>
+__device__ __forceinline__ void load_page(unsigned char* stage, const bf16* __restrict__ k_pages,
+                                          const bf16* __restrict__ v_pages, int page, int kvh, int nkv, int valid_rows) {
+  using L = AtLayout<HD>;
+  constexpr int CH = HD / 8;                           // 16-byte chunks per row
+  const size_t base = ((size_t)page * nkv + kvh) * SX_PAGE * HD;
+  for (int c = threadIdx.x; c < 64 * CH; c += AT_THREADS) {
+    const int r = c / CH, ch = c % CH;
+    const bool ok = r < valid_rows;
+    const size_t off = base + (size_t)(ok ? r : 0) * HD + ch * 8;
+    cp_async16(smem_addr(stage + r * L::ROW + ch * 16), k_pages + off, ok);
+    cp_async16(smem_addr(stage + L::TILE + r * L::ROW + ch * 16), v_pages + off, ok);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Scores of one 16-row query fragment against NKT key tiles (8 keys each) starting at key
+// row `key0` of the staged page, masking, online softmax update, and O += P V.
+//   qf     query fragments [HD/16][4]
+//   pos_lo/pos_hi  absolute positions of fragment rows g and g + 8 (keys beyond are masked);
+//                  a negative position masks the whole row
+//   jbase  absolute index of the page's first key
+// ---------------------------------------------------------------------------------------
+template <int HD, int NKT>
+__device__ __forceinline__ void attend_tile(const uint32_t (&qf)[HD / 16][4], const unsigned char* kst,
+                                            const unsigned char* vst, int key0, int jbase, int pos_lo, int pos_hi,
+                                            int window, float scale_log2, float (&m)[2], float (&l)[2],
+                                            float (&o)[HD / 8][4]) {
+  using L = AtLayout<HD>;
+  const int lane = threadIdx.x & 31, t = lane & 3;
+  float s[NKT][4];
+#pragma unroll
+  for (int i = 0; i < NKT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+
+  // S = Q K^T : for each key tile, walk over head dim in steps of 32 (one ldmatrix.x4 = two k-steps)
+  const int lrow = lane & 7, lmat = lane >> 3;
+#pragma unroll
+  for (int kt = 0; kt < NKT; ++kt) {
+    const uint32_t kaddr = smem_addr(kst + (key0 + kt * 8 + lrow) * L::ROW + lmat * 16);
+#pragma unroll
+    for (int d = 0; d < HD / 32; ++d) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4(b0, b1, b2, b3, kaddr + d * 64);
+      mma16816(s[kt], qf[2 * d], b0, b1);
+      mma16816(s[kt], qf[2 * d + 1], b2, b3);
+    }
+  }
+  // mask and running maximum
+  float mx[2] = {m[0], m[1]};
+#pragma unroll
+  for (int kt = 0; kt < NKT; ++kt) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int j = jbase + key0 + kt * 8 + 2 * t + (e & 1);
+      const int p = (e < 2) ? pos_lo : pos_hi;
+      const bool vis = j <= p && (window == 0 || j > p - window);
+      const float v = vis ? s[kt][e] * scale_log2 : -INFINITY;
+      s[kt][e] = v;
+      mx[e >> 1] = fmaxf(mx[e >> 1], v);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+  }
+  float corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+  for (int r = 0; r < 2; ++r) corr[r] = (mx[r] == -INFINITY) ? 1.f : exp2f(m[r] - mx[r]);
+#pragma unroll
+  for (int kt = 0; kt < NKT; ++kt) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float mm = mx[e >> 1];
+      const float p = (mm == -INFINITY) ? 0.f : exp2f(s[kt][e] - mm);
+      s[kt][e] = p;
+      sum[e >> 1] += p;
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] = l[r] * corr[r] + sum[r];      // per-thread partial sums; lanes of a row are added at the end
+    m[r] = mx[r];
+  }
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) {
+    o[n][0] *= corr[0]; o[n][1] *= corr[0];
+    o[n][2] *= corr[1]; o[n][3] *= corr[1];
+  }
+  // O += P V : 16 keys a step; V fragments by transposing ldmatrix
+#pragma unroll
+  for (int kk = 0; kk < NKT / 2; ++kk) {
+    uint32_t pa[4];
+    pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    // matrices of one ldmatrix.x4.trans: (keys 0-7, d 0-7), (keys 8-15, d 0-7), (keys 0-7, d 8-15), (keys 8-15, d 8-15)
+    const uint32_t vaddr = smem_addr(vst + (key0 + kk * 16 + (lmat & 1) * 8 + lrow) * L::ROW + (lmat >> 1) * 16);
+#pragma unroll
+    for (int n = 0; n < HD / 16; ++n) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4_trans(b0, b1, b2, b3, vaddr + n * 32);
+      mma16816(o[2 * n], pa, b0, b1);
+      mma16816(o[2 * n + 1], pa, b2, b3);
+    }
+  }
+}
+
+// =======================================================================================
+// decode: grid (n_splits, nkv, S), one query token per sequence (token index = sequence index)
+// =======================================================================================
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+    bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+    const int* __restrict__ seq_lens, const int* __restrict__ block_table, int maxp, int nh, int nkv,
+    float scale_log2, int window, int n_splits) {
+  using L = AtLayout<HD>;
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+  const int G = nh / nkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int len = seq_lens[seq];
+  const int pos = len - 1;                                   // the query's position
+  const int lo = window > 0 ? max(0, len - window) : 0;      // first visible key
+  const int p_first = lo >> 6, p_end = (len + 63) >> 6;
+  const int total = p_end - p_first;
+  const int per = (total + n_splits - 1) / n_splits;
+  const int p0 = p_first + split * per, p1 = min(p_end, p0 + per);
+  const int* bt = block_table + (size_t)seq * maxp;
+
+  // query fragments: row r of the fragment is query head kvh*G + r (rows >= G are zero)
+  uint32_t qf[HD / 16][4];
+  {
+    const bf16* qb = q + ((size_t)seq * nh + (size_t)kvh * G) * HD;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      const int c = ks * 16 + 2 * t;
+      qf[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(qb + (size_t)g * HD + c) : 0u;
+      qf[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + (size_t)(g + 8) * HD + c) : 0u;
+      qf[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(qb + (size_t)g * HD + c + 8) : 0u;
+      qf[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + (size_t)(g + 8) * HD + c + 8) : 0u;
+    }
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+  const int npages = max(0, p1 - p0);
+#pragma unroll
+  for (int st = 0; st < AT_STAGES - 1; ++st) {
+    if (st < npages) load_page<HD>(smem + st * L::STAGE, k_pages, v_pages, bt[p0 + st], kvh, nkv, min(64, len - (p0 + st) * 64));
+    cp_async_commit();
+  }
+  for (int i = 0; i < npages; ++i) {
+    cp_async_wait<AT_STAGES - 2>();
+    __syncthreads();
+    const int nx = i + AT_STAGES - 1;
+    if (nx < npages)
+      load_page<HD>(smem + (nx % AT_STAGES) * L::STAGE, k_pages, v_pages, bt[p0 + nx], kvh, nkv, min(64, len - (p0 + nx) * 64));
+    cp_async_commit();
+    const unsigned char* st = smem + (i % AT_STAGES) * L::STAGE;
+    // this warp's 16 keys of the page; all fragment rows sit at the same position
+    attend_tile<HD, 2>(qf, st, st + L::TILE, warp * 16, (p0 + i) * 64, pos, pos, window, scale_log2, m, l, o);
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // rows' sums over the 4 lanes that share a row
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  // merge the 4 warps through shared memory (the stage buffers are free now)
+  float* wo = reinterpret_cast<float*>(smem);                 // [4][16][HD]
+  float* wml = wo + 4 * 16 * HD;                              // [4][16][2]
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) {
+    const int c = n * 8 + 2 * t;
+    wo[(warp * 16 + g) * HD + c] = o[n][0];
+    wo[(warp * 16 + g) * HD + c + 1] = o[n][1];
+    wo[(warp * 16 + g + 8) * HD + c] = o[n][2];
+    wo[(warp * 16 + g + 8) * HD + c + 1] = o[n][3];
+  }
+  if (t == 0) {
+    wml[(warp * 16 + g) * 2] = m[0];
+    wml[(warp * 16 + g) * 2 + 1] = l[0];
+    wml[(warp * 16 + g + 8) * 2] = m[1];
+    wml[(warp * 16 + g + 8) * 2 + 1] = l[1];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * HD; idx += AT_THREADS) {
+    const int r = idx / HD, d = idx % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, wml[(w * 16 + r) * 2]);
+    float Lsum = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = wml[(w * 16 + r) * 2];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      Lsum += wml[(w * 16 + r) * 2 + 1] * f;
+      O += wo[(w * 16 + r) * HD + d] * f;
+    }
+    const int head = kvh * G + r;
+    if (n_splits == 1) {
+      out[((size_t)seq * nh + head) * HD + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
+    } else {
+      const size_t pi = ((size_t)seq * nh + head) * n_splits + split;
+      part_o[pi * HD + d] = O;
+      if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = Lsum; }
+    }
+  }
+}
+
+// merge of the splits: grid (S * nh), HD threads
+template <int HD>
+__global__ void __launch_bounds__(HD) attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                        bf16* __restrict__ out, int n_splits) {
+  const size_t row = blockIdx.x;
+  const int d = threadIdx.x;
+  float M = -INFINITY;
+  for (int i = 0; i < n_splits; ++i) M = fmaxf(M, part_ml[(row * n_splits + i) * 2]);
+  float Lsum = 0.f, O = 0.f;
+  for (int i = 0; i < n_splits; ++i) {
+    const float mi = part_ml[(row * n_splits + i) * 2];
+    const float f = (mi == -INFINITY) ? 0.f : exp2f(mi - M);
+    Lsum += part_ml[(row * n_splits + i) * 2 + 1] * f;
+    O += part_o[(row * n_splits + i) * HD + d] * f;
+  }
+  out[row * HD + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
+}
+
+// =======================================================================================
+// prefill: grid (n_tiles, nh); tile i covers query rows tile_q0[i] .. +63 of sequence tile_seq[i]
+// =======================================================================================
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS) attn_prefill_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+    bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_q0,
+    const int* __restrict__ cu_seqlens, const int* __restrict__ seq_past, const int* __restrict__ seq_lens,
+    const int* __restrict__ block_table, int maxp, int nh, int nkv, float scale_log2, int window) {
+  using L = AtLayout<HD>;
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int tile = blockIdx.x, h = blockIdx.y;
+  const int seq = tile_seq[tile], q0 = tile_q0[tile];
+  const int kvh = h / (nh / nkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int t_begin = cu_seqlens[seq], n_new = cu_seqlens[seq + 1] - t_begin;
+  const int past = seq_past[seq], len = seq_lens[seq];
+  const int rows = min(64, n_new - q0);                       // query rows of this tile
+  const int* bt = block_table + (size_t)seq * maxp;
+
+  // this warp's rows, their packed token indices and positions
+  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
+  const bool ok_lo = r_lo < rows, ok_hi = r_hi < rows;
+  const int pos_lo = ok_lo ? past + q0 + r_lo : -1, pos_hi = ok_hi ? past + q0 + r_hi : -1;
+  uint32_t qf[HD / 16][4];
+  {
+    const bf16* qlo = q + ((size_t)(t_begin + q0 + (ok_lo ? r_lo : 0)) * nh + h) * HD;
+    const bf16* qhi = q + ((size_t)(t_begin + q0 + (ok_hi ? r_hi : 0)) * nh + h) * HD;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      const int c = ks * 16 + 2 * t;
+      qf[ks][0] = ok_lo ? *reinterpret_cast<const uint32_t*>(qlo + c) : 0u;
+      qf[ks][1] = ok_hi ? *reinterpret_cast<const uint32_t*>(qhi + c) : 0u;
+      qf[ks][2] = ok_lo ? *reinterpret_cast<const uint32_t*>(qlo + c + 8) : 0u;
+      qf[ks][3] = ok_hi ? *reinterpret_cast<const uint32_t*>(qhi + c + 8) : 0u;
+    }
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+  // pages the tile can see: from the first key visible to its first row to the last row's position
+  const int first_pos = past + q0, last_pos = past + q0 + rows - 1;
+  const int lo_key = window > 0 ? max(0, first_pos - window + 1) : 0;
+  const int p0 = lo_key >> 6, p1 = (last_pos >> 6) + 1;
+  const int npages = p1 - p0;
+  // this warp needs pages up to its own last row only
+  const int warp_last = past + q0 + min(rows - 1, warp * 16 + 15);
+  const bool warp_on = warp * 16 < rows;
+
+#pragma unroll
+  for (int st = 0; st < AT_STAGES - 1; ++st) {
+    if (st < npages) load_page<HD>(smem + st * L::STAGE, k_pages, v_pages, bt[p0 + st], kvh, nkv, min(64, len - (p0 + st) * 64));
+    cp_async_commit();
+  }
+  for (int i = 0; i < npages; ++i) {
+    cp_async_wait<AT_STAGES - 2>();
+    __syncthreads();
+    const int nx = i + AT_STAGES - 1;
+    if (nx < npages)
+      load_page<HD>(smem + (nx % AT_STAGES) * L::STAGE, k_pages, v_pages, bt[p0 + nx], kvh, nkv, min(64, len - (p0 + nx) * 64));
+    cp_async_commit();
+    const unsigned char* st = smem + (i % AT_STAGES) * L::STAGE;
+    const int jbase = (p0 + i) * 64;
+    if (warp_on && jbase <= warp_last)
+      attend_tile<HD, 8>(qf, st, st + L::TILE, 0, jbase, pos_lo, pos_hi, window, scale_log2, m, l, o);
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  const float inv_lo = l[0] > 0.f ? 1.f / l[0] : 0.f, inv_hi = l[1] > 0.f ? 1.f / l[1] : 0.f;
+  bf16* olo = out + ((size_t)(t_begin + q0 + r_lo) * nh + h) * HD;
+  bf16* ohi = out + ((size_t)(t_begin + q0 + r_hi) * nh + h) * HD;
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) {
+    const int c = n * 8 + 2 * t;
+    if (ok_lo) *reinterpret_cast<uint32_t*>(olo + c) = pack_bf16(o[n][0] * inv_lo, o[n][1] * inv_lo);
+    if (ok_hi) *reinterpret_cast<uint32_t*>(ohi + c) = pack_bf16(o[n][2] * inv_hi, o[n][3] * inv_hi);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+template <int HD>
+static int decode_launch(const bf16* q, const bf16* k, const bf16* v, bf16* out, float* part_o, float* part_ml,
+                         const int* seq_lens, const int* bt, int maxp, int S, int nh, int nkv, float scale_log2,
+                         int window, int n_splits, cudaStream_t stream) {
+  using L = AtLayout<HD>;
+  const size_t merge_bytes = (size_t)(4 * 16 * HD + 4 * 16 * 2) * sizeof(float);
+  const size_t smem = L::SMEM > merge_bytes ? L::SMEM : merge_bytes;
+  auto kern = attn_decode_kernel<HD>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid(n_splits, nkv, S);
+  kern<<<grid, AT_THREADS, smem, stream>>>(q, k, v, out, part_o, part_ml, seq_lens, bt, maxp, nh, nkv, scale_log2,
+                                          window, n_splits);
+  int rc = sx_launch_status();
+  if (rc || n_splits == 1) return rc;
+  attn_merge_kernel<HD><<<S * nh, HD, 0, stream>>>(part_o, part_ml, out, n_splits);
+  return sx_launch_status();
+}
+
+// q [S, nh, hd] (one token per sequence), out [S, nh*hd]; part_o f32 [S*nh*n_splits*hd] and
+// part_ml f32 [S*nh*n_splits*2] are scratch (unused when n_splits == 1).
+extern "C" int sx_attn_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o,
+                              float* part_ml, const int* seq_lens, const int* block_table, int maxp, int S, int nh,
+                              int nkv, int hd, float scale, int window, int n_splits, cudaStream_t stream) {
+  if (S <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || n_splits < 1 || nkv > 65535 || S > 65535) return SX_ERR_SIZE;
+  if (n_splits > 1 && (!part_o || !part_ml)) return SX_ERR_SIZE;
+  const float sl = scale * 1.4426950408889634f;
+  const bf16 *qb = (const bf16*)q, *kb = (const bf16*)k_pages, *vb = (const bf16*)v_pages;
+  if (hd == 128) return decode_launch<128>(qb, kb, vb, (bf16*)out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, sl, window, n_splits, stream);
+  if (hd == 64) return decode_launch<64>(qb, kb, vb, (bf16*)out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, sl, window, n_splits, stream);
+  if (hd == 32) return decode_launch<32>(qb, kb, vb, (bf16*)out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, sl, window, n_splits, stream);
+  return SX_ERR_SIZE;
+}
+
+template <int HD>
+static int prefill_launch(const bf16* q, const bf16* k, const bf16* v, bf16* out, const int* tile_seq, const int* tile_q0,
+                          int n_tiles, const int* cu, const int* past, const int* lens, const int* bt, int maxp, int nh,
+                          int nkv, float scale_log2, int window, cudaStream_t stream) {
+  using L = AtLayout<HD>;
+  auto kern = attn_prefill_kernel<HD>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid(n_tiles, nh);
+  kern<<<grid, AT_THREADS, L::SMEM, stream>>>(q, k, v, out, tile_seq, tile_q0, cu, past, lens, bt, maxp, nh, nkv,
+                                             scale_log2, window);
+  return sx_launch_status();
+}
+
+// q [T, nh, hd] packed tokens, out [T, nh*hd]; tile_seq/tile_q0 [n_tiles] list 64-row query tiles.
+extern "C" int sx_attn_prefill(const void* q, const void* k_pages, const void* v_pages, void* out,
+                               const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_seqlens,
+                               const int* seq_past, const int* seq_lens, const int* block_table, int maxp, int nh,
+                               int nkv, int hd, float scale, int window, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || nh > 65535) return SX_ERR_SIZE;
+  const float sl = scale * 1.4426950408889634f;
+  const bf16 *qb = (const bf16*)q, *kb = (const bf16*)k_pages, *vb = (const bf16*)v_pages;
+  if (hd == 128) return prefill_launch<128>(qb, kb, vb, (bf16*)out, tile_seq, tile_q0, n_tiles, cu_seqlens, seq_past, seq_lens, block_table, maxp, nh, nkv, sl, window, stream);
+  if (hd == 64) return prefill_launch<64>(qb, kb, vb, (bf16*)out, tile_seq, tile_q0, n_tiles, cu_seqlens, seq_past, seq_lens, block_table, maxp, nh, nkv, sl, window, stream);
+  if (hd == 32) return prefill_launch<32>(qb, kb, vb, (bf16*)out, tile_seq, tile_q0, n_tiles, cu_seqlens, seq_past, seq_lens, block_table, maxp, nh, nkv, sl, window, stream);
+  return SX_ERR_SIZE;
+}

@@ -13,6 +13,7 @@ import torch
 
 from ..csrc.build import KernelsUnavailable
 from ._lib import KernelError, set_launch_counter
+from .attention import attn_decode, attn_prefill, fast_supported, pick_splits, query_tiles
 from .decode import skinny_gemm, skinny_supported
 from .generic import (add_rmsnorm, attn_generic, decode_advance, embed_gather, gemm_generic, qkv_prepare,
                       residual_add,
@@ -47,5 +48,19 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx
               nh: int, nkv: int, hd: int, scale: float, window: Optional[int]) -> torch.Tensor:
     """Causal attention of the step's packed queries over the cache (which already holds
     this step's keys and values)."""
+    if fast_supported(q.dtype, nh, nkv, hd):
+        if ctx.all_single:
+            max_pages = (ctx.max_len + 63) // 64
+            return attn_decode(q, k_pages, v_pages, ctx.seq_lens, block_table, nh, nkv, hd, scale, window,
+                               pick_splits(ctx.n_seqs, nkv, max_pages, q.device))
+        if ctx.host is not None:
+            tiles = ctx.scratch.get("query_tiles")
+            if tiles is None:
+                import numpy as np
+                ts, t0 = query_tiles(ctx.host["cu_seqlens"])
+                both = torch.from_numpy(np.asarray([ts, t0], dtype=np.int32)).to(q.device, non_blocking=True)
+                tiles = ctx.scratch["query_tiles"] = (both[0], both[1])
+            return attn_prefill(q, k_pages, v_pages, tiles[0], tiles[1], ctx.cu_seqlens, ctx.seq_past, ctx.seq_lens,
+                                block_table, nh, nkv, hd, scale, window)
     return attn_generic(q, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, nh, nkv, hd,
                         scale, window)

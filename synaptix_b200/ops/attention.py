@@ -1,0 +1,84 @@
+"""Python faces of the tensor-core attention kernels in ``csrc/attention.cu`` (bfloat16)."""
+from __future__ import annotations
+
+from typing import Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ._lib import KernelError, c_float, c_int, check, fn, ptr, require_cuda, stream
+from .decode import sm_count
+
+FAST_HEAD_DIMS = (32, 64, 128)
+
+
+def fast_supported(dtype, nh: int, nkv: int, hd: int) -> bool:
+    return dtype == torch.bfloat16 and hd in FAST_HEAD_DIMS and nkv > 0 and nh % nkv == 0 and nh // nkv <= 16
+
+
+def pick_splits(n_seqs: int, nkv: int, max_pages: int, device) -> int:
+    """Splits of a sequence's pages over blocks, so that a few blocks per SM are busy."""
+    target = 4 * sm_count(device)
+    base = max(1, n_seqs * nkv)
+    return max(1, min(max_pages, (target + base - 1) // base))
+
+
+def attn_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, seq_lens: torch.Tensor,
+                block_table: torch.Tensor, nh: int, nkv: int, hd: int, scale: float, window: Optional[int],
+                n_splits: int, out: Optional[torch.Tensor] = None,
+                scratch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
+    """One query token per sequence (row ``s`` of ``q`` belongs to sequence ``s``) against the
+    sequence's ``seq_lens[s]`` cached keys (its own included).  ``n_splits > 1`` splits the
+    pages of every sequence over blocks; partial results go through float32 scratch
+    (``scratch = (part_o [S*nh*n_splits*hd], part_ml [S*nh*n_splits*2])``, allocated if absent)."""
+    require_cuda(q, k_pages, v_pages, seq_lens, block_table, out)
+    S = q.shape[0]
+    if not fast_supported(q.dtype, nh, nkv, hd) or k_pages.dtype != q.dtype:
+        raise KernelError("attn_decode: bfloat16, head size 32/64/128 and at most 16 query heads per kv head")
+    if out is None:
+        out = torch.empty((S, nh * hd), dtype=q.dtype, device=q.device)
+    part_o = part_ml = None
+    if n_splits > 1:
+        if scratch is None:
+            part_o = torch.empty(S * nh * n_splits * hd, dtype=torch.float32, device=q.device)
+            part_ml = torch.empty(S * nh * n_splits * 2, dtype=torch.float32, device=q.device)
+        else:
+            part_o, part_ml = scratch
+            if part_o.numel() < S * nh * n_splits * hd or part_ml.numel() < S * nh * n_splits * 2:
+                raise KernelError("attn_decode: scratch is too small")
+    check(fn("attention", "sx_attn_decode")(
+        ptr(q), ptr(k_pages), ptr(v_pages), ptr(out), ptr(part_o), ptr(part_ml), ptr(seq_lens), ptr(block_table),
+        c_int(block_table.shape[1]), c_int(S), c_int(nh), c_int(nkv), c_int(hd), c_float(scale),
+        c_int(0 if window is None else int(window)), c_int(n_splits), stream()), "attn_decode",
+        launches=2 if n_splits > 1 else 1)
+    return out
+
+
+def query_tiles(cu_seqlens: Sequence[int], rows: int = 64):
+    """Lists (sequence, first row) of the ``rows``-row query tiles of a packed batch."""
+    seqs, q0s = [], []
+    for s in range(len(cu_seqlens) - 1):
+        n = cu_seqlens[s + 1] - cu_seqlens[s]
+        for q0 in range(0, n, rows):
+            seqs.append(s)
+            q0s.append(q0)
+    return seqs, q0s
+
+
+def attn_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, tile_seq: torch.Tensor,
+                 tile_q0: torch.Tensor, cu_seqlens: torch.Tensor, seq_past: torch.Tensor, seq_lens: torch.Tensor,
+                 block_table: torch.Tensor, nh: int, nkv: int, hd: int, scale: float, window: Optional[int],
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Packed query tokens of sequences with unequal lengths against the cache (which already
+    holds this step's keys); ``tile_seq``/``tile_q0`` list the 64-row query tiles."""
+    require_cuda(q, k_pages, v_pages, tile_seq, tile_q0, cu_seqlens, seq_past, seq_lens, block_table, out)
+    T = q.shape[0]
+    if not (q.dtype == torch.bfloat16 and hd in FAST_HEAD_DIMS and nh % nkv == 0):
+        raise KernelError("attn_prefill: bfloat16 and head size 32/64/128")
+    if out is None:
+        out = torch.empty((T, nh * hd), dtype=q.dtype, device=q.device)
+    check(fn("attention", "sx_attn_prefill")(
+        ptr(q), ptr(k_pages), ptr(v_pages), ptr(out), ptr(tile_seq), ptr(tile_q0), c_int(tile_seq.numel()),
+        ptr(cu_seqlens), ptr(seq_past), ptr(seq_lens), ptr(block_table), c_int(block_table.shape[1]), c_int(nh),
+        c_int(nkv), c_int(hd), c_float(scale), c_int(0 if window is None else int(window)), stream()), "attn_prefill")
+    return out

@@ -424,3 +424,76 @@ def test_ring_gemm_with_norm_prologue(M, epilogue, N):
     assert torch.allclose(h_out.cpu(), s, atol=1e-6)
     assert torch.allclose(out.float().cpu().double(), y, atol=3e-2, rtol=2e-2)
     assert ring_status() == 0
+
+
+def fast_attention_case(nh, nkv, hd, window, past, new, seed, scale=None):
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(seed)
+    ks = [torch.randn(p + n, nkv, hd, generator=g).to(dtype).float() for p, n in zip(past, new)]
+    vs = [torch.randn(p + n, nkv, hd, generator=g).to(dtype).float() for p, n in zip(past, new)]
+    kp, vp, bt = make_paged(ks, vs, nkv, hd, dtype, seed=seed)
+    T = sum(new)
+    q = torch.randn(T, nh, hd, generator=g).to(dtype)
+    pos = torch.cat([torch.arange(p, p + n) for p, n in zip(past, new)]).to(torch.int32)
+    sot = torch.cat([torch.full((n,), i) for i, n in enumerate(new)]).to(torch.int32)
+    scale = 1 / math.sqrt(hd) if scale is None else scale
+    ref = attention_reference(q.float(), ks, vs, pos, sot, scale, window)
+    return q, kp, vp, bt, pos, sot, scale, ref
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 128, None), (32, 8, 128, None), (6, 2, 32, None), (5, 1, 64, 24),
+                                               (8, 8, 64, None), (16, 1, 128, 100), (3, 3, 32, 65)])
+def test_attention_decode_kernel(nh, nkv, hd, window):
+    from synaptix_b200.ops.attention import attn_decode
+    past, new = [0, 130, 1000, 63, 64, 255], [1] * 6
+    q, kp, vp, bt, pos, sot, scale, ref = fast_attention_case(nh, nkv, hd, window, past, new, 3)
+    lens = torch.tensor([p + 1 for p in past], dtype=torch.int32).cuda()
+    for n_splits in (1, 2, 5, 16):
+        out = attn_decode(q.view(6, nh * hd).cuda(), kp, vp, lens, bt, nh, nkv, hd, scale, window, n_splits)
+        err = (out.float().cpu().view(6, nh, hd) - ref).abs().max().item()
+        assert err < 2e-2, f"n_splits={n_splits}: {err}"
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 128, None), (6, 2, 32, None), (5, 1, 64, 24), (8, 8, 64, None),
+                                               (2, 1, 128, 100), (32, 8, 128, None)])
+def test_attention_prefill_kernel(nh, nkv, hd, window):
+    from synaptix_b200.ops.attention import attn_prefill, query_tiles
+    past, new = [0, 130, 200, 64, 0], [67, 1, 3, 130, 64]
+    q, kp, vp, bt, pos, sot, scale, ref = fast_attention_case(nh, nkv, hd, window, past, new, 4)
+    cu = [0]
+    for n in new:
+        cu.append(cu[-1] + n)
+    ts, t0 = query_tiles(cu)
+    dev = lambda x: torch.tensor(x, dtype=torch.int32).cuda()
+    T = sum(new)
+    out = attn_prefill(q.view(T, nh * hd).cuda(), kp, vp, dev(ts), dev(t0), dev(cu), dev(past),
+                       dev([p + n for p, n in zip(past, new)]), bt, nh, nkv, hd, scale, window)
+    err = (out.float().cpu().view(T, nh, hd) - ref).abs().max().item()
+    assert err < 2e-2, err
+
+
+def test_fast_attention_finds_one_far_key_and_respects_the_window_edge():
+    from synaptix_b200.ops.attention import attn_decode, attn_prefill, query_tiles
+    nh, nkv, hd = 4, 2, 64
+    dt = torch.bfloat16
+    dev = lambda x: torch.tensor(x, dtype=torch.int32).cuda()
+    for L, far, W in [(700, 0, None), (700, 333, None), (700, 699, None), (700, 63, None), (700, 64, None),
+                      (200, 130, 70), (134, 64, 70), (71, 1, 70)]:
+        k = torch.randn(L, nkv, hd) * 0.1
+        v = torch.randn(L, nkv, hd)
+        q = torch.randn(1, nh, hd)
+        q[0, 1], q[0, 3] = q[0, 0].clone(), q[0, 2].clone()
+        for kh in range(nkv):
+            k[far, kh] = q[0, kh * 2] / q[0, kh * 2].norm() * 40.0
+            if W is not None and far - 1 >= 0:          # far is the window's first key; the one before it must not count
+                assert far == L - W
+                k[far - 1, kh] = q[0, kh * 2] / q[0, kh * 2].norm() * 80.0
+                v[far - 1, kh] = 1000.0
+        kp, vp, bt = make_paged([k], [v], nkv, hd, dt, seed=L + far)
+        qd = q.view(1, nh * hd).to(dt).cuda()
+        want = torch.stack([v[far, h // 2].to(dt).float() for h in range(nh)])
+        for n_splits in (1, 3):
+            out = attn_decode(qd, kp, vp, dev([L]), bt, nh, nkv, hd, 1.0, W, n_splits).float().cpu().view(nh, hd)
+            assert torch.allclose(out, want, atol=2e-2), f"decode L={L} far={far} W={W} splits={n_splits}"
+        out = attn_prefill(qd, kp, vp, dev([0]), dev([0]), dev([0, 1]), dev([L - 1]), dev([L]), bt, nh, nkv, hd, 1.0, W)
+        assert torch.allclose(out.float().cpu().view(nh, hd), want, atol=2e-2), f"prefill L={L} far={far} W={W}"
