@@ -41,7 +41,7 @@ LIBRARIES: Dict[str, tuple] = {
     "sampling": ("sampling.cu", []),
     "decode": ("decode.cu", []),
     "attention": ("attention.cu", []),
-    "gemm_tc": ("gemm_tc.cu", ["-lcuda"]),
+    "gemm_tc": ("gemm_tc.cu", []),
 }
 
 

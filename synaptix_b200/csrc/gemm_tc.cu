@@ -1,0 +1,308 @@
+// C[M, N] = A[M, K] * W[N, K]^T for bfloat16 on the 5th-generation tensor cores (sm_100a):
+// operands staged in shared memory by TMA (128-byte swizzle), tcgen05.mma issued by one thread,
+// accumulator in tensor memory, read back with tcgen05.ld for the epilogue.
+//
+// This is the matrix product of prompt steps (hundreds to thousands of rows).  The reference's
+// kernels for it are mma.sync/ldmatrix tiles, some fed by TMA, tuned for sm_120a
+// (crates/synaptix-kernels-cuda/src/best_cu/gemm/gemm_bf16.cu:37-61,1678-2013); it has no
+// tcgen05 path.
+//
+// One block computes one 128 x 256 tile of C.
+//   warp 0   producer: for every 64-wide slice of K, one TMA load of A (128 rows x 64) and two of
+//            W (128 rows x 64 each) into a ring of STAGES stages, signalled through mbarriers
+//   warp 1   allocates 256 columns of tensor memory; one lane issues 4 tcgen05.mma (K = 16
+//            each) per stage, and tcgen05.commit hands the stage back to the producer
+//   warps 2-5 epilogue: each reads its 32 lanes of the accumulator in chunks of 32 columns,
+//            converts and stores
+// Rows of A beyond M, rows of W beyond N and the tail of K are zero-filled by TMA, so every size
+// with K % 8 == 0 is taken.  Epilogues: bfloat16 store; float32 store; SiLU(gate) * up for a
+// stacked [gate; up] matrix (the two W loads of a stage then fetch 128 gate rows and the 128
+// matching up rows, and the tile of C is 128 x 128).
+// Every wait on an mbarrier is bounded; a wait that runs out sets *status, and the block still
+// frees its tensor memory before it ends.
+#include <cuda.h>
+#include "common.cuh"
+
+#define TC_BM 128
+#define TC_BN 256
+#define TC_BK 64
+#define TC_STAGES 4
+#define TC_A_BYTES (TC_BM * TC_BK * 2)            // 16 KB
+#define TC_B_BYTES (TC_BN * TC_BK * 2)            // 32 KB
+#define TC_STAGE_BYTES (TC_A_BYTES + TC_B_BYTES)
+#define TC_THREADS 192
+#define TC_SPIN_LIMIT (1u << 26)
+
+enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SILU_MUL = 2 };
+
+__device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tc_mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void tc_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tc_tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);          // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                         // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                         // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
+  return d;
+}
+// instruction descriptor: D f32, A and B bf16, both K-major, N and M of the instruction
+__host__ __device__ constexpr uint32_t tc_instr_desc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                const __grid_constant__ CUtensorMap map_w,
+                                                                void* __restrict__ out, int M, int N, int K,
+                                                                int* __restrict__ status) {
+  extern __shared__ unsigned char tc_smem_raw[];
+  // the swizzled tiles must start on a 1024-byte boundary
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TC_STAGES * TC_STAGE_BYTES);   // full[S], empty[S], accum
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TC_STAGES + 1);
+  const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + TC_STAGES), accum = tc_smem(bars + 2 * TC_STAGES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;                 // columns of C
+  const int tile_n = (EPI == TC_EPI_SILU_MUL) ? TC_BN / 2 : TC_BN;        // columns of C per block
+  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * tile_n;
+  const int nkb = (K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TC_STAGES; ++s) {
+      tc_mbar_init(full0 + 8 * s, 1);
+      tc_mbar_init(empty0 + 8 * s, 1);
+    }
+    tc_mbar_init(accum, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"((uint32_t)TC_BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % TC_STAGES;
+        if (!tc_mbar_wait(empty0 + 8 * s, ((kb / TC_STAGES) & 1) ^ 1)) { atomicExch(status, 1); break; }
+        tc_mbar_expect_tx(full0 + 8 * s, TC_STAGE_BYTES);
+        const uint32_t a_dst = tc_smem(tiles + s * TC_STAGE_BYTES), b_dst = a_dst + TC_A_BYTES;
+        tc_tma_load_2d(a_dst, &map_a, kb * TC_BK, m0, full0 + 8 * s);
+        if (EPI == TC_EPI_SILU_MUL) {
+          tc_tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);                        // gate rows
+          tc_tma_load_2d(b_dst + TC_B_BYTES / 2, &map_w, kb * TC_BK, N / 2 + n0, full0 + 8 * s);  // up rows
+        } else {
+          tc_tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);
+          tc_tma_load_2d(b_dst + TC_B_BYTES / 2, &map_w, kb * TC_BK, n0 + TC_BN / 2, full0 + 8 * s);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc_instr_desc(TC_BM, TC_BN);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int s = kb % TC_STAGES;
+        if (!tc_mbar_wait(full0 + 8 * s, (kb / TC_STAGES) & 1)) { atomicExch(status, 2); ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t a_addr = tc_smem(tiles + s * TC_STAGE_BYTES), b_addr = a_addr + TC_A_BYTES;
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; ++k)
+          tc_mma(tmem_base, tc_smem_desc(a_addr + k * 32), tc_smem_desc(b_addr + k * 32), idesc, (kb | k) != 0);
+        tc_commit(empty0 + 8 * s);          // the stage is free once these MMAs have read it
+      }
+      tc_commit(accum);                     // the accumulator is complete once all MMAs are done
+    }
+    __syncwarp();
+  } else {
+    // epilogue warps 2..5: warp w may touch tensor-memory lanes 32*(w%4) .. +31
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    if (tc_mbar_wait(accum, 0)) {
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      const bool vec_ok = (n_out % 8) == 0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < tile_n; c0 += 32) {
+        uint32_t v[32];
+        tc_ld32(t_row + c0, v);
+        uint32_t u[32];
+        if (EPI == TC_EPI_SILU_MUL) tc_ld32(t_row + TC_BN / 2 + c0, u);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        if (row >= M || n0 + c0 >= n_out) continue;
+        float f[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          f[i] = __uint_as_float(v[i]);
+          if (EPI == TC_EPI_SILU_MUL) f[i] = f[i] / (1.f + expf(-f[i])) * __uint_as_float(u[i]);
+        }
+        const int ncol = min(32, n_out - (n0 + c0));
+        if (EPI == TC_EPI_F32) {
+          float* dst = reinterpret_cast<float*>(out) + (size_t)row * n_out + n0 + c0;
+          if (ncol == 32 && (n_out % 4) == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) reinterpret_cast<float4*>(dst)[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+          } else {
+            for (int i = 0; i < ncol; ++i) dst[i] = f[i];
+          }
+        } else {
+          bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)row * n_out + n0 + c0;
+          if (ncol == 32 && vec_ok) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 p;
+              __nv_bfloat162 t0 = __floats2bfloat162_rn(f[8 * i], f[8 * i + 1]), t1 = __floats2bfloat162_rn(f[8 * i + 2], f[8 * i + 3]);
+              __nv_bfloat162 t2 = __floats2bfloat162_rn(f[8 * i + 4], f[8 * i + 5]), t3 = __floats2bfloat162_rn(f[8 * i + 6], f[8 * i + 7]);
+              p.x = *reinterpret_cast<uint32_t*>(&t0); p.y = *reinterpret_cast<uint32_t*>(&t1);
+              p.z = *reinterpret_cast<uint32_t*>(&t2); p.w = *reinterpret_cast<uint32_t*>(&t3);
+              reinterpret_cast<uint4*>(dst)[i] = p;
+            }
+          } else {
+            for (int i = 0; i < ncol; ++i) dst[i] = __float2bfloat16_rn(f[i]);
+          }
+        }
+      }
+    } else {
+      if (lane == 0) atomicExch(status, 3);
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)TC_BN) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*tc_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static tc_encode_fn tc_get_encode() {
+  static tc_encode_fn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = (tc_encode_fn)p;
+  }
+  return fn;
+}
+
+// a [rows, K] row-major bfloat16 matrix as a 2-D tensor map with 128-row x 64-column boxes
+static int tc_make_map(CUtensorMap* map, const void* base, int rows, int K) {
+  tc_encode_fn enc = tc_get_encode();
+  if (!enc) return SX_ERR_SIZE;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {TC_BK, 128};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 20000 + (int)r;
+}
+
+static int* tc_status_word() {
+  static int* p = nullptr;
+  if (!p) {
+    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, sizeof(int));
+  }
+  return p;
+}
+
+template <int EPI>
+static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, cudaStream_t stream) {
+  int* status = tc_status_word();
+  if (!status) return (int)cudaErrorMemoryAllocation;
+  const int tile_n = (EPI == TC_EPI_SILU_MUL) ? TC_BN / 2 : TC_BN;
+  const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;
+  dim3 grid((n_out + tile_n - 1) / tile_n, (M + TC_BM - 1) / TC_BM);
+  if (grid.y > 65535) return SX_ERR_SIZE;
+  const size_t smem = 1024 + TC_STAGES * TC_STAGE_BYTES + (2 * TC_STAGES + 1) * sizeof(uint64_t) + 16;
+  auto kern = gemm_tc_kernel<EPI>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  kern<<<grid, TC_THREADS, smem, stream>>>(ma, mw, out, M, N, K, status);
+  return sx_launch_status();
+}
+
+// A [M, K], W [N, K] bfloat16 row-major, 16-byte aligned, K % 8 == 0.
+// epi 0: out bf16 [M, N]; 1: out f32 [M, N]; 2: W = [gate; up] stacked, out bf16 [M, N/2].
+extern "C" int sx_gemm_tc(const void* A, const void* W, void* out, int M, int N, int K, int epi, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7)) return SX_ERR_SIZE;
+  if (epi == TC_EPI_SILU_MUL && (N & 1)) return SX_ERR_SIZE;
+  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return SX_ERR_ALIGN;
+  CUtensorMap ma, mw;
+  int rc = tc_make_map(&ma, A, M, K);
+  if (rc) return rc;
+  rc = tc_make_map(&mw, W, N, K);
+  if (rc) return rc;
+  switch (epi) {
+    case TC_EPI_BF16: return tc_launch<TC_EPI_BF16>(ma, mw, out, M, N, K, stream);
+    case TC_EPI_F32: return tc_launch<TC_EPI_F32>(ma, mw, out, M, N, K, stream);
+    case TC_EPI_SILU_MUL: return tc_launch<TC_EPI_SILU_MUL>(ma, mw, out, M, N, K, stream);
+    default: return SX_ERR_DTYPE;
+  }
+}
+
+// 0, or which bounded wait ran out (1 producer, 2 MMA issuer, 3 epilogue)
+extern "C" int sx_gemm_tc_status(int* host_value) {
+  int* p = tc_status_word();
+  if (!p) return (int)cudaErrorMemoryAllocation;
+  return (int)cudaMemcpy(host_value, p, sizeof(int), cudaMemcpyDeviceToHost);
+}

@@ -15,6 +15,7 @@ from ..csrc.build import KernelsUnavailable
 from ._lib import KernelError, set_launch_counter
 from .attention import attn_decode, attn_prefill, fast_supported, pick_splits, query_tiles
 from .decode import skinny_gemm, skinny_supported
+from .gemm_tc import gemm_tc, tc_supported
 from .generic import (add_rmsnorm, attn_generic, decode_advance, embed_gather, gemm_generic, qkv_prepare,
                       residual_add,
                       silu_mul)
@@ -38,6 +39,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
                 return skinny_gemm(x, w, epilogue="silu_mul")
         else:
             return skinny_gemm(x, w, epilogue="f32" if out_dtype == torch.float32 else None)
+    if tc_supported(M, N, K, x.dtype, w.dtype) and out_dtype in (torch.bfloat16, torch.float32):
+        if epilogue == "silu_mul":
+            if out_dtype == torch.bfloat16:
+                return gemm_tc(x, w, epilogue="silu_mul")
+        else:
+            return gemm_tc(x, w, epilogue="f32" if out_dtype == torch.float32 else None)
     y = gemm_generic(x, w, out_dtype=out_dtype if epilogue is None else x.dtype)
     if epilogue == "silu_mul":
         y = silu_mul(y)

@@ -497,3 +497,31 @@ def test_fast_attention_finds_one_far_key_and_respects_the_window_edge():
             assert torch.allclose(out, want, atol=2e-2), f"decode L={L} far={far} W={W} splits={n_splits}"
         out = attn_prefill(qd, kp, vp, dev([0]), dev([0]), dev([0, 1]), dev([L - 1]), dev([L]), bt, nh, nkv, hd, 1.0, W)
         assert torch.allclose(out.float().cpu().view(nh, hd), want, atol=2e-2), f"prefill L={L} far={far} W={W}"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (65, 256, 2560), (200, 300, 72), (1000, 389, 96), (130, 24, 8),
+                                    (2048, 1024, 2560), (513, 2560, 1224)])
+def test_gemm_tc(M, N, K):
+    """The tcgen05 product against float64, at sizes with ragged edges in M, N and K."""
+    from synaptix_b200.ops.gemm_tc import gemm_tc, gemm_tc_status
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    out = gemm_tc(x.cuda(), w.cuda(), epilogue="f32")
+    assert torch.allclose(out.cpu().double(), ref, atol=2e-5 * math.sqrt(K), rtol=1e-5)
+    out = gemm_tc(x.cuda(), w.cuda())
+    assert out.dtype == torch.bfloat16 and torch.allclose(out.float().cpu().double(), ref, atol=2e-2, rtol=2e-2)
+    assert gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (77, 160, 200), (300, 1000, 2560), (2048, 129, 96)])
+def test_gemm_tc_silu_mul_epilogue(M, I, K):
+    from synaptix_b200.ops.gemm_tc import gemm_tc, gemm_tc_status
+    x = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K) * 2 / math.sqrt(K)).to(torch.bfloat16)
+    y = x.double() @ w.double().T
+    ref = y[:, :I] / (1 + torch.exp(-y[:, :I])) * y[:, I:]
+    out = gemm_tc(x.cuda(), w.cuda(), epilogue="silu_mul")
+    assert out.shape == (M, I) and torch.allclose(out.float().cpu().double(), ref, atol=3e-2, rtol=2e-2)
+    assert gemm_tc_status() == 0
