@@ -276,22 +276,46 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
   }
 }
 
-// merge of the splits: grid (S * nh), HD threads
+// merge of the splits: grid (S * nh), HD threads.  Maxima and sums of all splits are fetched at
+// once into shared memory and reduced by one warp; the weighted sum over splits then runs with
+// independent loads.
 template <int HD>
 __global__ void __launch_bounds__(HD) attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                         bf16* __restrict__ out, int n_splits) {
+  extern __shared__ float sm[];                  // m[n_splits] (then weights), l[n_splits]
+  float* fac = sm;
+  float* ls = sm + n_splits;
+  __shared__ float s_L;
   const size_t row = blockIdx.x;
   const int d = threadIdx.x;
-  float M = -INFINITY;
-  for (int i = 0; i < n_splits; ++i) M = fmaxf(M, part_ml[(row * n_splits + i) * 2]);
-  float Lsum = 0.f, O = 0.f;
-  for (int i = 0; i < n_splits; ++i) {
-    const float mi = part_ml[(row * n_splits + i) * 2];
-    const float f = (mi == -INFINITY) ? 0.f : exp2f(mi - M);
-    Lsum += part_ml[(row * n_splits + i) * 2 + 1] * f;
-    O += part_o[(row * n_splits + i) * HD + d] * f;
+  for (int i = d; i < n_splits; i += HD) {
+    const float2 ml = reinterpret_cast<const float2*>(part_ml)[row * n_splits + i];
+    fac[i] = ml.x;
+    ls[i] = ml.y;
   }
-  out[row * HD + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
+  __syncthreads();
+  if (d < 32) {
+    float M = -INFINITY;
+    for (int i = d; i < n_splits; i += 32) M = fmaxf(M, fac[i]);
+    M = warp_max(M);
+    float L = 0.f;
+    for (int i = d; i < n_splits; i += 32) {
+      const float mi = fac[i];
+      const float f = (mi == -INFINITY) ? 0.f : exp2f(mi - M);
+      fac[i] = f;
+      L += ls[i] * f;
+    }
+    // lanes in index order: a fixed order of addition
+    L = warp_sum(L);
+    if (d == 0) s_L = L;
+  }
+  __syncthreads();
+  float O = 0.f;
+  const float* po = part_o + row * n_splits * HD + d;
+#pragma unroll 8
+  for (int i = 0; i < n_splits; ++i) O += po[(size_t)i * HD] * fac[i];
+  const float L = s_L;
+  out[row * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
 }
 
 // =======================================================================================
@@ -398,7 +422,7 @@ static int decode_launch(const bf16* q, const bf16* k, const bf16* v, bf16* out,
                                           window, n_splits);
   int rc = sx_launch_status();
   if (rc || n_splits == 1) return rc;
-  attn_merge_kernel<HD><<<S * nh, HD, 0, stream>>>(part_o, part_ml, out, n_splits);
+  attn_merge_kernel<HD><<<S * nh, HD, 2 * n_splits * sizeof(float), stream>>>(part_o, part_ml, out, n_splits);
   return sx_launch_status();
 }
 

@@ -24,6 +24,7 @@
 #include "common.cuh"
 
 #define SK_WARPS 8
+#define XS_ROWS 2          // rows of activations the norm prologue takes
 #define SK_THREADS (SK_WARPS * 32)
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -61,32 +62,6 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(
   const int g = lane >> 2, t = lane & 3;
   const int rt = warp / KS, ks = warp % KS;
 
-  if (XS) {
-    // RMSNorm prologue, one warp per activation row, 32-bit throughout
-    for (int b = warp; b < NT * 8; b += SK_WARPS) {
-      bf16* xr = xs + (size_t)b * K;
-      if (b < M) {
-        const float* hr = h_in + (size_t)b * K;
-        const bf16* dr = delta ? delta + (size_t)b * K : nullptr;
-        float ss = 0.f;
-        for (int k = lane; k < K; k += 32) {
-          const float v = hr[k] + (dr ? __bfloat162float(dr[k]) : 0.f);
-          ss += v * v;
-        }
-        ss = warp_sum(ss);
-        const float inv = rsqrtf(ss / (float)K + eps);
-        for (int k = lane; k < K; k += 32) {
-          const float v = hr[k] + (dr ? __bfloat162float(dr[k]) : 0.f);
-          if (blockIdx.x == 0 && h_out) h_out[(size_t)b * K + k] = v;
-          xr[k] = __float2bfloat16_rn(v * inv * gain[k]);
-        }
-      } else {
-        for (int k = lane; k < K; k += 32) xr[k] = __float2bfloat16_rn(0.f);
-      }
-    }
-    __syncthreads();
-  }
-
   // rows of W this warp owns
   const int tile = blockIdx.x * RT + rt;
   int row_lo, row_hi;          // W rows behind fragment rows g and g + 8
@@ -102,6 +77,72 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(
     row_lo = min(tile * 16 + g, N - 1);
     row_hi = min(tile * 16 + g + 8, N - 1);
   }
+  const int nsteps = K >> 5;                       // 32 k-values a step
+  const int per = (nsteps + KS - 1) / KS;
+  const int s_begin = ks * per, s_end = min(nsteps, s_begin + per);
+  const bf16* wlo = W + (size_t)row_lo * K + t * 8;
+  const bf16* whi = W + (size_t)row_hi * K + t * 8;
+  constexpr int U = 4;
+
+  // the first weights are asked for before anything else, so that HBM is busy during the prologue
+  uint4 pa[U], pb[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int sc = min(s_begin + u, nsteps - 1);
+    pa[u] = ld_stream16(wlo + (size_t)sc * 32);
+    pb[u] = ld_stream16(whi + (size_t)sc * 32);
+  }
+
+  if (XS) {
+    // RMSNorm prologue by the whole block, one row after the other, the row held in registers:
+    // one round of loads, one reduction, 32-bit throughout.  K <= 4096, M <= XS_ROWS.
+    __shared__ float xs_red[SK_WARPS];
+    const int n4 = K >> 2;
+    for (int b = 0; b < M; ++b) {
+      const float4* hr = reinterpret_cast<const float4*>(h_in + (size_t)b * K);
+      const uint2* dr = delta ? reinterpret_cast<const uint2*>(delta + (size_t)b * K) : nullptr;
+      float4 v[4];
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = threadIdx.x + k * SK_THREADS;
+        v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < n4) {
+          v[k] = hr[i];
+          if (dr) {
+            const uint2 d = dr[i];
+            const __nv_bfloat162 d0 = *reinterpret_cast<const __nv_bfloat162*>(&d.x);
+            const __nv_bfloat162 d1 = *reinterpret_cast<const __nv_bfloat162*>(&d.y);
+            v[k].x += __low2float(d0); v[k].y += __high2float(d0); v[k].z += __low2float(d1); v[k].w += __high2float(d1);
+          }
+          ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+      }
+      ss = warp_sum(ss);
+      __syncthreads();                              // xs_red of the previous row has been read
+      if (lane == 0) xs_red[warp] = ss;
+      __syncthreads();
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < SK_WARPS; ++w) tot += xs_red[w];
+      const float inv = rsqrtf(tot / (float)K + eps);
+      bf16* xr = xs + (size_t)b * K;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = threadIdx.x + k * SK_THREADS;
+        if (i < n4) {
+          const float4 gn = reinterpret_cast<const float4*>(gain)[i];
+          if (blockIdx.x == 0 && h_out) reinterpret_cast<float4*>(h_out + (size_t)b * K)[i] = v[k];
+          __nv_bfloat162 o0 = __floats2bfloat162_rn(v[k].x * inv * gn.x, v[k].y * inv * gn.y);
+          __nv_bfloat162 o1 = __floats2bfloat162_rn(v[k].z * inv * gn.z, v[k].w * inv * gn.w);
+          uint2 o;
+          o.x = *reinterpret_cast<uint32_t*>(&o0); o.y = *reinterpret_cast<uint32_t*>(&o1);
+          reinterpret_cast<uint2*>(xr)[i] = o;
+        }
+      }
+    }
+    __syncthreads();
+  }
 
   float acc[NT][4];
 #pragma unroll
@@ -109,15 +150,24 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
-  const int nsteps = K >> 5;                       // 32 k-values a step
-  const int per = (nsteps + KS - 1) / KS;
-  const int s_begin = ks * per, s_end = min(nsteps, s_begin + per);
-
   if (tile_ok) {
-    const bf16* wlo = W + (size_t)row_lo * K + t * 8;
-    const bf16* whi = W + (size_t)row_hi * K + t * 8;
-    constexpr int U = 4;
-    int s = s_begin;
+    // the batch that was asked for up front
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int sc = s_begin + u;
+      if (sc < s_end) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const int b = nt * 8 + g;
+          uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+          if (XS) { if (b < M) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + sc * 32 + t * 8); }
+          else if (b < M) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + sc * 32 + t * 8));
+          mma_bf16_16816(acc[nt], pa[u].x, pb[u].x, pa[u].y, pb[u].y, xv.x, xv.y);
+          mma_bf16_16816(acc[nt], pa[u].z, pb[u].z, pa[u].w, pb[u].w, xv.z, xv.w);
+        }
+      }
+    }
+    int s = s_begin + U;
     for (; s + U <= s_end; s += U) {
       uint4 va[U], vb[U];
 #pragma unroll
@@ -131,24 +181,34 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(
         for (int nt = 0; nt < NT; ++nt) {
           const int b = nt * 8 + g;
           uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-          if (XS) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + (s + u) * 32 + t * 8);
+          if (XS) { if (b < M) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + (s + u) * 32 + t * 8); }
           else if (b < M) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + (s + u) * 32 + t * 8));
           mma_bf16_16816(acc[nt], va[u].x, vb[u].x, va[u].y, vb[u].y, xv.x, xv.y);
           mma_bf16_16816(acc[nt], va[u].z, vb[u].z, va[u].w, vb[u].w, xv.z, xv.w);
         }
       }
     }
-    for (; s < s_end; ++s) {
-      const uint4 va = ld_stream16(wlo + (size_t)s * 32);
-      const uint4 vb = ld_stream16(whi + (size_t)s * 32);
+    if (s < s_end) {                                 // the tail, asked for together
+      uint4 va[U], vb[U];
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        const int b = nt * 8 + g;
-        uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-        if (XS) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + s * 32 + t * 8);
-        else if (b < M) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + s * 32 + t * 8));
-        mma_bf16_16816(acc[nt], va.x, vb.x, va.y, vb.y, xv.x, xv.y);
-        mma_bf16_16816(acc[nt], va.z, vb.z, va.w, vb.w, xv.z, xv.w);
+      for (int u = 0; u < U; ++u) {
+        const int sc = min(s + u, nsteps - 1);
+        va[u] = ld_stream16(wlo + (size_t)sc * 32);
+        vb[u] = ld_stream16(whi + (size_t)sc * 32);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (s + u < s_end) {
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const int b = nt * 8 + g;
+            uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+            if (XS) { if (b < M) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + (s + u) * 32 + t * 8); }
+            else if (b < M) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + (s + u) * 32 + t * 8));
+            mma_bf16_16816(acc[nt], va[u].x, vb[u].x, va[u].y, vb[u].y, xv.x, xv.y);
+            mma_bf16_16816(acc[nt], va[u].z, vb[u].z, va[u].w, vb[u].w, xv.z, xv.w);
+          }
+        }
       }
     }
   }
@@ -206,7 +266,8 @@ static int skinny_launch(const bf16* x, const bf16* W, void* out, int M, int N, 
   constexpr int RT = SK_WARPS / KS;
   const int tiles = (EPI == EPI_SILU_MUL) ? (N / 2 + 7) / 8 : (N + 15) / 16;
   const int grid = (tiles + RT - 1) / RT;
-  size_t smem = (KS > 1 ? (size_t)SK_WARPS * NT * 4 * 32 * sizeof(float) : 0) + (XS ? (size_t)NT * 8 * K * sizeof(bf16) : 0);
+  size_t smem = (KS > 1 ? (size_t)SK_WARPS * NT * 4 * 32 * sizeof(float) : 0) +
+                (XS ? (size_t)XS_ROWS * K * sizeof(bf16) : 0);
   auto kern = skinny_gemm_kernel<NT, KS, EPI, XS>;
   if (smem > 48 * 1024) {
     if (smem > 200 * 1024) return SX_ERR_SIZE;
@@ -233,7 +294,7 @@ static int skinny_pick_nt(int ks, const bf16* x, const bf16* W, void* out, int M
                           const bf16* delta, float* h_out, const float* gain, float eps, cudaStream_t stream) {
   if (M <= 8) return skinny_pick_ks<1, EPI, XS>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
   if (M <= 16) return skinny_pick_ks<2, EPI, XS>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
-  if (XS) return SX_ERR_SIZE;   // the norm prologue keeps all rows in shared memory: up to 16 rows
+  if (XS) return SX_ERR_SIZE;
   if (M <= 32) return skinny_pick_ks<4, EPI, false>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
   if (M <= 64) return skinny_pick_ks<8, EPI, false>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
   return SX_ERR_SIZE;
@@ -254,8 +315,10 @@ extern "C" int sx_skinny_gemm(const void* x, const void* W, void* out, int M, in
   const bf16* wb = (const bf16*)W;
   const bf16* db = (const bf16*)delta;
   if (h_in) {
+    if (M > XS_ROWS || K > 4096 || (K & 3)) return SX_ERR_SIZE;   // the prologue holds a row in registers
     switch (epi) {
       case EPI_BF16: return skinny_pick_nt<EPI_BF16, true>(ks, xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, stream);
+      case EPI_F32: return skinny_pick_nt<EPI_F32, true>(ks, xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, stream);
       case EPI_SILU_MUL: return skinny_pick_nt<EPI_SILU_MUL, true>(ks, xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, stream);
       default: return SX_ERR_DTYPE;
     }
@@ -561,6 +624,7 @@ extern "C" int sx_ring_gemm(const void* x, const void* W, void* out, int M, int 
   if (h_in) {
     switch (epi) {
       case EPI_BF16: return ring_pick_nt<EPI_BF16, true>(xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, max_blocks, stream);
+      case EPI_F32: return ring_pick_nt<EPI_F32, true>(xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, max_blocks, stream);
       case EPI_SILU_MUL: return ring_pick_nt<EPI_SILU_MUL, true>(xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, max_blocks, stream);
       default: return SX_ERR_DTYPE;
     }

@@ -75,17 +75,70 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
   }
 }
 
+// the same with the whole row held in registers (one pass over memory, one reduction):
+// rows of up to 256 * 4 * VEC4 elements, H a multiple of 4, 16-byte aligned rows
+template <typename T, int VEC4>
+__global__ void __launch_bounds__(256) add_rmsnorm_reg_kernel(float* __restrict__ h, const T* __restrict__ delta,
+                                                              const float* __restrict__ w, float eps, T* __restrict__ y,
+                                                              const int* __restrict__ rows, int H, int write_h) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const int t = rows ? rows[r] : r;
+  float4* hr = reinterpret_cast<float4*>(h + (size_t)t * H);
+  const T* dr = delta ? delta + (size_t)t * H : nullptr;
+  const int n4 = H >> 2;
+  float4 v[VEC4];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VEC4; ++k) {
+    const int i = threadIdx.x + k * 256;
+    v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < n4) {
+      v[k] = hr[i];
+      if (dr) {
+        v[k].x += to_f32(dr[4 * i]); v[k].y += to_f32(dr[4 * i + 1]);
+        v[k].z += to_f32(dr[4 * i + 2]); v[k].w += to_f32(dr[4 * i + 3]);
+        if (write_h) hr[i] = v[k];
+      }
+      ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  T* yr = y + (size_t)r * H;
+#pragma unroll
+  for (int k = 0; k < VEC4; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < n4) {
+      const float4 g = reinterpret_cast<const float4*>(w)[i];
+      yr[4 * i] = from_f32<T>(v[k].x * inv * g.x);
+      yr[4 * i + 1] = from_f32<T>(v[k].y * inv * g.y);
+      yr[4 * i + 2] = from_f32<T>(v[k].z * inv * g.z);
+      yr[4 * i + 3] = from_f32<T>(v[k].w * inv * g.w);
+    }
+  }
+}
+
+template <typename T>
+static int add_rmsnorm_launch(float* h, const void* delta, const float* w, float eps, void* y, const int* rows, int R,
+                              int H, int write_h, cudaStream_t stream) {
+  const bool aligned = (H % 4 == 0) && (((uintptr_t)h | (uintptr_t)w) % 16 == 0);
+  if (aligned && H <= 256 * 4 * 4)
+    add_rmsnorm_reg_kernel<T, 4><<<R, 256, 0, stream>>>(h, (const T*)delta, w, eps, (T*)y, rows, H, write_h);
+  else if (aligned && H <= 256 * 4 * 8)
+    add_rmsnorm_reg_kernel<T, 8><<<R, 256, 0, stream>>>(h, (const T*)delta, w, eps, (T*)y, rows, H, write_h);
+  else
+    add_rmsnorm_kernel<T><<<R, 256, 0, stream>>>(h, (const T*)delta, w, eps, (T*)y, rows, H, write_h);
+  return sx_launch_status();
+}
+
 extern "C" int sx_add_rmsnorm(float* h, const void* delta, const float* w, float eps, void* y,
                               const int* rows, int R, int H, int dt, int write_h,
                               cudaStream_t stream) {
   if (R <= 0) return 0;
-  if (dt == SX_F32)
-    add_rmsnorm_kernel<float><<<R, 256, 0, stream>>>(h, (const float*)delta, w, eps, (float*)y, rows, H, write_h);
-  else if (dt == SX_BF16)
-    add_rmsnorm_kernel<bf16><<<R, 256, 0, stream>>>(h, (const bf16*)delta, w, eps, (bf16*)y, rows, H, write_h);
-  else
-    return SX_ERR_DTYPE;
-  return sx_launch_status();
+  if (dt == SX_F32) return add_rmsnorm_launch<float>(h, delta, w, eps, y, rows, R, H, write_h, stream);
+  if (dt == SX_BF16) return add_rmsnorm_launch<bf16>(h, delta, w, eps, y, rows, R, H, write_h, stream);
+  return SX_ERR_DTYPE;
 }
 
 // h[t] += delta[t] (32-bit residual sum), for the places where no norm follows
@@ -221,72 +274,84 @@ extern "C" int sx_gemm_generic(const void* A, int a_dt, const void* W, int w_dt,
 //   v heads: copied into the page.
 // qkv is [T, (nh + 2 nkv) * hd]: q heads, then k heads, then v heads.
 // ---------------------------------------------------------------------------------------
+// One block per token, one warp per head at a time.  A lane owns the rotation pairs
+// (p, p + rotary_dim/2) for p = lane, lane + 32, ...; their angles, sines and cosines are computed
+// once per token and reused for every q and k head.
+#define QP_WARPS 8
+#define QP_MAXP 8            // pairs per lane: head sizes up to 512
 template <typename T>
-__global__ void __launch_bounds__(128) qkv_prepare_kernel(
+__global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_kernel(
     const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
     const float* __restrict__ wq, const float* __restrict__ wk, const float* __restrict__ inv_freq,
     int rotary_dim, float eps, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ block_table, int maxp, int nh, int nkv, int hd, int n_pages) {
-  extern __shared__ float xs[];          // hd floats
-  __shared__ float red[33];
-  const int t = blockIdx.x, head = blockIdx.y;
-  const int row = (nh + 2 * nkv) * hd;
-  const T* src = qkv + (size_t)t * row + (size_t)head * hd;
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = positions[t];
-
-  const bool is_q = head < nh;
-  const bool is_k = !is_q && head < nh + nkv;
-  const int kvh = is_q ? 0 : (is_k ? head - nh : head - nh - nkv);
-
-  T* dst;
-  if (is_q) {
-    dst = q_out + ((size_t)t * nh + head) * hd;
-  } else {
-    const int s = seq_of_token[t];
-    const int page = block_table[(size_t)s * maxp + (pos >> 6)];
-    if (page < 0 || page >= n_pages) return;   // host guarantees a page; never write outside
-    T* base = is_k ? k_pages : v_pages;
-    if (!base) return;                           // a layer that reads another layer's cache writes nothing
-    dst = base + (((size_t)page * nkv + kvh) * SX_PAGE + (pos & 63)) * hd;
-  }
-
-  if (!is_q && !is_k) {                      // v: copy
-    for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = src[i];
-    return;
-  }
-
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
-    const float v = to_f32(src[i]);
-    xs[i] = v;
-    ss += v * v;
-  }
-  const float* w = is_q ? wq : wk;
-  float inv = 1.f;
-  if (w) {
-    ss = block_sum(ss, red);
-    inv = rsqrtf(ss / (float)hd + eps);
-  } else {
-    __syncthreads();
-  }
-  // normalised values stay in 32-bit until the rotation is done
-  for (int i = threadIdx.x; i < hd; i += blockDim.x)
-    if (w) xs[i] = xs[i] * inv * w[i];
-  __syncthreads();
-
+  const int row = (nh + 2 * nkv) * hd;
+  const T* src_tok = qkv + (size_t)t * row;
   const int half = inv_freq ? rotary_dim / 2 : 0;
-  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
-    float o;
-    if (i < 2 * half) {
-      const int j = i < half ? i : i - half;
-      float sn, cs;
-      sincosf((float)pos * inv_freq[j], &sn, &cs);
-      const float x1 = xs[j], x2 = xs[j + half];
-      o = i < half ? x1 * cs - x2 * sn : x1 * sn + x2 * cs;
+
+  float cs[QP_MAXP], sn[QP_MAXP];
+#pragma unroll
+  for (int k = 0; k < QP_MAXP; ++k) {
+    const int p = lane + 32 * k;
+    cs[k] = 1.f; sn[k] = 0.f;
+    if (p < half) sincosf((float)pos * inv_freq[p], &sn[k], &cs[k]);
+  }
+  // where this token's keys and values go
+  const int s = seq_of_token[t];
+  const int page = block_table[(size_t)s * maxp + (pos >> 6)];
+  const bool page_ok = page >= 0 && page < n_pages;     // the host guarantees a page; never write outside
+
+  for (int head = blockIdx.y * QP_WARPS + warp; head < nh + 2 * nkv; head += gridDim.y * QP_WARPS) {
+    const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
+    const int kvh = is_q ? 0 : (is_k ? head - nh : head - nh - nkv);
+    const T* src = src_tok + (size_t)head * hd;
+    T* dst;
+    if (is_q) {
+      dst = q_out + ((size_t)t * nh + head) * hd;
     } else {
-      o = xs[i];
+      T* base = is_k ? k_pages : v_pages;
+      if (!base || !page_ok) continue;                   // a layer that reads another layer's cache writes nothing
+      dst = base + (((size_t)page * nkv + kvh) * SX_PAGE + (pos & 63)) * hd;
     }
-    dst[i] = from_f32<T>(o);
+    if (!is_q && !is_k) {                                // v: copy
+      for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+      continue;
+    }
+    const float* w = is_q ? wq : wk;
+    float x1[QP_MAXP], x2[QP_MAXP];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < QP_MAXP; ++k) {
+      const int p = lane + 32 * k;
+      x1[k] = x2[k] = 0.f;
+      if (p < half) {
+        x1[k] = to_f32(src[p]);
+        x2[k] = to_f32(src[p + half]);
+        ss += x1[k] * x1[k] + x2[k] * x2[k];
+      }
+    }
+    for (int i = 2 * half + lane; i < hd; i += 32) {     // elements that are not rotated
+      const float v = to_f32(src[i]);
+      ss += v * v;
+    }
+    float inv = 1.f;
+    if (w) inv = rsqrtf(warp_sum(ss) / (float)hd + eps);
+#pragma unroll
+    for (int k = 0; k < QP_MAXP; ++k) {
+      const int p = lane + 32 * k;
+      if (p < half) {
+        const float a = w ? x1[k] * inv * w[p] : x1[k];
+        const float b = w ? x2[k] * inv * w[p + half] : x2[k];
+        dst[p] = from_f32<T>(a * cs[k] - b * sn[k]);
+        dst[p + half] = from_f32<T>(a * sn[k] + b * cs[k]);
+      }
+    }
+    for (int i = 2 * half + lane; i < hd; i += 32) {
+      const float v = to_f32(src[i]);
+      dst[i] = from_f32<T>(w ? v * inv * w[i] : v);
+    }
   }
 }
 
@@ -296,16 +361,16 @@ extern "C" int sx_qkv_prepare(const void* qkv, void* q_out, void* k_pages, void*
                               const int* block_table, int maxp, int n_tokens, int nh, int nkv, int hd,
                               int n_pages, int dt, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (hd <= 0 || (rotary_dim & 1) || rotary_dim > hd || nh + 2 * nkv > 65535) return SX_ERR_SIZE;
-  dim3 grid(n_tokens, nh + 2 * nkv);
-  const size_t smem = (size_t)hd * sizeof(float);
-  if (smem > 48 * 1024) return SX_ERR_SIZE;
+  if (hd <= 0 || (rotary_dim & 1) || rotary_dim > hd || rotary_dim / 2 > 32 * QP_MAXP) return SX_ERR_SIZE;
+  // few tokens: spread the heads over blocks too, so that the step is one round of work
+  const int heads = nh + 2 * nkv;
+  dim3 grid(n_tokens, n_tokens <= 64 ? (heads + QP_WARPS - 1) / QP_WARPS : 1);
   if (dt == SX_F32)
-    qkv_prepare_kernel<float><<<grid, 128, smem, stream>>>(
+    qkv_prepare_kernel<float><<<grid, QP_WARPS * 32, 0, stream>>>(
         (const float*)qkv, (float*)q_out, (float*)k_pages, (float*)v_pages, wq, wk, inv_freq, rotary_dim, eps,
         positions, seq_of_token, block_table, maxp, nh, nkv, hd, n_pages);
   else if (dt == SX_BF16)
-    qkv_prepare_kernel<bf16><<<grid, 128, smem, stream>>>(
+    qkv_prepare_kernel<bf16><<<grid, QP_WARPS * 32, 0, stream>>>(
         (const bf16*)qkv, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, wq, wk, inv_freq, rotary_dim, eps,
         positions, seq_of_token, block_table, maxp, nh, nkv, hd, n_pages);
   else

@@ -132,7 +132,7 @@ class _CapturedStep:
             token_ids=v["token_ids"], positions=v["positions"], seq_of_token=v["seq_of_token"],
             cu_seqlens=v["cu_seqlens"], seq_past=v["seq_past"], seq_lens=v["seq_lens"], seq_slots=v["seq_slots"],
             want_rows=v["want_rows"], block_tables=v["block_tables"], n_tokens=S, n_seqs=S, n_want=S, max_new=1,
-            max_len=maxp * PAGE_TOKENS, all_single=True, runtime=engine.runtime)
+            max_len=maxp * PAGE_TOKENS, all_single=True, runtime=engine.runtime, want_all=True)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.launches = 0
@@ -278,6 +278,7 @@ class Engine:
             want_rows=v["want_rows"], block_tables=v["block_tables"],
             n_tokens=T, n_seqs=S, n_want=R, max_new=max(new), max_len=max(p + n for p, n in zip(past, new)),
             all_single=all(n == 1 for n in new), runtime=self.runtime,
+            want_all=(R == T and all(tuple(e.want) == tuple(range(len(e.tokens))) for e in entries)),
             host={"cu_seqlens": lay.views(flat)["cu_seqlens"].tolist(), "seq_past": list(past),
                   "seq_lens": [p + n for p, n in zip(past, new)], "seq_slots": [e.slot for e in entries]})
 
@@ -344,7 +345,7 @@ class DecodeRun:
             token_ids=v["token_ids"], positions=v["positions"], seq_of_token=v["seq_of_token"],
             cu_seqlens=v["cu_seqlens"], seq_past=v["seq_past"], seq_lens=v["seq_lens"], seq_slots=v["seq_slots"],
             want_rows=v["want_rows"], block_tables=v["block_tables"], n_tokens=S, n_seqs=S, n_want=S, max_new=1,
-            max_len=maxp * PAGE_TOKENS, all_single=True, runtime=engine.runtime)
+            max_len=maxp * PAGE_TOKENS, all_single=True, runtime=engine.runtime, want_all=True)
         self.sampled = sampled = torch.empty(S, dtype=torch.int32, device=engine.device)
 
         def one():

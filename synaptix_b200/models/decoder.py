@@ -87,5 +87,8 @@ class DecoderModel(Part):
         for run in self.schedule:
             h, pending = self.layers[run.layer].forward(h, pending, ctx, cache.view(run.cache_entry),
                                                         run.write_cache)
-        x = self.final_norm.add_forward(h, pending, rows=ctx.want_rows)
+        if getattr(ctx, "want_all", False):        # every row, in order: no gather, and the norm may fuse
+            x = self.final_norm.add_forward(h, pending, lazy=True)
+        else:
+            x = self.final_norm.add_forward(h, pending, rows=ctx.want_rows)
         return self.head.forward(x)

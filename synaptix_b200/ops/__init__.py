@@ -21,7 +21,7 @@ from .generic import (add_rmsnorm, attn_generic, decode_advance, embed_gather, g
                       silu_mul)
 
 __all__ = ["KernelsUnavailable", "KernelError", "set_launch_counter", "decode_advance", "add_rmsnorm", "attn_generic", "embed_gather",
-           "gemm_generic", "qkv_prepare", "residual_add", "silu_mul", "linear", "attention"]
+           "gemm_generic", "qkv_prepare", "residual_add", "silu_mul", "linear", "linear_normed", "norm_fusable", "attention"]
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
@@ -36,9 +36,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if skinny_supported(M, N, K, x.dtype, w.dtype) and out_dtype in (torch.bfloat16, torch.float32):
         if epilogue == "silu_mul":
             if out_dtype == torch.bfloat16:
-                return skinny_gemm(x, w, epilogue="silu_mul")
+                return skinny_gemm(x, w, epilogue="silu_mul", ks=8)
         else:
-            return skinny_gemm(x, w, epilogue="f32" if out_dtype == torch.float32 else None)
+            return skinny_gemm(x, w, epilogue="f32" if out_dtype == torch.float32 else None, ks=8)
     if tc_supported(M, N, K, x.dtype, w.dtype) and out_dtype in (torch.bfloat16, torch.float32):
         if epilogue == "silu_mul":
             if out_dtype == torch.bfloat16:
@@ -49,6 +49,32 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if epilogue == "silu_mul":
         y = silu_mul(y)
     return y
+
+
+def norm_fusable(M: int, K: int, dtype) -> bool:
+    """Can ``rmsnorm(h + delta)`` of ``M`` rows of width ``K`` run inside the next product's prologue?"""
+    # every block repeats the norm, so it pays only while the rows are few
+    return dtype == torch.bfloat16 and 0 < M <= 2 and K % 32 == 0 and K <= 4096
+
+
+def linear_normed(pn, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                  epilogue: Optional[str] = None) -> Optional[torch.Tensor]:
+    """``rmsnorm(pn.h + pn.delta) * gain @ w.T`` in one kernel, or ``None`` if that cannot be fused."""
+    M, K = pn.h.shape
+    if out_dtype is None:
+        out_dtype = pn.dtype
+    if not (norm_fusable(M, K, pn.dtype) and w.dtype == torch.bfloat16 and w.shape[1] == K):
+        return None
+    if epilogue == "silu_mul":
+        if out_dtype != torch.bfloat16:
+            return None
+        epi = "silu_mul"
+    elif epilogue is None and out_dtype in (torch.bfloat16, torch.float32):
+        epi = "f32" if out_dtype == torch.float32 else None
+    else:
+        return None
+    return skinny_gemm(None, w, epilogue=epi, ks=8, norm_h=pn.h, norm_delta=pn.delta, norm_h_out=pn.h_out(),
+                       norm_gain=pn.gain, norm_eps=pn.eps)
 
 
 def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx, block_table: torch.Tensor,

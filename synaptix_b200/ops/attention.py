@@ -18,7 +18,7 @@ def fast_supported(dtype, nh: int, nkv: int, hd: int) -> bool:
 
 def pick_splits(n_seqs: int, nkv: int, max_pages: int, device) -> int:
     """Splits of a sequence's pages over blocks, so that a few blocks per SM are busy."""
-    target = 4 * sm_count(device)
+    target = 2 * sm_count(device)
     base = max(1, n_seqs * nkv)
     return max(1, min(max_pages, (target + base - 1) // base))
 

@@ -1,5 +1,5 @@
 from .attention import Attention
-from .base import FeedForward, Mixer, Norm, Part, PositionEncoding, Runtime, StepContext
+from .base import FeedForward, Mixer, Norm, Part, PendingNorm, PositionEncoding, Runtime, StepContext
 from .block import PreNormBlock
 from .embedding import Embedding, OutputHead
 from .linear import Linear
@@ -7,6 +7,6 @@ from .mlp import SwiGLU
 from .norm import RMSNorm
 from .rope import NoPosition, RotaryHalf, rotary_inv_freq
 
-__all__ = ["Attention", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime",
+__all__ = ["Attention", "FeedForward", "Mixer", "Norm", "Part", "PendingNorm", "PositionEncoding", "Runtime",
            "StepContext", "PreNormBlock", "Embedding", "OutputHead", "Linear", "SwiGLU", "RMSNorm",
            "NoPosition", "RotaryHalf", "rotary_inv_freq"]

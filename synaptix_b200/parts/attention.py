@@ -26,6 +26,8 @@ from .linear import Linear
 
 
 class Attention(Mixer):
+    accepts_lazy_input = True      # x goes straight into the fused q/k/v product
+
     def __init__(self, prefix: str, width: int, n_heads: int, n_kv_heads: int, head_dim: int, *,
                  position: PositionEncoding, qk_norm_eps: Optional[float] = None,
                  window: Optional[int] = None, scale: Optional[float] = None):
@@ -64,7 +66,7 @@ class Attention(Mixer):
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_view: KVView, write_cache: bool = True) -> torch.Tensor:
         T = x.shape[0]
         qkv = self.qkv.forward(x)
-        q = torch.empty((T, self.nh * self.hd), dtype=x.dtype, device=x.device)
+        q = torch.empty((T, self.nh * self.hd), dtype=qkv.dtype, device=qkv.device)
         rot = self.position.rotation()
         inv_freq, rotary_dim = rot if rot is not None else (None, 0)
         bt = ctx.block_tables[cache_view.group]

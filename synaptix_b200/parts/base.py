@@ -61,13 +61,60 @@ class StepContext:
     """
     __slots__ = ("token_ids", "positions", "seq_of_token", "cu_seqlens", "seq_past", "seq_lens",
                  "seq_slots", "block_tables", "want_rows", "n_tokens", "n_seqs", "n_want",
-                 "max_new", "max_len", "all_single", "runtime", "scratch", "host")
+                 "max_new", "max_len", "all_single", "runtime", "scratch", "host", "want_all")
 
     def __init__(self, **kw):
         self.scratch = {}
         self.host = None
+        self.want_all = False      # want_rows is 0..n_tokens-1 in order
         for k, v in kw.items():
             setattr(self, k, v)
+
+
+class PendingNorm:
+    """A normalised activation that has not been computed yet: ``rmsnorm(h + delta) * gain``.
+
+    A norm may hand this to a consumer that says it can take it (``accepts_lazy_input``); a
+    matrix product that can compute the norm in its own prologue then does so and writes the
+    residual sum to ``h_out``, so the norm needs no kernel and no round trip through memory.
+    Whoever cannot use it calls ``materialize()`` and gets the plain tensor.
+    """
+    __slots__ = ("h", "delta", "gain", "eps", "dtype", "_x", "_h_after")
+
+    def __init__(self, h, delta, gain, eps, dtype):
+        self.h, self.delta, self.gain, self.eps, self.dtype = h, delta, gain, eps, dtype
+        self._x = None
+        self._h_after = None
+
+    @property
+    def shape(self):
+        return self.h.shape
+
+    def h_out(self):
+        """Where a fused consumer writes ``h + delta`` (``None`` when there is no delta)."""
+        if self.delta is None:
+            self._h_after = self.h
+            return None
+        if self._h_after is None or self._h_after is self.h:
+            self._h_after = torch.empty_like(self.h)
+        return self._h_after
+
+    def materialize(self) -> torch.Tensor:
+        if self._x is None:
+            from .. import ops
+            if self._h_after is not None and self._h_after is not self.h:
+                # a fused consumer has already formed the sum; normalise that
+                self._x = ops.add_rmsnorm(self._h_after, None, self.gain, self.eps, self.dtype)
+            else:
+                self._x = ops.add_rmsnorm(self.h, self.delta, self.gain, self.eps, self.dtype)
+                self._h_after = self.h
+        return self._x
+
+    def h_after(self) -> torch.Tensor:
+        """The residual stream after the sum, whoever formed it."""
+        if self._h_after is None:
+            self.materialize()
+        return self._h_after
 
 
 class Part:
@@ -108,7 +155,8 @@ class Norm(Part):
         raise NotImplementedError
 
     def add_forward(self, h: torch.Tensor, delta: Optional[torch.Tensor],
-                    rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    rows: Optional[torch.Tensor] = None, lazy: bool = False):
+        """``lazy=True`` allows the norm to return a ``PendingNorm`` (see there)."""
         raise NotImplementedError
 
 
@@ -118,6 +166,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    accepts_lazy_input = False     # True: forward may be handed a PendingNorm instead of a tensor
+
     def cache_request(self):
         return None
 
@@ -126,6 +176,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_lazy_input = False
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 

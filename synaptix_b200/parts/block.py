@@ -11,7 +11,7 @@ from typing import List, Optional, Tuple
 
 import torch
 
-from .base import FeedForward, Mixer, Norm, Part, StepContext
+from .base import FeedForward, Mixer, Norm, Part, PendingNorm, StepContext
 
 
 class PreNormBlock(Part):
@@ -26,8 +26,12 @@ class PreNormBlock(Part):
 
     def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
                 cache_view, write_cache: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
-        x = self.norm1.add_forward(h, pending)
+        x = self.norm1.add_forward(h, pending, lazy=self.mixer.accepts_lazy_input)
         a = self.mixer.forward(x, ctx, cache_view, write_cache)
-        y = self.norm2.add_forward(h, a)
+        if isinstance(x, PendingNorm):
+            h = x.h_after()
+        y = self.norm2.add_forward(h, a, lazy=self.ffn.accepts_lazy_input)
         m = self.ffn.forward(y, ctx)
+        if isinstance(y, PendingNorm):
+            h = y.h_after()
         return h, m

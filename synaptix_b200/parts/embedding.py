@@ -54,5 +54,6 @@ class OutputHead(Part):
             self.linear.bind(tensors, rt)
         self.is_tied = tied
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x) -> torch.Tensor:
+        """``x``: the normalised rows, or a ``PendingNorm`` of them."""
         return self.linear.forward(x, out_dtype=torch.float32)

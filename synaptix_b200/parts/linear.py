@@ -14,7 +14,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorSpec
-from .base import Part, Runtime, to_device_matrix
+from .base import Part, PendingNorm, Runtime, to_device_matrix
 
 
 class Linear(Part):
@@ -47,4 +47,9 @@ class Linear(Part):
 
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                 epilogue: Optional[str] = None) -> torch.Tensor:
+        if isinstance(x, PendingNorm):
+            y = ops.linear_normed(x, self.weight, out_dtype=out_dtype, epilogue=epilogue)
+            if y is not None:
+                return y
+            x = x.materialize()
         return ops.linear(x, self.weight, out_dtype=out_dtype, epilogue=epilogue)

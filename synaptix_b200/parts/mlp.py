@@ -15,6 +15,8 @@ from .linear import Linear
 
 
 class SwiGLU(FeedForward):
+    accepts_lazy_input = True      # x goes straight into the fused gate/up product
+
     def __init__(self, prefix: str, width: int, intermediate: int):
         self.width, self.intermediate = width, intermediate
         self.gate_up = Linear([prefix + "gate_proj.weight", prefix + "up_proj.weight"], width,

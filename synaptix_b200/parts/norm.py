@@ -14,7 +14,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorSpec
-from .base import Norm, Runtime, to_device_f32
+from .base import Norm, PendingNorm, Runtime, to_device_f32
 
 
 class RMSNorm(Norm):
@@ -35,5 +35,7 @@ class RMSNorm(Norm):
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return ops.add_rmsnorm(h, None, self.weight, self.eps, self._dtype)
 
-    def add_forward(self, h, delta, rows=None):
+    def add_forward(self, h, delta, rows=None, lazy=False):
+        if lazy and rows is None and ops.norm_fusable(h.shape[0], h.shape[1], self._dtype):
+            return PendingNorm(h, delta, self.weight, self.eps, self._dtype)
         return ops.add_rmsnorm(h, delta, self.weight, self.eps, self._dtype, rows=rows)

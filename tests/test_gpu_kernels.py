@@ -347,11 +347,19 @@ def test_skinny_gemm_silu_mul_epilogue(M, I, K):
         assert torch.allclose(out.float().cpu().double(), ref, atol=3e-2, rtol=2e-2), f"ks={ks}"
 
 
-@pytest.mark.parametrize("M", [1, 5, 8, 16])
-@pytest.mark.parametrize("epilogue,N", [(None, 200), ("silu_mul", 144)])
-def test_skinny_gemm_with_norm_prologue(M, epilogue, N):
+def test_skinny_gemm_norm_prologue_refuses_many_rows():
+    from synaptix_b200.ops import KernelError
     from synaptix_b200.ops.decode import skinny_gemm
-    K = 320
+    w = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(KernelError, match="size"):
+        skinny_gemm(None, w, norm_h=torch.zeros(3, 64, device="cuda"), norm_gain=torch.ones(64, device="cuda"))
+
+
+@pytest.mark.parametrize("M", [1, 2])
+@pytest.mark.parametrize("epilogue,N", [(None, 200), ("silu_mul", 144), ("f32", 389)])
+@pytest.mark.parametrize("K", [320, 2560, 4096])
+def test_skinny_gemm_with_norm_prologue(M, epilogue, N, K):
+    from synaptix_b200.ops.decode import skinny_gemm
     h = torch.randn(M, K) * 2
     d = torch.randn(M, K).to(torch.bfloat16)
     gain = 1 + 0.2 * torch.randn(K)
@@ -364,7 +372,7 @@ def test_skinny_gemm_with_norm_prologue(M, epilogue, N):
         y = gate / (1 + torch.exp(-gate)) * up
     h_out = torch.full((M, K), float("nan"), device="cuda")
     out = skinny_gemm(None, w.cuda(), epilogue=epilogue, norm_h=h.cuda(), norm_delta=d.cuda(), norm_h_out=h_out,
-                      norm_gain=gain.cuda(), norm_eps=1e-5)
+                      norm_gain=gain.cuda(), norm_eps=1e-5, ks=8)
     assert torch.allclose(h_out.cpu(), s, atol=1e-6)
     assert torch.allclose(out.float().cpu().double(), y, atol=3e-2, rtol=2e-2)
     out = skinny_gemm(None, w.cuda(), epilogue=epilogue, norm_h=h.cuda(), norm_delta=None, norm_h_out=None,
