@@ -442,6 +442,59 @@ extern "C" int sx_attn_decode(const void* q, const void* k_pages, const void* v_
   return SX_ERR_SIZE;
 }
 
+// ---------------------------------------------------------------------------------------
+// The same decode attention with its scratch inside the library (see no_alloc.h for whom
+// this is meant and what it promises).  Only this function and the array below are new; the
+// kernels and the launch path are the ones sx_attn_decode uses.
+// ---------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a pointer a kernel can use.
+static __device__ __align__(256) unsigned char sx_noalloc_scratch[SX_NOALLOC_SCRATCH_BYTES];
+
+#define SX_NOALLOC_MAX_DEVICES 64
+
+// the array's device address on the current device, looked up once per device
+static int noalloc_scratch_address(float** out_ptr) {
+  static float* addr[SX_NOALLOC_MAX_DEVICES] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= SX_NOALLOC_MAX_DEVICES) return SX_ERR_SIZE;
+  if (!addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, sx_noalloc_scratch);      // the copy of the array that lives on `dev`
+    if (e != cudaSuccess) return (int)e;
+    addr[dev] = reinterpret_cast<float*>(p);
+  }
+  *out_ptr = addr[dev];
+  return 0;
+}
+
+extern "C" unsigned long long sx_attn_decode_noalloc_capacity(void) { return SX_NOALLOC_SCRATCH_BYTES; }
+
+extern "C" int sx_attn_decode_noalloc(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                      const int* seq_lens, const int* block_table, int maxp, int S, int nh, int nkv,
+                                      int hd, float scale, int window, int n_splits, cudaStream_t stream) {
+  if (S <= 0) return 0;
+  if (nkv <= 0 || nh <= 0 || nh % nkv != 0 || nh / nkv > 16 || n_splits < 1 || nkv > 65535 || S > 65535) return SX_ERR_SIZE;
+  if (hd != 128 && hd != 64 && hd != 32) return SX_ERR_SIZE;
+  float* part_o = nullptr;
+  float* part_ml = nullptr;
+  if (n_splits > 1) {
+    const unsigned long long slots = (unsigned long long)S * nh * n_splits;
+    const unsigned long long need = slots * (unsigned long long)(hd + 2) * sizeof(float);
+    if (need > SX_NOALLOC_SCRATCH_BYTES) return SX_ERR_NOALLOC_TOO_LARGE;
+    float* base = nullptr;
+    const int rc = noalloc_scratch_address(&base);
+    if (rc) return rc;
+    part_o = base;                          // [slots][hd]
+    part_ml = base + slots * hd;            // [slots][2]; slots * hd * 4 bytes keeps it 8-byte aligned
+  }
+  return sx_attn_decode(q, k_pages, v_pages, out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, hd, scale,
+                        window, n_splits, stream);
+}
+
 template <int HD>
 static int prefill_launch(const bf16* q, const bf16* k, const bf16* v, bf16* out, const int* tile_seq, const int* tile_q0,
                           int n_tiles, const int* cu, const int* past, const int* lens, const int* bt, int maxp, int nh,

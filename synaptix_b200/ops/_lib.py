@@ -11,7 +11,8 @@ from ..csrc.build import KernelsUnavailable, load_library
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
 _ERRORS = {10001: "unsupported dtype combination", 10002: "unsupported size", 10003: "misaligned pointer or stride",
-           10004: "a bounded wait inside the kernel ran out (see the kernel's status word)"}
+           10004: "a bounded wait inside the kernel ran out (see the kernel's status word)",
+           10005: "the problem needs more scratch than the library's built-in array holds"}
 
 
 class KernelError(RuntimeError):

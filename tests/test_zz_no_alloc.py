@@ -1,0 +1,96 @@
+"""The decode-attention entry point that allocates nothing, called the way its users call it:
+through the exported C symbol of the compiled library, with raw device pointers.
+
+It exists for host programs that cannot bring scratch memory of their own (the device is owned
+by someone else's memory pool, or the loop must not call cudaMalloc because that synchronises
+the device).  Its partial results go through an array built into the library, so the test
+checks it against the ordinary entry point, whose scratch the caller allocates, on two calls in
+a row with different inputs: the second call finds the first call's leftovers in the array and
+must not be disturbed by them.  This file sorts last so that a run which stops at the first
+failure has already run everything else.
+"""
+import ctypes
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+TOO_LARGE = 10005
+
+
+def _library():
+    from synaptix_b200.csrc.build import library_path, load_library
+    load_library("attention")                      # compiles it if this is a fresh checkout
+    lib = ctypes.CDLL(library_path("attention"))
+    lib.sx_attn_decode_noalloc.restype = ctypes.c_int
+    lib.sx_attn_decode_noalloc_capacity.restype = ctypes.c_ulonglong
+    return lib
+
+
+def _case(seed, S, nh, nkv, hd, lens):
+    """Random queries and a paged cache whose pages are in scrambled order, unused rows NaN."""
+    g = torch.Generator().manual_seed(seed)
+    need = [(n + 63) // 64 for n in lens]
+    n_pages = sum(need) + 2
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    kp = torch.full((n_pages, nkv, 64, hd), float("nan"), dtype=torch.bfloat16)
+    vp = torch.full((n_pages, nkv, 64, hd), float("nan"), dtype=torch.bfloat16)
+    bt = torch.zeros((S, max(need)), dtype=torch.int32)
+    for s, n in enumerate(lens):
+        for i in range(need[s]):
+            page = perm.pop()
+            bt[s, i] = page
+            rows = min(64, n - 64 * i)
+            kp[page, :, :rows] = torch.randn(nkv, rows, hd, generator=g).to(torch.bfloat16)
+            vp[page, :, :rows] = torch.randn(nkv, rows, hd, generator=g).to(torch.bfloat16)
+    q = torch.randn(S, nh * hd, generator=g).to(torch.bfloat16)
+    return q.cuda(), kp.cuda(), vp.cuda(), torch.tensor(lens, dtype=torch.int32).cuda(), bt.cuda()
+
+
+def _call(lib, q, kp, vp, lens, bt, nh, nkv, hd, scale, window, n_splits):
+    S = q.shape[0]
+    out = torch.full((S, nh * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    rc = lib.sx_attn_decode_noalloc(p(q), p(kp), p(vp), p(out), p(lens), p(bt), ctypes.c_int(bt.shape[1]),
+                                    ctypes.c_int(S), ctypes.c_int(nh), ctypes.c_int(nkv), ctypes.c_int(hd),
+                                    ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(n_splits),
+                                    ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    return rc, out
+
+
+def test_no_alloc_entry_point_matches_the_allocating_one_twice_in_a_row():
+    from synaptix_b200.ops.attention import attn_decode
+    lib = _library()
+    assert lib.sx_attn_decode_noalloc_capacity() == 4 << 20
+    nh, nkv, hd = 8, 2, 128
+    scale = 1 / math.sqrt(hd)
+    # two calls in a row, different inputs, sizes and split counts; the second also with a window
+    for seed, lens, n_splits, window in [(1, [700, 64, 1, 130], 6, 0), (2, [33, 900, 257], 9, 100)]:
+        q, kp, vp, ln, bt = _case(seed, len(lens), nh, nkv, hd, lens)
+        rc, got = _call(lib, q, kp, vp, ln, bt, nh, nkv, hd, scale, window, n_splits)
+        assert rc == 0
+        want = attn_decode(q, kp, vp, ln, bt, nh, nkv, hd, scale, window or None, n_splits)
+        torch.cuda.synchronize()
+        assert torch.isfinite(got.float()).all()
+        err = (got.float() - want.float()).abs().max().item()
+        assert err < 2e-2, f"call with seed {seed}: {err}"      # the tolerance of the kernel tests
+    # one split needs no scratch at all and goes the same way
+    q, kp, vp, ln, bt = _case(3, 2, nh, nkv, hd, [100, 5])
+    rc, got = _call(lib, q, kp, vp, ln, bt, nh, nkv, hd, scale, 0, 1)
+    want = attn_decode(q, kp, vp, ln, bt, nh, nkv, hd, scale, None, 1)
+    assert rc == 0 and (got.float() - want.float()).abs().max().item() < 2e-2
+
+
+def test_no_alloc_entry_point_refuses_what_its_array_cannot_hold():
+    lib = _library()
+    nh, nkv, hd = 32, 8, 128
+    q, kp, vp, ln, bt = _case(4, 8, nh, nkv, hd, [70] * 8)
+    # 8 sequences x 32 heads x 64 splits x 130 floats = 8.5 MB > 4 MiB
+    rc, out = _call(lib, q, kp, vp, ln, bt, nh, nkv, hd, 0.1, 0, 64)
+    torch.cuda.synchronize()
+    assert rc == TOO_LARGE
+    assert torch.isnan(out.float()).all()          # nothing was launched
+    rc, _ = _call(lib, q, kp, vp, ln, bt, nh, nkv, hd, 0.1, 0, 16)      # 2.1 MB: fits
+    assert rc == 0
