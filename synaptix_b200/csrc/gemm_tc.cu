@@ -24,16 +24,19 @@
 #include "common.cuh"
 
 #define TC_BM 128
-#define TC_BN 256
 #define TC_BK 64
-#define TC_STAGES 4
 #define TC_A_BYTES (TC_BM * TC_BK * 2)            // 16 KB
-#define TC_B_BYTES (TC_BN * TC_BK * 2)            // 32 KB
-#define TC_STAGE_BYTES (TC_A_BYTES + TC_B_BYTES)
 #define TC_THREADS 192
 #define TC_SPIN_LIMIT (1u << 26)
 
-enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SILU_MUL = 2 };
+enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SILU_MUL = 2, TC_EPI_PARTIAL = 3 };
+
+// BN: columns of W per block (256, or 128 for the split-K form); stages fill the shared memory
+template <int BN> struct TcShape {
+  static constexpr int B_BYTES = BN * TC_BK * 2;
+  static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
+  static constexpr int STAGES = BN == 256 ? 4 : 6;
+};
 
 __device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void tc_mbar_init(uint32_t bar, uint32_t count) {
@@ -90,11 +93,13 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
 }
 
-template <int EPI>
+template <int EPI, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                 const __grid_constant__ CUtensorMap map_w,
                                                                 void* __restrict__ out, int M, int N, int K,
                                                                 int* __restrict__ status) {
+  constexpr int TC_BN = BN, TC_STAGES = TcShape<BN>::STAGES, TC_B_BYTES = TcShape<BN>::B_BYTES,
+                TC_STAGE_BYTES = TcShape<BN>::STAGE_BYTES;
   extern __shared__ unsigned char tc_smem_raw[];
   // the swizzled tiles must start on a 1024-byte boundary
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -106,7 +111,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
   const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;                 // columns of C
   const int tile_n = (EPI == TC_EPI_SILU_MUL) ? TC_BN / 2 : TC_BN;        // columns of C per block
   const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * tile_n;
-  const int nkb = (K + TC_BK - 1) / TC_BK;
+  // split-K: block z of gridDim.z takes a contiguous range of the 64-wide slices of K and (with
+  // TC_EPI_PARTIAL) writes its float32 partial tile to out[z][M][N]; the host gives every z a non-empty range
+  const int nkb_all = (K + TC_BK - 1) / TC_BK;
+  const int kper = (nkb_all + gridDim.z - 1) / gridDim.z;
+  const int kb0 = blockIdx.z * kper;
+  const int nkb = max(0, min(nkb_all, kb0 + kper) - kb0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TC_STAGES; ++s) {
@@ -132,13 +142,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         if (!tc_mbar_wait(empty0 + 8 * s, ((kb / TC_STAGES) & 1) ^ 1)) { atomicExch(status, 1); break; }
         tc_mbar_expect_tx(full0 + 8 * s, TC_STAGE_BYTES);
         const uint32_t a_dst = tc_smem(tiles + s * TC_STAGE_BYTES), b_dst = a_dst + TC_A_BYTES;
-        tc_tma_load_2d(a_dst, &map_a, kb * TC_BK, m0, full0 + 8 * s);
+        const int kx = (kb0 + kb) * TC_BK;
+        tc_tma_load_2d(a_dst, &map_a, kx, m0, full0 + 8 * s);
         if (EPI == TC_EPI_SILU_MUL) {
-          tc_tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);                        // gate rows
-          tc_tma_load_2d(b_dst + TC_B_BYTES / 2, &map_w, kb * TC_BK, N / 2 + n0, full0 + 8 * s);  // up rows
+          tc_tma_load_2d(b_dst, &map_w, kx, n0, full0 + 8 * s);                        // gate rows
+          tc_tma_load_2d(b_dst + TC_B_BYTES / 2, &map_w, kx, N / 2 + n0, full0 + 8 * s);  // up rows
         } else {
-          tc_tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);
-          tc_tma_load_2d(b_dst + TC_B_BYTES / 2, &map_w, kb * TC_BK, n0 + TC_BN / 2, full0 + 8 * s);
+#pragma unroll
+          for (int j = 0; j < TC_BN / 128; ++j)
+            tc_tma_load_2d(b_dst + j * (128 * TC_BK * 2), &map_w, kx, n0 + j * 128, full0 + 8 * s);
         }
       }
     }
@@ -183,8 +195,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
           if (EPI == TC_EPI_SILU_MUL) f[i] = f[i] / (1.f + expf(-f[i])) * __uint_as_float(u[i]);
         }
         const int ncol = min(32, n_out - (n0 + c0));
-        if (EPI == TC_EPI_F32) {
-          float* dst = reinterpret_cast<float*>(out) + (size_t)row * n_out + n0 + c0;
+        if (EPI == TC_EPI_F32 || EPI == TC_EPI_PARTIAL) {
+          float* dst = reinterpret_cast<float*>(out) + ((size_t)(EPI == TC_EPI_PARTIAL ? blockIdx.z : 0) * M + row) * n_out + n0 + c0;
           if (ncol == 32 && (n_out % 4) == 0) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) reinterpret_cast<float4*>(dst)[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
@@ -264,27 +276,52 @@ static int* tc_status_word() {
   return p;
 }
 
-template <int EPI>
-static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, cudaStream_t stream) {
+template <int EPI, int BN>
+static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, int splits,
+                     cudaStream_t stream) {
   int* status = tc_status_word();
   if (!status) return (int)cudaErrorMemoryAllocation;
-  const int tile_n = (EPI == TC_EPI_SILU_MUL) ? TC_BN / 2 : TC_BN;
+  const int tile_n = (EPI == TC_EPI_SILU_MUL) ? BN / 2 : BN;
   const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;
-  dim3 grid((n_out + tile_n - 1) / tile_n, (M + TC_BM - 1) / TC_BM);
-  if (grid.y > 65535) return SX_ERR_SIZE;
-  const size_t smem = 1024 + TC_STAGES * TC_STAGE_BYTES + (2 * TC_STAGES + 1) * sizeof(uint64_t) + 16;
-  auto kern = gemm_tc_kernel<EPI>;
+  dim3 grid((n_out + tile_n - 1) / tile_n, (M + TC_BM - 1) / TC_BM, splits);
+  if (grid.y > 65535 || grid.z > 65535) return SX_ERR_SIZE;
+  const size_t smem = 1024 + TcShape<BN>::STAGES * TcShape<BN>::STAGE_BYTES + (2 * TcShape<BN>::STAGES + 1) * sizeof(uint64_t) + 16;
+  auto kern = gemm_tc_kernel<EPI, BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   kern<<<grid, TC_THREADS, smem, stream>>>(ma, mw, out, M, N, K, status);
   return sx_launch_status();
 }
 
+// sum of the split-K partial tiles ws[splits][M][N] in split order, then the epilogue
+template <int EPI>
+__global__ void tc_splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ out, int splits, int M, int N) {
+  const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)M * n_out) return;
+  const size_t m = idx / n_out;
+  const int n = (int)(idx - m * n_out);
+  const size_t plane = (size_t)M * N;
+  float a = 0.f, b = 0.f;
+  for (int z = 0; z < splits; ++z) {
+    a += ws[z * plane + m * N + n];
+    if (EPI == TC_EPI_SILU_MUL) b += ws[z * plane + m * N + n_out + n];
+  }
+  if (EPI == TC_EPI_SILU_MUL) reinterpret_cast<bf16*>(out)[idx] = __float2bfloat16_rn(a / (1.f + expf(-a)) * b);
+  else if (EPI == TC_EPI_F32) reinterpret_cast<float*>(out)[idx] = a;
+  else reinterpret_cast<bf16*>(out)[idx] = __float2bfloat16_rn(a);
+}
+
 // A [M, K], W [N, K] bfloat16 row-major, 16-byte aligned, K % 8 == 0.
 // epi 0: out bf16 [M, N]; 1: out f32 [M, N]; 2: W = [gate; up] stacked, out bf16 [M, N/2].
-extern "C" int sx_gemm_tc(const void* A, const void* W, void* out, int M, int N, int K, int epi, cudaStream_t stream) {
+// splits == 1: one block per 128 x 256 tile, epilogue in the kernel.
+// splits > 1 (for few rows, where whole tiles would leave most SMs idle): 128 x 128 tiles, K split over
+// `splits` blocks whose float32 partial tiles go to `workspace` [splits, M, N] and are added, in split
+// order, by a second kernel that applies the epilogue.  Every split gets a non-empty range of K.
+extern "C" int sx_gemm_tc(const void* A, const void* W, void* out, int M, int N, int K, int epi, int splits,
+                          float* workspace, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || (K & 7)) return SX_ERR_SIZE;
+  if (K <= 0 || (K & 7) || splits < 1) return SX_ERR_SIZE;
   if (epi == TC_EPI_SILU_MUL && (N & 1)) return SX_ERR_SIZE;
   if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return SX_ERR_ALIGN;
   CUtensorMap ma, mw;
@@ -292,12 +329,30 @@ extern "C" int sx_gemm_tc(const void* A, const void* W, void* out, int M, int N,
   if (rc) return rc;
   rc = tc_make_map(&mw, W, N, K);
   if (rc) return rc;
+  if (splits == 1) {
+    switch (epi) {
+      case TC_EPI_BF16: return tc_launch<TC_EPI_BF16, 256>(ma, mw, out, M, N, K, 1, stream);
+      case TC_EPI_F32: return tc_launch<TC_EPI_F32, 256>(ma, mw, out, M, N, K, 1, stream);
+      case TC_EPI_SILU_MUL: return tc_launch<TC_EPI_SILU_MUL, 256>(ma, mw, out, M, N, K, 1, stream);
+      default: return SX_ERR_DTYPE;
+    }
+  }
+  if (!workspace) return SX_ERR_SIZE;
+  const int nkb = (K + TC_BK - 1) / TC_BK;
+  if (splits > nkb) splits = nkb;
+  const int kper = (nkb + splits - 1) / splits;
+  splits = (nkb + kper - 1) / kper;                 // no empty range
+  rc = tc_launch<TC_EPI_PARTIAL, 128>(ma, mw, workspace, M, N, K, splits, stream);
+  if (rc) return rc;
+  const size_t n_elems = (size_t)M * (epi == TC_EPI_SILU_MUL ? N / 2 : N);
+  const unsigned grid = (unsigned)((n_elems + 255) / 256);
   switch (epi) {
-    case TC_EPI_BF16: return tc_launch<TC_EPI_BF16>(ma, mw, out, M, N, K, stream);
-    case TC_EPI_F32: return tc_launch<TC_EPI_F32>(ma, mw, out, M, N, K, stream);
-    case TC_EPI_SILU_MUL: return tc_launch<TC_EPI_SILU_MUL>(ma, mw, out, M, N, K, stream);
+    case TC_EPI_BF16: tc_splitk_reduce_kernel<TC_EPI_BF16><<<grid, 256, 0, stream>>>(workspace, out, splits, M, N); break;
+    case TC_EPI_F32: tc_splitk_reduce_kernel<TC_EPI_F32><<<grid, 256, 0, stream>>>(workspace, out, splits, M, N); break;
+    case TC_EPI_SILU_MUL: tc_splitk_reduce_kernel<TC_EPI_SILU_MUL><<<grid, 256, 0, stream>>>(workspace, out, splits, M, N); break;
     default: return SX_ERR_DTYPE;
   }
+  return sx_launch_status();
 }
 
 // 0, or which bounded wait ran out (1 producer, 2 MMA issuer, 3 epilogue)

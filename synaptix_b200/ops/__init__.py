@@ -24,6 +24,9 @@ __all__ = ["KernelsUnavailable", "KernelError", "set_launch_counter", "decode_ad
            "gemm_generic", "qkv_prepare", "residual_add", "silu_mul", "linear", "linear_normed", "norm_fusable", "attention"]
 
 
+SKINNY_MAX_ROWS = 16
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
            epilogue: Optional[str] = None) -> torch.Tensor:
     """``x[M, K] @ w[N, K].T`` with 32-bit accumulation; output in ``out_dtype`` (default ``x``'s).
@@ -33,7 +36,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     N = w.shape[0]
     if out_dtype is None:
         out_dtype = x.dtype
-    if skinny_supported(M, N, K, x.dtype, w.dtype) and out_dtype in (torch.bfloat16, torch.float32):
+    # few rows: stream W once on mma.sync; more than SKINNY_MAX_ROWS: tcgen05 (split over K while rows are few)
+    if (skinny_supported(M, N, K, x.dtype, w.dtype) and out_dtype in (torch.bfloat16, torch.float32)
+            and (M <= SKINNY_MAX_ROWS or not tc_supported(M, N, K, x.dtype, w.dtype))):
         if epilogue == "silu_mul":
             if out_dtype == torch.bfloat16:
                 return skinny_gemm(x, w, epilogue="silu_mul", ks=8)

@@ -7,6 +7,7 @@ from typing import Optional
 import torch
 
 from ._lib import KernelError, c_int, check, fn, ptr, require_cuda, stream
+from .decode import sm_count
 
 _EPI = {None: 0, "f32": 1, "silu_mul": 2}
 
@@ -15,9 +16,24 @@ def tc_supported(M: int, N: int, K: int, x_dtype, w_dtype) -> bool:
     return x_dtype == torch.bfloat16 and w_dtype == torch.bfloat16 and K > 0 and K % 8 == 0 and M > 0 and N > 0
 
 
+def plan_splits(M: int, N: int, K: int, n_sm: int) -> int:
+    """How many blocks split K: 1 when whole 128 x 256 tiles already fill the GPU, else enough
+    128 x 128 tiles x splits to give every SM a block (each split at least two 64-wide slices)."""
+    tiles_256 = ((N + 255) // 256) * ((M + 127) // 128)
+    if tiles_256 >= (n_sm * 3) // 4:
+        return 1
+    tiles_128 = ((N + 127) // 128) * ((M + 127) // 128)
+    nkb = (K + 63) // 64
+    return max(1, min(nkb // 2, (n_sm + tiles_128 // 2) // tiles_128))
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None,
-            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+            out: Optional[torch.Tensor] = None, splits: Optional[int] = None) -> torch.Tensor:
     """``x[M, K] @ w[N, K].T`` on the tcgen05 tensor cores, 32-bit accumulation in tensor memory.
+
+    ``splits``: blocks that split K (default: chosen so that the GPU is filled; more than one only
+    matters for few rows).  With ``splits > 1`` float32 partial tiles go through a workspace of
+    ``splits * M * N`` floats and a second kernel adds them in a fixed order.
 
     ``epilogue``: ``None`` -> bfloat16 ``[M, N]``; ``"f32"`` -> float32 ``[M, N]``; ``"silu_mul"`` ->
     ``w`` is ``[gate; up]`` stacked and the result is bfloat16 ``[M, N/2]``.  Needs ``K % 8 == 0``.
@@ -34,8 +50,12 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None,
     n_out = N // 2 if epilogue == "silu_mul" else N
     if out is None:
         out = torch.empty((M, n_out), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=x.device)
+    if splits is None:
+        splits = plan_splits(M, N, K, sm_count(x.device))
+    splits = max(1, min(int(splits), (K + 63) // 64))
+    ws = torch.empty(splits * M * N, dtype=torch.float32, device=x.device) if splits > 1 else None
     check(fn("gemm_tc", "sx_gemm_tc")(ptr(x), ptr(w), ptr(out), c_int(M), c_int(N), c_int(K), c_int(_EPI[epilogue]),
-                                      stream()), "gemm_tc")
+                                      c_int(splits), ptr(ws), stream()), "gemm_tc", launches=2 if splits > 1 else 1)
     return out
 
 

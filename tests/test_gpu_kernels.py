@@ -533,3 +533,25 @@ def test_gemm_tc_silu_mul_epilogue(M, I, K):
     out = gemm_tc(x.cuda(), w.cuda(), epilogue="silu_mul")
     assert out.shape == (M, I) and torch.allclose(out.float().cpu().double(), ref, atol=3e-2, rtol=2e-2)
     assert gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K,epilogue", [(64, 2560, 4096, None), (17, 389, 96, "f32"), (64, 6144, 2560, None),
+                                             (33, 320, 1224, "silu_mul"), (128, 256, 64, "f32"), (40, 2560, 9728, "f32")])
+def test_gemm_tc_split_k(M, N, K, epilogue):
+    """Few rows: K split over blocks, float32 partial tiles added in a fixed order by a second kernel."""
+    from synaptix_b200.ops.gemm_tc import gemm_tc, gemm_tc_status
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    if epilogue == "silu_mul":
+        ref = ref[:, :N // 2] / (1 + torch.exp(-ref[:, :N // 2])) * ref[:, N // 2:]
+    outs = []
+    for splits in (None, 2, 3, 7, 1000):
+        out = gemm_tc(x.cuda(), w.cuda(), epilogue=epilogue, splits=splits)
+        tol = dict(atol=2e-5 * math.sqrt(K), rtol=1e-5) if epilogue == "f32" else dict(atol=3e-2, rtol=2e-2)
+        assert torch.allclose(out.float().cpu().double(), ref, **tol), f"splits={splits}"
+        outs.append(out)
+    again = gemm_tc(x.cuda(), w.cuda(), epilogue=epilogue, splits=3)
+    assert torch.equal(again, outs[2])                  # the order of addition is fixed
+    assert gemm_tc_status() == 0
