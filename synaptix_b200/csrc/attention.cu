@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ seq_lens, const int* __restrict__ block_table, int maxp, int nh, int nkv,
-    float scale_log2, int window, int n_splits) {
+    float scale_log2, int window, int n_splits, int* __restrict__ counters) {
   using L = AtLayout<HD>;
   extern __shared__ __align__(16) unsigned char smem[];
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
@@ -273,6 +273,59 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
       part_o[pi * HD + d] = O;
       if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = Lsum; }
     }
+  }
+  if (n_splits == 1 || counters == nullptr) return;      // without counters a second kernel merges
+
+  // The block that finishes last for this (sequence, kv head) merges all splits, in split order.
+  // counters[seq * nkv + kvh] counts finished blocks and is set back to zero by the last one, so
+  // the array only has to be zero before the very first launch.
+  __shared__ int s_last;
+  __threadfence();                                       // this block's partials are visible before it counts
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* c = counters + (size_t)seq * nkv + kvh;
+    const int done = atomicAdd(c, 1);
+    s_last = (done == n_splits - 1);
+    if (s_last) *c = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();                                       // and the others' partials before they are read
+  float* fac = reinterpret_cast<float*>(smem);           // [G][n_splits] maxima, then weights
+  float* ls = fac + G * n_splits;                        // [G][n_splits] sums
+  float* gl = ls + G * n_splits;                         // [G] merged sums
+  for (int idx = threadIdx.x; idx < G * n_splits; idx += AT_THREADS) {
+    const int r = idx / n_splits, i = idx % n_splits;
+    const float2 ml = reinterpret_cast<const float2*>(part_ml)[((size_t)seq * nh + kvh * G + r) * n_splits + i];
+    fac[idx] = ml.x;
+    ls[idx] = ml.y;
+  }
+  __syncthreads();
+  for (int r = warp; r < G; r += 4) {                    // one warp per head: maximum, weights, sum
+    float M = -INFINITY;
+    for (int i = lane; i < n_splits; i += 32) M = fmaxf(M, fac[r * n_splits + i]);
+    M = warp_max(M);
+    float L = 0.f;
+    for (int i = lane; i < n_splits; i += 32) {
+      const float mi = fac[r * n_splits + i];
+      const float f = (mi == -INFINITY) ? 0.f : exp2f(mi - M);
+      fac[r * n_splits + i] = f;
+      L += ls[r * n_splits + i] * f;
+    }
+    L = warp_sum(L);
+    if (lane == 0) gl[r] = L;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * HD; idx += AT_THREADS) {
+    const int r = idx / HD, d = idx % HD;
+    const size_t row = (size_t)seq * nh + kvh * G + r;
+    const float* po = part_o + row * n_splits * HD + d;
+    const float* f = fac + r * n_splits;
+    float O = 0.f;
+#pragma unroll 8
+    for (int i = 0; i < n_splits; ++i) O += po[(size_t)i * HD] * f[i];
+    const float L = gl[r];
+    out[row * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
   }
 }
 
@@ -410,36 +463,56 @@ __global__ void __launch_bounds__(AT_THREADS) attn_prefill_kernel(
 template <int HD>
 static int decode_launch(const bf16* q, const bf16* k, const bf16* v, bf16* out, float* part_o, float* part_ml,
                          const int* seq_lens, const int* bt, int maxp, int S, int nh, int nkv, float scale_log2,
-                         int window, int n_splits, cudaStream_t stream) {
+                         int window, int n_splits, int* counters, cudaStream_t stream) {
   using L = AtLayout<HD>;
   const size_t merge_bytes = (size_t)(4 * 16 * HD + 4 * 16 * 2) * sizeof(float);
-  const size_t smem = L::SMEM > merge_bytes ? L::SMEM : merge_bytes;
+  const size_t last_bytes = (size_t)(2 * 16 * n_splits + 16) * sizeof(float);
+  size_t smem = L::SMEM > merge_bytes ? L::SMEM : merge_bytes;
+  if (last_bytes > smem) counters = nullptr;             // too many splits for the in-kernel merge
   auto kern = attn_decode_kernel<HD>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(n_splits, nkv, S);
   kern<<<grid, AT_THREADS, smem, stream>>>(q, k, v, out, part_o, part_ml, seq_lens, bt, maxp, nh, nkv, scale_log2,
-                                          window, n_splits);
+                                          window, n_splits, counters);
   int rc = sx_launch_status();
-  if (rc || n_splits == 1) return rc;
+  if (rc || n_splits == 1 || counters) return rc;
   attn_merge_kernel<HD><<<S * nh, HD, 2 * n_splits * sizeof(float), stream>>>(part_o, part_ml, out, n_splits);
   return sx_launch_status();
 }
 
 // q [S, nh, hd] (one token per sequence), out [S, nh*hd]; part_o f32 [S*nh*n_splits*hd] and
 // part_ml f32 [S*nh*n_splits*2] are scratch (unused when n_splits == 1).
-extern "C" int sx_attn_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o,
-                              float* part_ml, const int* seq_lens, const int* block_table, int maxp, int S, int nh,
-                              int nkv, int hd, float scale, int window, int n_splits, cudaStream_t stream) {
+static int attn_decode_any(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o,
+                           float* part_ml, const int* seq_lens, const int* block_table, int maxp, int S, int nh,
+                           int nkv, int hd, float scale, int window, int n_splits, int* counters, cudaStream_t stream) {
   if (S <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || n_splits < 1 || nkv > 65535 || S > 65535) return SX_ERR_SIZE;
   if (n_splits > 1 && (!part_o || !part_ml)) return SX_ERR_SIZE;
   const float sl = scale * 1.4426950408889634f;
   const bf16 *qb = (const bf16*)q, *kb = (const bf16*)k_pages, *vb = (const bf16*)v_pages;
-  if (hd == 128) return decode_launch<128>(qb, kb, vb, (bf16*)out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, sl, window, n_splits, stream);
-  if (hd == 64) return decode_launch<64>(qb, kb, vb, (bf16*)out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, sl, window, n_splits, stream);
-  if (hd == 32) return decode_launch<32>(qb, kb, vb, (bf16*)out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, sl, window, n_splits, stream);
+  if (hd == 128) return decode_launch<128>(qb, kb, vb, (bf16*)out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, sl, window, n_splits, counters, stream);
+  if (hd == 64) return decode_launch<64>(qb, kb, vb, (bf16*)out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, sl, window, n_splits, counters, stream);
+  if (hd == 32) return decode_launch<32>(qb, kb, vb, (bf16*)out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, sl, window, n_splits, counters, stream);
   return SX_ERR_SIZE;
+}
+
+// the splits are merged by a second kernel
+extern "C" int sx_attn_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o,
+                              float* part_ml, const int* seq_lens, const int* block_table, int maxp, int S, int nh,
+                              int nkv, int hd, float scale, int window, int n_splits, cudaStream_t stream) {
+  return attn_decode_any(q, k_pages, v_pages, out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, hd, scale,
+                         window, n_splits, nullptr, stream);
+}
+
+// the splits are merged inside the kernel by whichever block of a (sequence, kv head) finishes last;
+// counters int32 [S * nkv] must be zero before the first launch and is left zero by every launch
+extern "C" int sx_attn_decode_fused(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o,
+                                    float* part_ml, int* counters, const int* seq_lens, const int* block_table,
+                                    int maxp, int S, int nh, int nkv, int hd, float scale, int window, int n_splits,
+                                    cudaStream_t stream) {
+  return attn_decode_any(q, k_pages, v_pages, out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, hd, scale,
+                         window, n_splits, counters, stream);
 }
 
 // ---------------------------------------------------------------------------------------

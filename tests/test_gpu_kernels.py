@@ -456,10 +456,12 @@ def test_attention_decode_kernel(nh, nkv, hd, window):
     past, new = [0, 130, 1000, 63, 64, 255], [1] * 6
     q, kp, vp, bt, pos, sot, scale, ref = fast_attention_case(nh, nkv, hd, window, past, new, 3)
     lens = torch.tensor([p + 1 for p in past], dtype=torch.int32).cuda()
-    for n_splits in (1, 2, 5, 16):
-        out = attn_decode(q.view(6, nh * hd).cuda(), kp, vp, lens, bt, nh, nkv, hd, scale, window, n_splits)
-        err = (out.float().cpu().view(6, nh, hd) - ref).abs().max().item()
-        assert err < 2e-2, f"n_splits={n_splits}: {err}"
+    for n_splits in (1, 2, 5, 16, 37):
+        for fused in (True, False, True):          # fused twice: the counters must be left at zero
+            out = attn_decode(q.view(6, nh * hd).cuda(), kp, vp, lens, bt, nh, nkv, hd, scale, window, n_splits,
+                              fused_merge=fused)
+            err = (out.float().cpu().view(6, nh, hd) - ref).abs().max().item()
+            assert err < 2e-2, f"n_splits={n_splits} fused={fused}: {err}"
 
 
 @pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 128, None), (6, 2, 32, None), (5, 1, 64, 24), (8, 8, 64, None),
