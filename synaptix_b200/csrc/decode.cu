@@ -26,6 +26,7 @@
 #define SK_WARPS 8
 #define XS_ROWS 2          // rows of activations the norm prologue takes
 #define SK_THREADS (SK_WARPS * 32)
+#define SK_DEPTH 4          // steps (of 2 x 16 bytes) every thread keeps in flight; 4 measured best (more blocks per SM beat deeper rings)
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -82,16 +83,24 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(
   const int s_begin = ks * per, s_end = min(nsteps, s_begin + per);
   const bf16* wlo = W + (size_t)row_lo * K + t * 8;
   const bf16* whi = W + (size_t)row_hi * K + t * 8;
-  constexpr int U = 4;
-
-  // the first weights are asked for before anything else, so that HBM is busy during the prologue
-  uint4 pa[U], pb[U];
+  // Every thread keeps SK_DEPTH steps of its own weights in flight, copied asynchronously
+  // (cp.async, 16 bytes) into a ring in shared memory that only this thread reads back: no
+  // registers are held while the data travels, no barrier is needed, and all of a warp's first
+  // SK_DEPTH steps are asked for in ONE round trip to HBM instead of one round per batch of loads.
+  // The first steps are asked for before anything else, so that HBM is busy during the prologue.
+  uint4* ring = reinterpret_cast<uint4*>(smem_raw + (KS > 1 ? SK_WARPS * NT * 4 * 32 * sizeof(float) : 0) +
+                                         (XS ? (size_t)XS_ROWS * K * sizeof(bf16) : 0));      // [SK_DEPTH][2][SK_THREADS]
+  const uint32_t ring_base = (uint32_t)__cvta_generic_to_shared(ring) + threadIdx.x * 16;
+  auto ask = [&](int step, int slot) {
+    if (step < s_end && tile_ok) {
+      const uint32_t dst = ring_base + slot * (2 * SK_THREADS * 16);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(wlo + (size_t)step * 32) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + SK_THREADS * 16), "l"(whi + (size_t)step * 32) : "memory");
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");        // one group per step, empty or not
+  };
 #pragma unroll
-  for (int u = 0; u < U; ++u) {
-    const int sc = min(s_begin + u, nsteps - 1);
-    pa[u] = ld_stream16(wlo + (size_t)sc * 32);
-    pb[u] = ld_stream16(whi + (size_t)sc * 32);
-  }
+  for (int i = 0; i < SK_DEPTH; ++i) ask(s_begin + i, i);
 
   if (XS) {
     // RMSNorm prologue by the whole block, one row after the other, the row held in registers:
@@ -151,67 +160,25 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
   if (tile_ok) {
-    // the batch that was asked for up front
+    int slot = 0;
+    for (int sc = s_begin; sc < s_end; ++sc) {
+      asm volatile("cp.async.wait_group %0;\n" ::"n"(SK_DEPTH - 1) : "memory");   // step sc has landed
+      const uint4 va = ring[(slot * 2) * SK_THREADS + threadIdx.x];
+      const uint4 vb = ring[(slot * 2 + 1) * SK_THREADS + threadIdx.x];
+      ask(sc + SK_DEPTH, slot);                       // the slot is free again: next step into it
+      slot = slot + 1 == SK_DEPTH ? 0 : slot + 1;
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int sc = s_begin + u;
-      if (sc < s_end) {
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const int b = nt * 8 + g;
-          uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-          if (XS) { if (b < M) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + sc * 32 + t * 8); }
-          else if (b < M) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + sc * 32 + t * 8));
-          mma_bf16_16816(acc[nt], pa[u].x, pb[u].x, pa[u].y, pb[u].y, xv.x, xv.y);
-          mma_bf16_16816(acc[nt], pa[u].z, pb[u].z, pa[u].w, pb[u].w, xv.z, xv.w);
-        }
-      }
-    }
-    int s = s_begin + U;
-    for (; s + U <= s_end; s += U) {
-      uint4 va[U], vb[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        va[u] = ld_stream16(wlo + (size_t)(s + u) * 32);
-        vb[u] = ld_stream16(whi + (size_t)(s + u) * 32);
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const int b = nt * 8 + g;
-          uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-          if (XS) { if (b < M) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + (s + u) * 32 + t * 8); }
-          else if (b < M) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + (s + u) * 32 + t * 8));
-          mma_bf16_16816(acc[nt], va[u].x, vb[u].x, va[u].y, vb[u].y, xv.x, xv.y);
-          mma_bf16_16816(acc[nt], va[u].z, vb[u].z, va[u].w, vb[u].w, xv.z, xv.w);
-        }
-      }
-    }
-    if (s < s_end) {                                 // the tail, asked for together
-      uint4 va[U], vb[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int sc = min(s + u, nsteps - 1);
-        va[u] = ld_stream16(wlo + (size_t)sc * 32);
-        vb[u] = ld_stream16(whi + (size_t)sc * 32);
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (s + u < s_end) {
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            const int b = nt * 8 + g;
-            uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-            if (XS) { if (b < M) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + (s + u) * 32 + t * 8); }
-            else if (b < M) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + (s + u) * 32 + t * 8));
-            mma_bf16_16816(acc[nt], va[u].x, vb[u].x, va[u].y, vb[u].y, xv.x, xv.y);
-            mma_bf16_16816(acc[nt], va[u].z, vb[u].z, va[u].w, vb[u].w, xv.z, xv.w);
-          }
-        }
+      for (int nt = 0; nt < NT; ++nt) {
+        const int b = nt * 8 + g;
+        uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+        if (XS) { if (b < M) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + sc * 32 + t * 8); }
+        else if (b < M) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + sc * 32 + t * 8));
+        mma_bf16_16816(acc[nt], va.x, vb.x, va.y, vb.y, xv.x, xv.y);
+        mma_bf16_16816(acc[nt], va.z, vb.z, va.w, vb.w, xv.z, xv.w);
       }
     }
   }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 
   // add up the KS partial sums of a row tile in warp order
   if (KS > 1) {
@@ -267,7 +234,7 @@ static int skinny_launch(const bf16* x, const bf16* W, void* out, int M, int N, 
   const int tiles = (EPI == EPI_SILU_MUL) ? (N / 2 + 7) / 8 : (N + 15) / 16;
   const int grid = (tiles + RT - 1) / RT;
   size_t smem = (KS > 1 ? (size_t)SK_WARPS * NT * 4 * 32 * sizeof(float) : 0) +
-                (XS ? (size_t)XS_ROWS * K * sizeof(bf16) : 0);
+                (XS ? (size_t)XS_ROWS * K * sizeof(bf16) : 0) + (size_t)SK_DEPTH * 2 * SK_THREADS * 16;
   auto kern = skinny_gemm_kernel<NT, KS, EPI, XS>;
   if (smem > 48 * 1024) {
     if (smem > 200 * 1024) return SX_ERR_SIZE;
