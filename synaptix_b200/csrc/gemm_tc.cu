@@ -233,6 +233,177 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
   }
 }
 
+// =======================================================================================
+// The persistent form for many rows: one block per SM walks over the 128 x 256 tiles of C
+// (tile t -> row tile t % tiles_m, column tile t / tiles_m, so that blocks running at the same
+// time share W tiles through L2).  Tensor memory holds TWO accumulators (2 x 256 columns): while
+// the epilogue warps read tile i out of one, the MMA warp is already filling the other with tile
+// i + 1, and the TMA ring runs ahead across tiles.  Barriers: full/empty per stage, and
+// acc_full/acc_empty per accumulator.
+// =======================================================================================
+__device__ __forceinline__ void tc_mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+
+template <int EPI>
+__device__ __forceinline__ void tc_store_chunk(const uint32_t (&v)[32], const uint32_t (&u)[32], void* __restrict__ out,
+                                               int row, int col, int n_out) {
+  float f[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    f[i] = __uint_as_float(v[i]);
+    if (EPI == TC_EPI_SILU_MUL) f[i] = f[i] / (1.f + __expf(-f[i])) * __uint_as_float(u[i]);
+  }
+  const int ncol = min(32, n_out - col);
+  if (EPI == TC_EPI_F32) {
+    float* dst = reinterpret_cast<float*>(out) + (size_t)row * n_out + col;
+    if (ncol == 32 && (n_out % 4) == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) reinterpret_cast<float4*>(dst)[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) if (i < ncol) dst[i] = f[i];
+    }
+  } else {
+    bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)row * n_out + col;
+    if (ncol == 32 && (n_out % 8) == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 p;
+        __nv_bfloat162 t0 = __floats2bfloat162_rn(f[8 * i], f[8 * i + 1]), t1 = __floats2bfloat162_rn(f[8 * i + 2], f[8 * i + 3]);
+        __nv_bfloat162 t2 = __floats2bfloat162_rn(f[8 * i + 4], f[8 * i + 5]), t3 = __floats2bfloat162_rn(f[8 * i + 6], f[8 * i + 7]);
+        p.x = *reinterpret_cast<uint32_t*>(&t0); p.y = *reinterpret_cast<uint32_t*>(&t1);
+        p.z = *reinterpret_cast<uint32_t*>(&t2); p.w = *reinterpret_cast<uint32_t*>(&t3);
+        reinterpret_cast<uint4*>(dst)[i] = p;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) if (i < ncol) dst[i] = __float2bfloat16_rn(f[i]);
+    }
+  }
+}
+
+template <int EPI, int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                           const __grid_constant__ CUtensorMap map_w,
+                                                                           void* __restrict__ out, int M, int N, int K,
+                                                                           int* __restrict__ status) {
+  constexpr int STAGES = TcShape<BN>::STAGES, B_BYTES = TcShape<BN>::B_BYTES, STAGE_BYTES = TcShape<BN>::STAGE_BYTES;
+  extern __shared__ unsigned char tc_smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);   // full[S], empty[S], acc_full[2], acc_empty[2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + STAGES);
+  const uint32_t acc_full0 = tc_smem(bars + 2 * STAGES), acc_empty0 = tc_smem(bars + 2 * STAGES + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;
+  const int tile_n = (EPI == TC_EPI_SILU_MUL) ? BN / 2 : BN;
+  const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (n_out + tile_n - 1) / tile_n;
+  const int n_tiles = tiles_m * tiles_n;
+  const int nkb = (K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tc_mbar_init(full0 + 8 * s, 1);
+      tc_mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc_mbar_init(acc_full0 + 8 * b, 1);
+      tc_mbar_init(acc_empty0 + 8 * b, 4);          // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * tile_n;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          if (!tc_mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) { atomicExch(status, 1); ok = false; break; }
+          tc_mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+          const uint32_t a_dst = tc_smem(tiles + s * STAGE_BYTES), b_dst = a_dst + TC_A_BYTES;
+          tc_tma_load_2d(a_dst, &map_a, kb * TC_BK, m0, full0 + 8 * s);
+          tc_tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);
+          if (BN == 256)
+            tc_tma_load_2d(b_dst + B_BYTES / 2, &map_w, kb * TC_BK, (EPI == TC_EPI_SILU_MUL) ? N / 2 + n0 : n0 + BN / 2, full0 + 8 * s);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc_instr_desc(TC_BM, BN);
+      uint32_t it = 0, t = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
+        const uint32_t buf = t & 1;
+        if (!tc_mbar_wait(acc_empty0 + 8 * buf, ((t >> 1) & 1) ^ 1)) { atomicExch(status, 4); ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          if (!tc_mbar_wait(full0 + 8 * s, (it / STAGES) & 1)) { atomicExch(status, 2); ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const uint32_t a_addr = tc_smem(tiles + s * STAGE_BYTES), b_addr = a_addr + TC_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k)
+            tc_mma(d_tmem, tc_smem_desc(a_addr + k * 32), tc_smem_desc(b_addr + k * 32), idesc, (kb | k) != 0);
+          tc_commit(empty0 + 8 * s);
+        }
+        tc_commit(acc_full0 + 8 * buf);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    uint32_t t = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
+      const uint32_t buf = t & 1;
+      const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * tile_n;
+      const int row = m0 + quarter * 32 + lane;
+      if (!tc_mbar_wait(acc_full0 + 8 * buf, (t >> 1) & 1)) {
+        if (lane == 0) atomicExch(status, 3);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const uint32_t t_row = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < tile_n; c0 += 32) {
+        uint32_t v[32], u[32];
+        tc_ld32(t_row + c0, v);
+        if (EPI == TC_EPI_SILU_MUL) tc_ld32(t_row + BN / 2 + c0, u);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        if (c0 + 32 >= tile_n) {
+          // everything of this accumulator is in registers: hand it back before the last stores
+          asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+          __syncwarp();
+          if (lane == 0) tc_mbar_arrive(acc_empty0 + 8 * buf);
+        }
+        if (row < M && n0 + c0 < n_out) tc_store_chunk<EPI>(v, u, out, row, n0 + c0, n_out);
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------
@@ -293,6 +464,34 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, in
   return sx_launch_status();
 }
 
+static int tc_sm_count() {
+  static int n[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!n[dev]) {
+    if (cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n[dev] <= 0) n[dev] = 148;
+  }
+  return n[dev];
+}
+
+template <int EPI, int BN>
+static int tc_launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K,
+                                cudaStream_t stream) {
+  int* status = tc_status_word();
+  if (!status) return (int)cudaErrorMemoryAllocation;
+  const int tile_n = (EPI == TC_EPI_SILU_MUL) ? BN / 2 : BN;
+  const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;
+  const long long n_tiles = (long long)((n_out + tile_n - 1) / tile_n) * ((M + TC_BM - 1) / TC_BM);
+  const int sms = tc_sm_count();
+  const int grid = (int)(n_tiles < sms ? n_tiles : sms);
+  const size_t smem = 1024 + TcShape<BN>::STAGES * TcShape<BN>::STAGE_BYTES + (2 * TcShape<BN>::STAGES + 4) * sizeof(uint64_t) + 16;
+  auto kern = gemm_tc_persistent_kernel<EPI, BN>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  kern<<<grid, TC_THREADS, smem, stream>>>(ma, mw, out, M, N, K, status);
+  return sx_launch_status();
+}
+
 // sum of the split-K partial tiles ws[splits][M][N] in split order, then the epilogue
 template <int EPI>
 __global__ void tc_splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ out, int splits, int M, int N) {
@@ -331,9 +530,11 @@ extern "C" int sx_gemm_tc(const void* A, const void* W, void* out, int M, int N,
   if (rc) return rc;
   if (splits == 1) {
     switch (epi) {
-      case TC_EPI_BF16: return tc_launch<TC_EPI_BF16, 256>(ma, mw, out, M, N, K, 1, stream);
-      case TC_EPI_F32: return tc_launch<TC_EPI_F32, 256>(ma, mw, out, M, N, K, 1, stream);
-      case TC_EPI_SILU_MUL: return tc_launch<TC_EPI_SILU_MUL, 256>(ma, mw, out, M, N, K, 1, stream);
+      // (128-wide tiles were tried for shapes whose last wave is nearly empty: the MMA then waits on
+      //  shared-memory reads of A and the product got slower, 607 against 828 TFLOP/s)
+      case TC_EPI_BF16: return tc_launch_persistent<TC_EPI_BF16, 256>(ma, mw, out, M, N, K, stream);
+      case TC_EPI_F32: return tc_launch_persistent<TC_EPI_F32, 256>(ma, mw, out, M, N, K, stream);
+      case TC_EPI_SILU_MUL: return tc_launch_persistent<TC_EPI_SILU_MUL, 256>(ma, mw, out, M, N, K, stream);
       default: return SX_ERR_DTYPE;
     }
   }
