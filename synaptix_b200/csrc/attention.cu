@@ -22,10 +22,11 @@
 #include "common.cuh"
 
 #define AT_THREADS 128
-#define AT_STAGES 3
+#define AT_STAGES_DECODE 3      // pages in flight per block: decode streams the cache, three stages keep HBM busy
+#define AT_STAGES_PREFILL 2     // prompt steps reuse pages from L2; two stages leave room for three blocks per SM
 
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -50,11 +51,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-template <int HD> struct AtLayout {
+template <int HD, int STAGES = AT_STAGES_DECODE> struct AtLayout {
   static constexpr int ROW = HD * 2 + 16;              // bytes of a padded row: ldmatrix rows hit distinct banks
   static constexpr int TILE = 64 * ROW;                // one page of K (or V)
   static constexpr int STAGE = 2 * TILE;               // K then V
-  static constexpr int SMEM = AT_STAGES * STAGE;
+  static constexpr int SMEM = STAGES * STAGE;
 };
 
 // one page (64 keys) of K and V of (page, kvh) -> stage; rows >= valid_rows are zero-filled
@@ -81,7 +82,7 @@ __device__ __forceinline__ void load_page(unsigned char* stage, const bf16* __re
 //                  a negative position masks the whole row
 //   jbase  absolute index of the page's first key
 // ---------------------------------------------------------------------------------------
-template <int HD, int NKT>
+template <int HD, int NKT, bool MASKED>
 __device__ __forceinline__ void attend_tile(const uint32_t (&qf)[HD / 16][4], const unsigned char* kst,
                                             const unsigned char* vst, int key0, int jbase, int pos_lo, int pos_hi,
                                             int window, float scale_log2, float (&m)[2], float (&l)[2],
@@ -92,31 +93,41 @@ __device__ __forceinline__ void attend_tile(const uint32_t (&qf)[HD / 16][4], co
 #pragma unroll
   for (int i = 0; i < NKT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
 
-  // S = Q K^T : for each key tile, walk over head dim in steps of 32 (one ldmatrix.x4 = two k-steps)
+  // S = Q K^T.  One ldmatrix.x4 brings a key tile's fragments for two k-steps (32 of the head
+  // dim).  Key tiles are taken in groups (of 4 when there are that many) so that consecutive MMAs
+  // write different accumulators: a dependent pair is then a whole group of MMAs apart.
   const int lrow = lane & 7, lmat = lane >> 3;
+  constexpr int KG = NKT >= 4 ? 4 : NKT;
 #pragma unroll
-  for (int kt = 0; kt < NKT; ++kt) {
-    const uint32_t kaddr = smem_addr(kst + (key0 + kt * 8 + lrow) * L::ROW + lmat * 16);
+  for (int d = 0; d < HD / 32; ++d) {
 #pragma unroll
-    for (int d = 0; d < HD / 32; ++d) {
-      uint32_t b0, b1, b2, b3;
-      ldsm_x4(b0, b1, b2, b3, kaddr + d * 64);
-      mma16816(s[kt], qf[2 * d], b0, b1);
-      mma16816(s[kt], qf[2 * d + 1], b2, b3);
+    for (int k0 = 0; k0 < NKT; k0 += KG) {
+      uint32_t b[KG][4];
+#pragma unroll
+      for (int j = 0; j < KG; ++j)
+        ldsm_x4(b[j][0], b[j][1], b[j][2], b[j][3],
+                smem_addr(kst + (key0 + (k0 + j) * 8 + lrow) * L::ROW + lmat * 16) + d * 64);
+#pragma unroll
+      for (int j = 0; j < KG; ++j) mma16816(s[k0 + j], qf[2 * d], b[j][0], b[j][1]);
+#pragma unroll
+      for (int j = 0; j < KG; ++j) mma16816(s[k0 + j], qf[2 * d + 1], b[j][2], b[j][3]);
     }
   }
-  // mask and running maximum
+  // running maximum of the raw scores (the scale is positive, so it can be applied later inside
+  // the exponent: p = 2^(s * scale - m * scale), one FFMA and one EX2 per score).  A page that lies
+  // wholly inside every row's visible range (MASKED == false) needs no comparisons at all.
   float mx[2] = {m[0], m[1]};
 #pragma unroll
   for (int kt = 0; kt < NKT; ++kt) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int j = jbase + key0 + kt * 8 + 2 * t + (e & 1);
-      const int p = (e < 2) ? pos_lo : pos_hi;
-      const bool vis = j <= p && (window == 0 || j > p - window);
-      const float v = vis ? s[kt][e] * scale_log2 : -INFINITY;
-      s[kt][e] = v;
-      mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      if (MASKED) {
+        const int j = jbase + key0 + kt * 8 + 2 * t + (e & 1);
+        const int p = (e < 2) ? pos_lo : pos_hi;
+        const bool vis = j <= p && (window == 0 || j > p - window);
+        if (!vis) s[kt][e] = -INFINITY;
+      }
+      mx[e >> 1] = fmaxf(mx[e >> 1], s[kt][e]);
     }
   }
 #pragma unroll
@@ -124,15 +135,17 @@ __device__ __forceinline__ void attend_tile(const uint32_t (&qf)[HD / 16][4], co
     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
   }
-  float corr[2], sum[2] = {0.f, 0.f};
+  float corr[2], ms[2], sum[2] = {0.f, 0.f};
 #pragma unroll
-  for (int r = 0; r < 2; ++r) corr[r] = (mx[r] == -INFINITY) ? 1.f : exp2f(m[r] - mx[r]);
+  for (int r = 0; r < 2; ++r) {
+    corr[r] = (mx[r] == -INFINITY) ? 1.f : exp2f((m[r] - mx[r]) * scale_log2);
+    ms[r] = (mx[r] == -INFINITY) ? 0.f : mx[r] * scale_log2;      // a row with nothing visible yet: 2^(-inf - 0) = 0
+  }
 #pragma unroll
   for (int kt = 0; kt < NKT; ++kt) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const float mm = mx[e >> 1];
-      const float p = (mm == -INFINITY) ? 0.f : exp2f(s[kt][e] - mm);
+      const float p = exp2f(fmaf(s[kt][e], scale_log2, -ms[e >> 1]));
       s[kt][e] = p;
       sum[e >> 1] += p;
     }
@@ -210,24 +223,31 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
 
   const int npages = max(0, p1 - p0);
 #pragma unroll
-  for (int st = 0; st < AT_STAGES - 1; ++st) {
+  for (int st = 0; st < AT_STAGES_DECODE - 1; ++st) {
     if (st < npages) load_page<HD>(smem + st * L::STAGE, k_pages, v_pages, bt[p0 + st], kvh, nkv, min(64, len - (p0 + st) * 64));
     cp_async_commit();
   }
   for (int i = 0; i < npages; ++i) {
-    cp_async_wait<AT_STAGES - 2>();
+    cp_async_wait<AT_STAGES_DECODE - 2>();
     __syncthreads();
-    const int nx = i + AT_STAGES - 1;
+    const int nx = i + AT_STAGES_DECODE - 1;
     if (nx < npages)
-      load_page<HD>(smem + (nx % AT_STAGES) * L::STAGE, k_pages, v_pages, bt[p0 + nx], kvh, nkv, min(64, len - (p0 + nx) * 64));
+      load_page<HD>(smem + (nx % AT_STAGES_DECODE) * L::STAGE, k_pages, v_pages, bt[p0 + nx], kvh, nkv, min(64, len - (p0 + nx) * 64));
     cp_async_commit();
-    const unsigned char* st = smem + (i % AT_STAGES) * L::STAGE;
+    const unsigned char* st = smem + (i % AT_STAGES_DECODE) * L::STAGE;
     // this warp's 16 keys of the page; all fragment rows sit at the same position
-    attend_tile<HD, 2>(qf, st, st + L::TILE, warp * 16, (p0 + i) * 64, pos, pos, window, scale_log2, m, l, o);
+    const int jb = (p0 + i) * 64;
+    if (jb + 63 > pos || (window > 0 && jb <= pos - window))
+      attend_tile<HD, 2, true>(qf, st, st + L::TILE, warp * 16, jb, pos, pos, window, scale_log2, m, l, o);
+    else      // the whole page is visible: no comparisons
+      attend_tile<HD, 2, false>(qf, st, st + L::TILE, warp * 16, jb, pos, pos, window, scale_log2, m, l, o);
   }
   cp_async_wait<0>();
   __syncthreads();
 
+  // the running maxima are of raw scores; the merges below work in the scaled (log2) domain
+  m[0] *= scale_log2;
+  m[1] *= scale_log2;
   // rows' sums over the 4 lanes that share a row
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -375,14 +395,15 @@ __global__ void __launch_bounds__(HD) attn_merge_kernel(const float* __restrict_
 // prefill: grid (n_tiles, nh); tile i covers query rows tile_q0[i] .. +63 of sequence tile_seq[i]
 // =======================================================================================
 template <int HD>
-__global__ void __launch_bounds__(AT_THREADS) attn_prefill_kernel(
+__global__ void __launch_bounds__(AT_THREADS, 3) attn_prefill_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
     bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_q0,
     const int* __restrict__ cu_seqlens, const int* __restrict__ seq_past, const int* __restrict__ seq_lens,
     const int* __restrict__ block_table, int maxp, int nh, int nkv, float scale_log2, int window) {
-  using L = AtLayout<HD>;
+  using L = AtLayout<HD, AT_STAGES_PREFILL>;
   extern __shared__ __align__(16) unsigned char smem[];
-  const int tile = blockIdx.x, h = blockIdx.y;
+  // tiles late in a sequence see more keys: they are started first, so that the short ones fill the tail
+  const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
   const int seq = tile_seq[tile], q0 = tile_q0[tile];
   const int kvh = h / (nh / nkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -421,23 +442,30 @@ __global__ void __launch_bounds__(AT_THREADS) attn_prefill_kernel(
   // this warp needs pages up to its own last row only
   const int warp_last = past + q0 + min(rows - 1, warp * 16 + 15);
   const bool warp_on = warp * 16 < rows;
+  const int warp_first = past + q0 + warp * 16;
 
 #pragma unroll
-  for (int st = 0; st < AT_STAGES - 1; ++st) {
+  for (int st = 0; st < AT_STAGES_PREFILL - 1; ++st) {
     if (st < npages) load_page<HD>(smem + st * L::STAGE, k_pages, v_pages, bt[p0 + st], kvh, nkv, min(64, len - (p0 + st) * 64));
     cp_async_commit();
   }
   for (int i = 0; i < npages; ++i) {
-    cp_async_wait<AT_STAGES - 2>();
+    cp_async_wait<AT_STAGES_PREFILL - 2>();
     __syncthreads();
-    const int nx = i + AT_STAGES - 1;
+    const int nx = i + AT_STAGES_PREFILL - 1;
     if (nx < npages)
-      load_page<HD>(smem + (nx % AT_STAGES) * L::STAGE, k_pages, v_pages, bt[p0 + nx], kvh, nkv, min(64, len - (p0 + nx) * 64));
+      load_page<HD>(smem + (nx % AT_STAGES_PREFILL) * L::STAGE, k_pages, v_pages, bt[p0 + nx], kvh, nkv, min(64, len - (p0 + nx) * 64));
     cp_async_commit();
-    const unsigned char* st = smem + (i % AT_STAGES) * L::STAGE;
+    const unsigned char* st = smem + (i % AT_STAGES_PREFILL) * L::STAGE;
     const int jbase = (p0 + i) * 64;
-    if (warp_on && jbase <= warp_last)
-      attend_tile<HD, 8>(qf, st, st + L::TILE, 0, jbase, pos_lo, pos_hi, window, scale_log2, m, l, o);
+    if (warp_on && jbase <= warp_last) {
+      // visible to every row of this warp without a comparison: ends before the warp's first row's
+      // position and starts after the window's lower edge of its last row
+      if (jbase + 63 > warp_first || (window > 0 && jbase <= warp_last - window))
+        attend_tile<HD, 8, true>(qf, st, st + L::TILE, 0, jbase, pos_lo, pos_hi, window, scale_log2, m, l, o);
+      else
+        attend_tile<HD, 8, false>(qf, st, st + L::TILE, 0, jbase, pos_lo, pos_hi, window, scale_log2, m, l, o);
+    }
   }
   cp_async_wait<0>();
 
@@ -572,7 +600,7 @@ template <int HD>
 static int prefill_launch(const bf16* q, const bf16* k, const bf16* v, bf16* out, const int* tile_seq, const int* tile_q0,
                           int n_tiles, const int* cu, const int* past, const int* lens, const int* bt, int maxp, int nh,
                           int nkv, float scale_log2, int window, cudaStream_t stream) {
-  using L = AtLayout<HD>;
+  using L = AtLayout<HD, AT_STAGES_PREFILL>;
   auto kern = attn_prefill_kernel<HD>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM);
   if (e != cudaSuccess) return (int)e;
