@@ -279,7 +279,9 @@ extern "C" int sx_gemm_generic(const void* A, int a_dt, const void* W, int w_dt,
 // once per token and reused for every q and k head.
 #define QP_WARPS 8
 #define QP_MAXP 8            // pairs per lane: head sizes up to 512
-template <typename T>
+// PP: rotation pairs a lane owns (rotary_dim / 2 <= 32 * PP); angles, sines, cosines and the norm
+// gains of its pairs stay in registers for all heads of the token
+template <typename T, int PP>
 __global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_kernel(
     const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
     const float* __restrict__ wq, const float* __restrict__ wk, const float* __restrict__ inv_freq,
@@ -291,17 +293,23 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_kernel(
   const T* src_tok = qkv + (size_t)t * row;
   const int half = inv_freq ? rotary_dim / 2 : 0;
 
-  float cs[QP_MAXP], sn[QP_MAXP];
+  float cs[PP], sn[PP], gq1[PP], gq2[PP], gk1[PP], gk2[PP];
 #pragma unroll
-  for (int k = 0; k < QP_MAXP; ++k) {
+  for (int k = 0; k < PP; ++k) {
     const int p = lane + 32 * k;
     cs[k] = 1.f; sn[k] = 0.f;
-    if (p < half) sincosf((float)pos * inv_freq[p], &sn[k], &cs[k]);
+    gq1[k] = gq2[k] = gk1[k] = gk2[k] = 1.f;
+    if (p < half) {
+      sincosf((float)pos * inv_freq[p], &sn[k], &cs[k]);
+      if (wq) { gq1[k] = wq[p]; gq2[k] = wq[p + half]; }
+      if (wk) { gk1[k] = wk[p]; gk2[k] = wk[p + half]; }
+    }
   }
   // where this token's keys and values go
   const int s = seq_of_token[t];
   const int page = block_table[(size_t)s * maxp + (pos >> 6)];
   const bool page_ok = page >= 0 && page < n_pages;     // the host guarantees a page; never write outside
+  const bool vec_copy = (hd % 8 == 0) && sizeof(T) == 2;
 
   for (int head = blockIdx.y * QP_WARPS + warp; head < nh + 2 * nkv; head += gridDim.y * QP_WARPS) {
     const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
@@ -316,14 +324,18 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_kernel(
       dst = base + (((size_t)page * nkv + kvh) * SX_PAGE + (pos & 63)) * hd;
     }
     if (!is_q && !is_k) {                                // v: copy
-      for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+      if (vec_copy) {
+        for (int i = lane; i < hd / 8; i += 32) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+      } else {
+        for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+      }
       continue;
     }
     const float* w = is_q ? wq : wk;
-    float x1[QP_MAXP], x2[QP_MAXP];
+    float x1[PP], x2[PP];
     float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < QP_MAXP; ++k) {
+    for (int k = 0; k < PP; ++k) {
       const int p = lane + 32 * k;
       x1[k] = x2[k] = 0.f;
       if (p < half) {
@@ -339,11 +351,11 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_kernel(
     float inv = 1.f;
     if (w) inv = rsqrtf(warp_sum(ss) / (float)hd + eps);
 #pragma unroll
-    for (int k = 0; k < QP_MAXP; ++k) {
+    for (int k = 0; k < PP; ++k) {
       const int p = lane + 32 * k;
       if (p < half) {
-        const float a = w ? x1[k] * inv * w[p] : x1[k];
-        const float b = w ? x2[k] * inv * w[p + half] : x2[k];
+        const float a = x1[k] * inv * (is_q ? gq1[k] : gk1[k]);
+        const float b = x2[k] * inv * (is_q ? gq2[k] : gk2[k]);
         dst[p] = from_f32<T>(a * cs[k] - b * sn[k]);
         dst[p + half] = from_f32<T>(a * sn[k] + b * cs[k]);
       }
@@ -353,6 +365,127 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_kernel(
       dst[i] = from_f32<T>(w ? v * inv * w[i] : v);
     }
   }
+}
+
+// The common case (the whole head is rotated, head size a multiple of 4) with two adjacent pairs per
+// lane and iteration, so that every access is 4 bytes (bfloat16) or 8 bytes (float) wide:
+// a lane owns pairs p = 64 k + 2 lane + {0, 1}.
+template <typename T> struct qp_vec2;
+template <> struct qp_vec2<bf16> {
+  static __device__ __forceinline__ float2 load(const bf16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+  static __device__ __forceinline__ void store(bf16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
+};
+template <> struct qp_vec2<float> {
+  static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ void store(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+};
+
+template <typename T, int PQ>
+__global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_vec_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
+    const float* __restrict__ wq, const float* __restrict__ wk, const float* __restrict__ inv_freq, float eps,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+    int maxp, int nh, int nkv, int hd, int n_pages) {
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos = positions[t];
+  const int row = (nh + 2 * nkv) * hd;
+  const T* src_tok = qkv + (size_t)t * row;
+  const int half = hd / 2;
+
+  float cs[PQ][2], sn[PQ][2], gq1[PQ][2], gq2[PQ][2], gk1[PQ][2], gk2[PQ][2];
+#pragma unroll
+  for (int k = 0; k < PQ; ++k)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int p = 64 * k + 2 * lane + j;
+      cs[k][j] = 1.f; sn[k][j] = 0.f;
+      gq1[k][j] = gq2[k][j] = gk1[k][j] = gk2[k][j] = 1.f;
+      if (p < half) {
+        if (inv_freq) sincosf((float)pos * inv_freq[p], &sn[k][j], &cs[k][j]);
+        if (wq) { gq1[k][j] = wq[p]; gq2[k][j] = wq[p + half]; }
+        if (wk) { gk1[k][j] = wk[p]; gk2[k][j] = wk[p + half]; }
+      }
+    }
+  const int s = seq_of_token[t];
+  const int page = block_table[(size_t)s * maxp + (pos >> 6)];
+  const bool page_ok = page >= 0 && page < n_pages;
+
+  for (int head = blockIdx.y * QP_WARPS + warp; head < nh + 2 * nkv; head += gridDim.y * QP_WARPS) {
+    const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
+    const int kvh = is_q ? 0 : (is_k ? head - nh : head - nh - nkv);
+    const T* src = src_tok + (size_t)head * hd;
+    T* dst;
+    if (is_q) {
+      dst = q_out + ((size_t)t * nh + head) * hd;
+    } else {
+      T* base = is_k ? k_pages : v_pages;
+      if (!base || !page_ok) continue;
+      dst = base + (((size_t)page * nkv + kvh) * SX_PAGE + (pos & 63)) * hd;
+    }
+    if (!is_q && !is_k) {                                // v: copy, 4 elements a lane and round
+      for (int i = lane * 4; i < hd; i += 128) {
+        const float2 a = qp_vec2<T>::load(src + i), b = qp_vec2<T>::load(src + i + 2);
+        qp_vec2<T>::store(dst + i, a.x, a.y);
+        qp_vec2<T>::store(dst + i + 2, b.x, b.y);
+      }
+      continue;
+    }
+    const bool normed = (is_q ? wq : wk) != nullptr;
+    float2 x1[PQ], x2[PQ];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < PQ; ++k) {
+      const int p = 64 * k + 2 * lane;
+      x1[k] = x2[k] = make_float2(0.f, 0.f);
+      if (p < half) {
+        x1[k] = qp_vec2<T>::load(src + p);
+        x2[k] = qp_vec2<T>::load(src + p + half);
+        ss += x1[k].x * x1[k].x + x1[k].y * x1[k].y + x2[k].x * x2[k].x + x2[k].y * x2[k].y;
+      }
+    }
+    float inv = 1.f;
+    if (normed) inv = rsqrtf(warp_sum(ss) / (float)hd + eps);
+#pragma unroll
+    for (int k = 0; k < PQ; ++k) {
+      const int p = 64 * k + 2 * lane;
+      if (p < half) {
+        const float a0 = x1[k].x * inv * (is_q ? gq1[k][0] : gk1[k][0]), a1 = x1[k].y * inv * (is_q ? gq1[k][1] : gk1[k][1]);
+        const float b0 = x2[k].x * inv * (is_q ? gq2[k][0] : gk2[k][0]), b1 = x2[k].y * inv * (is_q ? gq2[k][1] : gk2[k][1]);
+        qp_vec2<T>::store(dst + p, a0 * cs[k][0] - b0 * sn[k][0], a1 * cs[k][1] - b1 * sn[k][1]);
+        qp_vec2<T>::store(dst + p + half, a0 * sn[k][0] + b0 * cs[k][0], a1 * sn[k][1] + b1 * cs[k][1]);
+      }
+    }
+  }
+}
+
+template <typename T>
+static int qkv_prepare_launch(dim3 grid, cudaStream_t stream, const void* qkv, void* q_out, void* k_pages, void* v_pages,
+                              const float* wq, const float* wk, const float* inv_freq, int rotary_dim, float eps,
+                              const int* positions, const int* seq_of_token, const int* block_table, int maxp, int nh,
+                              int nkv, int hd, int n_pages) {
+  const int pairs = inv_freq ? rotary_dim / 2 : 0;
+  const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 7) == 0;
+  if (hd % 4 == 0 && hd <= 512 && aligned && (!inv_freq || rotary_dim == hd)) {
+#define QP_VGO(PQ)                                                                                                     \
+  qkv_prepare_vec_kernel<T, PQ><<<grid, QP_WARPS * 32, 0, stream>>>((const T*)qkv, (T*)q_out, (T*)k_pages, (T*)v_pages, \
+                                                                    wq, wk, inv_freq, eps, positions, seq_of_token,    \
+                                                                    block_table, maxp, nh, nkv, hd, n_pages)
+    if (hd <= 128) QP_VGO(1);
+    else if (hd <= 256) QP_VGO(2);
+    else QP_VGO(4);
+#undef QP_VGO
+    return sx_launch_status();
+  }
+#define QP_GO(PP)                                                                                                   \
+  qkv_prepare_kernel<T, PP><<<grid, QP_WARPS * 32, 0, stream>>>((const T*)qkv, (T*)q_out, (T*)k_pages, (T*)v_pages, wq, \
+                                                                wk, inv_freq, rotary_dim, eps, positions, seq_of_token, \
+                                                                block_table, maxp, nh, nkv, hd, n_pages)
+  if (pairs <= 32) QP_GO(1);
+  else if (pairs <= 64) QP_GO(2);
+  else if (pairs <= 128) QP_GO(4);
+  else QP_GO(8);
+#undef QP_GO
+  return sx_launch_status();
 }
 
 extern "C" int sx_qkv_prepare(const void* qkv, void* q_out, void* k_pages, void* v_pages,
@@ -366,16 +499,12 @@ extern "C" int sx_qkv_prepare(const void* qkv, void* q_out, void* k_pages, void*
   const int heads = nh + 2 * nkv;
   dim3 grid(n_tokens, n_tokens <= 64 ? (heads + QP_WARPS - 1) / QP_WARPS : 1);
   if (dt == SX_F32)
-    qkv_prepare_kernel<float><<<grid, QP_WARPS * 32, 0, stream>>>(
-        (const float*)qkv, (float*)q_out, (float*)k_pages, (float*)v_pages, wq, wk, inv_freq, rotary_dim, eps,
-        positions, seq_of_token, block_table, maxp, nh, nkv, hd, n_pages);
-  else if (dt == SX_BF16)
-    qkv_prepare_kernel<bf16><<<grid, QP_WARPS * 32, 0, stream>>>(
-        (const bf16*)qkv, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, wq, wk, inv_freq, rotary_dim, eps,
-        positions, seq_of_token, block_table, maxp, nh, nkv, hd, n_pages);
-  else
-    return SX_ERR_DTYPE;
-  return sx_launch_status();
+    return qkv_prepare_launch<float>(grid, stream, qkv, q_out, k_pages, v_pages, wq, wk, inv_freq, rotary_dim, eps, positions,
+                                     seq_of_token, block_table, maxp, nh, nkv, hd, n_pages);
+  if (dt == SX_BF16)
+    return qkv_prepare_launch<bf16>(grid, stream, qkv, q_out, k_pages, v_pages, wq, wk, inv_freq, rotary_dim, eps, positions,
+                                    seq_of_token, block_table, maxp, nh, nkv, hd, n_pages);
+  return SX_ERR_DTYPE;
 }
 
 // ---------------------------------------------------------------------------------------
