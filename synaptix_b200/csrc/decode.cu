@@ -49,15 +49,17 @@ enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2 };
 // NT: activation rows in tiles of 8 (M <= 8 NT);  KS: warps that split K;  RT = SK_WARPS / KS row tiles per block
 // XS: activations are read from shared memory (filled by the norm prologue) instead of global memory
 template <int NT, int KS, int EPI, bool XS>
-__global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(
+__global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_gemm_kernel(
     const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int M, int N, int K,
     // norm prologue (XS only): x = rmsnorm(h_in + delta) * gain; block 0 writes h_in + delta to h_out
     const float* __restrict__ h_in, const bf16* __restrict__ delta, float* __restrict__ h_out,
     const float* __restrict__ gain, float eps) {
-  constexpr int RT = SK_WARPS / KS;
+  constexpr int WARPS = KS > SK_WARPS ? KS : SK_WARPS;      // 16 warps split K for matrices with few rows
+  constexpr int THREADS = WARPS * 32;
+  constexpr int RT = WARPS / KS;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* red = reinterpret_cast<float*>(smem_raw);                        // [SK_WARPS][NT][4][32]
-  bf16* xs = reinterpret_cast<bf16*>(smem_raw + (KS > 1 ? SK_WARPS * NT * 4 * 32 * sizeof(float) : 0));  // [NT*8][K]
+  float* red = reinterpret_cast<float*>(smem_raw);                        // [WARPS][NT][4][32]
+  bf16* xs = reinterpret_cast<bf16*>(smem_raw + (KS > 1 ? WARPS * NT * 4 * 32 * sizeof(float) : 0));  // [NT*8][K]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -88,14 +90,14 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(
   // registers are held while the data travels, no barrier is needed, and all of a warp's first
   // SK_DEPTH steps are asked for in ONE round trip to HBM instead of one round per batch of loads.
   // The first steps are asked for before anything else, so that HBM is busy during the prologue.
-  uint4* ring = reinterpret_cast<uint4*>(smem_raw + (KS > 1 ? SK_WARPS * NT * 4 * 32 * sizeof(float) : 0) +
-                                         (XS ? (size_t)XS_ROWS * K * sizeof(bf16) : 0));      // [SK_DEPTH][2][SK_THREADS]
+  uint4* ring = reinterpret_cast<uint4*>(smem_raw + (KS > 1 ? WARPS * NT * 4 * 32 * sizeof(float) : 0) +
+                                         (XS ? (size_t)XS_ROWS * K * sizeof(bf16) : 0));      // [SK_DEPTH][2][THREADS]
   const uint32_t ring_base = (uint32_t)__cvta_generic_to_shared(ring) + threadIdx.x * 16;
   auto ask = [&](int step, int slot) {
     if (step < s_end && tile_ok) {
-      const uint32_t dst = ring_base + slot * (2 * SK_THREADS * 16);
+      const uint32_t dst = ring_base + slot * (2 * THREADS * 16);
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(wlo + (size_t)step * 32) : "memory");
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + SK_THREADS * 16), "l"(whi + (size_t)step * 32) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + THREADS * 16), "l"(whi + (size_t)step * 32) : "memory");
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");        // one group per step, empty or not
   };
@@ -105,7 +107,7 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(
   if (XS) {
     // RMSNorm prologue by the whole block, one row after the other, the row held in registers:
     // one round of loads, one reduction, 32-bit throughout.  K <= 4096, M <= XS_ROWS.
-    __shared__ float xs_red[SK_WARPS];
+    __shared__ float xs_red[WARPS];
     const int n4 = K >> 2;
     for (int b = 0; b < M; ++b) {
       const float4* hr = reinterpret_cast<const float4*>(h_in + (size_t)b * K);
@@ -114,7 +116,7 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(
       float ss = 0.f;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const int i = threadIdx.x + k * SK_THREADS;
+        const int i = threadIdx.x + k * THREADS;
         v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (i < n4) {
           v[k] = hr[i];
@@ -133,12 +135,12 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(
       __syncthreads();
       float tot = 0.f;
 #pragma unroll
-      for (int w = 0; w < SK_WARPS; ++w) tot += xs_red[w];
+      for (int w = 0; w < WARPS; ++w) tot += xs_red[w];
       const float inv = rsqrtf(tot / (float)K + eps);
       bf16* xr = xs + (size_t)b * K;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const int i = threadIdx.x + k * SK_THREADS;
+        const int i = threadIdx.x + k * THREADS;
         if (i < n4) {
           const float4 gn = reinterpret_cast<const float4*>(gain)[i];
           if (blockIdx.x == 0 && h_out) reinterpret_cast<float4*>(h_out + (size_t)b * K)[i] = v[k];
@@ -163,8 +165,8 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(
     int slot = 0;
     for (int sc = s_begin; sc < s_end; ++sc) {
       asm volatile("cp.async.wait_group %0;\n" ::"n"(SK_DEPTH - 1) : "memory");   // step sc has landed
-      const uint4 va = ring[(slot * 2) * SK_THREADS + threadIdx.x];
-      const uint4 vb = ring[(slot * 2 + 1) * SK_THREADS + threadIdx.x];
+      const uint4 va = ring[(slot * 2) * THREADS + threadIdx.x];
+      const uint4 vb = ring[(slot * 2 + 1) * THREADS + threadIdx.x];
       ask(sc + SK_DEPTH, slot);                       // the slot is free again: next step into it
       slot = slot + 1 == SK_DEPTH ? 0 : slot + 1;
 #pragma unroll
@@ -230,18 +232,19 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_gemm_kernel(
 template <int NT, int KS, int EPI, bool XS>
 static int skinny_launch(const bf16* x, const bf16* W, void* out, int M, int N, int K, const float* h_in,
                          const bf16* delta, float* h_out, const float* gain, float eps, cudaStream_t stream) {
-  constexpr int RT = SK_WARPS / KS;
+  constexpr int WARPS = KS > SK_WARPS ? KS : SK_WARPS, THREADS = WARPS * 32;
+  constexpr int RT = WARPS / KS;
   const int tiles = (EPI == EPI_SILU_MUL) ? (N / 2 + 7) / 8 : (N + 15) / 16;
   const int grid = (tiles + RT - 1) / RT;
-  size_t smem = (KS > 1 ? (size_t)SK_WARPS * NT * 4 * 32 * sizeof(float) : 0) +
-                (XS ? (size_t)XS_ROWS * K * sizeof(bf16) : 0) + (size_t)SK_DEPTH * 2 * SK_THREADS * 16;
+  size_t smem = (KS > 1 ? (size_t)WARPS * NT * 4 * 32 * sizeof(float) : 0) +
+                (XS ? (size_t)XS_ROWS * K * sizeof(bf16) : 0) + (size_t)SK_DEPTH * 2 * THREADS * 16;
   auto kern = skinny_gemm_kernel<NT, KS, EPI, XS>;
   if (smem > 48 * 1024) {
     if (smem > 200 * 1024) return SX_ERR_SIZE;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  kern<<<grid, SK_THREADS, smem, stream>>>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps);
+  kern<<<grid, THREADS, smem, stream>>>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps);
   return sx_launch_status();
 }
 
@@ -249,6 +252,7 @@ template <int NT, int EPI, bool XS>
 static int skinny_pick_ks(int ks, const bf16* x, const bf16* W, void* out, int M, int N, int K, const float* h_in,
                           const bf16* delta, float* h_out, const float* gain, float eps, cudaStream_t stream) {
   switch (ks) {
+    case 16: return skinny_launch<NT, 16, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
     case 8: return skinny_launch<NT, 8, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
     case 4: return skinny_launch<NT, 4, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
     case 2: return skinny_launch<NT, 2, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
@@ -269,7 +273,7 @@ static int skinny_pick_nt(int ks, const bf16* x, const bf16* W, void* out, int M
 
 // x [M, K] bf16 (or, with h_in, computed as rmsnorm(h_in + delta) * gain), W [N, K] bf16.
 // epi 0: out bf16 [M, N];  1: out f32 [M, N];  2: W is [gate; up] stacked, out bf16 [M, N/2] = silu(gate) * up.
-// ks: warps that split K (1, 2, 4, 8).  Requires K % 32 == 0, 16-byte aligned x and W, M <= 64
+// ks: warps that split K (1, 2, 4, 8, or 16 with blocks of 16 warps).  Requires K % 32 == 0, 16-byte aligned x and W, M <= 64
 // (M <= 16 with the norm prologue).
 extern "C" int sx_skinny_gemm(const void* x, const void* W, void* out, int M, int N, int K, int epi, int ks,
                               const float* h_in, const void* delta, float* h_out, const float* gain, float eps,

@@ -41,9 +41,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
             and (M <= SKINNY_MAX_ROWS or not tc_supported(M, N, K, x.dtype, w.dtype))):
         if epilogue == "silu_mul":
             if out_dtype == torch.bfloat16:
-                return skinny_gemm(x, w, epilogue="silu_mul", ks=8)
+                return skinny_gemm(x, w, epilogue="silu_mul")
         else:
-            return skinny_gemm(x, w, epilogue="f32" if out_dtype == torch.float32 else None, ks=8)
+            return skinny_gemm(x, w, epilogue="f32" if out_dtype == torch.float32 else None)
     if tc_supported(M, N, K, x.dtype, w.dtype) and out_dtype in (torch.bfloat16, torch.float32):
         if epilogue == "silu_mul":
             if out_dtype == torch.bfloat16:
@@ -78,7 +78,7 @@ def linear_normed(pn, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
         epi = "f32" if out_dtype == torch.float32 else None
     else:
         return None
-    return skinny_gemm(None, w, epilogue=epi, ks=8, norm_h=pn.h, norm_delta=pn.delta, norm_h_out=pn.h_out(),
+    return skinny_gemm(None, w, epilogue=epi, norm_h=pn.h, norm_delta=pn.delta, norm_h_out=pn.h_out(),
                        norm_gain=pn.gain, norm_eps=pn.eps)
 
 

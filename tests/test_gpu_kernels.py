@@ -324,7 +324,7 @@ def test_skinny_gemm(M, N, K):
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
     ref = x.double() @ w.double().T
-    for ks in (1, 2, 4, 8):
+    for ks in (1, 2, 4, 8, 16):
         out = skinny_gemm(x.cuda(), w.cuda(), epilogue="f32", ks=ks)
         assert out.shape == (M, N)
         assert torch.allclose(out.cpu().double(), ref, atol=2e-5 * math.sqrt(K), rtol=1e-5), f"ks={ks}"
