@@ -65,3 +65,15 @@ def make_folder(name: str, out_dir: str) -> str:
 def random_tokens(vocab: int, n: int, seed: int):
     g = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+# the benchmark model's layer sizes (Qwen3-4B: width 2560, 32 heads over 8 kv heads of size 128,
+# feed-forward 9728) with 2 layers and a shorter, odd vocabulary: the kernels run at the sizes and
+# through the code paths of the real model, and the plain implementation still finishes in seconds
+WIDE = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=2560, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+    intermediate_size=9728, vocab_size=32003, rope_theta=1000000.0, rms_norm_eps=1e-6,
+    max_position_embeddings=40960, tie_word_embeddings=True, hidden_act="silu", attention_bias=False,
+    use_sliding_window=False, sliding_window=None)
+WIDE_INIT = dict(seed=11, std_matrix=0.02, std_embedding=0.02, std_gain=0.05)
+CONFIGS["WIDE"] = (WIDE, WIDE_INIT)
