@@ -127,6 +127,9 @@ def main():
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1/64 points, the prefill and the e2e run")
+    ap.add_argument("--phase", default="all", choices=["all", "prefill"],
+                    help="prefill: time only the 2,048-token prompt step (small cases for profilers)")
+    ap.add_argument("--no-graph", action="store_true", help="run decode steps eagerly instead of replaying CUDA graphs")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -160,8 +163,36 @@ def main():
     start_len = a.context - (K + W) - 1          # the timed steps end at the context length
     if start_len < 1:
         raise SystemExit("--context is too short for --steps + --warmup")
-    engine = Engine(model, max_tokens=max(batches) * (a.context + 64))
+    engine = Engine(model, max_tokens=max(batches) * (a.context + 64) if a.phase == "all" else 4096,
+                    use_graphs=not a.no_graph)
     g = torch.Generator().manual_seed(1)
+
+    def time_prefill():
+        """Median time of a 2,048-token prompt step of one sequence, a fresh slot each time."""
+        T = 2048
+        toks = torch.randint(0, cfg.vocab_size, (T,), generator=g).tolist()
+        times = []
+        for it in range(3 + 5):
+            s = engine.open()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            engine.step([Entry(s, toks, [T - 1])], keep=False)
+            e1.record()
+            torch.cuda.synchronize()
+            engine.close(s)
+            if it >= 3:
+                times.append(e0.elapsed_time(e1))
+        pms = sorted(times)[len(times) // 2]
+        fl = prefill_flops(cfgd, a.layers, T)
+        return {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
+                "frac": round(fl / (pms / 1e3) / 1e12 / pk["bf16_tflops"], 4), "of": pk["source"],
+                "tflops": round(fl / (pms / 1e3) / 1e12, 1)}
+
+    if a.phase == "prefill":
+        print(json.dumps({"metric": "prefill tok/s at 2,048 tokens (Qwen3-4B shape, bf16, random weights)", "impl": "ours",
+                          "layers": a.layers, "layers_of_config": FULL_LAYERS, "prefill": time_prefill()}))
+        return 0
 
     def fill(B):
         """Open B sequences and run their prompts (a few sequences a step)."""
@@ -222,32 +253,13 @@ def main():
     if not a.no_points:
         line["points"] = {f"decode_b{B}": round(r["tok_s"], 2) for B, r in results.items() if B != a.batch}
         line["points"][f"decode_b{a.batch}"] = round(main_r["tok_s"], 2)
-        # prefill of 2,048 tokens, one sequence, fresh slot each time
-        T = 2048
-        toks = torch.randint(0, cfg.vocab_size, (T,), generator=g).tolist()
-        times = []
-        for it in range(3 + 5):
-            s = engine.open()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            e0.record()
-            engine.step([Entry(s, toks, [T - 1])], keep=False)
-            e1.record()
-            torch.cuda.synchronize()
-            engine.close(s)
-            if it >= 3:
-                times.append(e0.elapsed_time(e1))
-        pms = sorted(times)[len(times) // 2]
-        fl = prefill_flops(cfgd, a.layers, T)
-        line["prefill"] = {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
-                           "frac": round(fl / (pms / 1e3) / 1e12 / pk["bf16_tflops"], 4), "of": pk["source"],
-                           "tflops": round(fl / (pms / 1e3) / 1e12, 1)}
+        line["prefill"] = time_prefill()
         # end to end through the Python entry point: host tokens in and out every step
         del engine
         torch.cuda.empty_cache()
         llm = LLM.__new__(LLM)
         llm.model = model
-        llm.engine = Engine(model, max_tokens=a.batch * (a.context + 64))
+        llm.engine = Engine(model, max_tokens=a.batch * (a.context + 64), use_graphs=not a.no_graph)
         llm.last_stats = None
         e2e_steps = K
         prompts = [torch.randint(0, cfg.vocab_size, (a.context - e2e_steps - 1,), generator=g).tolist()

@@ -91,6 +91,69 @@ extern "C" int sx_argmax_rows(const float* logits, int* out, int R, int V, cudaS
   return sx_launch_status();
 }
 
+// The same in two kernels, for wide vocabularies: one block per row scans 150 thousand logits
+// in a long serial loop per thread; here each row is cut into chunks scanned by blocks of their own
+// (partial maxima to scratch [R, chunks] values and indices), and a small kernel finishes.
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ pv,
+                                                             int* __restrict__ pi, int V, int chunk) {
+  __shared__ float red_v[33];
+  __shared__ int red_i[33];
+  const int r = blockIdx.y, c = blockIdx.x;
+  const int b = c * chunk, e = min(V, b + chunk);
+  const float* row = logits + (size_t)r * V;
+  float bv = -INFINITY;
+  int bi = -1;
+  for (int i = b + threadIdx.x; i < e; i += 256) {
+    float v = row[i];
+    if (v != v) v = -INFINITY;
+    argmax_combine(bv, bi, v, i);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    argmax_combine(bv, bi, ov, oi);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float v = red_v[0];
+    int i = red_i[0];
+    for (int w = 1; w < 8; ++w) argmax_combine(v, i, red_v[w], red_i[w]);
+    pv[(size_t)r * gridDim.x + c] = v;
+    pi[(size_t)r * gridDim.x + c] = i;
+  }
+}
+
+__global__ void __launch_bounds__(32) argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi,
+                                                          int* __restrict__ out, int chunks, int V) {
+  const int r = blockIdx.x;
+  float bv = -INFINITY;
+  int bi = -1;
+  for (int c = threadIdx.x; c < chunks; c += 32) argmax_combine(bv, bi, pv[(size_t)r * chunks + c], pi[(size_t)r * chunks + c]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    argmax_combine(bv, bi, ov, oi);
+  }
+  if (threadIdx.x == 0) out[r] = bi < 0 ? V - 1 : bi;
+}
+
+// scratch_v float [R * chunks], scratch_i int [R * chunks]; chunks <= 1024
+extern "C" int sx_argmax_rows_chunked(const float* logits, int* out, float* scratch_v, int* scratch_i, int R, int V,
+                                      int chunks, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (V <= 0 || chunks <= 0 || chunks > 1024 || R > 65535) return SX_ERR_SIZE;
+  const int chunk = (V + chunks - 1) / chunks;
+  argmax_partial_kernel<<<dim3(chunks, R), 256, 0, stream>>>(logits, scratch_v, scratch_i, V, chunk);
+  int rc = sx_launch_status();
+  if (rc) return rc;
+  argmax_final_kernel<<<R, 32, 0, stream>>>(scratch_v, scratch_i, out, chunks, V);
+  return sx_launch_status();
+}
+
 // ---------------------------------------------------------------------------------------
 // penalties over a window of each row's context (crates/synaptix-infer/src/sampling/
 // repetition.rs:7-77).  hist is [R, hist_stride]; row r's context is hist[r, 0..hist_len[r]);

@@ -16,10 +16,18 @@ def _rows(logits: torch.Tensor):
 
 
 def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """int32 ``[rows]``: index of each row's maximum (the last one among equals)."""
+    """int32 ``[rows]``: index of each row's maximum (the last one among equals).  Wide rows are
+    cut into chunks scanned by blocks of their own, with a small second kernel to finish."""
     R, V = _rows(logits)
     if out is None:
         out = torch.empty(R, dtype=torch.int32, device=logits.device)
+    if V >= 16384:
+        chunks = min(64, (V + 4095) // 4096)
+        sv = torch.empty(R * chunks, dtype=torch.float32, device=logits.device)
+        si = torch.empty(R * chunks, dtype=torch.int32, device=logits.device)
+        check(fn("sampling", "sx_argmax_rows_chunked")(ptr(logits), ptr(out), ptr(sv), ptr(si), c_int(R), c_int(V),
+                                                       c_int(chunks), stream()), "argmax_rows", launches=2)
+        return out
     check(fn("sampling", "sx_argmax_rows")(ptr(logits), ptr(out), c_int(R), c_int(V), stream()), "argmax_rows")
     return out
 

@@ -248,6 +248,18 @@ def test_argmax_last_of_equal_maxima():
     assert got == [P.greedy(r) for r in x]
 
 
+def test_argmax_wide_rows_in_chunks():
+    from synaptix_b200.ops import sampling as K
+    x = torch.randn(9, 151936)
+    x[0, 151935] = 9.0
+    x[1, 0] = 9.0
+    x[2, 70000] = x[2, 4096] = x[2, 4095] = 9.0          # equal maxima in different chunks: the last one wins
+    x[3, :] = 0.5
+    got = K.argmax_rows(x.cuda()).tolist()
+    assert got == [P.greedy(r) for r in x]
+    assert got[:4] == [151935, 0, 70000, 151935]
+
+
 def test_penalties_match_the_plain_processors():
     from synaptix_b200.ops import sampling as K
     V = 500
