@@ -191,6 +191,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
     float scale_log2, int window, int n_splits, int* __restrict__ counters) {
   using L = AtLayout<HD>;
   extern __shared__ __align__(16) unsigned char smem[];
+  pdl_wait();
+  pdl_trigger();
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   const int G = nh / nkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -359,6 +361,8 @@ __global__ void __launch_bounds__(HD) attn_merge_kernel(const float* __restrict_
   float* fac = sm;
   float* ls = sm + n_splits;
   __shared__ float s_L;
+  pdl_wait();
+  pdl_trigger();
   const size_t row = blockIdx.x;
   const int d = threadIdx.x;
   for (int i = d; i < n_splits; i += HD) {
@@ -501,12 +505,11 @@ static int decode_launch(const bf16* q, const bf16* k, const bf16* v, bf16* out,
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(n_splits, nkv, S);
-  kern<<<grid, AT_THREADS, smem, stream>>>(q, k, v, out, part_o, part_ml, seq_lens, bt, maxp, nh, nkv, scale_log2,
-                                          window, n_splits, counters);
-  int rc = sx_launch_status();
+  int rc = sx_launch(kern, grid, dim3(AT_THREADS), smem, stream, q, k, v, out, part_o, part_ml, seq_lens, bt, maxp, nh, nkv,
+                     scale_log2, window, n_splits, counters);
   if (rc || n_splits == 1 || counters) return rc;
-  attn_merge_kernel<HD><<<S * nh, HD, 2 * n_splits * sizeof(float), stream>>>(part_o, part_ml, out, n_splits);
-  return sx_launch_status();
+  return sx_launch(attn_merge_kernel<HD>, dim3(S * nh), dim3(HD), 2 * n_splits * sizeof(float), stream,
+                   (const float*)part_o, (const float*)part_ml, out, n_splits);
 }
 
 // q [S, nh, hd] (one token per sequence), out [S, nh*hd]; part_o f32 [S*nh*n_splits*hd] and

@@ -74,4 +74,42 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 
 static inline int sx_launch_status() { return (int)cudaGetLastError(); }
 
+// ---------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched through sx_launch may be scheduled while its
+// predecessor in the stream is still running.  It must call pdl_wait() before it reads anything
+// an earlier kernel wrote or writes anything an earlier kernel may still read; what it does
+// before that (asking for its weights) overlaps the predecessor's end.  pdl_trigger() lets the
+// NEXT kernel be scheduled; it is called only AFTER pdl_wait(), so that at most one kernel waits
+// behind the running one (a kernel that triggered before waiting would let the whole chain of
+// later kernels pile up on the SMs, spinning).  Both are no-ops for a kernel launched normally.
+// SYNAPTIX_PDL=0 in the environment turns the launch attribute off.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#include <stdlib.h>
+static inline bool sx_pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SYNAPTIX_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int sx_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = sx_pdl_enabled() ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 #define SX_PAGE 64

@@ -103,6 +103,8 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
   };
 #pragma unroll
   for (int i = 0; i < SK_DEPTH; ++i) ask(s_begin + i, i);
+  pdl_wait();          // the weights depend on no earlier kernel; everything below may
+  pdl_trigger();
 
   if (XS) {
     // RMSNorm prologue by the whole block, one row after the other, the row held in registers:
@@ -244,8 +246,7 @@ static int skinny_launch(const bf16* x, const bf16* W, void* out, int M, int N, 
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  kern<<<grid, THREADS, smem, stream>>>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps);
-  return sx_launch_status();
+  return sx_launch(kern, dim3(grid), dim3(THREADS), smem, stream, x, W, out, M, N, K, h_in, delta, h_out, gain, eps);
 }
 
 template <int NT, int EPI, bool XS>

@@ -22,6 +22,8 @@
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int H, int V) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < V;
@@ -34,12 +36,10 @@ extern "C" int sx_embed_gather(const void* table, int dt, const int* ids, float*
                                int n_tokens, int H, int V, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (dt == SX_F32)
-    embed_gather_kernel<float><<<n_tokens, 256, 0, stream>>>((const float*)table, ids, out, H, V);
-  else if (dt == SX_BF16)
-    embed_gather_kernel<bf16><<<n_tokens, 256, 0, stream>>>((const bf16*)table, ids, out, H, V);
-  else
-    return SX_ERR_DTYPE;
-  return sx_launch_status();
+    return sx_launch(embed_gather_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, (const float*)table, ids, out, H, V);
+  if (dt == SX_BF16)
+    return sx_launch(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream, (const bf16*)table, ids, out, H, V);
+  return SX_ERR_DTYPE;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -52,6 +52,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
                                    const float* __restrict__ w, float eps, T* __restrict__ y,
                                    const int* __restrict__ rows, int H, int write_h) {
   __shared__ float red[33];
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   const int t = rows ? rows[r] : r;
   float* hr = h + (size_t)t * H;
@@ -82,6 +84,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_reg_kernel(float* __restrict_
                                                               const float* __restrict__ w, float eps, T* __restrict__ y,
                                                               const int* __restrict__ rows, int H, int write_h) {
   __shared__ float red[33];
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   const int t = rows ? rows[r] : r;
   float4* hr = reinterpret_cast<float4*>(h + (size_t)t * H);
@@ -124,12 +128,10 @@ static int add_rmsnorm_launch(float* h, const void* delta, const float* w, float
                               int H, int write_h, cudaStream_t stream) {
   const bool aligned = (H % 4 == 0) && (((uintptr_t)h | (uintptr_t)w) % 16 == 0);
   if (aligned && H <= 256 * 4 * 4)
-    add_rmsnorm_reg_kernel<T, 4><<<R, 256, 0, stream>>>(h, (const T*)delta, w, eps, (T*)y, rows, H, write_h);
-  else if (aligned && H <= 256 * 4 * 8)
-    add_rmsnorm_reg_kernel<T, 8><<<R, 256, 0, stream>>>(h, (const T*)delta, w, eps, (T*)y, rows, H, write_h);
-  else
-    add_rmsnorm_kernel<T><<<R, 256, 0, stream>>>(h, (const T*)delta, w, eps, (T*)y, rows, H, write_h);
-  return sx_launch_status();
+    return sx_launch(add_rmsnorm_reg_kernel<T, 4>, dim3(R), dim3(256), 0, stream, h, (const T*)delta, w, eps, (T*)y, rows, H, write_h);
+  if (aligned && H <= 256 * 4 * 8)
+    return sx_launch(add_rmsnorm_reg_kernel<T, 8>, dim3(R), dim3(256), 0, stream, h, (const T*)delta, w, eps, (T*)y, rows, H, write_h);
+  return sx_launch(add_rmsnorm_kernel<T>, dim3(R), dim3(256), 0, stream, h, (const T*)delta, w, eps, (T*)y, rows, H, write_h);
 }
 
 extern "C" int sx_add_rmsnorm(float* h, const void* delta, const float* w, float eps, void* y,
@@ -287,6 +289,8 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_kernel(
     const float* __restrict__ wq, const float* __restrict__ wk, const float* __restrict__ inv_freq,
     int rotary_dim, float eps, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ block_table, int maxp, int nh, int nkv, int hd, int n_pages) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = positions[t];
   const int row = (nh + 2 * nkv) * hd;
@@ -386,6 +390,8 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_vec_kernel(
     const float* __restrict__ wq, const float* __restrict__ wk, const float* __restrict__ inv_freq, float eps,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
     int maxp, int nh, int nkv, int hd, int n_pages) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = positions[t];
   const int row = (nh + 2 * nkv) * hd;
@@ -467,25 +473,21 @@ static int qkv_prepare_launch(dim3 grid, cudaStream_t stream, const void* qkv, v
   const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 7) == 0;
   if (hd % 4 == 0 && hd <= 512 && aligned && (!inv_freq || rotary_dim == hd)) {
 #define QP_VGO(PQ)                                                                                                     \
-  qkv_prepare_vec_kernel<T, PQ><<<grid, QP_WARPS * 32, 0, stream>>>((const T*)qkv, (T*)q_out, (T*)k_pages, (T*)v_pages, \
-                                                                    wq, wk, inv_freq, eps, positions, seq_of_token,    \
-                                                                    block_table, maxp, nh, nkv, hd, n_pages)
+  return sx_launch(qkv_prepare_vec_kernel<T, PQ>, grid, dim3(QP_WARPS * 32), 0, stream, (const T*)qkv, (T*)q_out, (T*)k_pages, \
+                   (T*)v_pages, wq, wk, inv_freq, eps, positions, seq_of_token, block_table, maxp, nh, nkv, hd, n_pages)
     if (hd <= 128) QP_VGO(1);
     else if (hd <= 256) QP_VGO(2);
     else QP_VGO(4);
 #undef QP_VGO
-    return sx_launch_status();
   }
 #define QP_GO(PP)                                                                                                   \
-  qkv_prepare_kernel<T, PP><<<grid, QP_WARPS * 32, 0, stream>>>((const T*)qkv, (T*)q_out, (T*)k_pages, (T*)v_pages, wq, \
-                                                                wk, inv_freq, rotary_dim, eps, positions, seq_of_token, \
-                                                                block_table, maxp, nh, nkv, hd, n_pages)
+  return sx_launch(qkv_prepare_kernel<T, PP>, grid, dim3(QP_WARPS * 32), 0, stream, (const T*)qkv, (T*)q_out, (T*)k_pages, \
+                   (T*)v_pages, wq, wk, inv_freq, rotary_dim, eps, positions, seq_of_token, block_table, maxp, nh, nkv, hd, n_pages)
   if (pairs <= 32) QP_GO(1);
   else if (pairs <= 64) QP_GO(2);
   else if (pairs <= 128) QP_GO(4);
   else QP_GO(8);
 #undef QP_GO
-  return sx_launch_status();
 }
 
 extern "C" int sx_qkv_prepare(const void* qkv, void* q_out, void* k_pages, void* v_pages,
@@ -627,6 +629,8 @@ extern "C" int sx_silu_mul(const void* gu, void* out, int n_tokens, int I, int d
 __global__ void decode_advance_kernel(int* __restrict__ token_ids, const int* __restrict__ sampled,
                                       int* __restrict__ positions, int* __restrict__ seq_past,
                                       int* __restrict__ seq_lens, int S) {
+  pdl_wait();
+  pdl_trigger();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= S) return;
   token_ids[i] = sampled[i];
@@ -637,6 +641,6 @@ __global__ void decode_advance_kernel(int* __restrict__ token_ids, const int* __
 extern "C" int sx_decode_advance(int* token_ids, const int* sampled, int* positions, int* seq_past,
                                  int* seq_lens, int S, cudaStream_t stream) {
   if (S <= 0) return 0;
-  decode_advance_kernel<<<(S + 127) / 128, 128, 0, stream>>>(token_ids, sampled, positions, seq_past, seq_lens, S);
-  return sx_launch_status();
+  return sx_launch(decode_advance_kernel, dim3((S + 127) / 128), dim3(128), 0, stream, token_ids, sampled, positions,
+                   seq_past, seq_lens, S);
 }

@@ -98,6 +98,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __rest
                                                              int* __restrict__ pi, int V, int chunk) {
   __shared__ float red_v[33];
   __shared__ int red_i[33];
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.y, c = blockIdx.x;
   const int b = c * chunk, e = min(V, b + chunk);
   const float* row = logits + (size_t)r * V;
@@ -128,6 +130,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __rest
 
 __global__ void __launch_bounds__(32) argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi,
                                                           int* __restrict__ out, int chunks, int V) {
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   float bv = -INFINITY;
   int bi = -1;
@@ -147,11 +151,9 @@ extern "C" int sx_argmax_rows_chunked(const float* logits, int* out, float* scra
   if (R <= 0) return 0;
   if (V <= 0 || chunks <= 0 || chunks > 1024 || R > 65535) return SX_ERR_SIZE;
   const int chunk = (V + chunks - 1) / chunks;
-  argmax_partial_kernel<<<dim3(chunks, R), 256, 0, stream>>>(logits, scratch_v, scratch_i, V, chunk);
-  int rc = sx_launch_status();
+  int rc = sx_launch(argmax_partial_kernel, dim3(chunks, R), dim3(256), 0, stream, logits, scratch_v, scratch_i, V, chunk);
   if (rc) return rc;
-  argmax_final_kernel<<<R, 32, 0, stream>>>(scratch_v, scratch_i, out, chunks, V);
-  return sx_launch_status();
+  return sx_launch(argmax_final_kernel, dim3(R), dim3(32), 0, stream, (const float*)scratch_v, (const int*)scratch_i, out, chunks, V);
 }
 
 // ---------------------------------------------------------------------------------------
