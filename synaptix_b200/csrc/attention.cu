@@ -406,6 +406,8 @@ __global__ void __launch_bounds__(AT_THREADS, 3) attn_prefill_kernel(
     const int* __restrict__ block_table, int maxp, int nh, int nkv, float scale_log2, int window) {
   using L = AtLayout<HD, AT_STAGES_PREFILL>;
   extern __shared__ __align__(16) unsigned char smem[];
+  pdl_wait();
+  pdl_trigger();
   // tiles late in a sequence see more keys: they are started first, so that the short ones fill the tail
   const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
   const int seq = tile_seq[tile], q0 = tile_q0[tile];
@@ -608,9 +610,8 @@ static int prefill_launch(const bf16* q, const bf16* k, const bf16* v, bf16* out
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(n_tiles, nh);
-  kern<<<grid, AT_THREADS, L::SMEM, stream>>>(q, k, v, out, tile_seq, tile_q0, cu, past, lens, bt, maxp, nh, nkv,
-                                             scale_log2, window);
-  return sx_launch_status();
+  return sx_launch(kern, grid, dim3(AT_THREADS), L::SMEM, stream, q, k, v, out, tile_seq, tile_q0, cu, past, lens, bt, maxp, nh,
+                   nkv, scale_log2, window);
 }
 
 // q [T, nh, hd] packed tokens, out [T, nh*hd]; tile_seq/tile_q0 [n_tiles] list 64-row query tiles.

@@ -134,6 +134,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();          // barriers and tensor memory are set up; the operands may come from the kernel before
+  pdl_trigger();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -322,6 +324,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();          // barriers and tensor memory are set up; the operands may come from the kernel before
+  pdl_trigger();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -460,8 +464,7 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, in
   auto kern = gemm_tc_kernel<EPI, BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  kern<<<grid, TC_THREADS, smem, stream>>>(ma, mw, out, M, N, K, status);
-  return sx_launch_status();
+  return sx_launch(kern, grid, dim3(TC_THREADS), smem, stream, ma, mw, out, M, N, K, status);
 }
 
 static int tc_sm_count() {
@@ -488,13 +491,14 @@ static int tc_launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, vo
   auto kern = gemm_tc_persistent_kernel<EPI, BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  kern<<<grid, TC_THREADS, smem, stream>>>(ma, mw, out, M, N, K, status);
-  return sx_launch_status();
+  return sx_launch(kern, grid, dim3(TC_THREADS), smem, stream, ma, mw, out, M, N, K, status);
 }
 
 // sum of the split-K partial tiles ws[splits][M][N] in split order, then the epilogue
 template <int EPI>
 __global__ void tc_splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ out, int splits, int M, int N) {
+  pdl_wait();
+  pdl_trigger();
   const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (size_t)M * n_out) return;
@@ -548,12 +552,11 @@ extern "C" int sx_gemm_tc(const void* A, const void* W, void* out, int M, int N,
   const size_t n_elems = (size_t)M * (epi == TC_EPI_SILU_MUL ? N / 2 : N);
   const unsigned grid = (unsigned)((n_elems + 255) / 256);
   switch (epi) {
-    case TC_EPI_BF16: tc_splitk_reduce_kernel<TC_EPI_BF16><<<grid, 256, 0, stream>>>(workspace, out, splits, M, N); break;
-    case TC_EPI_F32: tc_splitk_reduce_kernel<TC_EPI_F32><<<grid, 256, 0, stream>>>(workspace, out, splits, M, N); break;
-    case TC_EPI_SILU_MUL: tc_splitk_reduce_kernel<TC_EPI_SILU_MUL><<<grid, 256, 0, stream>>>(workspace, out, splits, M, N); break;
+    case TC_EPI_BF16: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_BF16>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N);
+    case TC_EPI_F32: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_F32>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N);
+    case TC_EPI_SILU_MUL: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_SILU_MUL>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N);
     default: return SX_ERR_DTYPE;
   }
-  return sx_launch_status();
 }
 
 // 0, or which bounded wait ran out (1 producer, 2 MMA issuer, 3 epilogue)
