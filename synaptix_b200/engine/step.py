@@ -172,6 +172,7 @@ class Engine:
         self._staging = _Staging(rt.device)
         self.use_graphs = bool(use_graphs) and model.all_graph_safe()
         self._captured: Dict[Tuple[int, int], _CapturedStep] = {}
+        self._last_decode = None
         self.kernel_launches = 0         # kernels of this package launched (graph replays counted by content)
         ops.set_launch_counter(self)
 
@@ -193,6 +194,7 @@ class Engine:
         return self.cache.open()
 
     def close(self, slot: int) -> None:
+        self._last_decode = None
         self.cache.close(slot)
 
     def length(self, slot: int) -> int:
@@ -288,6 +290,10 @@ class Engine:
         With ``keep=False`` the result may be a buffer that the next step overwrites
         (the generation loop samples from it at once and needs no copy)."""
         entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
+        if self.use_graphs:
+            logits = self._step_again(entries)
+            if logits is not None:
+                return logits.clone() if keep else logits
         past, new = self._check(entries)
         single = all(n == 1 and tuple(e.want) == (0,) for n, e in zip(new, entries))
         if single and self.use_graphs:
@@ -296,15 +302,52 @@ class Engine:
             cap = self._captured.get((S, maxp))
             if cap is None:
                 cap = self._captured[(S, maxp)] = _CapturedStep(self, S, maxp)
-            self._staging.upload(self._fill(cap.layout, entries, past, new), into=cap.flat)
+            flat = self._fill(cap.layout, entries, past, new)
+            self._staging.upload(flat, into=cap.flat)
             logits = cap.run()[:len(entries)]
+            # remembered for the next step of the same sequences (see _step_again)
+            self._last_decode = (tuple(e.slot for e in entries), [p + 1 for p in past], cap, flat)
             if keep:
                 logits = logits.clone()
         else:
+            self._last_decode = None
             ctx = self.plan(entries, past, new)
             logits = self._forward(ctx)
         for e in entries:
             self.cache.slots.advance(e.slot, len(e.tokens))
+        return logits
+
+    def _step_again(self, entries: Sequence[Entry]) -> Optional[torch.Tensor]:
+        """The common case of decoding: the same sequences as in the last step, one more token
+        each, and nobody crosses into a new page.  Then the index arrays of the last step are
+        still right but for the tokens and the positions, which move on by one: no planning."""
+        last = self._last_decode
+        if last is None:
+            return None
+        key, lens, cap, flat = last
+        n = len(entries)
+        if n != len(key):
+            return None
+        vocab = self.model.embedding.vocab
+        slots = self.cache.slots
+        toks = []
+        for e, s, ln in zip(entries, key, lens):
+            if e.slot != s or len(e.tokens) != 1 or tuple(e.want) != (0,) or ln % PAGE_TOKENS == 0:
+                return None
+            t = e.tokens[0]
+            if not (0 <= t < vocab) or slots._len.get(s) != ln:
+                return None
+            toks.append(t)
+        v = cap.layout.views(flat)
+        v["token_ids"][:n] = toks
+        v["positions"][:n] += 1
+        v["seq_past"][:n] += 1
+        v["seq_lens"][:n] += 1
+        self._staging.upload(flat, into=cap.flat)
+        logits = cap.run()[:n]
+        for i, s in enumerate(key):
+            slots.advance(s, 1)
+            lens[i] += 1
         return logits
 
     # -- decoding without coming back to the host ------------------------------------

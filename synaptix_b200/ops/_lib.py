@@ -42,7 +42,16 @@ def ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+try:                                    # the raw handle without building a Stream object (an order of magnitude cheaper)
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+except AttributeError:                  # pragma: no cover - older torch
+    _raw_stream = None
+
+
 def stream() -> ctypes.c_void_p:
+    """The current CUDA stream of the current device (the capturing stream inside a graph capture)."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
