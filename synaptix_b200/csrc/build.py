@@ -41,6 +41,7 @@ LIBRARIES: Dict[str, tuple] = {
     "sampling": ("sampling.cu", []),
     "decode": ("decode.cu", []),
     "attention": ("attention.cu", []),
+    "decode_stream": ("decode_stream.cu", []),
     "gemm_tc": ("gemm_tc.cu", []),
 }
 

@@ -20,6 +20,8 @@ per-row positions, replayed as a CUDA graph
 """
 from __future__ import annotations
 
+import contextlib
+import gc
 from typing import Dict, List, NamedTuple, Optional, Sequence, Tuple
 
 import numpy as np
@@ -44,6 +46,21 @@ class StepError(ValueError):
 
 def _align4(n: int) -> int:
     return (n + 3) & ~3
+
+
+@contextlib.contextmanager
+def _capture(graph: "torch.cuda.CUDAGraph"):
+    """Stream capture with Python's cyclic garbage collector held off.  If the collector ran in the
+    middle of a capture and freed an engine dropped earlier (its graphs and their memory pools), the
+    driver calls made by those destructors would invalidate the capture."""
+    was_on = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph):
+            yield
+    finally:
+        if was_on:
+            gc.enable()
 
 
 class _Layout:
@@ -147,7 +164,7 @@ class _CapturedStep:
         out = eng._forward(self.ctx)                    # eager: the real result of this step
         self.launches = eng.kernel_launches - before
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):                       # recorded, not run: the cache is untouched
+        with _capture(g):                               # recorded, not run: the cache is untouched
             self.logits = eng._forward(self.ctx)
         eng.kernel_launches = before + self.launches
         self.graph = g
@@ -415,7 +432,7 @@ class DecodeRun:
                 self.launches_per_step = eng.kernel_launches - before
                 if eng.use_graphs:
                     g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g):
+                    with _capture(g):
                         self._one()                           # recorded, not run
                     eng.kernel_launches = before + self.launches_per_step
                     self.graph = g

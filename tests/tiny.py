@@ -43,8 +43,18 @@ TINY_F = dict(
     use_sliding_window=False, sliding_window=None)
 TINY_F_INIT = dict(seed=9, std_matrix=0.04, std_embedding=0.04, std_gain=0.1)
 
+# head size 64 with three kv heads, windows of 40 keys in the upper two layers, widths that are
+# multiples of 32: the sizes the fused layer kernel takes, with options F does not have
+TINY_S = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=3, hidden_size=192, num_attention_heads=6, num_key_value_heads=3, head_dim=64,
+    intermediate_size=224, vocab_size=517, rope_theta=10000.0, rms_norm_eps=1e-5,
+    max_position_embeddings=1024, tie_word_embeddings=False, hidden_act="silu", attention_bias=False,
+    use_sliding_window=True, sliding_window=40, max_window_layers=1)
+TINY_S_INIT = dict(seed=13, std_matrix=0.05, std_embedding=0.05, std_gain=0.1)
+
 CONFIGS = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "W": (TINY_W, TINY_W_INIT),
-           "F": (TINY_F, TINY_F_INIT)}
+           "F": (TINY_F, TINY_F_INIT), "S": (TINY_S, TINY_S_INIT)}
 
 
 def make_folder(name: str, out_dir: str) -> str:
