@@ -42,6 +42,7 @@ LIBRARIES: Dict[str, tuple] = {
     "decode": ("decode.cu", []),
     "attention": ("attention.cu", []),
     "decode_stream": ("decode_stream.cu", []),
+    "attn_tc": ("attn_tc.cu", []),
     "gemm_tc": ("gemm_tc.cu", []),
 }
 

@@ -13,7 +13,8 @@ import torch
 
 from ..csrc.build import KernelsUnavailable
 from ._lib import KernelError, set_launch_counter
-from .attention import attn_decode, attn_prefill, fast_supported, pick_splits, query_tiles
+from .attention import (TC_TILE_ROWS, attn_decode, attn_prefill, attn_prefill_tc, fast_supported, pick_splits,
+                        query_tiles, tc_prefill_supported)
 from .decode import skinny_gemm, skinny_supported
 from .gemm_tc import gemm_tc, tc_supported
 from .generic import (add_rmsnorm, attn_generic, decode_advance, embed_gather, gemm_generic, qkv_prepare,
@@ -92,13 +93,17 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx
             return attn_decode(q, k_pages, v_pages, ctx.seq_lens, block_table, nh, nkv, hd, scale, window,
                                pick_splits(ctx.n_seqs, nkv, max_pages, q.device))
         if ctx.host is not None:
-            tiles = ctx.scratch.get("query_tiles")
+            # prompt steps: tcgen05 kernel (128-row tiles) for head size 128, else the mma.sync kernel (64-row tiles)
+            tc = tc_prefill_supported(q.dtype, nh, nkv, hd)
+            rows = TC_TILE_ROWS if tc else 64
+            tiles = ctx.scratch.get(("query_tiles", rows))
             if tiles is None:
                 import numpy as np
-                ts, t0 = query_tiles(ctx.host["cu_seqlens"])
+                ts, t0 = query_tiles(ctx.host["cu_seqlens"], rows)
                 both = torch.from_numpy(np.asarray([ts, t0], dtype=np.int32)).to(q.device, non_blocking=True)
-                tiles = ctx.scratch["query_tiles"] = (both[0], both[1])
-            return attn_prefill(q, k_pages, v_pages, tiles[0], tiles[1], ctx.cu_seqlens, ctx.seq_past, ctx.seq_lens,
-                                block_table, nh, nkv, hd, scale, window)
+                tiles = ctx.scratch[("query_tiles", rows)] = (both[0], both[1])
+            kernel = attn_prefill_tc if tc else attn_prefill
+            return kernel(q, k_pages, v_pages, tiles[0], tiles[1], ctx.cu_seqlens, ctx.seq_past, ctx.seq_lens,
+                          block_table, nh, nkv, hd, scale, window)
     return attn_generic(q, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, nh, nkv, hd,
                         scale, window)

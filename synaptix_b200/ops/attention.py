@@ -6,7 +6,10 @@ from typing import Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ._lib import KernelError, c_float, c_int, check, fn, ptr, require_cuda, stream
+import ctypes
+import os
+
+from ._lib import KernelError, c_float, c_int, c_longlong, check, fn, ptr, require_cuda, stream
 from .decode import sm_count
 
 FAST_HEAD_DIMS = (32, 64, 128)
@@ -104,3 +107,40 @@ def attn_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, 
         ptr(cu_seqlens), ptr(seq_past), ptr(seq_lens), ptr(block_table), c_int(block_table.shape[1]), c_int(nh),
         c_int(nkv), c_int(hd), c_float(scale), c_int(0 if window is None else int(window)), stream()), "attn_prefill")
     return out
+
+
+TC_HEAD_DIM = 128
+TC_TILE_ROWS = 128
+
+
+def tc_prefill_supported(dtype, nh: int, nkv: int, hd: int) -> bool:
+    """The tcgen05 prompt-attention kernel takes bfloat16 and head size 128 (``SYNAPTIX_ATTN_TC=0`` turns it off)."""
+    return (dtype == torch.bfloat16 and hd == TC_HEAD_DIM and nkv > 0 and nh % nkv == 0
+            and os.environ.get("SYNAPTIX_ATTN_TC", "1") != "0")
+
+
+def attn_prefill_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, tile_seq: torch.Tensor,
+                    tile_q0: torch.Tensor, cu_seqlens: torch.Tensor, seq_past: torch.Tensor, seq_lens: torch.Tensor,
+                    block_table: torch.Tensor, nh: int, nkv: int, hd: int, scale: float, window: Optional[int],
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``attn_prefill`` on the tcgen05 tensor cores (``csrc/attn_tc.cu``); ``tile_seq``/``tile_q0`` list
+    128-row query tiles."""
+    require_cuda(q, k_pages, v_pages, tile_seq, tile_q0, cu_seqlens, seq_past, seq_lens, block_table, out)
+    T = q.shape[0]
+    if not tc_prefill_supported(q.dtype, nh, nkv, hd) or k_pages.dtype != q.dtype:
+        raise KernelError("attn_prefill_tc: bfloat16 and head size 128")
+    if out is None:
+        out = torch.empty((T, nh * hd), dtype=q.dtype, device=q.device)
+    check(fn("attn_tc", "sx_attn_prefill_tc")(
+        ptr(q), ptr(k_pages), ptr(v_pages), ptr(out), c_longlong(T), c_longlong(k_pages.shape[0]), ptr(tile_seq),
+        ptr(tile_q0), c_int(tile_seq.numel()), ptr(cu_seqlens), ptr(seq_past), ptr(seq_lens), ptr(block_table),
+        c_int(block_table.shape[1]), c_int(nh), c_int(nkv), c_int(hd), c_float(scale),
+        c_int(0 if window is None else int(window)), stream()), "attn_prefill_tc")
+    return out
+
+
+def attn_tc_status() -> int:
+    """0, or which bounded wait of the tcgen05 attention kernel ran out.  Synchronises the device."""
+    v = ctypes.c_int(0)
+    check(fn("attn_tc", "sx_attn_tc_status")(ctypes.byref(v)), "attn_tc_status", launches=0)
+    return int(v.value)

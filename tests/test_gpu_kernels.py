@@ -494,6 +494,29 @@ def test_attention_prefill_kernel(nh, nkv, hd, window):
     assert err < 2e-2, err
 
 
+@pytest.mark.parametrize("nh,nkv,window", [(4, 2, None), (2, 1, 100), (32, 8, None), (6, 6, 200), (5, 1, 129)])
+def test_attention_prefill_tcgen05_kernel(nh, nkv, window):
+    """Prompts of unequal lengths, with and without keys held before the step, tiles that end inside a page,
+    sequences longer than one 128-key block; pages are scrambled and unwritten places hold NaN."""
+    from synaptix_b200.ops.attention import attn_prefill_tc, attn_tc_status, query_tiles
+    hd = 128
+    past, new = [0, 130, 200, 64, 0, 700, 5], [67, 1, 3, 130, 64, 300, 129]
+    q, kp, vp, bt, pos, sot, scale, ref = fast_attention_case(nh, nkv, hd, window, past, new, 4)
+    cu = [0]
+    for n in new:
+        cu.append(cu[-1] + n)
+    ts, t0 = query_tiles(cu, 128)
+    dev = lambda x: torch.tensor(x, dtype=torch.int32).cuda()
+    T = sum(new)
+    out = attn_prefill_tc(q.view(T, nh * hd).cuda(), kp, vp, dev(ts), dev(t0), dev(cu), dev(past),
+                          dev([p + n for p, n in zip(past, new)]), bt, nh, nkv, hd, scale, window)
+    assert attn_tc_status() == 0
+    got = out.float().cpu().view(T, nh, hd)
+    assert torch.isfinite(got).all()
+    err = (got - ref).abs().max().item()
+    assert err < 2e-2, err
+
+
 def test_fast_attention_finds_one_far_key_and_respects_the_window_edge():
     from synaptix_b200.ops.attention import attn_decode, attn_prefill, query_tiles
     nh, nkv, hd = 4, 2, 64
@@ -519,6 +542,32 @@ def test_fast_attention_finds_one_far_key_and_respects_the_window_edge():
             assert torch.allclose(out, want, atol=2e-2), f"decode L={L} far={far} W={W} splits={n_splits}"
         out = attn_prefill(qd, kp, vp, dev([0]), dev([0]), dev([0, 1]), dev([L - 1]), dev([L]), bt, nh, nkv, hd, 1.0, W)
         assert torch.allclose(out.float().cpu().view(nh, hd), want, atol=2e-2), f"prefill L={L} far={far} W={W}"
+
+
+def test_tcgen05_attention_finds_one_far_key_and_respects_the_window_edge():
+    """One key among hundreds carries the whole weight; with a window, the key just before its edge would win if
+    it counted.  The last query of a sequence held in the cache, as a one-row prompt step."""
+    from synaptix_b200.ops.attention import attn_prefill_tc
+    nh, nkv, hd = 4, 2, 128
+    dt = torch.bfloat16
+    dev = lambda x: torch.tensor(x, dtype=torch.int32).cuda()
+    for L, far, W in [(700, 0, None), (700, 333, None), (700, 699, None), (700, 127, None), (700, 128, None),
+                      (200, 130, 70), (134, 64, 70), (71, 1, 70), (300, 128, 172)]:
+        k = torch.randn(L, nkv, hd) * 0.1
+        v = torch.randn(L, nkv, hd)
+        q = torch.randn(1, nh, hd)
+        q[0, 1], q[0, 3] = q[0, 0].clone(), q[0, 2].clone()
+        for kh in range(nkv):
+            k[far, kh] = q[0, kh * 2] / q[0, kh * 2].norm() * 40.0
+            if W is not None and far - 1 >= 0:
+                assert far == L - W
+                k[far - 1, kh] = q[0, kh * 2] / q[0, kh * 2].norm() * 80.0
+                v[far - 1, kh] = 1000.0
+        kp, vp, bt = make_paged([k], [v], nkv, hd, dt, seed=L + far)
+        qd = q.view(1, nh * hd).to(dt).cuda()
+        want = torch.stack([v[far, h // 2].to(dt).float() for h in range(nh)])
+        out = attn_prefill_tc(qd, kp, vp, dev([0]), dev([0]), dev([0, 1]), dev([L - 1]), dev([L]), bt, nh, nkv, hd, 1.0, W)
+        assert torch.allclose(out.float().cpu().view(nh, hd), want, atol=2e-2), f"L={L} far={far} W={W}"
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (65, 256, 2560), (200, 300, 72), (1000, 389, 96), (130, 24, 8),
