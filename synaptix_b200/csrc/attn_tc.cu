@@ -4,14 +4,16 @@
 //
 // One block works on one (128 query rows of a sequence, query head).  Keys go by in blocks of 128
 // (two cache pages).  Roles:
-//   warps 0-3  softmax: thread r owns query row r = lane r of tensor memory.  It reads its row of S
-//              (tcgen05.ld), masks, keeps the running maximum and sum, writes P = 2^(s*c - m*c) as
-//              bfloat16 into shared memory in the swizzled layout the MMA reads, rescales its row of O
-//              in tensor memory when the maximum moved, and at the end writes O / l
-//   warp 4     one lane issues the MMAs: S(j+1) = Q K(j+1)^T is issued BEFORE it waits for P(j), so
+//   warps 0-7  softmax: threads r and r + 128 own query row r = lane r of tensor memory, 64 columns
+//              each.  A thread reads its half row of S (tcgen05.ld), masks, takes the maximum (the two
+//              halves meet through shared memory), writes P = 2^(s*c - m*c) as bfloat16 into shared
+//              memory in the swizzled layout the MMA reads, rescales its half row of O in tensor
+//              memory when the reference point m moved, and at the end writes O / l.  m moves lazily
+//              (only when the maximum grew by more than 2^8), which spares most rescalings
+//   warp 8     one lane issues the MMAs: S(j+1) = Q K(j+1)^T is issued BEFORE it waits for P(j), so
 //              the tensor cores work on the next scores while the softmax warps are busy (S is
 //              double-buffered in tensor memory); then O += P(j) V(j)
-//   warp 5     one lane issues the TMA loads: Q once, then K and V of every block into a ring of two
+//   warp 9     one lane issues the TMA loads: Q once, then K and V of every block into a ring of two
 //              stages
 // V is read as an MN-major operand (rows of the cache are keys, the MMA contracts over keys), so the
 // cache layout [page, kv head, 64 tokens, head size] serves both products as it is.
@@ -31,7 +33,11 @@
 #define FT_HD 128
 #define FT_BM 128                       // query rows of a block
 #define FT_BN 128                       // keys of a block
-#define FT_THREADS 192
+#define FT_SOFTMAX_THREADS 256
+#define FT_MMA_WARP 8
+#define FT_TMA_WARP 9
+#define FT_THREADS 320
+#define FT_HALF 64                     // columns of S (and of O) a softmax thread owns
 #define FT_CHUNK (128 * 128)            // bytes of [128 rows][64 values]: one swizzled half of a 128 x 128 bf16 tile
 #define FT_TILE (2 * FT_CHUNK)          // 32 KB
 #define FT_STAGE (2 * FT_TILE)          // K then V
@@ -41,6 +47,7 @@
 #define FT_COL_S0 0
 #define FT_COL_S1 128
 #define FT_COL_O 256
+#define FT_LAZY 8.0f
 
 __device__ __forceinline__ uint32_t ft_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ft_mbar_init(uint32_t bar, uint32_t count) {
@@ -133,12 +140,18 @@ __device__ __forceinline__ void ft_st32(uint32_t taddr, const float* r) {
         "r"(__float_as_uint(r[28])), "r"(__float_as_uint(r[29])), "r"(__float_as_uint(r[30])), "r"(__float_as_uint(r[31]))
       : "memory");
 }
+// 2^x on the special-function unit: one instruction, -inf -> 0
+__device__ __forceinline__ float ft_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t ft_pack(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-enum { FT_B_QFULL = 0, FT_B_KVFULL = 1, FT_B_KVEMPTY = 3, FT_B_SFULL = 5, FT_B_SFREE = 7, FT_B_PREADY = 9, FT_B_PVDONE = 10, FT_NBARS = 11 };
+enum { FT_B_QFULL = 0, FT_B_KVFULL = 1, FT_B_KVEMPTY = 3, FT_B_SFULL = 5, FT_B_SFREE = 7, FT_B_PREADY = 9, FT_B_PVDONE = 10, FT_B_XCH = 11, FT_NBARS = 14 };
 
 __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -153,6 +166,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
   unsigned char* kv_s = tiles + 2 * FT_TILE;                     // [2][K tile, V tile]
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + FT_SMEM_TILES);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + FT_NBARS);
+  float* xch = reinterpret_cast<float*>(tmem_slot + 4);          // [6][128]: the halves' maxima (two buffers), their sums
   const uint32_t bar0 = ft_smem(bars);
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
@@ -176,13 +190,14 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
       ft_mbar_init(bar(FT_B_KVFULL + s), 1);
       ft_mbar_init(bar(FT_B_KVEMPTY + s), 1);
       ft_mbar_init(bar(FT_B_SFULL + s), 1);
-      ft_mbar_init(bar(FT_B_SFREE + s), 128);
+      ft_mbar_init(bar(FT_B_SFREE + s), FT_SOFTMAX_THREADS);
     }
-    ft_mbar_init(bar(FT_B_PREADY), 128);
+    ft_mbar_init(bar(FT_B_PREADY), FT_SOFTMAX_THREADS);
     ft_mbar_init(bar(FT_B_PVDONE), 1);
+    for (int s = 0; s < 3; ++s) ft_mbar_init(bar(FT_B_XCH + s), FT_SOFTMAX_THREADS);      // the halves' exchanges
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 4) {
+  if (warp == FT_MMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(ft_smem(tmem_slot)), "r"((uint32_t)FT_TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
@@ -193,7 +208,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
   pdl_wait();
   pdl_trigger();
 
-  if (warp == 5) {
+  if (warp == FT_TMA_WARP) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       ft_mbar_expect_tx(bar(FT_B_QFULL), FT_TILE);
@@ -219,7 +234,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
       }
     }
     __syncwarp();
-  } else if (warp == 4) {
+  } else if (warp == FT_MMA_WARP) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ft_idesc(FT_BM, FT_BN, false);
@@ -260,19 +275,19 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
     }
     __syncwarp();
   } else {
-    // ------------------------------ softmax: thread r owns query row r ------------------------------
-    const int r = threadIdx.x;                                   // 0..127
-    const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+    // ---------------- softmax: threads r and r + 128 own query row r, 64 columns each ----------------
+    const int r = threadIdx.x & 127, hf = threadIdx.x >> 7;      // row; which half of the columns
+    const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const int pos = r < rows ? past + q0 + r : -1;
-    float m = -INFINITY, l = 0.f;
+    float m = -INFINITY, l = 0.f;                                 // l: this thread's columns only
     bool ok = true;
     for (int j = 0; j < nb && ok; ++j) {
       const int s = j & 1, u = j >> 1;
       if (!ft_mbar_wait(bar(FT_B_SFULL + s), u & 1)) { atomicExch(status, 6); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      float sc[FT_BN];
+      float sc[FT_HALF];
 #pragma unroll
-      for (int c = 0; c < FT_BN / 32; ++c) ft_ld32(t_row + (s ? FT_COL_S1 : FT_COL_S0) + c * 32, sc + c * 32);
+      for (int c = 0; c < FT_HALF / 32; ++c) ft_ld32(t_row + (s ? FT_COL_S1 : FT_COL_S0) + hf * FT_HALF + c * 32, sc + c * 32);
       asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       ft_mbar_arrive(bar(FT_B_SFREE + s));
@@ -281,57 +296,70 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
       const bool need_mask = key0 + FT_BN - 1 > first_pos || (window > 0 && key0 <= last_pos - window);
       if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < FT_BN; ++i) {
-          const int ja = key0 + i;
+        for (int i = 0; i < FT_HALF; ++i) {
+          const int ja = key0 + hf * FT_HALF + i;
           const bool vis = ja <= pos && (window == 0 || ja > pos - window);
           sc[i] = vis ? sc[i] : -INFINITY;
         }
       }
-      float mx = m;
+      // the maximum of this thread's columns with 8 independent chains, then of the row through shared memory
+      float mxs[8];
 #pragma unroll
-      for (int i = 0; i < FT_BN; ++i) mx = fmaxf(mx, sc[i]);
-      const float ms = (mx == -INFINITY) ? 0.f : mx * scale_log2;
-      const float corr = (mx == -INFINITY) ? 1.f : exp2f((m - mx) * scale_log2);      // m = -inf: 0
-      float sum = 0.f;
-      uint32_t pk[FT_BN / 2];
+      for (int i = 0; i < 8; ++i) mxs[i] = sc[i];
 #pragma unroll
-      for (int i = 0; i < FT_BN; i += 2) {
-        const float p0 = exp2f(fmaf(sc[i], scale_log2, -ms));
-        const float p1 = exp2f(fmaf(sc[i + 1], scale_log2, -ms));
-        sum += p0 + p1;
+      for (int i = 8; i < FT_HALF; ++i) mxs[i & 7] = fmaxf(mxs[i & 7], sc[i]);
+      const float hmax = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])), fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
+      xch[(s * 2 + hf) * FT_BM + r] = hmax;
+      ft_mbar_arrive(bar(FT_B_XCH + s));           // (a bounded wait instead of a named barrier: a thread that gave up does not hang the rest)
+      if (!ft_mbar_wait(bar(FT_B_XCH + s), u & 1)) { atomicExch(status, 9); ok = false; break; }
+      const float bmax = fmaxf(hmax, xch[(s * 2 + (hf ^ 1)) * FT_BM + r]);
+      // The reference point m moves only when the maximum has grown by more than FT_LAZY (in the exponent's
+      // units): until then p = 2^(s*c - m*c) may exceed 1 by at most 2^FT_LAZY, which float32 sums and
+      // bfloat16 P hold without loss, and O needs no rescaling.  The final O / l is the same either way.
+      // Both threads of a row see the same bmax and m, so they decide alike.
+      float corr = 1.f;
+      if (bmax != -INFINITY && (m == -INFINITY || (bmax - m) * scale_log2 > FT_LAZY)) {
+        corr = (m == -INFINITY) ? 0.f : ft_ex2((m - bmax) * scale_log2);
+        m = bmax;
+      }
+      const float ms = (m == -INFINITY) ? 0.f : m * scale_log2;
+      float sums[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[FT_HALF / 2];
+#pragma unroll
+      for (int i = 0; i < FT_HALF; i += 2) {
+        const float p0 = ft_ex2(fmaf(sc[i], scale_log2, -ms));
+        const float p1 = ft_ex2(fmaf(sc[i + 1], scale_log2, -ms));
+        sums[(i >> 1) & 3] += p0 + p1;
         pk[i >> 1] = ft_pack(p0, p1);
       }
-      l = l * corr + sum;
-      m = mx;
+      l = l * corr + ((sums[0] + sums[1]) + (sums[2] + sums[3]));
 
       // P's buffer and O are free once the previous block's P V has been done
       if (j > 0 && !ft_mbar_wait(bar(FT_B_PVDONE), (j - 1) & 1)) { atomicExch(status, 7); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      // this thread's 64 keys are one swizzled chunk of P
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int p = 0; p < 8; ++p) {
-          const uint4 v = make_uint4(pk[c * 32 + p * 4], pk[c * 32 + p * 4 + 1], pk[c * 32 + p * 4 + 2], pk[c * 32 + p * 4 + 3]);
-          *reinterpret_cast<uint4*>(p_s + c * FT_CHUNK + r * 128 + ((p ^ (r & 7)) << 4)) = v;
-        }
-      // rows of V at or beyond the sequence's length (thread r stands for key r of the block here)
-      if (key0 + r >= len) {
-        unsigned char* vrow = kv_s + s * FT_STAGE + FT_TILE + r * 128;
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int p = 0; p < 8; ++p) *reinterpret_cast<uint4*>(vrow + c * FT_CHUNK + p * 16) = make_uint4(0u, 0u, 0u, 0u);
+      for (int p = 0; p < 8; ++p) {
+        const uint4 v = make_uint4(pk[p * 4], pk[p * 4 + 1], pk[p * 4 + 2], pk[p * 4 + 3]);
+        *reinterpret_cast<uint4*>(p_s + hf * FT_CHUNK + r * 128 + ((p ^ (r & 7)) << 4)) = v;
       }
-      // O *= corr, when some row of this warp moved its maximum
+      // rows of V at or beyond the sequence's length (thread r stands for key r of the block here,
+      // and hf for the half of the head's values)
+      if (key0 + r >= len) {
+        unsigned char* vrow = kv_s + s * FT_STAGE + FT_TILE + hf * FT_CHUNK + r * 128;
+#pragma unroll
+        for (int p = 0; p < 8; ++p) *reinterpret_cast<uint4*>(vrow + p * 16) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      // O *= corr (this thread's 64 columns), when some row of this warp moved its reference point
       if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll 1
-        for (int c = 0; c < FT_HD / 32; ++c) {
+        for (int c = 0; c < FT_HALF / 32; ++c) {
           float o[32];
-          ft_ld32(t_row + FT_COL_O + c * 32, o);
+          ft_ld32(t_row + FT_COL_O + hf * FT_HALF + c * 32, o);
           asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] *= corr;
-          ft_st32(t_row + FT_COL_O + c * 32, o);
+          ft_st32(t_row + FT_COL_O + hf * FT_HALF + c * 32, o);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
       }
@@ -339,15 +367,20 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       ft_mbar_arrive(bar(FT_B_PREADY));
     }
+    // the row's sum: both halves
+    xch[(4 + hf) * FT_BM + r] = l;
+    ft_mbar_arrive(bar(FT_B_XCH + 2));
+    if (ok && !ft_mbar_wait(bar(FT_B_XCH + 2), 0)) { atomicExch(status, 9); ok = false; }
+    l += xch[(4 + (hf ^ 1)) * FT_BM + r];
     if (ok && !ft_mbar_wait(bar(FT_B_PVDONE), (nb - 1) & 1)) { atomicExch(status, 8); ok = false; }
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* dst = out + ((size_t)(t_begin + q0 + r) * nh + h) * FT_HD;
+      bf16* dst = out + ((size_t)(t_begin + q0 + r) * nh + h) * FT_HD + hf * FT_HALF;
 #pragma unroll 1
-      for (int c = 0; c < FT_HD / 32; ++c) {
+      for (int c = 0; c < FT_HALF / 32; ++c) {
         float o[32];
-        ft_ld32(t_row + FT_COL_O + c * 32, o);
+        ft_ld32(t_row + FT_COL_O + hf * FT_HALF + c * 32, o);
         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
         if (r < rows) {
 #pragma unroll
@@ -366,7 +399,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
 
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
-  if (warp == 4) {
+  if (warp == FT_MMA_WARP) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)FT_TMEM_COLS) : "memory");
   }
@@ -443,7 +476,7 @@ extern "C" int sx_attn_prefill_tc(const void* q, const void* k_pages, const void
   if (rc) return rc;
   if ((rc = ft_map_pages(&mk, k_pages, n_pages, nkv))) return rc;
   if ((rc = ft_map_pages(&mv, v_pages, n_pages, nkv))) return rc;
-  const size_t smem = 1024 + FT_SMEM_TILES + FT_NBARS * sizeof(uint64_t) + 16;
+  const size_t smem = 1024 + FT_SMEM_TILES + FT_NBARS * sizeof(uint64_t) + 16 + 6 * FT_BM * sizeof(float);
   auto kern = attn_tc_prefill_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
@@ -451,7 +484,7 @@ extern "C" int sx_attn_prefill_tc(const void* q, const void* k_pages, const void
                    cu_seqlens, seq_past, seq_lens, block_table, maxp, nh, nkv, scale * 1.4426950408889634f, window, status);
 }
 
-// 0, or which bounded wait ran out (1 producer, 2-5 MMA issuer, 6-8 softmax)
+// 0, or which bounded wait ran out (1 producer, 2-5 MMA issuer, 6-9 softmax)
 extern "C" int sx_attn_tc_status(int* host_value) {
   int* p = ft_status_word();
   if (!p) return (int)cudaErrorMemoryAllocation;
