@@ -6,14 +6,18 @@
 // (two cache pages).  Roles:
 //   warps 0-7  softmax: threads r and r + 128 own query row r = lane r of tensor memory, 64 columns
 //              each.  A thread reads its half row of S (tcgen05.ld), masks, takes the maximum (the two
-//              halves meet through shared memory), writes P = 2^(s*c - m*c) as bfloat16 into shared
-//              memory in the swizzled layout the MMA reads, rescales its half row of O in tensor
-//              memory when the reference point m moved, and at the end writes O / l.  m moves lazily
-//              (only when the maximum grew by more than 2^8), which spares most rescalings
+//              halves meet through shared memory), writes P = 2^(s*c - m*c) as packed bfloat16 back
+//              into tensor memory over the scores it has read (tcgen05.st), rescales its half row of O
+//              when the reference point m moved, and at the end writes O / l.  m moves lazily (only
+//              when the maximum grew by more than 2^8), which spares most rescalings.  At the start
+//              the same threads copy the Q tile from shared memory into tensor memory
+// Both products take their A operand (Q, P) from tensor memory, so an MMA reads only its B operand
+// (K, V) from shared memory: with A in shared memory as well, a 128 x 128 x 16 MMA needs all of the
+// 128 bytes a clock that shared memory delivers, and the first version ran at half the rate.
 //   warp 8     one lane issues the MMAs: S(j+1) = Q K(j+1)^T is issued BEFORE it waits for P(j), so
 //              the tensor cores work on the next scores while the softmax warps are busy (S is
 //              double-buffered in tensor memory); then O += P(j) V(j)
-//   warp 9     one lane issues the TMA loads: Q once, then K and V of every block into a ring of two
+//   warp 9     one lane issues the TMA loads: Q once, then K and V of every block into a ring of three
 //              stages
 // V is read as an MN-major operand (rows of the cache are keys, the MMA contracts over keys), so the
 // cache layout [page, kv head, 64 tokens, head size] serves both products as it is.
@@ -41,12 +45,14 @@
 #define FT_CHUNK (128 * 128)            // bytes of [128 rows][64 values]: one swizzled half of a 128 x 128 bf16 tile
 #define FT_TILE (2 * FT_CHUNK)          // 32 KB
 #define FT_STAGE (2 * FT_TILE)          // K then V
-#define FT_SMEM_TILES (FT_TILE /*Q*/ + FT_TILE /*P*/ + 2 * FT_STAGE)
+#define FT_KV_STAGES 3                  // K/V blocks in flight: with two, every block waited for its loads (measured 1.85 us a block)
+#define FT_SMEM_TILES (FT_KV_STAGES * FT_STAGE)      // Q lands in the last stage's K tile and moves on to tensor memory before that stage is first used
 #define FT_SPIN_LIMIT (1u << 26)
 #define FT_TMEM_COLS 512
 #define FT_COL_S0 0
 #define FT_COL_S1 128
 #define FT_COL_O 256
+#define FT_COL_Q 384                    // Q as packed bf16: 64 columns; P(j) lies over the first 64 columns of S(j)
 #define FT_LAZY 8.0f
 
 __device__ __forceinline__ uint32_t ft_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -110,6 +116,22 @@ __device__ __forceinline__ void ft_mma(uint32_t tmem_d, uint64_t da, uint64_t db
       "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
       ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same with the A operand in tensor memory (128 lanes x 8 columns of packed bf16 pairs per K = 16)
+__device__ __forceinline__ void ft_mma_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void ft_st32u(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
 __device__ __forceinline__ void ft_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
@@ -151,7 +173,8 @@ __device__ __forceinline__ uint32_t ft_pack(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-enum { FT_B_QFULL = 0, FT_B_KVFULL = 1, FT_B_KVEMPTY = 3, FT_B_SFULL = 5, FT_B_SFREE = 7, FT_B_PREADY = 9, FT_B_PVDONE = 10, FT_B_XCH = 11, FT_NBARS = 14 };
+enum { FT_B_QFULL = 0, FT_B_KVFULL = 1, FT_B_KVEMPTY = 1 + FT_KV_STAGES, FT_B_SFULL = 1 + 2 * FT_KV_STAGES, FT_B_QREADY = FT_B_SFULL + 2,
+       FT_B_PREADY = FT_B_QREADY + 1, FT_B_PVDONE = FT_B_PREADY + 1, FT_B_XCH = FT_B_PVDONE + 1, FT_NBARS = FT_B_XCH + 12 };
 
 __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -161,9 +184,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
     float scale_log2, int window, int* __restrict__ status) {
   extern __shared__ unsigned char ft_smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(ft_smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char* q_s = tiles;
-  unsigned char* p_s = tiles + FT_TILE;
-  unsigned char* kv_s = tiles + 2 * FT_TILE;                     // [2][K tile, V tile]
+  unsigned char* kv_s = tiles;                                   // [FT_KV_STAGES][K tile, V tile]
+  unsigned char* q_s = kv_s + (FT_KV_STAGES - 1) * FT_STAGE;
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + FT_SMEM_TILES);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + FT_NBARS);
   float* xch = reinterpret_cast<float*>(tmem_slot + 4);          // [6][128]: the halves' maxima (two buffers), their sums
@@ -171,8 +193,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // tiles late in a sequence see more keys: they are started first, so that the short ones fill the tail
-  const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
+  // Tiles late in a sequence see more keys: they are started first, for all heads (blocks are handed out
+  // with x running fastest), so that the short ones fill the tail
+  const int tile = gridDim.y - 1 - blockIdx.y, h = blockIdx.x;
   const int seq = tile_seq[tile], q0 = tile_q0[tile];
   const int kvh = h / (nh / nkv);
   const int t_begin = cu_seqlens[seq], n_new = cu_seqlens[seq + 1] - t_begin;
@@ -186,15 +209,17 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
 
   if (threadIdx.x == 0) {
     ft_mbar_init(bar(FT_B_QFULL), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < FT_KV_STAGES; ++s) {
       ft_mbar_init(bar(FT_B_KVFULL + s), 1);
       ft_mbar_init(bar(FT_B_KVEMPTY + s), 1);
-      ft_mbar_init(bar(FT_B_SFULL + s), 1);
-      ft_mbar_init(bar(FT_B_SFREE + s), FT_SOFTMAX_THREADS);
     }
-    ft_mbar_init(bar(FT_B_PREADY), FT_SOFTMAX_THREADS);
+    for (int s = 0; s < 2; ++s) ft_mbar_init(bar(FT_B_SFULL + s), 1);
+    // one arrival per softmax warp (its lane 0, after the warp has synchronised): 256 arrivals on one
+    // barrier word cost more than the softmax itself
+    ft_mbar_init(bar(FT_B_QREADY), FT_SOFTMAX_THREADS / 32);
+    ft_mbar_init(bar(FT_B_PREADY), FT_SOFTMAX_THREADS / 32);
     ft_mbar_init(bar(FT_B_PVDONE), 1);
-    for (int s = 0; s < 3; ++s) ft_mbar_init(bar(FT_B_XCH + s), FT_SOFTMAX_THREADS);      // the halves' exchanges
+    for (int s = 0; s < 12; ++s) ft_mbar_init(bar(FT_B_XCH + s), 2);      // the exchanges between warps w and w + 4: [3][4]
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == FT_MMA_WARP) {
@@ -215,8 +240,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
       ft_tma_2d(ft_smem(q_s), &map_q, h * FT_HD, t_begin + q0, bar(FT_B_QFULL));
       ft_tma_2d(ft_smem(q_s + FT_CHUNK), &map_q, h * FT_HD + 64, t_begin + q0, bar(FT_B_QFULL));
       for (int j = 0; j < nb; ++j) {
-        const int s = j & 1, u = j >> 1;
+        const int s = j % FT_KV_STAGES, u = j / FT_KV_STAGES;
         if (!ft_mbar_wait(bar(FT_B_KVEMPTY + s), (u & 1) ^ 1)) { atomicExch(status, 1); break; }
+        if (j == FT_KV_STAGES - 1 && !ft_mbar_wait(bar(FT_B_QREADY), 0)) { atomicExch(status, 1); break; }      // Q has left this stage
         ft_mbar_expect_tx(bar(FT_B_KVFULL + s), FT_STAGE);
         const uint32_t k_dst = ft_smem(kv_s + s * FT_STAGE), v_dst = k_dst + FT_TILE;
         const int key0 = kb0 + j * FT_BN;
@@ -239,19 +265,22 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ft_idesc(FT_BM, FT_BN, false);
       constexpr uint32_t idesc_pv = ft_idesc(FT_BM, FT_HD, true);
-      bool ok = ft_mbar_wait(bar(FT_B_QFULL), 0);
+      // Q is in tensor memory once the softmax threads have copied it there
+      bool ok = ft_mbar_wait(bar(FT_B_QREADY), 0);
       if (!ok) atomicExch(status, 2);
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      // MMAs run in the order they are issued, so S(j+2) = Q K(j+2)^T, issued after P(j) V(j), does not
+      // overwrite P(j), which lies over S(j)
       auto issue_qk = [&](int j) -> bool {
-        const int s = j & 1, u = j >> 1;
-        if (!ft_mbar_wait(bar(FT_B_KVFULL + s), u & 1)) { atomicExch(status, 3); return false; }
-        if (u > 0 && !ft_mbar_wait(bar(FT_B_SFREE + s), (u - 1) & 1)) { atomicExch(status, 4); return false; }
+        const int ks = j % FT_KV_STAGES, ku = j / FT_KV_STAGES, s = j & 1;
+        if (!ft_mbar_wait(bar(FT_B_KVFULL + ks), ku & 1)) { atomicExch(status, 3); return false; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t qa = ft_smem(q_s), ka = ft_smem(kv_s + s * FT_STAGE);
+        const uint32_t ka = ft_smem(kv_s + ks * FT_STAGE);
         const uint32_t d = tmem_base + (s ? FT_COL_S1 : FT_COL_S0);
 #pragma unroll
         for (int k = 0; k < FT_HD / 16; ++k) {
           const uint32_t off = (k >> 2) * FT_CHUNK + (k & 3) * 32;
-          ft_mma(d, ft_desc_kmajor(qa + off), ft_desc_kmajor(ka + off), idesc_qk, k != 0);
+          ft_mma_ta(d, tmem_base + FT_COL_Q + k * 8, ft_desc_kmajor(ka + off), idesc_qk, k != 0);
         }
         ft_commit(bar(FT_B_SFULL + s));
         return true;
@@ -262,15 +291,12 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
         if (!ok) break;
         if (!ft_mbar_wait(bar(FT_B_PREADY), j & 1)) { atomicExch(status, 5); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t pa = ft_smem(p_s), va = ft_smem(kv_s + (j & 1) * FT_STAGE + FT_TILE);
+        const uint32_t pa = tmem_base + ((j & 1) ? FT_COL_S1 : FT_COL_S0), va = ft_smem(kv_s + (j % FT_KV_STAGES) * FT_STAGE + FT_TILE);
 #pragma unroll
-        for (int k = 0; k < FT_BN / 16; ++k) {
-          const uint32_t aoff = (k >> 2) * FT_CHUNK + (k & 3) * 32;      // P: 16 keys further along its rows
-          const uint32_t boff = k * 2048;                                 // V: 16 keys = 16 rows of 128 bytes further
-          ft_mma(tmem_base + FT_COL_O, ft_desc_kmajor(pa + aoff), ft_desc_mnmajor(va + boff), idesc_pv, (j | k) != 0);
-        }
+        for (int k = 0; k < FT_BN / 16; ++k)       // P: 8 columns (16 keys) further; V: 16 rows of 128 bytes further
+          ft_mma_ta(tmem_base + FT_COL_O, pa + k * 8, ft_desc_mnmajor(va + k * 2048), idesc_pv, (j | k) != 0);
         ft_commit(bar(FT_B_PVDONE));
-        ft_commit(bar(FT_B_KVEMPTY + (j & 1)));
+        ft_commit(bar(FT_B_KVEMPTY + j % FT_KV_STAGES));
       }
     }
     __syncwarp();
@@ -281,6 +307,21 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
     const int pos = r < rows ? past + q0 + r : -1;
     float m = -INFINITY, l = 0.f;                                 // l: this thread's columns only
     bool ok = true;
+    // this thread's half row of Q (64 values = one swizzled chunk row) from shared into tensor memory
+    if (!ft_mbar_wait(bar(FT_B_QFULL), 0)) { atomicExch(status, 6); ok = false; }
+    {
+      uint32_t qv[32];
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {
+        const uint4 v = *reinterpret_cast<const uint4*>(q_s + hf * FT_CHUNK + r * 128 + ((p ^ (r & 7)) << 4));
+        qv[p * 4] = v.x; qv[p * 4 + 1] = v.y; qv[p * 4 + 2] = v.z; qv[p * 4 + 3] = v.w;
+      }
+      ft_st32u(t_row + FT_COL_Q + hf * 32, qv);
+      asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) ft_mbar_arrive(bar(FT_B_QREADY));
+    }
     for (int j = 0; j < nb && ok; ++j) {
       const int s = j & 1, u = j >> 1;
       if (!ft_mbar_wait(bar(FT_B_SFULL + s), u & 1)) { atomicExch(status, 6); ok = false; break; }
@@ -289,8 +330,6 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
 #pragma unroll
       for (int c = 0; c < FT_HALF / 32; ++c) ft_ld32(t_row + (s ? FT_COL_S1 : FT_COL_S0) + hf * FT_HALF + c * 32, sc + c * 32);
       asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-      ft_mbar_arrive(bar(FT_B_SFREE + s));
 
       const int key0 = kb0 + j * FT_BN;
       const bool need_mask = key0 + FT_BN - 1 > first_pos || (window > 0 && key0 <= last_pos - window);
@@ -310,8 +349,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
       for (int i = 8; i < FT_HALF; ++i) mxs[i & 7] = fmaxf(mxs[i & 7], sc[i]);
       const float hmax = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])), fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
       xch[(s * 2 + hf) * FT_BM + r] = hmax;
-      ft_mbar_arrive(bar(FT_B_XCH + s));           // (a bounded wait instead of a named barrier: a thread that gave up does not hang the rest)
-      if (!ft_mbar_wait(bar(FT_B_XCH + s), u & 1)) { atomicExch(status, 9); ok = false; break; }
+      __syncwarp();                                // (a bounded wait instead of a named barrier: a warp that gave up does not hang its partner)
+      if (lane == 0) ft_mbar_arrive(bar(FT_B_XCH + s * 4 + (warp & 3)));
+      if (!ft_mbar_wait(bar(FT_B_XCH + s * 4 + (warp & 3)), u & 1)) { atomicExch(status, 9); ok = false; break; }
       const float bmax = fmaxf(hmax, xch[(s * 2 + (hf ^ 1)) * FT_BM + r]);
       // The reference point m moves only when the maximum has grown by more than FT_LAZY (in the exponent's
       // units): until then p = 2^(s*c - m*c) may exceed 1 by at most 2^FT_LAZY, which float32 sums and
@@ -334,21 +374,18 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
       }
       l = l * corr + ((sums[0] + sums[1]) + (sums[2] + sums[3]));
 
-      // P's buffer and O are free once the previous block's P V has been done
+      // P goes over the scores of this block (every thread of the row has read its scores: the
+      // exchange of the maxima came after the loads); O is free once the previous block's P V is done
+      ft_st32u(t_row + (s ? FT_COL_S1 : FT_COL_S0) + hf * 32, pk);
       if (j > 0 && !ft_mbar_wait(bar(FT_B_PVDONE), (j - 1) & 1)) { atomicExch(status, 7); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      // this thread's 64 keys are one swizzled chunk of P
-#pragma unroll
-      for (int p = 0; p < 8; ++p) {
-        const uint4 v = make_uint4(pk[p * 4], pk[p * 4 + 1], pk[p * 4 + 2], pk[p * 4 + 3]);
-        *reinterpret_cast<uint4*>(p_s + hf * FT_CHUNK + r * 128 + ((p ^ (r & 7)) << 4)) = v;
-      }
       // rows of V at or beyond the sequence's length (thread r stands for key r of the block here,
       // and hf for the half of the head's values)
       if (key0 + r >= len) {
-        unsigned char* vrow = kv_s + s * FT_STAGE + FT_TILE + hf * FT_CHUNK + r * 128;
+        unsigned char* vrow = kv_s + (j % FT_KV_STAGES) * FT_STAGE + FT_TILE + hf * FT_CHUNK + r * 128;
 #pragma unroll
         for (int p = 0; p < 8; ++p) *reinterpret_cast<uint4*>(vrow + p * 16) = make_uint4(0u, 0u, 0u, 0u);
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");    // the zeroed rows, for the tensor cores
       }
       // O *= corr (this thread's 64 columns), when some row of this warp moved its reference point
       if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
@@ -361,16 +398,17 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
           for (int i = 0; i < 32; ++i) o[i] *= corr;
           ft_st32(t_row + FT_COL_O + hf * FT_HALF + c * 32, o);
         }
-        asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
       }
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // P and the zeroed rows, for the tensor cores
+      asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-      ft_mbar_arrive(bar(FT_B_PREADY));
+      __syncwarp();
+      if (lane == 0) ft_mbar_arrive(bar(FT_B_PREADY));
     }
     // the row's sum: both halves
     xch[(4 + hf) * FT_BM + r] = l;
-    ft_mbar_arrive(bar(FT_B_XCH + 2));
-    if (ok && !ft_mbar_wait(bar(FT_B_XCH + 2), 0)) { atomicExch(status, 9); ok = false; }
+    __syncwarp();
+    if (lane == 0) ft_mbar_arrive(bar(FT_B_XCH + 8 + (warp & 3)));
+    if (ok && !ft_mbar_wait(bar(FT_B_XCH + 8 + (warp & 3)), 0)) { atomicExch(status, 9); ok = false; }
     l += xch[(4 + (hf ^ 1)) * FT_BM + r];
     if (ok && !ft_mbar_wait(bar(FT_B_PVDONE), (nb - 1) & 1)) { atomicExch(status, 8); ok = false; }
     if (ok) {
@@ -467,7 +505,7 @@ extern "C" int sx_attn_prefill_tc(const void* q, const void* k_pages, const void
                                   const int* cu_seqlens, const int* seq_past, const int* seq_lens, const int* block_table,
                                   int maxp, int nh, int nkv, int hd, float scale, int window, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
-  if (hd != FT_HD || nkv <= 0 || nh % nkv != 0 || nh > 65535 || T <= 0 || n_pages <= 0) return SX_ERR_SIZE;
+  if (hd != FT_HD || nkv <= 0 || nh % nkv != 0 || n_tiles > 65535 || T <= 0 || n_pages <= 0) return SX_ERR_SIZE;
   if (((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || ((uintptr_t)out & 15)) return SX_ERR_ALIGN;
   int* status = ft_status_word();
   if (!status) return (int)cudaErrorMemoryAllocation;
@@ -480,7 +518,7 @@ extern "C" int sx_attn_prefill_tc(const void* q, const void* k_pages, const void
   auto kern = attn_tc_prefill_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  return sx_launch(kern, dim3(n_tiles, nh), dim3(FT_THREADS), smem, stream, mq, mk, mv, (bf16*)out, tile_seq, tile_q0,
+  return sx_launch(kern, dim3(nh, n_tiles), dim3(FT_THREADS), smem, stream, mq, mk, mv, (bf16*)out, tile_seq, tile_q0,
                    cu_seqlens, seq_past, seq_lens, block_table, maxp, nh, nkv, scale * 1.4426950408889634f, window, status);
 }
 
