@@ -289,12 +289,16 @@ template <int EPI, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                            const __grid_constant__ CUtensorMap map_w,
                                                                            void* __restrict__ out, int M, int N, int K,
+                                                                           int tail_tiles, int tail_splits,
+                                                                           float* __restrict__ tail_ws,
+                                                                           int* __restrict__ tail_count,
                                                                            int* __restrict__ status) {
   constexpr int STAGES = TcShape<BN>::STAGES, B_BYTES = TcShape<BN>::B_BYTES, STAGE_BYTES = TcShape<BN>::STAGE_BYTES;
   extern __shared__ unsigned char tc_smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);   // full[S], empty[S], acc_full[2], acc_empty[2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* tail_last = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + STAGES);
   const uint32_t acc_full0 = tc_smem(bars + 2 * STAGES), acc_empty0 = tc_smem(bars + 2 * STAGES + 2);
 
@@ -302,8 +306,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
   const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;
   const int tile_n = (EPI == TC_EPI_SILU_MUL) ? BN / 2 : BN;
   const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (n_out + tile_n - 1) / tile_n;
-  const int n_tiles = tiles_m * tiles_n;
   const int nkb = (K + TC_BK - 1) / TC_BK;
+  // Work items.  Each of the last tail_tiles tiles (the bottom of the last column of tiles) is cut into
+  // tail_splits items that take a range of K each and leave a float32 partial tile in tail_ws [split][rows
+  // of the tail][columns of the last column of tiles]; the blocks of a tile's items then add the partial
+  // tiles up together, in split order.  These short items come FIRST (one round, padded to the grid), the
+  // whole tiles after them, so that the adding-up hides behind the next tile's MMAs.
+  const int n_full = tiles_m * tiles_n - tail_tiles;
+  const int n_tail_items = tail_tiles * tail_splits;
+  const int tail_round = n_tail_items > 0 ? ((n_tail_items + (int)gridDim.x - 1) / (int)gridDim.x) * (int)gridDim.x : 0;
+  const int n_items = tail_round + n_full;
+  const int tail_kper = tail_splits > 0 ? (nkb + tail_splits - 1) / tail_splits : nkb;
+  // false: a padding item, nothing to do
+  auto item_of = [&](int item, int& tile, int& kb_lo, int& kb_hi, int& z) -> bool {
+    if (item >= tail_round) { tile = item - tail_round; kb_lo = 0; kb_hi = nkb; z = -1; return true; }
+    if (item >= n_tail_items) return false;
+    tile = n_full + item / tail_splits;
+    z = item % tail_splits;
+    kb_lo = z * tail_kper;
+    kb_hi = min(nkb, kb_lo + tail_kper);
+    return true;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -331,9 +354,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        int tile, kb_lo, kb_hi, z;
+        if (!item_of(item, tile, kb_lo, kb_hi, z)) continue;
         const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * tile_n;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           if (!tc_mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) { atomicExch(status, 1); ok = false; break; }
           tc_mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
@@ -351,19 +376,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
       constexpr uint32_t idesc = tc_instr_desc(TC_BM, BN);
       uint32_t it = 0, t = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++t) {
-        const uint32_t buf = t & 1;
-        if (!tc_mbar_wait(acc_empty0 + 8 * buf, ((t >> 1) & 1) ^ 1)) { atomicExch(status, 4); ok = false; break; }
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        int tile, kb_lo, kb_hi, z;
+        if (!item_of(item, tile, kb_lo, kb_hi, z)) continue;
+        const uint32_t buf = t & 1, use = t >> 1;
+        ++t;
+        if (!tc_mbar_wait(acc_empty0 + 8 * buf, (use & 1) ^ 1)) { atomicExch(status, 4); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           if (!tc_mbar_wait(full0 + 8 * s, (it / STAGES) & 1)) { atomicExch(status, 2); ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
           const uint32_t a_addr = tc_smem(tiles + s * STAGE_BYTES), b_addr = a_addr + TC_A_BYTES;
 #pragma unroll
           for (int k = 0; k < TC_BK / 16; ++k)
-            tc_mma(d_tmem, tc_smem_desc(a_addr + k * 32), tc_smem_desc(b_addr + k * 32), idesc, (kb | k) != 0);
+            tc_mma(d_tmem, tc_smem_desc(a_addr + k * 32), tc_smem_desc(b_addr + k * 32), idesc, kb != kb_lo || k != 0);
           tc_commit(empty0 + 8 * s);
         }
         tc_commit(acc_full0 + 8 * buf);
@@ -373,11 +401,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
   } else {
     const int quarter = warp & 3;
     uint32_t t = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
-      const uint32_t buf = t & 1;
+    // the tail's block of the output: rows from tail_m0 on, the last column of tiles
+    const int tail_m0 = (tiles_m - tail_tiles) * TC_BM, tail_n0 = (tiles_n - 1) * tile_n;
+    const int tail_rows = M - tail_m0, tail_cols = n_out - tail_n0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      int tile, kb_lo, kb_hi, z;
+      if (!item_of(item, tile, kb_lo, kb_hi, z)) continue;
+      const uint32_t buf = t & 1, use = t >> 1;
+      ++t;
       const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * tile_n;
       const int row = m0 + quarter * 32 + lane;
-      if (!tc_mbar_wait(acc_full0 + 8 * buf, (t >> 1) & 1)) {
+      if (!tc_mbar_wait(acc_full0 + 8 * buf, use & 1)) {
         if (lane == 0) atomicExch(status, 3);
         break;
       }
@@ -395,7 +429,92 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
           __syncwarp();
           if (lane == 0) tc_mbar_arrive(acc_empty0 + 8 * buf);
         }
-        if (row < M && n0 + c0 < n_out) tc_store_chunk<EPI>(v, u, out, row, n0 + c0, n_out);
+        if (row < M && n0 + c0 < n_out) {
+          if (z < 0) tc_store_chunk<EPI>(v, u, out, row, n0 + c0, n_out);
+          else tc_store_chunk<TC_EPI_F32>(v, u, tail_ws + (size_t)z * tail_rows * tail_cols, row - tail_m0, c0, tail_cols);
+        }
+      }
+      if (z >= 0) {
+        // The blocks that hold the items of one tile add its partial tiles up together: each waits (bounded)
+        // until all of them have stored theirs, then takes a share of the tile's rows and adds the partial
+        // tiles in split order.  All items of the tail run in the same first round on blocks that are
+        // resident together, so the wait is short.  tail_count[2 tile], [2 tile + 1] count arrivals and
+        // departures; the last block to leave sets both back to zero.
+        int* cnt = tail_count + 2 * (tile - n_full);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");                 // the four epilogue warps
+        if (threadIdx.x == 64) {
+          atomicAdd(cnt, 1);
+          bool all = false;
+          for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
+            int v;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(cnt) : "memory");
+            if (v >= tail_splits) { all = true; break; }
+          }
+          if (!all) atomicExch(status, 5);
+          *tail_last = all;
+        }
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        if (*tail_last) {
+          __threadfence();
+          const int et = threadIdx.x - 64;                                // 0..127 among the epilogue threads
+          const int per = (TC_BM + tail_splits - 1) / tail_splits;
+          const int r_lo = m0 + z * per, r_hi = min(min(m0 + TC_BM, M), r_lo + per);
+          const size_t plane = (size_t)tail_rows * tail_cols;
+          if ((tail_cols & 3) == 0) {
+            // two rows at a time: 64 threads a row, four columns a thread
+            const int c4 = (et & 63) * 4;
+            // six of a thread's rows at a time, so that 24 loads are in flight (a row at a time took one
+            // round trip to L2 per four loads: 18 us for this step, now 3)
+            for (int rb = r_lo + (et >> 6); rb < r_hi && c4 < tail_cols; rb += 12) {
+              float4 acc[6];
+#pragma unroll
+              for (int i = 0; i < 6; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+              for (int zz = 0; zz < tail_splits; ++zz) {
+#pragma unroll
+                for (int i = 0; i < 6; ++i) {
+                  const int r = rb + 2 * i;
+                  if (r < r_hi) {
+                    const float4 f = __ldcg(reinterpret_cast<const float4*>(tail_ws + zz * plane + (size_t)(r - tail_m0) * tail_cols + c4));
+                    acc[i].x += f.x; acc[i].y += f.y; acc[i].z += f.z; acc[i].w += f.w;
+                  }
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < 6; ++i) {
+                const int r = rb + 2 * i;
+                if (r >= r_hi) continue;
+                if (EPI == TC_EPI_F32) {
+                  *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)r * n_out + tail_n0 + c4) = acc[i];
+                } else {
+                  bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)r * n_out + tail_n0 + c4;
+                  __nv_bfloat162 lo = __floats2bfloat162_rn(acc[i].x, acc[i].y), hi = __floats2bfloat162_rn(acc[i].z, acc[i].w);
+                  if ((n_out & 3) == 0) {
+                    uint2 pkd;
+                    pkd.x = *reinterpret_cast<uint32_t*>(&lo); pkd.y = *reinterpret_cast<uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(dst) = pkd;
+                  } else {
+                    dst[0] = __low2bfloat16(lo); dst[1] = __high2bfloat16(lo); dst[2] = __low2bfloat16(hi); dst[3] = __high2bfloat16(hi);
+                  }
+                }
+              }
+            }
+          } else {
+            for (int r = r_lo; r < r_hi; ++r)
+              for (int c = et; c < tail_cols; c += 128) {
+                const float* src = tail_ws + (size_t)(r - tail_m0) * tail_cols + c;
+                float acc = 0.f;
+                for (int zz = 0; zz < tail_splits; ++zz) acc += __ldcg(src + zz * plane);
+                if (EPI == TC_EPI_F32) reinterpret_cast<float*>(out)[(size_t)r * n_out + tail_n0 + c] = acc;
+                else reinterpret_cast<bf16*>(out)[(size_t)r * n_out + tail_n0 + c] = __float2bfloat16_rn(acc);
+              }
+          }
+        }
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");                 // everyone has read; tail_last is free again
+        if (threadIdx.x == 64 && *tail_last) {
+          if (atomicAdd(cnt + 1, 1) == tail_splits - 1) { cnt[1] = 0; __threadfence(); cnt[0] = 0; }
+        }
       }
     }
   }
@@ -479,24 +598,27 @@ static int tc_sm_count() {
 
 template <int EPI, int BN>
 static int tc_launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K,
-                                cudaStream_t stream) {
+                                int tail_tiles, int tail_splits, float* tail_ws, int* tail_count, cudaStream_t stream) {
   int* status = tc_status_word();
   if (!status) return (int)cudaErrorMemoryAllocation;
   const int tile_n = (EPI == TC_EPI_SILU_MUL) ? BN / 2 : BN;
   const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;
-  const long long n_tiles = (long long)((n_out + tile_n - 1) / tile_n) * ((M + TC_BM - 1) / TC_BM);
+  const long long n_tiles = (long long)((n_out + tile_n - 1) / tile_n) * ((M + TC_BM - 1) / TC_BM) - tail_tiles;
+  if (n_tiles <= 0 || n_tiles > 0x3fffffffLL) return SX_ERR_SIZE;
   const int sms = tc_sm_count();
   const int grid = (int)(n_tiles < sms ? n_tiles : sms);
-  const size_t smem = 1024 + TcShape<BN>::STAGES * TcShape<BN>::STAGE_BYTES + (2 * TcShape<BN>::STAGES + 4) * sizeof(uint64_t) + 16;
+  const size_t smem = 1024 + TcShape<BN>::STAGES * TcShape<BN>::STAGE_BYTES + (2 * TcShape<BN>::STAGES + 4) * sizeof(uint64_t) + 32;
   auto kern = gemm_tc_persistent_kernel<EPI, BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  return sx_launch(kern, grid, dim3(TC_THREADS), smem, stream, ma, mw, out, M, N, K, status);
+  return sx_launch(kern, grid, dim3(TC_THREADS), smem, stream, ma, mw, out, M, N, K, tail_tiles, tail_splits, tail_ws, tail_count, status);
 }
 
 // sum of the split-K partial tiles ws[splits][M][N] in split order, then the epilogue
 template <int EPI>
-__global__ void tc_splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ out, int splits, int M, int N) {
+// (out has rows of ldo values: a block of a larger matrix when ldo > the block's width)
+__global__ void tc_splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ out, int splits, int M, int N,
+                                        long long ldo) {
   pdl_wait();
   pdl_trigger();
   const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;
@@ -510,39 +632,20 @@ __global__ void tc_splitk_reduce_kernel(const float* __restrict__ ws, void* __re
     a += ws[z * plane + m * N + n];
     if (EPI == TC_EPI_SILU_MUL) b += ws[z * plane + m * N + n_out + n];
   }
-  if (EPI == TC_EPI_SILU_MUL) reinterpret_cast<bf16*>(out)[idx] = __float2bfloat16_rn(a / (1.f + expf(-a)) * b);
-  else if (EPI == TC_EPI_F32) reinterpret_cast<float*>(out)[idx] = a;
-  else reinterpret_cast<bf16*>(out)[idx] = __float2bfloat16_rn(a);
+  const size_t o = m * (size_t)ldo + n;
+  if (EPI == TC_EPI_SILU_MUL) reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(a / (1.f + expf(-a)) * b);
+  else if (EPI == TC_EPI_F32) reinterpret_cast<float*>(out)[o] = a;
+  else reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(a);
 }
 
-// A [M, K], W [N, K] bfloat16 row-major, 16-byte aligned, K % 8 == 0.
-// epi 0: out bf16 [M, N]; 1: out f32 [M, N]; 2: W = [gate; up] stacked, out bf16 [M, N/2].
-// splits == 1: one block per 128 x 256 tile, epilogue in the kernel.
-// splits > 1 (for few rows, where whole tiles would leave most SMs idle): 128 x 128 tiles, K split over
-// `splits` blocks whose float32 partial tiles go to `workspace` [splits, M, N] and are added, in split
-// order, by a second kernel that applies the epilogue.  Every split gets a non-empty range of K.
-extern "C" int sx_gemm_tc(const void* A, const void* W, void* out, int M, int N, int K, int epi, int splits,
-                          float* workspace, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || (K & 7) || splits < 1) return SX_ERR_SIZE;
-  if (epi == TC_EPI_SILU_MUL && (N & 1)) return SX_ERR_SIZE;
-  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return SX_ERR_ALIGN;
+// K split over `splits` blocks per 128 x 128 tile, float32 partial tiles in `workspace` [splits, M, N], then the sum
+// in split order with the epilogue into out (rows of ldo values)
+static int tc_split_product(const void* A, const void* W, void* out, int M, int N, int K, int epi, int splits,
+                            float* workspace, long long ldo, cudaStream_t stream) {
   CUtensorMap ma, mw;
   int rc = tc_make_map(&ma, A, M, K);
   if (rc) return rc;
-  rc = tc_make_map(&mw, W, N, K);
-  if (rc) return rc;
-  if (splits == 1) {
-    switch (epi) {
-      // (128-wide tiles were tried for shapes whose last wave is nearly empty: the MMA then waits on
-      //  shared-memory reads of A and the product got slower, 607 against 828 TFLOP/s)
-      case TC_EPI_BF16: return tc_launch_persistent<TC_EPI_BF16, 256>(ma, mw, out, M, N, K, stream);
-      case TC_EPI_F32: return tc_launch_persistent<TC_EPI_F32, 256>(ma, mw, out, M, N, K, stream);
-      case TC_EPI_SILU_MUL: return tc_launch_persistent<TC_EPI_SILU_MUL, 256>(ma, mw, out, M, N, K, stream);
-      default: return SX_ERR_DTYPE;
-    }
-  }
-  if (!workspace) return SX_ERR_SIZE;
+  if ((rc = tc_make_map(&mw, W, N, K))) return rc;
   const int nkb = (K + TC_BK - 1) / TC_BK;
   if (splits > nkb) splits = nkb;
   const int kper = (nkb + splits - 1) / splits;
@@ -552,14 +655,63 @@ extern "C" int sx_gemm_tc(const void* A, const void* W, void* out, int M, int N,
   const size_t n_elems = (size_t)M * (epi == TC_EPI_SILU_MUL ? N / 2 : N);
   const unsigned grid = (unsigned)((n_elems + 255) / 256);
   switch (epi) {
-    case TC_EPI_BF16: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_BF16>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N);
-    case TC_EPI_F32: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_F32>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N);
-    case TC_EPI_SILU_MUL: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_SILU_MUL>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N);
+    case TC_EPI_BF16: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_BF16>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N, ldo);
+    case TC_EPI_F32: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_F32>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N, ldo);
+    case TC_EPI_SILU_MUL: return sx_launch(tc_splitk_reduce_kernel<TC_EPI_SILU_MUL>, dim3(grid), dim3(256), 0, stream, (const float*)workspace, out, splits, M, N, ldo);
     default: return SX_ERR_DTYPE;
   }
 }
 
-// 0, or which bounded wait ran out (1 producer, 2 MMA issuer, 3 epilogue)
+// A [M, K], W [N, K] bfloat16 row-major, 16-byte aligned, K % 8 == 0.
+// epi 0: out bf16 [M, N]; 1: out f32 [M, N]; 2: W = [gate; up] stacked, out bf16 [M, N/2].
+// splits == 1: the persistent kernel over 128 x 256 tiles, epilogue in the kernel.  With tail_tiles > 0 (epi 0 and 1)
+//   each of the LAST tail_tiles tiles (the bottom rows of the last column of tiles; tail_tiles <= row tiles) is
+//   computed as tail_splits work items that split K and leave float32 partial tiles in the workspace; the blocks
+//   of a tile's items then add them up together, in split order: when the last round of tiles would keep only a
+//   few SMs busy, the whole product otherwise takes a full tile's time longer.
+// splits > 1 (for few rows, where whole tiles would leave most SMs idle): 128 x 128 tiles, K split over
+//   `splits` blocks whose float32 partial tiles go to `workspace` [splits, M, N] and are added, in split
+//   order, by a second kernel that applies the epilogue.  Every split gets a non-empty range of K.
+// workspace: splits * M * N floats, or tail_splits * (rows of the tail) * (columns of the last column of tiles) floats.
+// tail_count: 2 * tail_tiles ints that are zero (the kernel leaves them zero).
+extern "C" int sx_gemm_tc(const void* A, const void* W, void* out, int M, int N, int K, int epi, int splits,
+                          float* workspace, int tail_tiles, int tail_splits, int* tail_count, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7) || splits < 1 || tail_tiles < 0) return SX_ERR_SIZE;
+  if (epi == TC_EPI_SILU_MUL && (N & 1)) return SX_ERR_SIZE;
+  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return SX_ERR_ALIGN;
+  if (splits > 1) {
+    if (!workspace || tail_tiles) return SX_ERR_SIZE;
+    return tc_split_product(A, W, out, M, N, K, epi, splits, workspace, epi == TC_EPI_SILU_MUL ? N / 2 : N, stream);
+  }
+  CUtensorMap ma, mw;
+  int rc = tc_make_map(&ma, A, M, K);
+  if (rc) return rc;
+  rc = tc_make_map(&mw, W, N, K);
+  if (rc) return rc;
+  if (tail_tiles > 0) {
+    const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + 255) / 256;
+    const int nkb = (K + TC_BK - 1) / TC_BK;
+    if (epi == TC_EPI_SILU_MUL || tail_tiles > tiles_m || tail_tiles >= tiles_m * tiles_n || tail_splits < 1 || !workspace || !tail_count)
+      return SX_ERR_SIZE;
+    if (tail_splits > nkb) tail_splits = nkb;
+    const int kper = (nkb + tail_splits - 1) / tail_splits;
+    tail_splits = (nkb + kper - 1) / kper;          // no empty range
+    return epi == TC_EPI_F32
+               ? tc_launch_persistent<TC_EPI_F32, 256>(ma, mw, out, M, N, K, tail_tiles, tail_splits, workspace, tail_count, stream)
+               : tc_launch_persistent<TC_EPI_BF16, 256>(ma, mw, out, M, N, K, tail_tiles, tail_splits, workspace, tail_count, stream);
+  }
+  switch (epi) {
+    // (128-wide tiles were tried for shapes whose last wave is nearly empty: the MMA then waits on
+    //  shared-memory reads of A and the product got slower, 607 against 828 TFLOP/s)
+    case TC_EPI_BF16: return tc_launch_persistent<TC_EPI_BF16, 256>(ma, mw, out, M, N, K, 0, 0, nullptr, nullptr, stream);
+    case TC_EPI_F32: return tc_launch_persistent<TC_EPI_F32, 256>(ma, mw, out, M, N, K, 0, 0, nullptr, nullptr, stream);
+    case TC_EPI_SILU_MUL: return tc_launch_persistent<TC_EPI_SILU_MUL, 256>(ma, mw, out, M, N, K, 0, 0, nullptr, nullptr, stream);
+    default: return SX_ERR_DTYPE;
+  }
+}
+
+// 0, or which bounded wait ran out (1 producer, 2 and 4 MMA issuer, 3 epilogue, 5 the tail's blocks waiting for one another)
 extern "C" int sx_gemm_tc_status(int* host_value) {
   int* p = tc_status_word();
   if (!p) return (int)cudaErrorMemoryAllocation;

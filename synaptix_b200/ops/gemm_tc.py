@@ -27,13 +27,43 @@ def plan_splits(M: int, N: int, K: int, n_sm: int) -> int:
     return max(1, min(nkb // 2, (n_sm + tiles_128 // 2) // tiles_128))
 
 
+_TAIL_COUNTS = {}
+
+
+def _tail_counts(device) -> torch.Tensor:
+    """Zeroed int32 counters, one array per device; the kernel leaves them zero."""
+    key = torch.device(device).index or 0
+    if key not in _TAIL_COUNTS:
+        _TAIL_COUNTS[key] = torch.zeros(1024, dtype=torch.int32, device=device)
+    return _TAIL_COUNTS[key]
+
+
+def plan_tail(M: int, N: int, K: int, n_sm: int):
+    """``(tail_tiles, tail_splits)``: how many of the LAST 128 x 256 tiles are computed as several work items
+    that split K, and into how many.  The persistent kernel runs one block per SM
+    over whole tiles; when the tiles of the last round would keep at most a quarter of the SMs busy (2,048
+    rows by 2,560 columns: 160 tiles on 148 SMs), that round costs a full tile's time for little work.
+    The tail is the bottom of the last column of tiles, so it must fit there; ``(0, 0)`` otherwise."""
+    tiles_m, tiles_n = (M + 127) // 128, (N + 255) // 256
+    n_tiles = tiles_m * tiles_n
+    rem = n_tiles % n_sm
+    if n_tiles <= n_sm or rem == 0 or rem > n_sm // 4 or rem > tiles_m or rem > 512:
+        return 0, 0
+    nkb = (K + 63) // 64
+    splits = max(1, min(nkb // 2, n_sm // rem))
+    return (rem, splits) if splits >= 2 else (0, 0)
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None,
-            out: Optional[torch.Tensor] = None, splits: Optional[int] = None) -> torch.Tensor:
+            out: Optional[torch.Tensor] = None, splits: Optional[int] = None,
+            tail: Optional[bool] = None) -> torch.Tensor:
     """``x[M, K] @ w[N, K].T`` on the tcgen05 tensor cores, 32-bit accumulation in tensor memory.
 
     ``splits``: blocks that split K (default: chosen so that the GPU is filled; more than one only
     matters for few rows).  With ``splits > 1`` float32 partial tiles go through a workspace of
     ``splits * M * N`` floats and a second kernel adds them in a fixed order.
+
+    ``tail`` (default: on, ``False`` turns it off): see ``plan_tail``.
 
     ``epilogue``: ``None`` -> bfloat16 ``[M, N]``; ``"f32"`` -> float32 ``[M, N]``; ``"silu_mul"`` ->
     ``w`` is ``[gate; up]`` stacked and the result is bfloat16 ``[M, N/2]``.  Needs ``K % 8 == 0``.
@@ -53,9 +83,19 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None,
     if splits is None:
         splits = plan_splits(M, N, K, sm_count(x.device))
     splits = max(1, min(int(splits), (K + 63) // 64))
-    ws = torch.empty(splits * M * N, dtype=torch.float32, device=x.device) if splits > 1 else None
+    tail_tiles = tail_splits = 0
+    if splits == 1 and epilogue != "silu_mul" and tail is not False:
+        tail_tiles, tail_splits = plan_tail(M, N, K, sm_count(x.device))
+    ws = None
+    if splits > 1:
+        ws = torch.empty(splits * M * N, dtype=torch.float32, device=x.device)
+    elif tail_tiles:
+        m_rows, n_cols = M - ((M + 127) // 128 - tail_tiles) * 128, N - ((N + 255) // 256 - 1) * 256
+        ws = torch.empty(tail_splits * m_rows * n_cols, dtype=torch.float32, device=x.device)
     check(fn("gemm_tc", "sx_gemm_tc")(ptr(x), ptr(w), ptr(out), c_int(M), c_int(N), c_int(K), c_int(_EPI[epilogue]),
-                                      c_int(splits), ptr(ws), stream()), "gemm_tc", launches=2 if splits > 1 else 1)
+                                      c_int(splits), ptr(ws), c_int(tail_tiles), c_int(tail_splits),
+                                      ptr(_tail_counts(x.device) if tail_tiles else None), stream()), "gemm_tc",
+          launches=2 if splits > 1 else 1)
     return out
 
 

@@ -586,6 +586,27 @@ def test_gemm_tc(M, N, K):
     assert gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 2560, 512), (2048, 2560, 4096), (2000, 2500, 328), (1300, 3484, 264)])
+def test_gemm_tc_tail_tiles_by_split_k(M, N, K):
+    """Shapes whose last round of 128 x 256 tiles is nearly empty: those tiles are split over K.  The
+    result must be the product everywhere, on both sides of the seam, for ragged M, N and K as well."""
+    from synaptix_b200.ops.decode import sm_count
+    from synaptix_b200.ops.gemm_tc import gemm_tc, gemm_tc_status, plan_tail
+    tail_tiles, tail_splits = plan_tail(M, N, K, sm_count(torch.device("cuda")))
+    assert tail_tiles > 0 and tail_splits >= 2, "the shape is meant to have a tail on this GPU"
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    for epilogue, tol in (("f32", dict(atol=2e-5 * math.sqrt(K), rtol=1e-5)), (None, dict(atol=2e-2, rtol=2e-2))):
+        out = torch.full((M, N), float("nan"), dtype=torch.float32 if epilogue else torch.bfloat16, device="cuda")
+        gemm_tc(x.cuda(), w.cuda(), epilogue=epilogue, out=out)
+        whole = gemm_tc(x.cuda(), w.cuda(), epilogue=epilogue, tail=False)
+        assert torch.allclose(out.float().cpu().double(), ref, **tol)
+        assert torch.allclose(whole.float().cpu().double(), ref, **tol)
+    assert gemm_tc_status() == 0
+
+
 @pytest.mark.parametrize("M,I,K", [(128, 128, 64), (77, 160, 200), (300, 1000, 2560), (2048, 129, 96)])
 def test_gemm_tc_silu_mul_epilogue(M, I, K):
     from synaptix_b200.ops.gemm_tc import gemm_tc, gemm_tc_status
