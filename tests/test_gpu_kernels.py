@@ -102,7 +102,11 @@ def test_silu_mul(dtype):
 
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("nh,nkv,hd,rot,norm", [(4, 2, 16, 16, True), (6, 2, 32, 32, True), (5, 1, 48, 24, True),
-                                                 (3, 3, 80, 80, False), (2, 1, 256, 0, True)])
+                                                 (3, 3, 80, 80, False), (2, 1, 256, 0, True),
+                                                 # head sizes 64 and 128 (the wide bfloat16 kernel): head counts that do
+                                                 # not fill a warp's group, no rotation, no norm, the benchmark's counts
+                                                 (5, 1, 128, 128, True), (6, 3, 64, 64, True), (3, 1, 128, 0, False),
+                                                 (7, 7, 64, 0, True), (32, 8, 128, 128, True)])
 def test_qkv_prepare_norm_rotation_and_cache_write(dtype, nh, nkv, hd, rot, norm):
     from synaptix_b200 import ops
     from synaptix_b200.parts import rotary_inv_freq
