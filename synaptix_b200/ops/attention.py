@@ -21,10 +21,14 @@ def fast_supported(dtype, nh: int, nkv: int, hd: int) -> bool:
 
 def pick_splits(n_seqs: int, nkv: int, max_pages: int, device) -> int:
     """Splits of a sequence's pages over blocks: as many as keep all blocks in ONE wave (two
-    blocks fit an SM), since a second, partly filled wave costs as much as a full one."""
+    blocks fit an SM), since a second, partly filled wave costs as much as a full one; then
+    no more than give every split a page (a kernel cuts ``ceil(pages / splits)`` pages a split:
+    37 splits of 64 pages are 32 splits of 2 pages and 5 empty blocks, measured 12.5 against 10.3 us)."""
     slots = 2 * sm_count(device)
     base = max(1, n_seqs * nkv)
-    return max(1, min(max_pages, slots // base))
+    s = max(1, min(max_pages, slots // base))
+    per = -(-max_pages // s)
+    return max(1, -(-max_pages // per))
 
 
 _COUNTERS = {}
