@@ -28,6 +28,7 @@
 #define TC_A_BYTES (TC_BM * TC_BK * 2)            // 16 KB
 #define TC_THREADS 192
 #define TC_SPIN_LIMIT (1u << 26)
+#define TC_RED_ROWS 6
 
 enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SILU_MUL = 2, TC_EPI_PARTIAL = 3 };
 
@@ -241,7 +242,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
 // time share W tiles through L2).  Tensor memory holds TWO accumulators (2 x 256 columns): while
 // the epilogue warps read tile i out of one, the MMA warp is already filling the other with tile
 // i + 1, and the TMA ring runs ahead across tiles.  Barriers: full/empty per stage, and
-// acc_full/acc_empty per accumulator.
+// acc_full/acc_empty per accumulator.  When the tiles do not fill a round of all SMs (a nearly empty last
+// round, or fewer tiles than SMs as in steps of a few dozen rows), those tiles are cut over K (TcPlan below).
 // =======================================================================================
 __device__ __forceinline__ void tc_mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
@@ -285,20 +287,76 @@ __device__ __forceinline__ void tc_store_chunk(const uint32_t (&v)[32], const ui
   }
 }
 
+// The work of the persistent kernel.  The tiles are numbered m-fastest.  The first n_whole of them are
+// computed whole, block c taking tiles c, c + G, ...  The remaining R = n_tiles - n_whole tiles (the
+// last round, when it would keep few SMs busy; or ALL tiles, when there is one row of them and they are
+// fewer than SMs) are cut over K into PIECES.  For all tiles cut, "stream-K" fashion: their R * nkb
+// slices of K (64 wide) form one sequence that is dealt out to the G blocks in equal contiguous shares, so
+// a block gets at most two pieces (the end of one tile and the start of the next), and a tile is covered
+// by the pieces of a few consecutive blocks.  For a last round: equal pieces per tile (see tc_piece).
+struct TcPlan {
+  int n_whole, R, nkb, G;
+  int sp;                      // > 0: every cut tile has exactly sp pieces of equal length and no block has two (see tc_piece)
+  long long U;                 // R * nkb
+  __host__ __device__ long long share_begin(int c) const { return U * c / G; }
+  // the block whose share holds unit u
+  __host__ __device__ int block_of(long long u) const { return (int)(((u + 1) * G - 1) / U); }
+};
+struct TcPiece {
+  int tile;                    // tile number (n_whole + index among the cut tiles)
+  int kb_lo, kb_hi;            // its slices of K
+  int z, nz;                   // which of the tile's pieces this is, and how many there are
+};
+// piece i (0 or 1) of block c; false if the block has no such piece.
+// With whole tiles after the pieces (p.sp > 0) the shares are NOT dealt out stream-K fashion: a block with two
+// pieces stores two partial tiles and adds up twice, which took longer than the whole tile's MMAs it should hide
+// behind (measured 51 against 38 us for 2,048 x 2,560 x 4,096).  Tile t then simply has the sp = G / R pieces of
+// blocks t sp .. t sp + sp - 1, and G - R sp blocks have none.
+__host__ __device__ inline bool tc_piece(const TcPlan& p, int c, int i, TcPiece& out) {
+  if (p.R <= 0) return false;
+  if (p.sp > 0) {
+    if (i != 0 || c >= p.R * p.sp) return false;
+    const int t = c / p.sp, z = c % p.sp;
+    const int kper = (p.nkb + p.sp - 1) / p.sp;
+    out.tile = p.n_whole + t;
+    out.kb_lo = z * kper;
+    out.kb_hi = out.kb_lo + kper < p.nkb ? out.kb_lo + kper : p.nkb;
+    out.z = z;
+    out.nz = (p.nkb + kper - 1) / kper;              // pieces that are not empty
+    return out.kb_lo < out.kb_hi;
+  }
+  long long u0 = p.share_begin(c);
+  const long long u1 = p.share_begin(c + 1);
+  if (u0 >= u1) return false;
+  long long t = u0 / p.nkb;
+  if (i == 1) {
+    u0 = (t + 1) * p.nkb;
+    if (u0 >= u1) return false;
+    ++t;
+  }
+  out.tile = p.n_whole + (int)t;
+  out.kb_lo = (int)(u0 - t * p.nkb);
+  out.kb_hi = (int)((u1 < (t + 1) * p.nkb ? u1 : (t + 1) * p.nkb) - t * p.nkb);
+  const int c_lo = p.block_of(t * p.nkb), c_hi = p.block_of((t + 1) * p.nkb - 1);
+  out.z = c - c_lo;
+  out.nz = c_hi - c_lo + 1;
+  return true;
+}
+
 template <int EPI, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                            const __grid_constant__ CUtensorMap map_w,
                                                                            void* __restrict__ out, int M, int N, int K,
-                                                                           int tail_tiles, int tail_splits,
-                                                                           float* __restrict__ tail_ws,
-                                                                           int* __restrict__ tail_count,
+                                                                           int n_whole, int zmax, int sp,
+                                                                           float* __restrict__ piece_ws,
+                                                                           int* __restrict__ piece_count,
                                                                            int* __restrict__ status) {
   constexpr int STAGES = TcShape<BN>::STAGES, B_BYTES = TcShape<BN>::B_BYTES, STAGE_BYTES = TcShape<BN>::STAGE_BYTES;
   extern __shared__ unsigned char tc_smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);   // full[S], empty[S], acc_full[2], acc_empty[2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
-  volatile int* tail_last = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* piece_ok = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + STAGES);
   const uint32_t acc_full0 = tc_smem(bars + 2 * STAGES), acc_empty0 = tc_smem(bars + 2 * STAGES + 2);
 
@@ -307,25 +365,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
   const int tile_n = (EPI == TC_EPI_SILU_MUL) ? BN / 2 : BN;
   const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (n_out + tile_n - 1) / tile_n;
   const int nkb = (K + TC_BK - 1) / TC_BK;
-  // Work items.  Each of the last tail_tiles tiles (the bottom of the last column of tiles) is cut into
-  // tail_splits items that take a range of K each and leave a float32 partial tile in tail_ws [split][rows
-  // of the tail][columns of the last column of tiles]; the blocks of a tile's items then add the partial
-  // tiles up together, in split order.  These short items come FIRST (one round, padded to the grid), the
-  // whole tiles after them, so that the adding-up hides behind the next tile's MMAs.
-  const int n_full = tiles_m * tiles_n - tail_tiles;
-  const int n_tail_items = tail_tiles * tail_splits;
-  const int tail_round = n_tail_items > 0 ? ((n_tail_items + (int)gridDim.x - 1) / (int)gridDim.x) * (int)gridDim.x : 0;
-  const int n_items = tail_round + n_full;
-  const int tail_kper = tail_splits > 0 ? (nkb + tail_splits - 1) / tail_splits : nkb;
-  // false: a padding item, nothing to do
-  auto item_of = [&](int item, int& tile, int& kb_lo, int& kb_hi, int& z) -> bool {
-    if (item >= tail_round) { tile = item - tail_round; kb_lo = 0; kb_hi = nkb; z = -1; return true; }
-    if (item >= n_tail_items) return false;
-    tile = n_full + item / tail_splits;
-    z = item % tail_splits;
-    kb_lo = z * tail_kper;
-    kb_hi = min(nkb, kb_lo + tail_kper);
-    return true;
+  TcPlan plan;
+  plan.n_whole = n_whole; plan.R = tiles_m * tiles_n - n_whole; plan.nkb = nkb; plan.G = (int)gridDim.x;
+  plan.sp = sp;
+  plan.U = (long long)plan.R * nkb;
+  const bool coop = sp > 0;            // the blocks of a cut tile add up in this kernel (else a second kernel does)
+  // This block's work in order: its pieces of the cut tiles FIRST (short, so that adding the partial tiles up
+  // hides behind the MMAs of the whole tiles), then whole tiles blockIdx.x, blockIdx.x + G, ...
+  TcPiece pc[2];
+  int n_pc = 0;
+  if (tc_piece(plan, blockIdx.x, 0, pc[0])) { n_pc = 1; if (tc_piece(plan, blockIdx.x, 1, pc[1])) n_pc = 2; }
+  const int n_mine = n_whole > (int)blockIdx.x ? (n_whole - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const int n_work = n_pc + n_mine;
+  auto work_of = [&](int w, int& tile, int& kb_lo, int& kb_hi) {
+    if (w < n_pc) { tile = pc[w].tile; kb_lo = pc[w].kb_lo; kb_hi = pc[w].kb_hi; }
+    else { tile = blockIdx.x + (w - n_pc) * gridDim.x; kb_lo = 0; kb_hi = nkb; }
   };
 
   if (threadIdx.x == 0) {
@@ -354,9 +408,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        int tile, kb_lo, kb_hi, z;
-        if (!item_of(item, tile, kb_lo, kb_hi, z)) continue;
+      for (int w = 0; w < n_work && ok; ++w) {
+        int tile, kb_lo, kb_hi;
+        work_of(w, tile, kb_lo, kb_hi);
         const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * tile_n;
         for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const uint32_t s = it % STAGES;
@@ -374,13 +428,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = tc_instr_desc(TC_BM, BN);
-      uint32_t it = 0, t = 0;
+      uint32_t it = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        int tile, kb_lo, kb_hi, z;
-        if (!item_of(item, tile, kb_lo, kb_hi, z)) continue;
-        const uint32_t buf = t & 1, use = t >> 1;
-        ++t;
+      for (int w = 0; w < n_work && ok; ++w) {
+        int tile, kb_lo, kb_hi;
+        work_of(w, tile, kb_lo, kb_hi);
+        const uint32_t buf = w & 1, use = w >> 1;
         if (!tc_mbar_wait(acc_empty0 + 8 * buf, (use & 1) ^ 1)) { atomicExch(status, 4); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t d_tmem = tmem_base + buf * BN;
@@ -400,20 +453,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
     __syncwarp();
   } else {
     const int quarter = warp & 3;
-    uint32_t t = 0;
-    // the tail's block of the output: rows from tail_m0 on, the last column of tiles
-    const int tail_m0 = (tiles_m - tail_tiles) * TC_BM, tail_n0 = (tiles_n - 1) * tile_n;
-    const int tail_rows = M - tail_m0, tail_cols = n_out - tail_n0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-      int tile, kb_lo, kb_hi, z;
-      if (!item_of(item, tile, kb_lo, kb_hi, z)) continue;
-      const uint32_t buf = t & 1, use = t >> 1;
-      ++t;
+    const int et = threadIdx.x - 64;                                    // 0..127 among the epilogue threads
+    // a partial tile in the workspace: [tile among the cut ones][piece][128 rows][BN columns] float32
+    auto ws_of = [&](int tile, int z) { return piece_ws + ((size_t)(tile - n_whole) * zmax + z) * (TC_BM * BN); };
+    // a finished accumulator -> out, with the epilogue
+    auto finish_tile = [&](int w, int tile) -> bool {
+      const uint32_t buf = w & 1, use = w >> 1;
       const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * tile_n;
       const int row = m0 + quarter * 32 + lane;
       if (!tc_mbar_wait(acc_full0 + 8 * buf, use & 1)) {
         if (lane == 0) atomicExch(status, 3);
-        break;
+        return false;
       }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const uint32_t t_row = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
@@ -429,93 +479,153 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
           __syncwarp();
           if (lane == 0) tc_mbar_arrive(acc_empty0 + 8 * buf);
         }
-        if (row < M && n0 + c0 < n_out) {
-          if (z < 0) tc_store_chunk<EPI>(v, u, out, row, n0 + c0, n_out);
-          else tc_store_chunk<TC_EPI_F32>(v, u, tail_ws + (size_t)z * tail_rows * tail_cols, row - tail_m0, c0, tail_cols);
+        if (row < M && n0 + c0 < n_out) tc_store_chunk<EPI>(v, u, out, row, n0 + c0, n_out);
+      }
+      return true;
+    };
+    bool alive = true;
+    // 1: this block's pieces.  A piece that is a whole tile is finished at once; the others leave their raw
+    // accumulators (all BN columns) in the workspace and are counted.  Nobody waits yet: a block stores ALL its
+    // pieces first, so that no block's second piece waits behind its neighbour's first.
+    for (int w = 0; w < n_pc && alive; ++w) {
+      const int tile = pc[w].tile;
+      if (pc[w].nz == 1) { alive = finish_tile(w, tile); continue; }
+      const uint32_t buf = w & 1, use = w >> 1;
+      const int m0 = (tile % tiles_m) * TC_BM;
+      const int row = m0 + quarter * 32 + lane;
+      if (!tc_mbar_wait(acc_full0 + 8 * buf, use & 1)) {
+        if (lane == 0) atomicExch(status, 3);
+        alive = false;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const uint32_t t_row = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+      float* dst = ws_of(tile, pc[w].z) + (size_t)(quarter * 32 + lane) * BN;
+      // (four tcgen05.ld on the way per wait)
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 128) {
+        uint32_t v[4][32];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) tc_ld32(t_row + c0 + 32 * j, v[j]);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        if (c0 + 128 >= BN) {
+          asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+          __syncwarp();
+          if (lane == 0) tc_mbar_arrive(acc_empty0 + 8 * buf);
+        }
+        if (row < M) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              reinterpret_cast<float4*>(dst + c0 + 32 * j)[i] = make_float4(__uint_as_float(v[j][4 * i]), __uint_as_float(v[j][4 * i + 1]),
+                                                                            __uint_as_float(v[j][4 * i + 2]), __uint_as_float(v[j][4 * i + 3]));
         }
       }
-      if (z >= 0) {
-        // The blocks that hold the items of one tile add its partial tiles up together: each waits (bounded)
-        // until all of them have stored theirs, then takes a share of the tile's rows and adds the partial
-        // tiles in split order.  All items of the tail run in the same first round on blocks that are
-        // resident together, so the wait is short.  tail_count[2 tile], [2 tile + 1] count arrivals and
-        // departures; the last block to leave sets both back to zero.
-        int* cnt = tail_count + 2 * (tile - n_full);
+      if (coop) {
         __threadfence();
         asm volatile("bar.sync 1, 128;\n" ::: "memory");                 // the four epilogue warps
-        if (threadIdx.x == 64) {
-          atomicAdd(cnt, 1);
-          bool all = false;
-          for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
-            int v;
-            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(cnt) : "memory");
-            if (v >= tail_splits) { all = true; break; }
-          }
-          if (!all) atomicExch(status, 5);
-          *tail_last = all;
+        if (threadIdx.x == 64) atomicAdd(piece_count + 2 * (tile - n_whole), 1);
+      }
+    }
+    // 2: the blocks that hold the pieces of one tile add its partial tiles up together: each waits (bounded)
+    // until all of them have stored theirs, then takes a share of the tile's rows and adds the partial tiles
+    // in piece order, with the epilogue.  All pieces are computed first thing by blocks that are resident
+    // together, so the wait is short, and the MMAs of this block's first whole tile run meanwhile.
+    // piece_count[2 t], [2 t + 1] count arrivals and departures at tile t; the last block to leave zeroes both.
+    // (Without whole tiles to hide behind, coop == 0, a second kernel adds up instead: tc_pieces_reduce_kernel.)
+    for (int w = 0; w < n_pc && alive && coop; ++w) {
+      if (pc[w].nz == 1) continue;
+      const int tile = pc[w].tile, nz = pc[w].nz, z = pc[w].z;
+      int* cnt = piece_count + 2 * (tile - n_whole);
+      if (threadIdx.x == 64) {
+        bool all = false;
+        for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
+          int v;
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(cnt) : "memory");
+          if (v >= nz) { all = true; break; }
         }
-        asm volatile("bar.sync 1, 128;\n" ::: "memory");
-        if (*tail_last) {
-          __threadfence();
-          const int et = threadIdx.x - 64;                                // 0..127 among the epilogue threads
-          const int per = (TC_BM + tail_splits - 1) / tail_splits;
-          const int r_lo = m0 + z * per, r_hi = min(min(m0 + TC_BM, M), r_lo + per);
-          const size_t plane = (size_t)tail_rows * tail_cols;
-          if ((tail_cols & 3) == 0) {
-            // two rows at a time: 64 threads a row, four columns a thread
-            const int c4 = (et & 63) * 4;
-            // six of a thread's rows at a time, so that 24 loads are in flight (a row at a time took one
-            // round trip to L2 per four loads: 18 us for this step, now 3)
-            for (int rb = r_lo + (et >> 6); rb < r_hi && c4 < tail_cols; rb += 12) {
-              float4 acc[6];
+        if (!all) atomicExch(status, 5);
+        *piece_ok = all;
+      }
+      asm volatile("bar.sync 1, 128;\n" ::: "memory");
+      if (*piece_ok) {
+        __threadfence();
+        const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * tile_n;
+        const int rows_here = min(TC_BM, M - m0);
+        const int per = (rows_here + nz - 1) / nz;
+        const int r_lo = m0 + z * per, r_hi = min(m0 + rows_here, r_lo + per);
+        const int cols = min(tile_n, n_out - n0);                        // output columns of this tile
+        constexpr int TPR = EPI == TC_EPI_SILU_MUL ? 32 : 64;            // threads a row (four columns a thread)
+        constexpr int RPI = 128 / TPR;                                   // rows at a time
+        const int c4 = (et % TPR) * 4;
+        const float* base = ws_of(tile, 0);
+        const size_t plane = (size_t)TC_BM * BN;
+        // TC_RED_ROWS of a thread's rows at a time and four pieces unrolled, so that dozens of loads are in flight:
+        // this adding-up runs on 128 threads a block, and with 8 loads in flight it took 40 us for a tile cut
+        // into 13 pieces (longer than the 26 us of MMAs it is meant to hide behind)
+        for (int rb = r_lo + et / TPR; rb < r_hi && c4 < cols; rb += TC_RED_ROWS * RPI) {
+          float4 a[TC_RED_ROWS], b[TC_RED_ROWS];
 #pragma unroll
-              for (int i = 0; i < 6; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int i = 0; i < TC_RED_ROWS; ++i) a[i] = b[i] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
-              for (int zz = 0; zz < tail_splits; ++zz) {
+          for (int zz = 0; zz < nz; ++zz) {
 #pragma unroll
-                for (int i = 0; i < 6; ++i) {
-                  const int r = rb + 2 * i;
-                  if (r < r_hi) {
-                    const float4 f = __ldcg(reinterpret_cast<const float4*>(tail_ws + zz * plane + (size_t)(r - tail_m0) * tail_cols + c4));
-                    acc[i].x += f.x; acc[i].y += f.y; acc[i].z += f.z; acc[i].w += f.w;
-                  }
-                }
-              }
-#pragma unroll
-              for (int i = 0; i < 6; ++i) {
-                const int r = rb + 2 * i;
-                if (r >= r_hi) continue;
-                if (EPI == TC_EPI_F32) {
-                  *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)r * n_out + tail_n0 + c4) = acc[i];
-                } else {
-                  bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)r * n_out + tail_n0 + c4;
-                  __nv_bfloat162 lo = __floats2bfloat162_rn(acc[i].x, acc[i].y), hi = __floats2bfloat162_rn(acc[i].z, acc[i].w);
-                  if ((n_out & 3) == 0) {
-                    uint2 pkd;
-                    pkd.x = *reinterpret_cast<uint32_t*>(&lo); pkd.y = *reinterpret_cast<uint32_t*>(&hi);
-                    *reinterpret_cast<uint2*>(dst) = pkd;
-                  } else {
-                    dst[0] = __low2bfloat16(lo); dst[1] = __high2bfloat16(lo); dst[2] = __low2bfloat16(hi); dst[3] = __high2bfloat16(hi);
-                  }
+            for (int i = 0; i < TC_RED_ROWS; ++i) {
+              const int r = rb + i * RPI;
+              if (r < r_hi) {
+                const float* p = base + zz * plane + (size_t)(r - m0) * BN + c4;
+                const float4 f = __ldcg(reinterpret_cast<const float4*>(p));
+                a[i].x += f.x; a[i].y += f.y; a[i].z += f.z; a[i].w += f.w;
+                if (EPI == TC_EPI_SILU_MUL) {
+                  const float4 h = __ldcg(reinterpret_cast<const float4*>(p + BN / 2));
+                  b[i].x += h.x; b[i].y += h.y; b[i].z += h.z; b[i].w += h.w;
                 }
               }
             }
-          } else {
-            for (int r = r_lo; r < r_hi; ++r)
-              for (int c = et; c < tail_cols; c += 128) {
-                const float* src = tail_ws + (size_t)(r - tail_m0) * tail_cols + c;
-                float acc = 0.f;
-                for (int zz = 0; zz < tail_splits; ++zz) acc += __ldcg(src + zz * plane);
-                if (EPI == TC_EPI_F32) reinterpret_cast<float*>(out)[(size_t)r * n_out + tail_n0 + c] = acc;
-                else reinterpret_cast<bf16*>(out)[(size_t)r * n_out + tail_n0 + c] = __float2bfloat16_rn(acc);
+          }
+#pragma unroll
+          for (int i = 0; i < TC_RED_ROWS; ++i) {
+            const int r = rb + i * RPI;
+            if (r >= r_hi) continue;
+            float o[4] = {a[i].x, a[i].y, a[i].z, a[i].w};
+            if (EPI == TC_EPI_SILU_MUL) {
+              const float u[4] = {b[i].x, b[i].y, b[i].z, b[i].w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) o[j] = o[j] / (1.f + __expf(-o[j])) * u[j];
+            }
+            const size_t at = (size_t)r * n_out + n0 + c4;
+            const bool vec = c4 + 3 < cols && (n_out & 3) == 0;
+            if (EPI == TC_EPI_F32) {
+              float* dst = reinterpret_cast<float*>(out) + at;
+              if (vec) *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+              else
+#pragma unroll
+                for (int j = 0; j < 4; ++j) if (c4 + j < cols) dst[j] = o[j];
+            } else {
+              bf16* dst = reinterpret_cast<bf16*>(out) + at;
+              if (vec) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+                uint2 pkd;
+                pkd.x = *reinterpret_cast<uint32_t*>(&lo); pkd.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(dst) = pkd;
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) if (c4 + j < cols) dst[j] = __float2bfloat16_rn(o[j]);
               }
+            }
           }
         }
-        asm volatile("bar.sync 1, 128;\n" ::: "memory");                 // everyone has read; tail_last is free again
-        if (threadIdx.x == 64 && *tail_last) {
-          if (atomicAdd(cnt + 1, 1) == tail_splits - 1) { cnt[1] = 0; __threadfence(); cnt[0] = 0; }
-        }
       }
+      asm volatile("bar.sync 1, 128;\n" ::: "memory");                   // everyone has read; piece_ok is free again
+      if (threadIdx.x == 64 && *piece_ok) {
+        if (atomicAdd(cnt + 1, 1) == nz - 1) { cnt[1] = 0; __threadfence(); cnt[0] = 0; }
+      }
+      asm volatile("bar.sync 1, 128;\n" ::: "memory");
+    }
+    // 3: the whole tiles
+    for (int w = n_pc; w < n_work && alive; ++w) {
+      alive = finish_tile(w, blockIdx.x + (w - n_pc) * gridDim.x);
     }
   }
 
@@ -570,6 +680,7 @@ static int* tc_status_word() {
   return p;
 }
 
+
 template <int EPI, int BN>
 static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, int splits,
                      cudaStream_t stream) {
@@ -596,22 +707,137 @@ static int tc_sm_count() {
   return n[dev];
 }
 
+// The partial tiles of the cut tiles, added up in piece order, with the epilogue: one thread per (cut tile, row,
+// four columns).  Used when the persistent kernel had no whole tiles to hide its own adding-up behind.
+template <int EPI, int BN>
+__global__ void tc_pieces_reduce_kernel(const float* __restrict__ ws, void* __restrict__ out, int M, int N, int n_whole,
+                                        int R, int nkb, int G, int zmax, int sp) {
+  pdl_wait();
+  pdl_trigger();
+  const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;
+  const int tile_n = (EPI == TC_EPI_SILU_MUL) ? BN / 2 : BN;
+  const int tiles_m = (M + TC_BM - 1) / TC_BM;
+  const int per_row = tile_n / 4;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)R * TC_BM * per_row;
+  if (idx >= total) return;
+  const int t = (int)(idx / (TC_BM * per_row));
+  const int rem = (int)(idx - (long long)t * TC_BM * per_row);
+  const int rr = rem / per_row, c4 = (rem % per_row) * 4;
+  const int tile = n_whole + t;
+  const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * tile_n;
+  const int r = m0 + rr, cols = min(tile_n, n_out - n0);
+  if (r >= M || c4 >= cols) return;
+  TcPlan p;
+  p.n_whole = n_whole; p.R = R; p.nkb = nkb; p.G = G; p.sp = sp; p.U = (long long)R * nkb;
+  const int nz = p.block_of((long long)(t + 1) * nkb - 1) - p.block_of((long long)t * nkb) + 1;      // (stream-K shares: sp == 0 here)
+  if (nz == 1) return;                               // that tile was one block's and is finished
+  const float* src = ws + ((size_t)t * zmax) * (TC_BM * BN) + (size_t)rr * BN + c4;
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+  for (int z = 0; z < nz; ++z) {
+    const float4 f = *reinterpret_cast<const float4*>(src + (size_t)z * (TC_BM * BN));
+    a.x += f.x; a.y += f.y; a.z += f.z; a.w += f.w;
+    if (EPI == TC_EPI_SILU_MUL) {
+      const float4 h = *reinterpret_cast<const float4*>(src + (size_t)z * (TC_BM * BN) + BN / 2);
+      b.x += h.x; b.y += h.y; b.z += h.z; b.w += h.w;
+    }
+  }
+  float o[4] = {a.x, a.y, a.z, a.w};
+  if (EPI == TC_EPI_SILU_MUL) {
+    const float u[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = o[j] / (1.f + __expf(-o[j])) * u[j];
+  }
+  const size_t at = (size_t)r * n_out + n0 + c4;
+  const bool vec = c4 + 3 < cols && (n_out & 3) == 0;
+  if (EPI == TC_EPI_F32) {
+    float* dst = reinterpret_cast<float*>(out) + at;
+    if (vec) *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+    else
+      for (int j = 0; j < 4; ++j) if (c4 + j < cols) dst[j] = o[j];
+  } else {
+    bf16* dst = reinterpret_cast<bf16*>(out) + at;
+    if (vec) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+      uint2 pkd;
+      pkd.x = *reinterpret_cast<uint32_t*>(&lo); pkd.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(dst) = pkd;
+    } else {
+      for (int j = 0; j < 4; ++j) if (c4 + j < cols) dst[j] = __float2bfloat16_rn(o[j]);
+    }
+  }
+}
+
+// What the persistent kernel does for a product: how many tiles are computed whole, how many are cut, the most
+// pieces a cut tile has, and the grid.
+struct TcHostPlan { int n_whole, R, zmax, G, sp; };
+static TcHostPlan tc_plan_stream(int M, int N, int K, int epi, bool allow_cut) {
+  const int tile_n = epi == TC_EPI_SILU_MUL ? 128 : 256;
+  const int n_out = epi == TC_EPI_SILU_MUL ? N / 2 : N;
+  const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (n_out + tile_n - 1) / tile_n;
+  const long long n_tiles_ll = (long long)tiles_m * tiles_n;
+  const int sms = tc_sm_count();
+  const int nkb = (K + TC_BK - 1) / TC_BK;
+  TcHostPlan h;
+  h.sp = 0;
+  if (n_tiles_ll > 0x3fffffffLL) { h.n_whole = -1; h.R = h.zmax = h.G = 0; return h; }
+  const int n_tiles = (int)n_tiles_ll;
+  const int R0 = n_tiles >= sms ? n_tiles % sms : n_tiles;
+  // cut when the round would be at most half full, or for a single row of tiles (few rows: the partial tiles are small)
+  const long long U = (long long)R0 * nkb;
+  // (every block must get at least one slice, so that the blocks of a tile are consecutive: with whole tiles
+  //  before them the grid is all SMs and there must be that many slices; alone, the grid shrinks to the slices)
+  // Fewer tiles than SMs are cut only when they are at least half as many (each then falls into two or three
+  // pieces); a handful of tiles would fall into a dozen pieces each, and the older uniform split (sx_gemm_tc with
+  // splits > 1: 128-wide tiles, fewer and larger partial tiles) measured faster there.
+  // Behind three or more rounds of whole tiles a short last round costs little, and cutting it did not pay
+  // (gate/up at 2,048 rows: 1,216 tiles, 164 us cut against 155 us whole).
+  const bool cut = allow_cut && R0 > 0 && nkb >= 2 && R0 < sms &&
+                   (n_tiles >= sms ? (2 * R0 <= sms && U >= sms && n_tiles < 3 * sms) : (tiles_m == 1 && 2 * R0 >= sms));
+  if (!cut) { h.n_whole = n_tiles; h.R = 0; h.zmax = 0; h.G = n_tiles < sms ? n_tiles : sms; return h; }
+  h.n_whole = n_tiles - R0; h.R = R0; h.G = U < sms ? (int)U : sms;
+  if (h.n_whole > 0) {                               // equal pieces per tile, one piece a block
+    h.sp = sms / R0;
+    if (h.sp > nkb) h.sp = nkb;
+    h.zmax = h.sp;
+    return h;
+  }
+  TcPlan p;
+  p.n_whole = h.n_whole; p.R = R0; p.nkb = nkb; p.G = h.G; p.sp = 0; p.U = U;
+  h.zmax = 1;
+  for (int t = 0; t < R0; ++t) {
+    const int nz = p.block_of((long long)(t + 1) * nkb - 1) - p.block_of((long long)t * nkb) + 1;
+    if (nz > h.zmax) h.zmax = nz;
+  }
+  return h;
+}
+
+// n_whole, cut tiles, most pieces a tile, grid: what sx_gemm_tc will do with a workspace (out4[1] * out4[2] * 128 * 256 floats)
+extern "C" int sx_gemm_tc_plan(int M, int N, int K, int epi, int* out4) {
+  if (M <= 0 || N <= 0 || K <= 0) return SX_ERR_SIZE;
+  const TcHostPlan h = tc_plan_stream(M, N, K, epi, true);
+  if (h.n_whole < 0) return SX_ERR_SIZE;
+  out4[0] = h.n_whole; out4[1] = h.R; out4[2] = h.zmax; out4[3] = h.G;
+  return 0;
+}
+
 template <int EPI, int BN>
 static int tc_launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K,
-                                int tail_tiles, int tail_splits, float* tail_ws, int* tail_count, cudaStream_t stream) {
+                                const TcHostPlan& h, float* ws, int* counts, cudaStream_t stream) {
   int* status = tc_status_word();
   if (!status) return (int)cudaErrorMemoryAllocation;
-  const int tile_n = (EPI == TC_EPI_SILU_MUL) ? BN / 2 : BN;
-  const int n_out = (EPI == TC_EPI_SILU_MUL) ? N / 2 : N;
-  const long long n_tiles = (long long)((n_out + tile_n - 1) / tile_n) * ((M + TC_BM - 1) / TC_BM) - tail_tiles;
-  if (n_tiles <= 0 || n_tiles > 0x3fffffffLL) return SX_ERR_SIZE;
-  const int sms = tc_sm_count();
-  const int grid = (int)(n_tiles < sms ? n_tiles : sms);
+  if (h.n_whole < 0 || h.G <= 0) return SX_ERR_SIZE;
   const size_t smem = 1024 + TcShape<BN>::STAGES * TcShape<BN>::STAGE_BYTES + (2 * TcShape<BN>::STAGES + 4) * sizeof(uint64_t) + 32;
   auto kern = gemm_tc_persistent_kernel<EPI, BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  return sx_launch(kern, grid, dim3(TC_THREADS), smem, stream, ma, mw, out, M, N, K, tail_tiles, tail_splits, tail_ws, tail_count, status);
+  // with whole tiles after them, the blocks of a cut tile add up inside the kernel; without, a second kernel does
+  int rc = sx_launch(kern, h.G, dim3(TC_THREADS), smem, stream, ma, mw, out, M, N, K, h.n_whole, h.zmax, h.sp, ws, counts, status);
+  if (rc || h.R == 0 || h.sp > 0) return rc;
+  const int tile_n = (EPI == TC_EPI_SILU_MUL) ? BN / 2 : BN;
+  const long long total = (long long)h.R * TC_BM * (tile_n / 4);
+  return sx_launch(tc_pieces_reduce_kernel<EPI, BN>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const float*)ws, out,
+                   M, N, h.n_whole, h.R, (K + TC_BK - 1) / TC_BK, h.G, h.zmax, 0);
 }
 
 // sum of the split-K partial tiles ws[splits][M][N] in split order, then the epilogue
@@ -664,24 +890,21 @@ static int tc_split_product(const void* A, const void* W, void* out, int M, int 
 
 // A [M, K], W [N, K] bfloat16 row-major, 16-byte aligned, K % 8 == 0.
 // epi 0: out bf16 [M, N]; 1: out f32 [M, N]; 2: W = [gate; up] stacked, out bf16 [M, N/2].
-// splits == 1: the persistent kernel over 128 x 256 tiles, epilogue in the kernel.  With tail_tiles > 0 (epi 0 and 1)
-//   each of the LAST tail_tiles tiles (the bottom rows of the last column of tiles; tail_tiles <= row tiles) is
-//   computed as tail_splits work items that split K and leave float32 partial tiles in the workspace; the blocks
-//   of a tile's items then add them up together, in split order: when the last round of tiles would keep only a
-//   few SMs busy, the whole product otherwise takes a full tile's time longer.
-// splits > 1 (for few rows, where whole tiles would leave most SMs idle): 128 x 128 tiles, K split over
-//   `splits` blocks whose float32 partial tiles go to `workspace` [splits, M, N] and are added, in split
-//   order, by a second kernel that applies the epilogue.  Every split gets a non-empty range of K.
-// workspace: splits * M * N floats, or tail_splits * (rows of the tail) * (columns of the last column of tiles) floats.
-// tail_count: 2 * tail_tiles ints that are zero (the kernel leaves them zero).
+// splits == 1: the persistent kernel over 128 x 256 tiles, epilogue in the kernel.  With a workspace it cuts the
+//   tiles that would not fill a round of all SMs over K (sx_gemm_tc_plan says how): `workspace` holds
+//   ws_floats >= cut tiles * most pieces a tile * 128 * 256 floats, `counts` 2 * cut tiles ints that are zero
+//   (the kernel leaves them zero).  Without a workspace every tile is computed whole.
+// splits > 1: 128 x 128 tiles, K split over `splits` blocks whose float32 partial tiles go to `workspace`
+//   [splits, M, N] and are added, in split order, by a second kernel that applies the epilogue.  Every split
+//   gets a non-empty range of K.
 extern "C" int sx_gemm_tc(const void* A, const void* W, void* out, int M, int N, int K, int epi, int splits,
-                          float* workspace, int tail_tiles, int tail_splits, int* tail_count, cudaStream_t stream) {
+                          float* workspace, unsigned long long ws_floats, int* counts, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || (K & 7) || splits < 1 || tail_tiles < 0) return SX_ERR_SIZE;
+  if (K <= 0 || (K & 7) || splits < 1) return SX_ERR_SIZE;
   if (epi == TC_EPI_SILU_MUL && (N & 1)) return SX_ERR_SIZE;
   if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return SX_ERR_ALIGN;
   if (splits > 1) {
-    if (!workspace || tail_tiles) return SX_ERR_SIZE;
+    if (!workspace || ws_floats < (unsigned long long)splits * M * N) return SX_ERR_SIZE;
     return tc_split_product(A, W, out, M, N, K, epi, splits, workspace, epi == TC_EPI_SILU_MUL ? N / 2 : N, stream);
   }
   CUtensorMap ma, mw;
@@ -689,29 +912,19 @@ extern "C" int sx_gemm_tc(const void* A, const void* W, void* out, int M, int N,
   if (rc) return rc;
   rc = tc_make_map(&mw, W, N, K);
   if (rc) return rc;
-  if (tail_tiles > 0) {
-    const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + 255) / 256;
-    const int nkb = (K + TC_BK - 1) / TC_BK;
-    if (epi == TC_EPI_SILU_MUL || tail_tiles > tiles_m || tail_tiles >= tiles_m * tiles_n || tail_splits < 1 || !workspace || !tail_count)
-      return SX_ERR_SIZE;
-    if (tail_splits > nkb) tail_splits = nkb;
-    const int kper = (nkb + tail_splits - 1) / tail_splits;
-    tail_splits = (nkb + kper - 1) / kper;          // no empty range
-    return epi == TC_EPI_F32
-               ? tc_launch_persistent<TC_EPI_F32, 256>(ma, mw, out, M, N, K, tail_tiles, tail_splits, workspace, tail_count, stream)
-               : tc_launch_persistent<TC_EPI_BF16, 256>(ma, mw, out, M, N, K, tail_tiles, tail_splits, workspace, tail_count, stream);
-  }
+  TcHostPlan h = tc_plan_stream(M, N, K, epi, workspace != nullptr && counts != nullptr);
+  if (h.R > 0 && (ws_floats < (unsigned long long)h.R * h.zmax * TC_BM * 256 || ((uintptr_t)workspace & 15))) return SX_ERR_SIZE;
   switch (epi) {
     // (128-wide tiles were tried for shapes whose last wave is nearly empty: the MMA then waits on
     //  shared-memory reads of A and the product got slower, 607 against 828 TFLOP/s)
-    case TC_EPI_BF16: return tc_launch_persistent<TC_EPI_BF16, 256>(ma, mw, out, M, N, K, 0, 0, nullptr, nullptr, stream);
-    case TC_EPI_F32: return tc_launch_persistent<TC_EPI_F32, 256>(ma, mw, out, M, N, K, 0, 0, nullptr, nullptr, stream);
-    case TC_EPI_SILU_MUL: return tc_launch_persistent<TC_EPI_SILU_MUL, 256>(ma, mw, out, M, N, K, 0, 0, nullptr, nullptr, stream);
+    case TC_EPI_BF16: return tc_launch_persistent<TC_EPI_BF16, 256>(ma, mw, out, M, N, K, h, workspace, counts, stream);
+    case TC_EPI_F32: return tc_launch_persistent<TC_EPI_F32, 256>(ma, mw, out, M, N, K, h, workspace, counts, stream);
+    case TC_EPI_SILU_MUL: return tc_launch_persistent<TC_EPI_SILU_MUL, 256>(ma, mw, out, M, N, K, h, workspace, counts, stream);
     default: return SX_ERR_DTYPE;
   }
 }
 
-// 0, or which bounded wait ran out (1 producer, 2 and 4 MMA issuer, 3 epilogue, 5 the tail's blocks waiting for one another)
+// 0, or which bounded wait ran out (1 producer, 2 and 4 MMA issuer, 3 epilogue, 5 the blocks of a cut tile waiting for one another)
 extern "C" int sx_gemm_tc_status(int* host_value) {
   int* p = tc_status_word();
   if (!p) return (int)cudaErrorMemoryAllocation;

@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -16,9 +17,21 @@ def tc_supported(M: int, N: int, K: int, x_dtype, w_dtype) -> bool:
     return x_dtype == torch.bfloat16 and w_dtype == torch.bfloat16 and K > 0 and K % 8 == 0 and M > 0 and N > 0
 
 
+_COUNTS = {}
+
+
+def _counts(device) -> torch.Tensor:
+    """Zeroed int32 counters, one array per device; the kernel leaves them zero."""
+    key = torch.device(device).index or 0
+    if key not in _COUNTS:
+        _COUNTS[key] = torch.zeros(2048, dtype=torch.int32, device=device)
+    return _COUNTS[key]
+
+
 def plan_splits(M: int, N: int, K: int, n_sm: int) -> int:
-    """How many blocks split K: 1 when whole 128 x 256 tiles already fill the GPU, else enough
-    128 x 128 tiles x splits to give every SM a block (each split at least two 64-wide slices)."""
+    """Blocks that split K in the two-kernel form, for products with only a handful of 128 x 256 tiles (few rows
+    and a narrow matrix): 1 when whole tiles already fill three quarters of the GPU, else enough 128 x 128
+    tiles x splits to give every SM a block (each split at least two 64-wide slices)."""
     tiles_256 = ((N + 255) // 256) * ((M + 127) // 128)
     if tiles_256 >= (n_sm * 3) // 4:
         return 1
@@ -27,43 +40,28 @@ def plan_splits(M: int, N: int, K: int, n_sm: int) -> int:
     return max(1, min(nkb // 2, (n_sm + tiles_128 // 2) // tiles_128))
 
 
-_TAIL_COUNTS = {}
-
-
-def _tail_counts(device) -> torch.Tensor:
-    """Zeroed int32 counters, one array per device; the kernel leaves them zero."""
-    key = torch.device(device).index or 0
-    if key not in _TAIL_COUNTS:
-        _TAIL_COUNTS[key] = torch.zeros(1024, dtype=torch.int32, device=device)
-    return _TAIL_COUNTS[key]
-
-
-def plan_tail(M: int, N: int, K: int, n_sm: int):
-    """``(tail_tiles, tail_splits)``: how many of the LAST 128 x 256 tiles are computed as several work items
-    that split K, and into how many.  The persistent kernel runs one block per SM
-    over whole tiles; when the tiles of the last round would keep at most a quarter of the SMs busy (2,048
-    rows by 2,560 columns: 160 tiles on 148 SMs), that round costs a full tile's time for little work.
-    The tail is the bottom of the last column of tiles, so it must fit there; ``(0, 0)`` otherwise."""
-    tiles_m, tiles_n = (M + 127) // 128, (N + 255) // 256
-    n_tiles = tiles_m * tiles_n
-    rem = n_tiles % n_sm
-    if n_tiles <= n_sm or rem == 0 or rem > n_sm // 4 or rem > tiles_m or rem > 512:
-        return 0, 0
-    nkb = (K + 63) // 64
-    splits = max(1, min(nkb // 2, n_sm // rem))
-    return (rem, splits) if splits >= 2 else (0, 0)
+def plan_stream(M: int, N: int, K: int, epilogue: Optional[str] = None):
+    """``(whole tiles, cut tiles, most pieces a cut tile has, grid)`` of the persistent kernel on the current
+    device.  Tiles that would not fill a round of all SMs (a last round at most half full: 2,048 x 2,560 has
+    160 tiles for 148 SMs; or all tiles of a step with at most 128 rows) are cut over K: their 64-wide slices
+    of K form one sequence that is dealt out to the blocks in equal contiguous shares, the blocks of a tile
+    leave float32 partial tiles in a workspace and add them up together, in a fixed order."""
+    out = (ctypes.c_int * 4)()
+    check(fn("gemm_tc", "sx_gemm_tc_plan")(c_int(M), c_int(N), c_int(K), c_int(_EPI[epilogue]), out), "gemm_tc_plan",
+          launches=0)
+    return tuple(int(v) for v in out)
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None,
             out: Optional[torch.Tensor] = None, splits: Optional[int] = None,
-            tail: Optional[bool] = None) -> torch.Tensor:
+            cut: Optional[bool] = None) -> torch.Tensor:
     """``x[M, K] @ w[N, K].T`` on the tcgen05 tensor cores, 32-bit accumulation in tensor memory.
 
-    ``splits``: blocks that split K (default: chosen so that the GPU is filled; more than one only
-    matters for few rows).  With ``splits > 1`` float32 partial tiles go through a workspace of
-    ``splits * M * N`` floats and a second kernel adds them in a fixed order.
-
-    ``tail`` (default: on, ``False`` turns it off): see ``plan_tail``.
+    Default: the persistent kernel, which cuts tiles over K where whole tiles would leave SMs idle (see
+    ``plan_stream``; ``cut=False`` turns that off); for a handful of tiles the two-kernel form instead
+    (``plan_splits``).  ``splits > 1`` asks for that form: K split over ``splits`` blocks per 128 x 128 tile,
+    float32 partial tiles in a workspace of ``splits * M * N`` floats, added in a fixed order by a second kernel;
+    ``splits=1`` for whole tiles (or cut ones) in any case.
 
     ``epilogue``: ``None`` -> bfloat16 ``[M, N]``; ``"f32"`` -> float32 ``[M, N]``; ``"silu_mul"`` ->
     ``w`` is ``[gate; up]`` stacked and the result is bfloat16 ``[M, N/2]``.  Needs ``K % 8 == 0``.
@@ -80,22 +78,23 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None,
     n_out = N // 2 if epilogue == "silu_mul" else N
     if out is None:
         out = torch.empty((M, n_out), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=x.device)
+    ws = counts = None
+    n_cut = zmax = 0
+    if cut is None and os.environ.get("SYNAPTIX_GEMM_CUT", "1") == "0":      # a switch for measurements
+        cut = False
+    if splits is None and cut is not False:
+        _, n_cut, zmax, _ = plan_stream(M, N, K, epilogue)
     if splits is None:
-        splits = plan_splits(M, N, K, sm_count(x.device))
+        splits = 1 if n_cut else plan_splits(M, N, K, sm_count(x.device))
     splits = max(1, min(int(splits), (K + 63) // 64))
-    tail_tiles = tail_splits = 0
-    if splits == 1 and epilogue != "silu_mul" and tail is not False:
-        tail_tiles, tail_splits = plan_tail(M, N, K, sm_count(x.device))
-    ws = None
     if splits > 1:
         ws = torch.empty(splits * M * N, dtype=torch.float32, device=x.device)
-    elif tail_tiles:
-        m_rows, n_cols = M - ((M + 127) // 128 - tail_tiles) * 128, N - ((N + 255) // 256 - 1) * 256
-        ws = torch.empty(tail_splits * m_rows * n_cols, dtype=torch.float32, device=x.device)
+    elif n_cut:
+        ws = torch.empty(n_cut * zmax * 128 * 256, dtype=torch.float32, device=x.device)
+        counts = _counts(x.device)
     check(fn("gemm_tc", "sx_gemm_tc")(ptr(x), ptr(w), ptr(out), c_int(M), c_int(N), c_int(K), c_int(_EPI[epilogue]),
-                                      c_int(splits), ptr(ws), c_int(tail_tiles), c_int(tail_splits),
-                                      ptr(_tail_counts(x.device) if tail_tiles else None), stream()), "gemm_tc",
-          launches=2 if splits > 1 else 1)
+                                      c_int(splits), ptr(ws), ctypes.c_ulonglong(0 if ws is None else ws.numel()),
+                                      ptr(counts), stream()), "gemm_tc", launches=2 if splits > 1 else 1)
     return out
 
 

@@ -590,24 +590,36 @@ def test_gemm_tc(M, N, K):
     assert gemm_tc_status() == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(2048, 2560, 512), (2048, 2560, 4096), (2000, 2500, 328), (1300, 3484, 264)])
-def test_gemm_tc_tail_tiles_by_split_k(M, N, K):
-    """Shapes whose last round of 128 x 256 tiles is nearly empty: those tiles are split over K.  The
-    result must be the product everywhere, on both sides of the seam, for ragged M, N and K as well."""
-    from synaptix_b200.ops.decode import sm_count
-    from synaptix_b200.ops.gemm_tc import gemm_tc, gemm_tc_status, plan_tail
-    tail_tiles, tail_splits = plan_tail(M, N, K, sm_count(torch.device("cuda")))
-    assert tail_tiles > 0 and tail_splits >= 2, "the shape is meant to have a tail on this GPU"
+@pytest.mark.parametrize("M,N,K,epilogue,is_cut", [
+    # a nearly empty last round of whole tiles: its tiles are cut, the blocks add up inside the kernel
+    (2048, 2560, 4096, "f32", True), (2048, 2560, 9728, None, True), (2000, 2500, 1032, "f32", True), (1300, 3484, 1672, None, True),
+    (2048, 2560, 512, None, False),
+    # one row of tiles, at least half as many as SMs: all tiles cut, a second kernel adds up
+    (64, 19456, 2560, "silu_mul", True), (100, 20000, 136, None, True), (33, 30000, 264, "f32", True), (17, 25000, 200, "silu_mul", True),
+    # a handful of tiles: the two-kernel split form
+    (64, 6144, 2560, None, False), (64, 2560, 4096, "f32", False), (17, 389, 96, "f32", False), (128, 256, 64, "f32", False),
+    (200, 700, 1224, "silu_mul", False), (40, 24, 8, "f32", False)])
+def test_gemm_tc_tiles_cut_over_k(M, N, K, epilogue, is_cut):
+    """Shapes whose tiles do not fill a round of all SMs: the persistent kernel cuts them over K and the blocks
+    of a tile add their partial tiles up.  The result must be the product everywhere, for ragged M, N and K,
+    and the same bits twice (the order of addition is fixed)."""
+    from synaptix_b200.ops.gemm_tc import gemm_tc, gemm_tc_status, plan_stream
+    n_whole, n_cut, zmax, grid = plan_stream(M, N, K, epilogue)
+    assert (n_cut > 0) == is_cut, "what this GPU's SM count makes of the shape"
     g = torch.Generator().manual_seed(M + N + K)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
-    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * (2 if epilogue == "silu_mul" else 1) / math.sqrt(K)).to(torch.bfloat16)
     ref = x.double() @ w.double().T
-    for epilogue, tol in (("f32", dict(atol=2e-5 * math.sqrt(K), rtol=1e-5)), (None, dict(atol=2e-2, rtol=2e-2))):
-        out = torch.full((M, N), float("nan"), dtype=torch.float32 if epilogue else torch.bfloat16, device="cuda")
-        gemm_tc(x.cuda(), w.cuda(), epilogue=epilogue, out=out)
-        whole = gemm_tc(x.cuda(), w.cuda(), epilogue=epilogue, tail=False)
-        assert torch.allclose(out.float().cpu().double(), ref, **tol)
-        assert torch.allclose(whole.float().cpu().double(), ref, **tol)
+    if epilogue == "silu_mul":
+        ref = ref[:, :N // 2] / (1 + torch.exp(-ref[:, :N // 2])) * ref[:, N // 2:]
+    tol = dict(atol=2e-5 * math.sqrt(K), rtol=1e-5) if epilogue == "f32" else dict(atol=3e-2, rtol=2e-2)
+    out = torch.full(ref.shape, float("nan"), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device="cuda")
+    gemm_tc(x.cuda(), w.cuda(), epilogue=epilogue, out=out)
+    assert torch.allclose(out.float().cpu().double(), ref, **tol)
+    again = gemm_tc(x.cuda(), w.cuda(), epilogue=epilogue)
+    assert torch.equal(again, out)
+    whole = gemm_tc(x.cuda(), w.cuda(), epilogue=epilogue, cut=False, splits=1)
+    assert torch.allclose(whole.float().cpu().double(), ref, **tol)
     assert gemm_tc_status() == 0
 
 
