@@ -53,8 +53,18 @@ TINY_S = dict(
     use_sliding_window=True, sliding_window=40, max_window_layers=1)
 TINY_S_INIT = dict(seed=13, std_matrix=0.05, std_embedding=0.05, std_gain=0.1)
 
+# head size 128 with windows of 70 keys in the upper layer, group 3, widths that are no powers of two: the tcgen05
+# prompt attention's window path at engine level
+TINY_G = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=160, num_attention_heads=6, num_key_value_heads=2, head_dim=128,
+    intermediate_size=224, vocab_size=611, rope_theta=500000.0, rms_norm_eps=1e-6,
+    max_position_embeddings=2048, tie_word_embeddings=True, hidden_act="silu", attention_bias=False,
+    use_sliding_window=True, sliding_window=70, max_window_layers=1)
+TINY_G_INIT = dict(seed=17, std_matrix=0.05, std_embedding=0.05, std_gain=0.1)
+
 CONFIGS = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "W": (TINY_W, TINY_W_INIT),
-           "F": (TINY_F, TINY_F_INIT), "S": (TINY_S, TINY_S_INIT)}
+           "F": (TINY_F, TINY_F_INIT), "S": (TINY_S, TINY_S_INIT), "G": (TINY_G, TINY_G_INIT)}
 
 
 def make_folder(name: str, out_dir: str) -> str:
