@@ -26,14 +26,29 @@
 // =======================================================================================
 // decode: grid (n_splits, nkv, S), one query token per sequence (token index = sequence index)
 // =======================================================================================
-template <int HD>
+// PREP: q is the raw fused projection [S, (nh + 2 nkv) HD] of the step's tokens, and the kernel does what
+// qkv_prepare_kernel does on the way: per-head RMSNorm of the group's query heads and of the new key, rotation by
+// the token's position, the new key and value into the cache (by the block whose pages hold the token's place,
+// which also puts them into its staged page), so that a decode step needs no kernel for it.
+struct AtPrep {
+  const float* wq;          // [HD] gains of the q and k norms, or null
+  const float* wk;
+  const float* inv_freq;    // [HD / 2] or null (no rotation)
+  float eps;
+  int write;                // 0: this layer reads a cache another layer wrote (the token's key and value are there)
+  int n_pages;
+};
+
+template <int HD, bool PREP>
 __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
-    const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+    const bf16* __restrict__ q, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ seq_lens, const int* __restrict__ block_table, int maxp, int nh, int nkv,
-    float scale_log2, int window, int n_splits, int* __restrict__ counters) {
+    float scale_log2, int window, int n_splits, int* __restrict__ counters, const AtPrep prep) {
   using L = AtLayout<HD>;
   extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ __align__(16) bf16 q_s[PREP ? 16 * HD : 8];       // the group's prepared query heads
+  __shared__ __align__(16) bf16 kv_new[PREP ? 2 * HD : 8];     // the token's prepared key and value
   pdl_wait();
   pdl_trigger();
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
@@ -48,10 +63,72 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
   const int p0 = p_first + split * per, p1 = min(p_end, p0 + per);
   const int* bt = block_table + (size_t)seq * maxp;
 
+  // does this block hold the page of the token's own place?  (PREP with a cache to write: it prepares the new
+  // key and value, writes them to the cache and patches them into its staged page)
+  const int p_last = pos >> 6;
+  const bool has_last = PREP && prep.write && p0 <= p_last && p_last < p1;
+  if (PREP) {
+    constexpr int half = HD / 2;
+    const int heads = nh + 2 * nkv;
+    const bf16* tok = q + (size_t)seq * heads * HD;
+    float cs[2] = {1.f, 1.f}, sn[2] = {0.f, 0.f};
+    const int p = 2 * lane;                                   // this lane's pairs (p, p + half), (p + 1, p + 1 + half)
+    if (prep.inv_freq && p < half) {
+      sincosf((float)pos * prep.inv_freq[p], &sn[0], &cs[0]);
+      sincosf((float)pos * prep.inv_freq[p + 1], &sn[1], &cs[1]);
+    }
+    bf16* k_row = nullptr;
+    bf16* v_row = nullptr;
+    if (has_last) {
+      const int page = bt[p_last];
+      if (page >= 0 && page < prep.n_pages) {                 // the host guarantees a page; never write outside
+        const size_t at = (((size_t)page * nkv + kvh) * SX_PAGE + (pos & 63)) * HD;
+        k_row = k_pages + at;
+        v_row = v_pages + at;
+      }
+    }
+    // jobs: the G query heads of the group, then (has_last) the key head and the value head
+    const int jobs = G + (has_last ? 2 : 0);
+    for (int j = warp; j < jobs; j += AT_THREADS / 32) {
+      const bool is_q = j < G, is_k = j == G;
+      const bf16* src = tok + (size_t)(is_q ? kvh * G + j : (is_k ? nh + kvh : nh + nkv + kvh)) * HD;
+      if (!is_q && !is_k) {                                   // value: copy
+        for (int i = lane * 8; i < HD; i += 256) {
+          const uint4 v = *reinterpret_cast<const uint4*>(src + i);
+          *reinterpret_cast<uint4*>(kv_new + HD + i) = v;
+          if (v_row) *reinterpret_cast<uint4*>(v_row + i) = v;
+        }
+        continue;
+      }
+      const float* w = is_q ? prep.wq : prep.wk;
+      float2 x1 = make_float2(0.f, 0.f), x2 = x1;
+      if (p < half) {
+        x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + p));
+        x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + p + half));
+      }
+      float inv = 1.f;
+      if (w) inv = rsqrtf(warp_sum(x1.x * x1.x + x1.y * x1.y + x2.x * x2.x + x2.y * x2.y) / (float)HD + prep.eps);
+      if (p < half) {
+        const float a0 = x1.x * inv * (w ? w[p] : 1.f), a1 = x1.y * inv * (w ? w[p + 1] : 1.f);
+        const float b0 = x2.x * inv * (w ? w[p + half] : 1.f), b1 = x2.y * inv * (w ? w[p + 1 + half] : 1.f);
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(a0 * cs[0] - b0 * sn[0], a1 * cs[1] - b1 * sn[1]);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(a0 * sn[0] + b0 * cs[0], a1 * sn[1] + b1 * cs[1]);
+        bf16* dst = is_q ? q_s + j * HD : kv_new;
+        *reinterpret_cast<__nv_bfloat162*>(dst + p) = lo;
+        *reinterpret_cast<__nv_bfloat162*>(dst + p + half) = hi;
+        if (is_k && k_row) {
+          *reinterpret_cast<__nv_bfloat162*>(k_row + p) = lo;
+          *reinterpret_cast<__nv_bfloat162*>(k_row + p + half) = hi;
+        }
+      }
+    }
+    __syncthreads();
+  }
+
   // query fragments: row r of the fragment is query head kvh*G + r (rows >= G are zero)
   uint32_t qf[HD / 16][4];
   {
-    const bf16* qb = q + ((size_t)seq * nh + (size_t)kvh * G) * HD;
+    const bf16* qb = PREP ? q_s : q + ((size_t)seq * nh + (size_t)kvh * G) * HD;
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks) {
       const int c = ks * 16 + 2 * t;
@@ -67,9 +144,11 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
   for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
   const int npages = max(0, p1 - p0);
+  // rows of a page that come from the cache: with has_last the token's own row does not (it is not there yet)
+  auto rows_of = [&](int pg) { return min(64, (has_last ? len - 1 : len) - pg * 64); };
 #pragma unroll
   for (int st = 0; st < AT_STAGES_DECODE - 1; ++st) {
-    if (st < npages) load_page<HD>(smem + st * L::STAGE, k_pages, v_pages, bt[p0 + st], kvh, nkv, min(64, len - (p0 + st) * 64));
+    if (st < npages) load_page<HD>(smem + st * L::STAGE, k_pages, v_pages, bt[p0 + st], kvh, nkv, rows_of(p0 + st));
     cp_async_commit();
   }
   for (int i = 0; i < npages; ++i) {
@@ -77,8 +156,15 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
     __syncthreads();
     const int nx = i + AT_STAGES_DECODE - 1;
     if (nx < npages)
-      load_page<HD>(smem + (nx % AT_STAGES_DECODE) * L::STAGE, k_pages, v_pages, bt[p0 + nx], kvh, nkv, min(64, len - (p0 + nx) * 64));
+      load_page<HD>(smem + (nx % AT_STAGES_DECODE) * L::STAGE, k_pages, v_pages, bt[p0 + nx], kvh, nkv, rows_of(p0 + nx));
     cp_async_commit();
+    if (PREP && has_last && p0 + i == p_last) {               // the token's key and value into their row of the staged page
+      unsigned char* stw = smem + (i % AT_STAGES_DECODE) * L::STAGE + (pos & 63) * L::ROW;
+      if (threadIdx.x < HD / 8) *reinterpret_cast<uint4*>(stw + threadIdx.x * 16) = reinterpret_cast<const uint4*>(kv_new)[threadIdx.x];
+      else if (threadIdx.x < HD / 4)
+        *reinterpret_cast<uint4*>(stw + L::TILE + (threadIdx.x - HD / 8) * 16) = reinterpret_cast<const uint4*>(kv_new + HD)[threadIdx.x - HD / 8];
+      __syncthreads();
+    }
     const unsigned char* st = smem + (i % AT_STAGES_DECODE) * L::STAGE;
     // this warp's 16 keys of the page; all fragment rows sit at the same position
     const int jb = (p0 + i) * 64;
@@ -337,21 +423,21 @@ __global__ void __launch_bounds__(AT_THREADS, 3) attn_prefill_kernel(
 // ---------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------
-template <int HD>
-static int decode_launch(const bf16* q, const bf16* k, const bf16* v, bf16* out, float* part_o, float* part_ml,
+template <int HD, bool PREP>
+static int decode_launch(const bf16* q, bf16* k, bf16* v, bf16* out, float* part_o, float* part_ml,
                          const int* seq_lens, const int* bt, int maxp, int S, int nh, int nkv, float scale_log2,
-                         int window, int n_splits, int* counters, cudaStream_t stream) {
+                         int window, int n_splits, int* counters, const AtPrep& prep, cudaStream_t stream) {
   using L = AtLayout<HD>;
   const size_t merge_bytes = (size_t)(4 * 16 * HD + 4 * 16 * 2) * sizeof(float);
   const size_t last_bytes = (size_t)(2 * 16 * n_splits + 16) * sizeof(float);
   size_t smem = L::SMEM > merge_bytes ? L::SMEM : merge_bytes;
   if (last_bytes > smem) counters = nullptr;             // too many splits for the in-kernel merge
-  auto kern = attn_decode_kernel<HD>;
+  auto kern = attn_decode_kernel<HD, PREP>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid(n_splits, nkv, S);
   int rc = sx_launch(kern, grid, dim3(AT_THREADS), smem, stream, q, k, v, out, part_o, part_ml, seq_lens, bt, maxp, nh, nkv,
-                     scale_log2, window, n_splits, counters);
+                     scale_log2, window, n_splits, counters, prep);
   if (rc || n_splits == 1 || counters) return rc;
   return sx_launch(attn_merge_kernel<HD>, dim3(S * nh), dim3(HD), 2 * n_splits * sizeof(float), stream,
                    (const float*)part_o, (const float*)part_ml, out, n_splits);
@@ -361,15 +447,24 @@ static int decode_launch(const bf16* q, const bf16* k, const bf16* v, bf16* out,
 // part_ml f32 [S*nh*n_splits*2] are scratch (unused when n_splits == 1).
 static int attn_decode_any(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o,
                            float* part_ml, const int* seq_lens, const int* block_table, int maxp, int S, int nh,
-                           int nkv, int hd, float scale, int window, int n_splits, int* counters, cudaStream_t stream) {
+                           int nkv, int hd, float scale, int window, int n_splits, int* counters, const AtPrep* prep,
+                           cudaStream_t stream) {
   if (S <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || n_splits < 1 || nkv > 65535 || S > 65535) return SX_ERR_SIZE;
   if (n_splits > 1 && (!part_o || !part_ml)) return SX_ERR_SIZE;
   const float sl = scale * 1.4426950408889634f;
-  const bf16 *qb = (const bf16*)q, *kb = (const bf16*)k_pages, *vb = (const bf16*)v_pages;
-  if (hd == 128) return decode_launch<128>(qb, kb, vb, (bf16*)out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, sl, window, n_splits, counters, stream);
-  if (hd == 64) return decode_launch<64>(qb, kb, vb, (bf16*)out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, sl, window, n_splits, counters, stream);
-  if (hd == 32) return decode_launch<32>(qb, kb, vb, (bf16*)out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, sl, window, n_splits, counters, stream);
+  const bf16* qb = (const bf16*)q;
+  bf16 *kb = (bf16*)const_cast<void*>(k_pages), *vb = (bf16*)const_cast<void*>(v_pages), *ob = (bf16*)out;
+  const AtPrep none = {nullptr, nullptr, nullptr, 0.f, 0, 0};
+#define AT_GO(HD)                                                                                                            \
+  return prep ? decode_launch<HD, true>(qb, kb, vb, ob, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, sl, window, \
+                                        n_splits, counters, *prep, stream)                                                     \
+              : decode_launch<HD, false>(qb, kb, vb, ob, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, sl, window, \
+                                         n_splits, counters, none, stream)
+  if (hd == 128) AT_GO(128);
+  if (hd == 64) AT_GO(64);
+  if (hd == 32) AT_GO(32);
+#undef AT_GO
   return SX_ERR_SIZE;
 }
 
@@ -378,7 +473,21 @@ extern "C" int sx_attn_decode(const void* q, const void* k_pages, const void* v_
                               float* part_ml, const int* seq_lens, const int* block_table, int maxp, int S, int nh,
                               int nkv, int hd, float scale, int window, int n_splits, cudaStream_t stream) {
   return attn_decode_any(q, k_pages, v_pages, out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, hd, scale,
-                         window, n_splits, nullptr, stream);
+                         window, n_splits, nullptr, nullptr, stream);
+}
+
+// The same for a step's raw fused projection qkv [S, (nh + 2 nkv) hd]: per-head RMSNorm of q and k (gains wq, wk in
+// float32, or null), rotate-half rotation of the whole head by seq_lens[s] - 1 (inv_freq [hd / 2], or null), the new
+// key and value written into the cache (write != 0; pages [n_pages, nkv, 64, hd]) happen inside the attention kernel.
+extern "C" int sx_attn_decode_prep(const void* qkv, void* k_pages, void* v_pages, void* out, float* part_o, float* part_ml,
+                                   const float* wq, const float* wk, const float* inv_freq, float eps, int write,
+                                   long long n_pages, const int* seq_lens, const int* block_table, int maxp, int S, int nh,
+                                   int nkv, int hd, float scale, int window, int n_splits, cudaStream_t stream) {
+  if (((uintptr_t)qkv & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15)) return SX_ERR_ALIGN;
+  if (n_pages <= 0 || n_pages > 0x7fffffffLL) return SX_ERR_SIZE;
+  const AtPrep prep = {wq, wk, inv_freq, eps, write, (int)n_pages};
+  return attn_decode_any(qkv, k_pages, v_pages, out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, hd, scale,
+                         window, n_splits, nullptr, &prep, stream);
 }
 
 // the splits are merged inside the kernel by whichever block of a (sequence, kv head) finishes last;
@@ -388,7 +497,7 @@ extern "C" int sx_attn_decode_fused(const void* q, const void* k_pages, const vo
                                     int maxp, int S, int nh, int nkv, int hd, float scale, int window, int n_splits,
                                     cudaStream_t stream) {
   return attn_decode_any(q, k_pages, v_pages, out, part_o, part_ml, seq_lens, block_table, maxp, S, nh, nkv, hd, scale,
-                         window, n_splits, counters, stream);
+                         window, n_splits, counters, nullptr, stream);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -7,13 +7,14 @@ the kernels, every call raises ``KernelsUnavailable``.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
 
 from ..csrc.build import KernelsUnavailable
 from ._lib import KernelError, set_launch_counter
-from .attention import (TC_TILE_ROWS, attn_decode, attn_prefill, attn_prefill_tc, fast_supported, pick_splits,
+from .attention import (TC_TILE_ROWS, attn_decode, attn_decode_prep, attn_prefill, attn_prefill_tc, fast_supported, pick_splits,
                         query_tiles, tc_prefill_supported)
 from .decode import skinny_gemm, skinny_supported
 from .gemm_tc import gemm_tc, tc_supported
@@ -22,7 +23,8 @@ from .generic import (add_rmsnorm, attn_generic, decode_advance, embed_gather, g
                       silu_mul)
 
 __all__ = ["KernelsUnavailable", "KernelError", "set_launch_counter", "decode_advance", "add_rmsnorm", "attn_generic", "embed_gather",
-           "gemm_generic", "qkv_prepare", "residual_add", "silu_mul", "linear", "linear_normed", "norm_fusable", "attention"]
+           "gemm_generic", "qkv_prepare", "residual_add", "silu_mul", "linear", "linear_normed", "norm_fusable", "attention",
+           "attention_from_projection", "decode_attention_takes_projection"]
 
 
 SKINNY_MAX_ROWS = 16
@@ -81,6 +83,22 @@ def linear_normed(pn, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
         return None
     return skinny_gemm(None, w, epilogue=epi, norm_h=pn.h, norm_delta=pn.delta, norm_h_out=pn.h_out(),
                        norm_gain=pn.gain, norm_eps=pn.eps)
+
+
+def decode_attention_takes_projection(dtype, nh: int, nkv: int, hd: int, rotary_dim: Optional[int], ctx) -> bool:
+    """Can the attention kernel of a single-token step prepare the heads itself (norm, rotation, cache write) from
+    the fused projection?  (``SYNAPTIX_ATTN_PREP=0`` turns it off.)"""
+    return (fast_supported(dtype, nh, nkv, hd) and rotary_dim in (None, 0, hd) and ctx.all_single
+            and os.environ.get("SYNAPTIX_ATTN_PREP", "1") != "0")
+
+
+def attention_from_projection(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx,
+                              block_table: torch.Tensor, nh: int, nkv: int, hd: int, scale: float,
+                              window: Optional[int], wq, wk, inv_freq, eps: float, write_cache: bool) -> torch.Tensor:
+    """Single-token steps: head preparation and attention in one kernel (see ``attn_decode_prep``)."""
+    max_pages = (ctx.max_len + 63) // 64
+    return attn_decode_prep(qkv, k_pages, v_pages, ctx.seq_lens, block_table, nh, nkv, hd, scale, window,
+                            pick_splits(ctx.n_seqs, nkv, max_pages, qkv.device), wq, wk, inv_freq, eps, write_cache)
 
 
 def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx, block_table: torch.Tensor,

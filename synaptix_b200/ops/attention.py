@@ -83,6 +83,35 @@ def attn_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, s
     return out
 
 
+def attn_decode_prep(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, seq_lens: torch.Tensor,
+                     block_table: torch.Tensor, nh: int, nkv: int, hd: int, scale: float, window: Optional[int],
+                     n_splits: int, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor],
+                     inv_freq: Optional[torch.Tensor], eps: float, write_cache: bool,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``attn_decode`` straight from the step's fused projection ``qkv [S, (nh + 2 nkv) hd]``: the kernel
+    normalises and rotates the query heads and the new key itself (what ``qkv_prepare`` does), writes the new key
+    and value into the cache (``write_cache``) and attends.  The rotation is of the whole head or none."""
+    require_cuda(qkv, k_pages, v_pages, seq_lens, block_table, out, wq, wk, inv_freq)
+    S = qkv.shape[0]
+    if not fast_supported(qkv.dtype, nh, nkv, hd) or k_pages.dtype != qkv.dtype or qkv.shape[1] != (nh + 2 * nkv) * hd:
+        raise KernelError("attn_decode_prep: bfloat16 [S, (nh + 2 nkv) hd], head size 32/64/128, at most 16 query heads per kv head")
+    if inv_freq is not None and inv_freq.numel() != hd // 2:
+        raise KernelError("attn_decode_prep: the rotation must cover the whole head")
+    if out is None:
+        out = torch.empty((S, nh * hd), dtype=qkv.dtype, device=qkv.device)
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty(S * nh * n_splits * hd, dtype=torch.float32, device=qkv.device)
+        part_ml = torch.empty(S * nh * n_splits * 2, dtype=torch.float32, device=qkv.device)
+    check(fn("attention", "sx_attn_decode_prep")(
+        ptr(qkv), ptr(k_pages), ptr(v_pages), ptr(out), ptr(part_o), ptr(part_ml), ptr(wq), ptr(wk), ptr(inv_freq),
+        c_float(eps), c_int(1 if write_cache else 0), c_longlong(k_pages.shape[0]), ptr(seq_lens), ptr(block_table),
+        c_int(block_table.shape[1]), c_int(S), c_int(nh), c_int(nkv), c_int(hd), c_float(scale),
+        c_int(0 if window is None else int(window)), c_int(n_splits), stream()), "attn_decode_prep",
+        launches=2 if n_splits > 1 else 1)
+    return out
+
+
 def query_tiles(cu_seqlens: Sequence[int], rows: int = 64):
     """Lists (sequence, first row) of the ``rows``-row query tiles of a packed batch."""
     seqs, q0s = [], []

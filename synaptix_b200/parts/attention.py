@@ -76,10 +76,16 @@ class Attention(Mixer):
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_view: KVView, write_cache: bool = True) -> torch.Tensor:
         T = x.shape[0]
         qkv = self.qkv.forward(x)
-        q = torch.empty((T, self.nh * self.hd), dtype=qkv.dtype, device=qkv.device)
         rot = self.position.rotation()
         inv_freq, rotary_dim = rot if rot is not None else (None, 0)
         bt = ctx.block_tables[cache_view.group]
+        if ops.decode_attention_takes_projection(qkv.dtype, self.nh, self.nkv, self.hd, rotary_dim, ctx):
+            # single-token steps: the attention kernel prepares the heads and writes the cache itself
+            a = ops.attention_from_projection(qkv, cache_view.k, cache_view.v, ctx, bt, self.nh, self.nkv, self.hd,
+                                              self.scale, self.window, self.wq, self.wk, inv_freq,
+                                              self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_cache)
+            return self.o.forward(a)
+        q = torch.empty((T, self.nh * self.hd), dtype=qkv.dtype, device=qkv.device)
         ops.qkv_prepare(qkv, q, cache_view.k if write_cache else None, cache_view.v if write_cache else None,
                         self.wq, self.wk, inv_freq, rotary_dim,
                         self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,

@@ -480,6 +480,69 @@ def test_attention_decode_kernel(nh, nkv, hd, window):
             assert err < 2e-2, f"n_splits={n_splits} fused={fused}: {err}"
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window,rot,norm", [(4, 2, 128, None, True, True), (32, 8, 128, None, True, True),
+                                                        (6, 2, 32, None, True, False), (5, 1, 64, 24, False, True),
+                                                        (8, 8, 64, None, True, True), (16, 1, 128, 100, False, False),
+                                                        (3, 3, 32, 65, True, True)])
+def test_attention_decode_kernel_that_prepares_the_heads(nh, nkv, hd, window, rot, norm):
+    """From the raw fused projection: the kernel's output equals attention over (cache + the prepared new key and
+    value), the cache holds the new key and value afterwards and nothing else moved; a second pass that only reads
+    the cache (write_cache=False) gives the same output.  New tokens at a page's first, last and middle place."""
+    from synaptix_b200.ops.attention import attn_decode_prep
+    from synaptix_b200.parts import rotary_inv_freq
+    dtype = torch.bfloat16
+    past = [0, 130, 1000, 63, 64, 255]
+    S = len(past)
+    eps, theta = 1e-5, 30000.0
+    g = torch.Generator().manual_seed(11)
+    qkv = torch.randn(S, (nh + 2 * nkv) * hd, generator=g).to(dtype)
+    wq, wk = 1 + 0.3 * torch.randn(hd, generator=g), 1 + 0.3 * torch.randn(hd, generator=g)
+    pos = torch.tensor(past)
+    x = qkv.float()
+    q = x[:, :nh * hd].view(S, nh, hd)
+    k_new = x[:, nh * hd:(nh + nkv) * hd].view(S, nkv, hd)
+    v_new = x[:, (nh + nkv) * hd:].view(S, nkv, hd)
+    if norm:
+        q, k_new = P.rms_norm(q, wq, eps), P.rms_norm(k_new, wk, eps)
+    if rot:
+        f = P.rotary_freqs(theta, hd)
+        q, k_new = P.rope_rotate_half(q, pos, f), P.rope_rotate_half(k_new, pos, f)
+    q, k_new, v_new = q.to(dtype).float(), k_new.to(dtype).float(), v_new.to(dtype).float()
+    ks = [torch.cat([torch.randn(p, nkv, hd, generator=g).to(dtype).float(), k_new[i:i + 1]]) for i, p in enumerate(past)]
+    vs = [torch.cat([torch.randn(p, nkv, hd, generator=g).to(dtype).float(), v_new[i:i + 1]]) for i, p in enumerate(past)]
+    scale = 1 / math.sqrt(hd)
+    ref = attention_reference(q, ks, vs, pos.to(torch.int32), torch.arange(S, dtype=torch.int32), scale, window)
+    # the cache WITHOUT the new tokens (their places hold NaN, like everything unwritten)
+    kp, vp, bt = make_paged(ks, vs, nkv, hd, dtype, seed=5)
+    for i, p in enumerate(past):
+        page = int(bt[i, p // 64])
+        kp[page, :, p % 64] = float("nan")
+        vp[page, :, p % 64] = float("nan")
+    before_k, before_v = kp.clone(), vp.clone()
+    lens = torch.tensor([p + 1 for p in past], dtype=torch.int32).cuda()
+    inv = torch.from_numpy(rotary_inv_freq(theta, hd)).cuda() if rot else None
+    gq, gk = (wq.cuda(), wk.cuda()) if norm else (None, None)
+    for n_splits in (1, 3, 16):
+        kp.copy_(before_k); vp.copy_(before_v)
+        out = attn_decode_prep(qkv.cuda(), kp, vp, lens, bt, nh, nkv, hd, scale, window, n_splits, gq, gk, inv, eps, True)
+        err = (out.float().cpu().view(S, nh, hd) - ref).abs().max().item()
+        assert err < 2e-2, f"n_splits={n_splits}: {err}"
+        kc, vc, bc = kp.float().cpu(), vp.float().cpu(), bt.cpu()
+        changed = torch.zeros(kc.shape[0], 64, dtype=torch.bool)
+        for i, p in enumerate(past):
+            page = int(bc[i, p // 64])
+            assert torch.allclose(kc[page, :, p % 64], k_new[i], atol=2e-2, rtol=2e-2)
+            assert torch.equal(vc[page, :, p % 64], v_new[i])
+            changed[page, p % 64] = True
+        same = lambda a, b: torch.equal(torch.nan_to_num(a.float().cpu(), nan=12345.0), torch.nan_to_num(b.float().cpu(), nan=12345.0))
+        keep = ~changed[:, None, :, None].expand_as(kc)
+        assert same(torch.where(keep, kp.float().cpu(), torch.zeros(())), torch.where(keep, before_k.float().cpu(), torch.zeros(())))
+        assert same(torch.where(keep, vp.float().cpu(), torch.zeros(())), torch.where(keep, before_v.float().cpu(), torch.zeros(())))
+        # the cache now holds the tokens: a pass that writes nothing must see them there
+        again = attn_decode_prep(qkv.cuda(), kp, vp, lens, bt, nh, nkv, hd, scale, window, n_splits, gq, gk, inv, eps, False)
+        assert (again.float() - out.float()).abs().max().item() < 1e-2
+
+
 @pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 128, None), (6, 2, 32, None), (5, 1, 64, 24), (8, 8, 64, None),
                                                (2, 1, 128, 100), (32, 8, 128, None)])
 def test_attention_prefill_kernel(nh, nkv, hd, window):
