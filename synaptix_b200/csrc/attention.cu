@@ -49,8 +49,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ __align__(16) bf16 q_s[PREP ? 16 * HD : 8];       // the group's prepared query heads
   __shared__ __align__(16) bf16 kv_new[PREP ? 2 * HD : 8];     // the token's prepared key and value
-  pdl_wait();
-  pdl_trigger();
+  if (!PREP) { pdl_wait(); pdl_trigger(); }
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   const int G = nh / nkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -67,7 +66,24 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
   // key and value, writes them to the cache and patches them into its staged page)
   const int p_last = pos >> 6;
   const bool has_last = PREP && prep.write && p0 <= p_last && p_last < p1;
+  const int npages = max(0, p1 - p0);
+  // rows of a page that come from the cache: with has_last the token's own row does not (it is not there yet)
+  auto rows_of = [&](int pg) { return min(64, (has_last ? len - 1 : len) - pg * 64); };
+  auto first_pages = [&]() {
+#pragma unroll
+    for (int st = 0; st < AT_STAGES_DECODE - 1; ++st) {
+      if (st < npages) load_page<HD>(smem + st * L::STAGE, k_pages, v_pages, bt[p0 + st], kvh, nkv, rows_of(p0 + st));
+      cp_async_commit();
+    }
+  };
   if (PREP) {
+    // The first pages are asked for while the product before this kernel still runs: what they hold (every row
+    // but the token's own, which this kernel makes) and the lengths and block tables were written at least two
+    // launches ago, and a kernel behind a programmatic launch starts only when the one before its predecessor
+    // has ended.
+    first_pages();
+    pdl_wait();
+    pdl_trigger();
     constexpr int half = HD / 2;
     const int heads = nh + 2 * nkv;
     const bf16* tok = q + (size_t)seq * heads * HD;
@@ -143,14 +159,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
 #pragma unroll
   for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
-  const int npages = max(0, p1 - p0);
-  // rows of a page that come from the cache: with has_last the token's own row does not (it is not there yet)
-  auto rows_of = [&](int pg) { return min(64, (has_last ? len - 1 : len) - pg * 64); };
-#pragma unroll
-  for (int st = 0; st < AT_STAGES_DECODE - 1; ++st) {
-    if (st < npages) load_page<HD>(smem + st * L::STAGE, k_pages, v_pages, bt[p0 + st], kvh, nkv, rows_of(p0 + st));
-    cp_async_commit();
-  }
+  if (!PREP) first_pages();
   for (int i = 0; i < npages; ++i) {
     cp_async_wait<AT_STAGES_DECODE - 2>();
     __syncthreads();
