@@ -103,6 +103,15 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
   };
 #pragma unroll
   for (int i = 0; i < SK_DEPTH; ++i) ask(s_begin + i, i);
+  // the norm's gains are weights too: fetched before the wait
+  float4 gn[XS ? 4 : 1];
+  if (XS) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int i = threadIdx.x + k * THREADS;
+      gn[k] = i < (K >> 2) ? __ldg(reinterpret_cast<const float4*>(gain) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
   pdl_wait();          // the weights depend on no earlier kernel; everything below may
   pdl_trigger();
 
@@ -144,10 +153,9 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
       for (int k = 0; k < 4; ++k) {
         const int i = threadIdx.x + k * THREADS;
         if (i < n4) {
-          const float4 gn = reinterpret_cast<const float4*>(gain)[i];
           if (blockIdx.x == 0 && h_out) reinterpret_cast<float4*>(h_out + (size_t)b * K)[i] = v[k];
-          __nv_bfloat162 o0 = __floats2bfloat162_rn(v[k].x * inv * gn.x, v[k].y * inv * gn.y);
-          __nv_bfloat162 o1 = __floats2bfloat162_rn(v[k].z * inv * gn.z, v[k].w * inv * gn.w);
+          __nv_bfloat162 o0 = __floats2bfloat162_rn(v[k].x * inv * gn[k].x, v[k].y * inv * gn[k].y);
+          __nv_bfloat162 o1 = __floats2bfloat162_rn(v[k].z * inv * gn[k].z, v[k].w * inv * gn[k].w);
           uint2 o;
           o.x = *reinterpret_cast<uint32_t*>(&o0); o.y = *reinterpret_cast<uint32_t*>(&o1);
           reinterpret_cast<uint2*>(xr)[i] = o;
@@ -165,7 +173,27 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
 
   if (tile_ok) {
     int slot = 0;
+    // Activations from global memory are asked for one step ahead (up to 16 rows: the registers allow it), before
+    // the wait for this step's weights: a step's 64 bytes of a row are a trip to L2 that would otherwise stand
+    // between the arrival of the weights and their use.
+    constexpr bool XAHEAD = !XS && NT <= 2;
+    uint4 xn[XAHEAD ? NT : 1];
+    auto ask_x = [&](int step) {
+#pragma unroll
+      for (int nt = 0; nt < (XAHEAD ? NT : 1); ++nt) {
+        const int b = nt * 8 + g;
+        xn[nt] = make_uint4(0u, 0u, 0u, 0u);
+        if (step < s_end && b < M) xn[nt] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + step * 32 + t * 8));
+      }
+    };
+    if (XAHEAD) ask_x(s_begin);
     for (int sc = s_begin; sc < s_end; ++sc) {
+      uint4 xc[XAHEAD ? NT : 1];
+      if (XAHEAD) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) xc[nt] = xn[nt];
+        ask_x(sc + 1);
+      }
       asm volatile("cp.async.wait_group %0;\n" ::"n"(SK_DEPTH - 1) : "memory");   // step sc has landed
       const uint4 va = ring[(slot * 2) * THREADS + threadIdx.x];
       const uint4 vb = ring[(slot * 2 + 1) * THREADS + threadIdx.x];
@@ -175,7 +203,8 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
       for (int nt = 0; nt < NT; ++nt) {
         const int b = nt * 8 + g;
         uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-        if (XS) { if (b < M) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + sc * 32 + t * 8); }
+        if (XAHEAD) xv = xc[nt];
+        else if (XS) { if (b < M) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + sc * 32 + t * 8); }
         else if (b < M) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + sc * 32 + t * 8));
         mma_bf16_16816(acc[nt], va.x, vb.x, va.y, vb.y, xv.x, xv.y);
         mma_bf16_16816(acc[nt], va.z, vb.z, va.w, vb.w, xv.z, xv.w);
