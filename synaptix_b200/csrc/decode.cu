@@ -21,6 +21,11 @@
 //               warp's 16 rows are 8 gate rows and the 8 matching up rows;
 //               optional RMSNorm prologue: x = rmsnorm(h + delta) * gain computed per block
 //               (h float32), so that the norm needs no kernel and no round trip of x.
+//   RMSNorm split between producer and consumer (SkNorm): the product whose result is a branch of the
+//               residual stream adds it into h (float32, in place), writes x~ = bf16(h * gain) of the NEXT norm
+//               and one partial sum of squares of h per row and 16-column tile (EPI_RESID); the product that
+//               consumes x~ multiplies its own results by rsqrt(sum of the partials / K + eps) per row.  A row's
+//               norm then costs no kernel, no pass over h and no reduction in anybody's critical path.
 #include "common.cuh"
 
 #define SK_WARPS 8
@@ -44,7 +49,18 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   return v;
 }
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_RESID = 3 };
+
+struct SkNorm {
+  // consumer side: the rows of x lack the factor rsqrt(sum_i ssq_in[b * n_in + i] / K + eps_in); null: they do not
+  const float* ssq_in;
+  int n_in;
+  float eps_in;
+  // producer side (EPI_RESID): h [M, N] += result; out = bf16(h * gain_next); ssq_out [M, ceil(N / 16)]
+  float* h_io;
+  const float* gain_next;
+  float* ssq_out;
+};
 
 // NT: activation rows in tiles of 8 (M <= 8 NT);  KS: warps that split K;  RT = SK_WARPS / KS row tiles per block
 // XS: activations are read from shared memory (filled by the norm prologue) instead of global memory
@@ -53,7 +69,7 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
     const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int M, int N, int K,
     // norm prologue (XS only): x = rmsnorm(h_in + delta) * gain; block 0 writes h_in + delta to h_out
     const float* __restrict__ h_in, const bf16* __restrict__ delta, float* __restrict__ h_out,
-    const float* __restrict__ gain, float eps) {
+    const float* __restrict__ gain, float eps, const SkNorm nrm) {
   constexpr int WARPS = KS > SK_WARPS ? KS : SK_WARPS;      // 16 warps split K for matrices with few rows
   constexpr int THREADS = WARPS * 32;
   constexpr int RT = WARPS / KS;
@@ -112,8 +128,25 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
       gn[k] = i < (K >> 2) ? __ldg(reinterpret_cast<const float4*>(gain) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }
+  // the next norm's gains of this warp's columns (EPI_RESID) are weights as well
+  float gnext[2] = {0.f, 0.f};
+  if (EPI == EPI_RESID && tile_ok) {
+    gnext[0] = __ldg(nrm.gain_next + row_lo);
+    gnext[1] = __ldg(nrm.gain_next + row_hi);
+  }
   pdl_wait();          // the weights depend on no earlier kernel; everything below may
   pdl_trigger();
+
+  __shared__ float row_factor[NT * 8];
+  if (nrm.ssq_in) {           // one warp per row: the partial sums in index order, then the lanes' butterfly
+    for (int b = warp; b < M; b += WARPS) {
+      float ss = 0.f;
+      for (int i = lane; i < nrm.n_in; i += 32) ss += nrm.ssq_in[(size_t)b * nrm.n_in + i];
+      ss = warp_sum(ss);
+      if (lane == 0) row_factor[b] = rsqrtf(ss / (float)K + nrm.eps_in);
+    }
+    if (KS == 1) __syncthreads();      // with KS > 1 the barrier of the add-up below orders it
+  }
 
   if (XS) {
     // RMSNorm prologue by the whole block, one row after the other, the row held in registers:
@@ -173,27 +206,7 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
 
   if (tile_ok) {
     int slot = 0;
-    // Activations from global memory are asked for one step ahead (up to 16 rows: the registers allow it), before
-    // the wait for this step's weights: a step's 64 bytes of a row are a trip to L2 that would otherwise stand
-    // between the arrival of the weights and their use.
-    constexpr bool XAHEAD = !XS && NT <= 2;
-    uint4 xn[XAHEAD ? NT : 1];
-    auto ask_x = [&](int step) {
-#pragma unroll
-      for (int nt = 0; nt < (XAHEAD ? NT : 1); ++nt) {
-        const int b = nt * 8 + g;
-        xn[nt] = make_uint4(0u, 0u, 0u, 0u);
-        if (step < s_end && b < M) xn[nt] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + step * 32 + t * 8));
-      }
-    };
-    if (XAHEAD) ask_x(s_begin);
-    for (int sc = s_begin; sc < s_end; ++sc) {
-      uint4 xc[XAHEAD ? NT : 1];
-      if (XAHEAD) {
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) xc[nt] = xn[nt];
-        ask_x(sc + 1);
-      }
+    auto step = [&](int sc, const uint4 (&xv)[NT]) {
       asm volatile("cp.async.wait_group %0;\n" ::"n"(SK_DEPTH - 1) : "memory");   // step sc has landed
       const uint4 va = ring[(slot * 2) * THREADS + threadIdx.x];
       const uint4 vb = ring[(slot * 2 + 1) * THREADS + threadIdx.x];
@@ -201,17 +214,68 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
       slot = slot + 1 == SK_DEPTH ? 0 : slot + 1;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        const int b = nt * 8 + g;
-        uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-        if (XAHEAD) xv = xc[nt];
-        else if (XS) { if (b < M) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + sc * 32 + t * 8); }
-        else if (b < M) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + sc * 32 + t * 8));
-        mma_bf16_16816(acc[nt], va.x, vb.x, va.y, vb.y, xv.x, xv.y);
-        mma_bf16_16816(acc[nt], va.z, vb.z, va.w, vb.w, xv.z, xv.w);
+        mma_bf16_16816(acc[nt], va.x, vb.x, va.y, vb.y, xv[nt].x, xv[nt].y);
+        mma_bf16_16816(acc[nt], va.z, vb.z, va.w, vb.w, xv[nt].z, xv[nt].w);
+      }
+    };
+    // Activations from global memory (up to 16 rows: the registers allow it) are asked for XD steps ahead into a
+    // ring of registers, always before the wait for a step's weights: a step's 64 bytes of a row are a trip to L2
+    // that would otherwise stand between the arrival of the weights and their use.
+    constexpr bool XAHEAD = !XS && NT <= 2;
+    constexpr int XD = 1;        // steps ahead; 4 (as deep as the weights) measured slower: 475 against 489 tok/s at one row
+    if (XAHEAD) {
+      uint4 xr[XD][NT];
+      auto ask_x = [&](int sc, uint4 (&dst)[NT]) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const int b = nt * 8 + g;
+          dst[nt] = make_uint4(0u, 0u, 0u, 0u);
+          if (sc < s_end && b < M) dst[nt] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + sc * 32 + t * 8));
+        }
+      };
+#pragma unroll
+      for (int u = 0; u < XD; ++u) ask_x(s_begin + u, xr[u]);
+      for (int sc = s_begin; sc < s_end; sc += XD) {
+#pragma unroll
+        for (int u = 0; u < XD; ++u) {
+          if (sc + u < s_end) {
+            uint4 xc[NT];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) xc[nt] = xr[u][nt];
+            ask_x(sc + u + XD, xr[u]);
+            step(sc + u, xc);
+          }
+        }
+      }
+    } else {
+      for (int sc = s_begin; sc < s_end; ++sc) {
+        uint4 xv[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const int b = nt * 8 + g;
+          xv[nt] = make_uint4(0u, 0u, 0u, 0u);
+          if (XS) { if (b < M) xv[nt] = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + sc * 32 + t * 8); }
+          else if (b < M) xv[nt] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + sc * 32 + t * 8));
+        }
+        step(sc, xv);
       }
     }
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+
+  // EPI_RESID: the residual stream's values of this warp's results, asked for before the add-up hides the trip
+  float hv[EPI == EPI_RESID ? NT : 1][4];
+  if (EPI == EPI_RESID && ks == 0 && tile_ok) {
+    const int n0 = tile * 16 + g, n1 = n0 + 8;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int b = nt * 8 + t * 2 + j;
+        hv[nt][j] = (b < M && n0 < N) ? nrm.h_io[(size_t)b * N + n0] : 0.f;
+        hv[nt][2 + j] = (b < M && n1 < N) ? nrm.h_io[(size_t)b * N + n1] : 0.f;
+      }
+  }
 
   // add up the KS partial sums of a row tile in warp order
   if (KS > 1) {
@@ -233,6 +297,47 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
   if (!tile_ok) return;
 
   // fragment element (j): row g (j < 2) or g + 8 of the tile, activation row nt*8 + t*2 + (j & 1)
+  if (nrm.ssq_in) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int b = nt * 8 + t * 2 + j;
+        const float f = b < M ? row_factor[b] : 0.f;
+        acc[nt][j] *= f;
+        acc[nt][2 + j] *= f;
+      }
+  }
+  if (EPI == EPI_RESID) {
+    const int n0 = tile * 16 + g, n1 = n0 + 8;
+    const int tiles = (N + 15) >> 4;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int b = nt * 8 + t * 2 + j;             // uniform over the 8 lanes that share t
+        float ss = 0.f;
+        if (b < M) {
+          if (n0 < N) {
+            const float v = hv[nt][j] + acc[nt][j];
+            nrm.h_io[(size_t)b * N + n0] = v;
+            reinterpret_cast<bf16*>(out)[(size_t)b * N + n0] = __float2bfloat16_rn(v * gnext[0]);
+            ss += v * v;
+          }
+          if (n1 < N) {
+            const float v = hv[nt][2 + j] + acc[nt][2 + j];
+            nrm.h_io[(size_t)b * N + n1] = v;
+            reinterpret_cast<bf16*>(out)[(size_t)b * N + n1] = __float2bfloat16_rn(v * gnext[1]);
+            ss += v * v;
+          }
+        }
+        ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 8);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 16);
+        if (g == 0 && b < M) nrm.ssq_out[(size_t)b * tiles + tile] = ss;
+      }
+    }
+  } else {
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -258,11 +363,12 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
       }
     }
   }
+  }
 }
 
 template <int NT, int KS, int EPI, bool XS>
 static int skinny_launch(const bf16* x, const bf16* W, void* out, int M, int N, int K, const float* h_in,
-                         const bf16* delta, float* h_out, const float* gain, float eps, cudaStream_t stream) {
+                         const bf16* delta, float* h_out, const float* gain, float eps, const SkNorm& nrm, cudaStream_t stream) {
   constexpr int WARPS = KS > SK_WARPS ? KS : SK_WARPS, THREADS = WARPS * 32;
   constexpr int RT = WARPS / KS;
   const int tiles = (EPI == EPI_SILU_MUL) ? (N / 2 + 7) / 8 : (N + 15) / 16;
@@ -275,29 +381,29 @@ static int skinny_launch(const bf16* x, const bf16* W, void* out, int M, int N, 
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return sx_launch(kern, dim3(grid), dim3(THREADS), smem, stream, x, W, out, M, N, K, h_in, delta, h_out, gain, eps);
+  return sx_launch(kern, dim3(grid), dim3(THREADS), smem, stream, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm);
 }
 
 template <int NT, int EPI, bool XS>
 static int skinny_pick_ks(int ks, const bf16* x, const bf16* W, void* out, int M, int N, int K, const float* h_in,
-                          const bf16* delta, float* h_out, const float* gain, float eps, cudaStream_t stream) {
+                          const bf16* delta, float* h_out, const float* gain, float eps, const SkNorm& nrm, cudaStream_t stream) {
   switch (ks) {
-    case 16: return skinny_launch<NT, 16, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
-    case 8: return skinny_launch<NT, 8, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
-    case 4: return skinny_launch<NT, 4, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
-    case 2: return skinny_launch<NT, 2, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
-    default: return skinny_launch<NT, 1, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
+    case 16: return skinny_launch<NT, 16, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
+    case 8: return skinny_launch<NT, 8, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
+    case 4: return skinny_launch<NT, 4, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
+    case 2: return skinny_launch<NT, 2, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
+    default: return skinny_launch<NT, 1, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
   }
 }
 
 template <int EPI, bool XS>
 static int skinny_pick_nt(int ks, const bf16* x, const bf16* W, void* out, int M, int N, int K, const float* h_in,
-                          const bf16* delta, float* h_out, const float* gain, float eps, cudaStream_t stream) {
-  if (M <= 8) return skinny_pick_ks<1, EPI, XS>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
-  if (M <= 16) return skinny_pick_ks<2, EPI, XS>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
+                          const bf16* delta, float* h_out, const float* gain, float eps, const SkNorm& nrm, cudaStream_t stream) {
+  if (M <= 8) return skinny_pick_ks<1, EPI, XS>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
+  if (M <= 16) return skinny_pick_ks<2, EPI, XS>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
   if (XS) return SX_ERR_SIZE;
-  if (M <= 32) return skinny_pick_ks<4, EPI, false>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
-  if (M <= 64) return skinny_pick_ks<8, EPI, false>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, stream);
+  if (M <= 32) return skinny_pick_ks<4, EPI, false>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
+  if (M <= 64) return skinny_pick_ks<8, EPI, false>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
   return SX_ERR_SIZE;
 }
 
@@ -315,19 +421,45 @@ extern "C" int sx_skinny_gemm(const void* x, const void* W, void* out, int M, in
   const bf16* xb = (const bf16*)x;
   const bf16* wb = (const bf16*)W;
   const bf16* db = (const bf16*)delta;
+  const SkNorm none = {nullptr, 0, 0.f, nullptr, nullptr, nullptr};
   if (h_in) {
     if (M > XS_ROWS || K > 4096 || (K & 3)) return SX_ERR_SIZE;   // the prologue holds a row in registers
     switch (epi) {
-      case EPI_BF16: return skinny_pick_nt<EPI_BF16, true>(ks, xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, stream);
-      case EPI_F32: return skinny_pick_nt<EPI_F32, true>(ks, xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, stream);
-      case EPI_SILU_MUL: return skinny_pick_nt<EPI_SILU_MUL, true>(ks, xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, stream);
+      case EPI_BF16: return skinny_pick_nt<EPI_BF16, true>(ks, xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, none, stream);
+      case EPI_F32: return skinny_pick_nt<EPI_F32, true>(ks, xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, none, stream);
+      case EPI_SILU_MUL: return skinny_pick_nt<EPI_SILU_MUL, true>(ks, xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, none, stream);
       default: return SX_ERR_DTYPE;
     }
   }
   switch (epi) {
-    case EPI_BF16: return skinny_pick_nt<EPI_BF16, false>(ks, xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, stream);
-    case EPI_F32: return skinny_pick_nt<EPI_F32, false>(ks, xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, stream);
-    case EPI_SILU_MUL: return skinny_pick_nt<EPI_SILU_MUL, false>(ks, xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, stream);
+    case EPI_BF16: return skinny_pick_nt<EPI_BF16, false>(ks, xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, none, stream);
+    case EPI_F32: return skinny_pick_nt<EPI_F32, false>(ks, xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, none, stream);
+    case EPI_SILU_MUL: return skinny_pick_nt<EPI_SILU_MUL, false>(ks, xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, none, stream);
+    default: return SX_ERR_DTYPE;
+  }
+}
+
+// The same product with an RMSNorm split between the product before it and itself (see SkNorm above).
+//   ssq_in [M, n_in] (or null): x lacks the factor rsqrt(sum_i ssq_in[b, i] / K + eps_in) per row; the results get it.
+//   epi 3: h_io f32 [M, N] += x W^T in place, out bf16 [M, N] = h_io * gain_next, ssq_out f32 [M, ceil(N / 16)] =
+//          sums of squares of h_io over each 16-column tile.  Other epilogues as in sx_skinny_gemm.
+extern "C" int sx_skinny_gemm_norm(const void* x, const void* W, void* out, int M, int N, int K, int epi, int ks,
+                                   const float* ssq_in, int n_in, float eps_in, float* h_io, const float* gain_next,
+                                   float* ssq_out, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 31) || M > 64 || !x) return SX_ERR_SIZE;
+  if (epi == EPI_SILU_MUL && (N & 1)) return SX_ERR_SIZE;
+  if (ssq_in && n_in <= 0) return SX_ERR_SIZE;
+  if (epi == EPI_RESID && (!h_io || !gain_next || !ssq_out)) return SX_ERR_SIZE;
+  if (((uintptr_t)W & 15) || ((uintptr_t)x & 15)) return SX_ERR_ALIGN;
+  const bf16* xb = (const bf16*)x;
+  const bf16* wb = (const bf16*)W;
+  const SkNorm nrm = {ssq_in, n_in, eps_in, h_io, gain_next, ssq_out};
+  switch (epi) {
+    case EPI_BF16: return skinny_pick_nt<EPI_BF16, false>(ks, xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, nrm, stream);
+    case EPI_F32: return skinny_pick_nt<EPI_F32, false>(ks, xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, nrm, stream);
+    case EPI_SILU_MUL: return skinny_pick_nt<EPI_SILU_MUL, false>(ks, xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, nrm, stream);
+    case EPI_RESID: return skinny_pick_nt<EPI_RESID, false>(ks, xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, nrm, stream);
     default: return SX_ERR_DTYPE;
   }
 }

@@ -22,7 +22,7 @@ import torch
 from .. import ops
 from ..cache.store import CacheRequest
 from ..ops.decode_stream import enabled as stream_enabled
-from ..parts.base import Norm, Part, Runtime, StepContext
+from ..parts.base import Norm, Part, PendingLinear, Runtime, StepContext, plain
 from ..parts.embedding import Embedding, OutputHead
 from ..weights.loader import TensorSpec, WeightSource, bind_tensors
 
@@ -132,13 +132,17 @@ class DecoderModel(Part):
         for first, last, plan in segments:
             if plan is not None:
                 if pending is not None:
-                    ops.residual_add(h, pending)
+                    ops.residual_add(h, plain(pending))
                     pending = None
                 plan.run(h, ctx.positions, ctx.seq_lens, ctx.block_tables, ctx.max_len)
                 continue
             for run in self.schedule[first:last]:
+                if isinstance(pending, PendingLinear) and not getattr(self.layers[run.layer], "takes_pending_product", False):
+                    pending = pending.materialize()
                 h, pending = self.layers[run.layer].forward(h, pending, ctx, cache.view(run.cache_entry),
                                                             run.write_cache)
+        if isinstance(pending, PendingLinear) and not self.final_norm.takes_pending_product:
+            pending = pending.materialize()
         if getattr(ctx, "want_all", False):        # every row, in order: no gather, and the norm may fuse
             x = self.final_norm.add_forward(h, pending, lazy=True)
         else:

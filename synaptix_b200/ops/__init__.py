@@ -16,7 +16,7 @@ from ..csrc.build import KernelsUnavailable
 from ._lib import KernelError, set_launch_counter
 from .attention import (TC_TILE_ROWS, attn_decode, attn_decode_prep, attn_prefill, attn_prefill_tc, fast_supported, pick_splits,
                         query_tiles, tc_prefill_supported)
-from .decode import skinny_gemm, skinny_supported
+from .decode import skinny_gemm, skinny_gemm_residual, skinny_gemm_scaled, skinny_supported
 from .gemm_tc import gemm_tc, tc_supported
 from .generic import (add_rmsnorm, attn_generic, decode_advance, embed_gather, gemm_generic, qkv_prepare,
                       residual_add,
@@ -24,7 +24,8 @@ from .generic import (add_rmsnorm, attn_generic, decode_advance, embed_gather, g
 
 __all__ = ["KernelsUnavailable", "KernelError", "set_launch_counter", "decode_advance", "add_rmsnorm", "attn_generic", "embed_gather",
            "gemm_generic", "qkv_prepare", "residual_add", "silu_mul", "linear", "linear_normed", "norm_fusable", "attention",
-           "attention_from_projection", "decode_attention_takes_projection"]
+           "attention_from_projection", "decode_attention_takes_projection", "residual_product_fusable",
+           "linear_into_residual", "linear_scaled"]
 
 
 SKINNY_MAX_ROWS = 16
@@ -83,6 +84,41 @@ def linear_normed(pn, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
         return None
     return skinny_gemm(None, w, epilogue=epi, norm_h=pn.h, norm_delta=pn.delta, norm_h_out=pn.h_out(),
                        norm_gain=pn.gain, norm_eps=pn.eps)
+
+
+def residual_product_fusable(M: int, N: int, K: int, dtype) -> bool:
+    """Can the product ``x[M, K] @ w[N, K].T`` add itself into the residual stream and prepare the norm after the
+    sum (``linear_into_residual``)?  3 to 16 rows in bfloat16; ``SYNAPTIX_RESID=0`` turns it off."""
+    # one or two rows: the norm in the consumer's prologue (norm_fusable) measured faster (489 against 471 tok/s)
+    return (dtype == torch.bfloat16 and 2 < M <= SKINNY_MAX_ROWS and K % 32 == 0 and K > 0
+            and os.environ.get("SYNAPTIX_RESID", "1") != "0")
+
+
+def linear_into_residual(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, gain: torch.Tensor):
+    """``h += x @ w.T`` (float32, in place); returns ``(bf16(h * gain), ssq)``: the rows of the RMSNorm after the
+    sum without their factor ``rsqrt(mean(h^2) + eps)``, and partial sums of squares of ``h`` from which
+    ``linear_scaled`` forms that factor."""
+    return skinny_gemm_residual(x, w, h, gain)
+
+
+def linear_scaled(x: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tensor,
+                  out_dtype: Optional[torch.dtype] = None, epilogue: Optional[str] = None) -> Optional[torch.Tensor]:
+    """``(x * rsqrt(sum(ssq) / K + eps)) @ w.T`` with the factor applied to the results; ``None`` if no kernel
+    does that for these sizes."""
+    M, K = x.shape
+    if out_dtype is None:
+        out_dtype = x.dtype
+    if not (skinny_supported(M, w.shape[0], K, x.dtype, w.dtype) and M <= SKINNY_MAX_ROWS and w.shape[1] == K):
+        return None
+    if epilogue == "silu_mul":
+        if out_dtype != torch.bfloat16:
+            return None
+        epi = "silu_mul"
+    elif epilogue is None and out_dtype in (torch.bfloat16, torch.float32):
+        epi = "f32" if out_dtype == torch.float32 else None
+    else:
+        return None
+    return skinny_gemm_scaled(x, w, ssq, eps, epilogue=epi)
 
 
 def decode_attention_takes_projection(dtype, nh: int, nkv: int, hd: int, rotary_dim: Optional[int], ctx) -> bool:

@@ -59,6 +59,52 @@ def skinny_gemm(x: Optional[torch.Tensor], w: torch.Tensor, *, epilogue: Optiona
     return out
 
 
+def skinny_gemm_scaled(x: torch.Tensor, w: torch.Tensor, ssq: Optional[torch.Tensor], eps: float, *,
+                       epilogue: Optional[str] = None, ks: Optional[int] = None) -> torch.Tensor:
+    """``skinny_gemm`` for rows of ``x`` that lack their RMSNorm factor: row ``b`` of the result is multiplied by
+    ``rsqrt(sum(ssq[b]) / K + eps)`` (``ssq`` float32 ``[M, n]``: partial sums of squares of the row the norm is of)."""
+    require_cuda(x, w, ssq)
+    N, K = w.shape
+    M = x.shape[0]
+    if x.shape[1] != K or epilogue not in _EPI:
+        raise KernelError("skinny_gemm_scaled: inner sizes differ or unknown epilogue")
+    if ssq is not None and (ssq.dtype != torch.float32 or ssq.shape[0] != M or not ssq.is_contiguous()):
+        raise KernelError("skinny_gemm_scaled: ssq must be contiguous float32 [M, n]")
+    n_out = N // 2 if epilogue == "silu_mul" else N
+    out = torch.empty((M, n_out), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=w.device)
+    tiles = (n_out + 7) // 8 if epilogue == "silu_mul" else (N + 15) // 16
+    if ks is None:
+        ks = pick_ks(tiles, K)
+    check(fn("decode", "sx_skinny_gemm_norm")(
+        ptr(x), ptr(w), ptr(out), c_int(M), c_int(N), c_int(K), c_int(_EPI[epilogue]), c_int(ks), ptr(ssq),
+        c_int(0 if ssq is None else ssq.shape[1]), c_float(eps), ptr(None), ptr(None), ptr(None), stream()),
+        "skinny_gemm_scaled")
+    return out
+
+
+def skinny_gemm_residual(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, gain: torch.Tensor, *,
+                         ks: Optional[int] = None):
+    """``h += x @ w.T`` in place (``h`` float32 ``[M, N]``), and what the RMSNorm after that sum needs: returns
+    ``(bf16(h * gain) [M, N], ssq float32 [M, ceil(N / 16)])`` with ``ssq`` the sums of squares of the new ``h``
+    over tiles of 16 columns.  ``skinny_gemm_scaled`` takes both."""
+    require_cuda(x, w, h, gain)
+    N, K = w.shape
+    M = x.shape[0]
+    if x.shape[1] != K or tuple(h.shape) != (M, N) or h.dtype != torch.float32 or not h.is_contiguous():
+        raise KernelError("skinny_gemm_residual: h must be contiguous float32 [M, N]")
+    if gain.dtype != torch.float32 or gain.numel() != N:
+        raise KernelError("skinny_gemm_residual: gain must be float32 [N]")
+    tiles = (N + 15) // 16
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=w.device)
+    ssq = torch.empty((M, tiles), dtype=torch.float32, device=w.device)
+    if ks is None:
+        ks = pick_ks(tiles, K)
+    check(fn("decode", "sx_skinny_gemm_norm")(
+        ptr(x), ptr(w), ptr(out), c_int(M), c_int(N), c_int(K), c_int(3), c_int(ks), ptr(None), c_int(0),
+        c_float(0.0), ptr(h), ptr(gain), ptr(ssq), stream()), "skinny_gemm_residual")
+    return out, ssq
+
+
 _SM_COUNT = {}
 
 

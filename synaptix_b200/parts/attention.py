@@ -27,6 +27,7 @@ from .linear import Linear
 
 class Attention(Mixer):
     accepts_lazy_input = True      # x goes straight into the fused q/k/v product
+    can_defer_output = True        # the output projection may be handed on unrun
 
     def __init__(self, prefix: str, width: int, n_heads: int, n_kv_heads: int, head_dim: int, *,
                  position: PositionEncoding, qk_norm_eps: Optional[float] = None,
@@ -73,7 +74,9 @@ class Attention(Mixer):
                 "k_pages": cache_view.k, "v_pages": cache_view.v, "group": cache_view.group,
                 "write_cache": write_cache}
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache_view: KVView, write_cache: bool = True) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache_view: KVView, write_cache: bool = True,
+                defer_output: bool = False) -> torch.Tensor:
+        out = self.o.deferred if defer_output else self.o.forward
         T = x.shape[0]
         qkv = self.qkv.forward(x)
         rot = self.position.rotation()
@@ -84,7 +87,7 @@ class Attention(Mixer):
             a = ops.attention_from_projection(qkv, cache_view.k, cache_view.v, ctx, bt, self.nh, self.nkv, self.hd,
                                               self.scale, self.window, self.wq, self.wk, inv_freq,
                                               self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, write_cache)
-            return self.o.forward(a)
+            return out(a)
         q = torch.empty((T, self.nh * self.hd), dtype=qkv.dtype, device=qkv.device)
         ops.qkv_prepare(qkv, q, cache_view.k if write_cache else None, cache_view.v if write_cache else None,
                         self.wq, self.wk, inv_freq, rotary_dim,
@@ -93,4 +96,4 @@ class Attention(Mixer):
                         pages_like=cache_view.k)
         a = ops.attention(q, cache_view.k, cache_view.v, ctx, bt, self.nh, self.nkv, self.hd,
                           self.scale, self.window)
-        return self.o.forward(a)
+        return out(a)

@@ -10,7 +10,8 @@ Interfaces (a new part of any kind implements the one of its kind):
 ``Part``           ``tensor_specs() -> {name: TensorSpec}``; ``bind(tensors, runtime)``.
 ``Norm``           ``forward(h)`` and ``add_forward(h, delta, rows=None)``: ``h`` is the
                    float32 residual stream ``[T, width]``; ``add_forward`` first adds
-                   ``delta`` into it; both return the normalised rows in the compute dtype.
+                   ``delta`` into it; both return the normalised rows in the compute dtype
+                   (or, with ``lazy=True``, a ``PendingNorm`` / ``ScaledRows`` that a product can finish).
 ``PositionEncoding`` ``rotation() -> (inv_freq float32 [rotary_dim/2], rotary_dim) | None``:
                    rotate-half rotation by ``position * inv_freq[i]``, applied to queries and
                    keys inside the fused head-preparation kernel.
@@ -117,6 +118,61 @@ class PendingNorm:
         return self._h_after
 
 
+class PendingLinear:
+    """A branch's last matrix product that has not run yet: ``x @ weight.T``.
+
+    A mixer or feed-forward that is asked to (``forward(..., defer_output=True)``; only parts with
+    ``can_defer_output`` are asked) may return this instead of the product.  A norm that says
+    ``takes_pending_product`` may then run the product so that it adds itself into the residual stream and
+    prepares the norm (``ScaledRows``); anybody else calls ``materialize()`` and gets the plain tensor.
+    """
+    __slots__ = ("x", "weight", "_y")
+
+    def __init__(self, x, weight):
+        self.x, self.weight = x, weight
+        self._y = None
+
+    @property
+    def shape(self):
+        return (self.x.shape[0], self.weight.shape[0])
+
+    def materialize(self) -> torch.Tensor:
+        if self._y is None:
+            from .. import ops
+            self._y = ops.linear(self.x, self.weight)
+        return self._y
+
+
+def plain(t):
+    """``t`` as a tensor, whatever deferred form it came in."""
+    return t.materialize() if isinstance(t, (PendingLinear, PendingNorm, ScaledRows)) else t
+
+
+class ScaledRows:
+    """A normalised activation that lacks its row factor: ``x = bf16(h * gain)`` and partial sums of squares
+    ``ssq [T, n]`` of ``h``, so that ``rmsnorm(h) * gain = x * rsqrt(sum(ssq) / width + eps)``.  The product that
+    formed the residual sum ``h`` made both on its way; a matrix product that takes this applies the factor to its
+    results, so the norm costs no kernel.  ``materialize()`` gives the plain tensor (one norm kernel over ``h``)."""
+    __slots__ = ("x", "ssq", "eps", "h", "gain", "dtype", "_plain")
+
+    def __init__(self, x, ssq, eps, h, gain, dtype):
+        self.x, self.ssq, self.eps, self.h, self.gain, self.dtype = x, ssq, eps, h, gain, dtype
+        self._plain = None
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    def materialize(self) -> torch.Tensor:
+        if self._plain is None:
+            from .. import ops
+            self._plain = ops.add_rmsnorm(self.h, None, self.gain, self.eps, self.dtype)
+        return self._plain
+
+    def h_after(self) -> torch.Tensor:
+        return self.h
+
+
 class Part:
     """Anything that owns tensors."""
 
@@ -157,6 +213,8 @@ class Part:
 
 
 class Norm(Part):
+    takes_pending_product = False  # True: add_forward may be handed a PendingLinear as delta
+
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
@@ -172,7 +230,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    accepts_lazy_input = False     # True: forward may be handed a PendingNorm instead of a tensor
+    accepts_lazy_input = False     # True: forward may be handed a PendingNorm or ScaledRows instead of a tensor
+    can_defer_output = False       # True: forward takes defer_output=True and may then return a PendingLinear
 
     def cache_request(self):
         return None
@@ -183,6 +242,7 @@ class Mixer(Part):
 
 class FeedForward(Part):
     accepts_lazy_input = False
+    can_defer_output = False
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError

@@ -14,7 +14,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorSpec
-from .base import Part, PendingNorm, Runtime, to_device_matrix
+from .base import Part, PendingLinear, PendingNorm, Runtime, ScaledRows, to_device_matrix
 
 
 class Linear(Part):
@@ -45,8 +45,17 @@ class Linear(Part):
         """Use an already bound matrix (a tied output head uses the embedding table)."""
         self.weight = weight
 
+    def deferred(self, x: torch.Tensor) -> PendingLinear:
+        """This product, not run yet (see ``PendingLinear``)."""
+        return PendingLinear(x, self.weight)
+
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                 epilogue: Optional[str] = None) -> torch.Tensor:
+        if isinstance(x, ScaledRows):
+            y = ops.linear_scaled(x.x, x.ssq, x.eps, self.weight, out_dtype=out_dtype, epilogue=epilogue)
+            if y is not None:
+                return y
+            x = x.materialize()
         if isinstance(x, PendingNorm):
             y = ops.linear_normed(x, self.weight, out_dtype=out_dtype, epilogue=epilogue)
             if y is not None:

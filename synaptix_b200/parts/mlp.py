@@ -16,6 +16,7 @@ from .linear import Linear
 
 class SwiGLU(FeedForward):
     accepts_lazy_input = True      # x goes straight into the fused gate/up product
+    can_defer_output = True        # the down projection may be handed on unrun
 
     def __init__(self, prefix: str, width: int, intermediate: int):
         self.width, self.intermediate = width, intermediate
@@ -30,6 +31,6 @@ class SwiGLU(FeedForward):
         return {"kind": "swiglu", "w_gu": self.gate_up.weight, "w_down": self.down.weight,
                 "H": self.width, "I": self.intermediate}
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx: StepContext, defer_output: bool = False) -> torch.Tensor:
         z = self.gate_up.forward(x, epilogue="silu_mul")
-        return self.down.forward(z)
+        return self.down.deferred(z) if defer_output else self.down.forward(z)

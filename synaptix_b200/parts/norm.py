@@ -14,7 +14,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorSpec
-from .base import Norm, PendingNorm, Runtime, to_device_f32
+from .base import Norm, PendingLinear, PendingNorm, Runtime, ScaledRows, to_device_f32
 
 
 class RMSNorm(Norm):
@@ -40,7 +40,18 @@ class RMSNorm(Norm):
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return ops.add_rmsnorm(h, None, self.weight, self.eps, self._dtype)
 
+    takes_pending_product = True
+
     def add_forward(self, h, delta, rows=None, lazy=False):
+        if isinstance(delta, PendingLinear):
+            N, K = delta.weight.shape
+            if (lazy and rows is None and N == self.width and h.dtype == torch.float32 and h.is_contiguous()
+                    and delta.weight.dtype == self._dtype and delta.x.dtype == self._dtype
+                    and ops.residual_product_fusable(h.shape[0], N, K, self._dtype)):
+                # the product adds itself into h and leaves the rows of this norm without their factor
+                x, ssq = ops.linear_into_residual(delta.x, delta.weight, h, self.weight)
+                return ScaledRows(x, ssq, self.eps, h, self.weight, self._dtype)
+            delta = delta.materialize()
         if lazy and rows is None and ops.norm_fusable(h.shape[0], h.shape[1], self._dtype):
             return PendingNorm(h, delta, self.weight, self.eps, self._dtype)
         return ops.add_rmsnorm(h, delta, self.weight, self.eps, self._dtype, rows=rows)

@@ -399,6 +399,42 @@ def test_skinny_gemm_with_norm_prologue(M, epilogue, N, K):
     assert torch.allclose(out.float().cpu().double(), y2, atol=3e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("M", [1, 2, 5, 8, 13, 16, 40])
+@pytest.mark.parametrize("N,K", [(2560, 4096), (176, 96), (100, 320), (24, 9728)])
+def test_skinny_gemm_adds_into_the_residual_and_prepares_the_norm(M, N, K):
+    """h += x W^T in place, x~ = bf16(h * gain) and partial sums of squares of h; then a second product takes x~
+    and the partial sums and must give what it gives for the plain rmsnorm(h) * gain (all three epilogues)."""
+    from synaptix_b200.ops.decode import skinny_gemm_residual, skinny_gemm_scaled
+    g = torch.Generator().manual_seed(M * 7919 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    h0 = torch.randn(M, N, generator=g) * torch.logspace(-1, 1, M)[:, None]      # rows of very different size
+    gain = 1 + 0.3 * torch.randn(N, generator=g)
+    eps = 1e-5
+    h_ref = h0.double() + x.double() @ w.double().T
+    for ks in (1, 4, 8, 16):
+        h = h0.clone().cuda()
+        xt, ssq = skinny_gemm_residual(x.cuda(), w.cuda(), h, gain.cuda(), ks=ks)
+        assert torch.allclose(h.cpu().double(), h_ref, atol=2e-5 * math.sqrt(K), rtol=1e-5), f"ks={ks}"
+        assert ssq.shape == (M, (N + 15) // 16)
+        assert torch.allclose(ssq.sum(1).cpu().double(), (h_ref ** 2).sum(1), rtol=1e-4), f"ks={ks}"
+        assert torch.allclose(xt.float().cpu().double(), h_ref * gain.double(), atol=1e-3, rtol=1e-2), f"ks={ks}"
+    # the consumer: N is its inner size now
+    if N % 32:
+        return
+    xn = P.rms_norm(h.cpu(), gain, eps)
+    for epilogue, N2 in ((None, 200), ("f32", 389), ("silu_mul", 144)):
+        w2 = (torch.randn(N2, N, generator=g) / math.sqrt(N)).to(torch.bfloat16)
+        y = xn.double() @ w2.double().T
+        if epilogue == "silu_mul":
+            y = y[:, :N2 // 2] / (1 + torch.exp(-y[:, :N2 // 2])) * y[:, N2 // 2:]
+        for ks in (1, 8):
+            out = skinny_gemm_scaled(xt, w2.cuda(), ssq, eps, epilogue=epilogue, ks=ks)
+            assert torch.allclose(out.float().cpu().double(), y, atol=3e-2, rtol=2e-2), f"{epilogue} ks={ks}"
+    out = skinny_gemm_scaled(xt, w2.cuda(), None, 0.0, epilogue="f32")          # without partial sums: a plain product
+    assert torch.allclose(out.cpu().double(), xt.float().cpu().double() @ w2.double().T, atol=2e-5 * math.sqrt(N) * 30, rtol=1e-4)
+
+
 @pytest.mark.parametrize("M", [1, 8, 9, 16, 40, 64])
 @pytest.mark.parametrize("N,K", [(389, 32), (100, 544), (2560, 2560), (48, 9728), (16, 512), (700, 1056)])
 def test_ring_gemm(M, N, K):
