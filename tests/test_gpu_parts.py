@@ -49,6 +49,42 @@ def test_rmsnorm_part(dtype):
     assert torch.allclose(n.forward(h).float().cpu(), P.rms_norm(ref_h, w.float(), 3e-5), **tol(dtype))
 
 
+@pytest.mark.parametrize("rows", [1, 5, 16, 20])
+def test_a_deferred_product_through_the_norm_and_the_next_product(rows):
+    """A branch's last product handed on unrun (PendingLinear): the norm lets it add itself into h and hands scaled
+    rows to the next product (3 to 16 rows), or runs it and norms as ever; either way the numbers are the plain ones.
+    A norm that does not say it takes such a thing never sees one (the block runs the product first)."""
+    from synaptix_b200.parts import Linear, RMSNorm
+    from synaptix_b200.parts.base import PendingLinear, ScaledRows
+    width, inner, out = 96, 160, 72
+    bf = torch.bfloat16
+    n = RMSNorm("n.weight", width, 2e-5)
+    gain = 1 + 0.2 * torch.randn(width)
+    n.bind({"n.weight": gain}, rt(bf))
+    down = Linear("d.weight", inner, width)
+    nxt = Linear("q.weight", width, out)
+    wd = (torch.randn(width, inner) / math.sqrt(inner)).to(bf)
+    wq = (torch.randn(out, width) / math.sqrt(width)).to(bf)
+    down.bind({"d.weight": wd}, rt(bf))
+    nxt.bind({"q.weight": wq}, rt(bf))
+    z = torch.randn(rows, inner).to(bf)
+    h0 = torch.randn(rows, width) * 3
+    ref_h = h0.double() + z.double() @ wd.double().T
+    ref_y = P.rms_norm(ref_h.float(), gain, 2e-5).double() @ wq.double().T
+    for lazy in (True, False):
+        h = h0.clone().cuda()
+        x = n.add_forward(h, down.deferred(z.cuda()), lazy=lazy)
+        assert isinstance(x, ScaledRows) == (lazy and 2 < rows <= 16)
+        y = nxt.forward(x, out_dtype=torch.float32)
+        h_after = x.h_after() if hasattr(x, "h_after") else h        # a lazy norm says where the sum went
+        assert torch.allclose(h_after.cpu().double(), ref_h, atol=3e-2, rtol=1e-2)          # the branch is rounded to bf16 when run alone
+        assert torch.allclose(y.cpu().double(), ref_y, atol=3e-2, rtol=2e-2)
+        if isinstance(x, ScaledRows):
+            assert torch.allclose(x.materialize().float().cpu(), P.rms_norm(ref_h.float(), gain, 2e-5), atol=3e-2, rtol=2e-2)
+    pl = PendingLinear(z.cuda(), down.weight)
+    assert pl.shape == (rows, width) and pl.materialize() is pl.materialize()
+
+
 def test_rotary_part_has_the_plain_frequencies():
     from synaptix_b200.parts import RotaryHalf
     r = RotaryHalf(48, 77777.0, rotary_dim=32)
