@@ -137,15 +137,19 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
   pdl_wait();          // the weights depend on no earlier kernel; everything below may
   pdl_trigger();
 
+  // The rows' factors (consumer side of SkNorm): one warp per row adds the partial sums, lane i those at i, i + 32,
+  // ... in that order, then the lanes' butterfly.  The partial sums are asked for here and added after the main
+  // loop, so that the trip to L2 is not in the way of the first weights.
   __shared__ float row_factor[NT * 8];
-  if (nrm.ssq_in) {           // one warp per row: the partial sums in index order, then the lanes' butterfly
-    for (int b = warp; b < M; b += WARPS) {
-      float ss = 0.f;
-      for (int i = lane; i < nrm.n_in; i += 32) ss += nrm.ssq_in[(size_t)b * nrm.n_in + i];
-      ss = warp_sum(ss);
-      if (lane == 0) row_factor[b] = rsqrtf(ss / (float)K + nrm.eps_in);
+  constexpr int PRE = 8;
+  float pre[PRE];
+  const bool pre_ok = nrm.ssq_in && nrm.n_in <= 32 * PRE && M <= WARPS;
+  if (pre_ok && warp < M) {
+#pragma unroll
+    for (int i = 0; i < PRE; ++i) {
+      const int idx = lane + 32 * i;
+      pre[i] = idx < nrm.n_in ? nrm.ssq_in[(size_t)warp * nrm.n_in + idx] : 0.f;
     }
-    if (KS == 1) __syncthreads();      // with KS > 1 the barrier of the add-up below orders it
   }
 
   if (XS) {
@@ -262,6 +266,26 @@ __global__ void __launch_bounds__(KS > SK_WARPS ? KS * 32 : SK_THREADS) skinny_g
     }
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+
+  if (nrm.ssq_in) {
+    if (pre_ok) {
+      if (warp < M) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < PRE; ++i) ss += pre[i];
+        ss = warp_sum(ss);
+        if (lane == 0) row_factor[warp] = rsqrtf(ss / (float)K + nrm.eps_in);
+      }
+    } else {
+      for (int b = warp; b < M; b += WARPS) {
+        float ss = 0.f;
+        for (int i = lane; i < nrm.n_in; i += 32) ss += nrm.ssq_in[(size_t)b * nrm.n_in + i];
+        ss = warp_sum(ss);
+        if (lane == 0) row_factor[b] = rsqrtf(ss / (float)K + nrm.eps_in);
+      }
+    }
+    if (KS == 1) __syncthreads();      // with KS > 1 the barrier of the add-up below orders it
+  }
 
   // EPI_RESID: the residual stream's values of this warp's results, asked for before the add-up hides the trip
   float hv[EPI == EPI_RESID ? NT : 1][4];
