@@ -1,11 +1,11 @@
 // Weight-streaming matrix products for decode steps (few rows of activations, bfloat16).
 //
-//   y[b, n] = sum_k x[b, k] * W[n, k]      b < M <= 64,  W [N, K] row-major,  32-bit accumulation
+//   y[b, n] = sum_k x[b, k] * W[n, k]      b < M <= 16,  W [N, K] row-major,  32-bit accumulation
 //
 // A decode step reads every weight once, so these kernels are bound by HBM, not by math.
 // The reference has a warp-per-row GEMV for one row of activations only and falls to a 32x32
 // GEMM tile for more (crates/synaptix-kernels-cuda/src/best_cu/gemv/mma_gemv.cu:19-133,
-// crates/synaptix-kernels-cuda/src/cuda_backend.rs:738-754); here one kernel serves 1..64 rows
+// crates/synaptix-kernels-cuda/src/cuda_backend.rs:738-754); here one kernel serves 1..16 rows
 // and reads W once for all of them.
 //
 // Shape of the kernel.  The roles of the operands are swapped: 16 rows of W are the M side of
@@ -408,38 +408,35 @@ static int skinny_launch(const bf16* x, const bf16* W, void* out, int M, int N, 
   return sx_launch(kern, dim3(grid), dim3(THREADS), smem, stream, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm);
 }
 
+// 8 warps split K, or 16 (blocks of 16 warps); 1, 2 and 4 measured slower everywhere and are not built
 template <int NT, int EPI, bool XS>
 static int skinny_pick_ks(int ks, const bf16* x, const bf16* W, void* out, int M, int N, int K, const float* h_in,
                           const bf16* delta, float* h_out, const float* gain, float eps, const SkNorm& nrm, cudaStream_t stream) {
   switch (ks) {
     case 16: return skinny_launch<NT, 16, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
     case 8: return skinny_launch<NT, 8, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
-    case 4: return skinny_launch<NT, 4, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
-    case 2: return skinny_launch<NT, 2, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
-    default: return skinny_launch<NT, 1, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
+    default: return SX_ERR_SIZE;
   }
 }
 
+// up to 16 rows (more go to the tcgen05 product, which takes every K this kernel takes)
 template <int EPI, bool XS>
 static int skinny_pick_nt(int ks, const bf16* x, const bf16* W, void* out, int M, int N, int K, const float* h_in,
                           const bf16* delta, float* h_out, const float* gain, float eps, const SkNorm& nrm, cudaStream_t stream) {
   if (M <= 8) return skinny_pick_ks<1, EPI, XS>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
   if (M <= 16) return skinny_pick_ks<2, EPI, XS>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
-  if (XS) return SX_ERR_SIZE;
-  if (M <= 32) return skinny_pick_ks<4, EPI, false>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
-  if (M <= 64) return skinny_pick_ks<8, EPI, false>(ks, x, W, out, M, N, K, h_in, delta, h_out, gain, eps, nrm, stream);
   return SX_ERR_SIZE;
 }
 
 // x [M, K] bf16 (or, with h_in, computed as rmsnorm(h_in + delta) * gain), W [N, K] bf16.
 // epi 0: out bf16 [M, N];  1: out f32 [M, N];  2: W is [gate; up] stacked, out bf16 [M, N/2] = silu(gate) * up.
-// ks: warps that split K (1, 2, 4, 8, or 16 with blocks of 16 warps).  Requires K % 32 == 0, 16-byte aligned x and W, M <= 64
-// (M <= 16 with the norm prologue).
+// ks: warps that split K (8, or 16 with blocks of 16 warps).  Requires K % 32 == 0, 16-byte aligned x and W, M <= 16
+// (M <= XS_ROWS = 2 with the norm prologue).
 extern "C" int sx_skinny_gemm(const void* x, const void* W, void* out, int M, int N, int K, int epi, int ks,
                               const float* h_in, const void* delta, float* h_out, const float* gain, float eps,
                               cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || (K & 31) || M > 64) return SX_ERR_SIZE;
+  if (K <= 0 || (K & 31) || M > 16) return SX_ERR_SIZE;
   if (epi == EPI_SILU_MUL && (N & 1)) return SX_ERR_SIZE;
   if (((uintptr_t)W & 15) || (x && ((uintptr_t)x & 15))) return SX_ERR_ALIGN;
   const bf16* xb = (const bf16*)x;
@@ -471,7 +468,7 @@ extern "C" int sx_skinny_gemm_norm(const void* x, const void* W, void* out, int 
                                    const float* ssq_in, int n_in, float eps_in, float* h_io, const float* gain_next,
                                    float* ssq_out, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || (K & 31) || M > 64 || !x) return SX_ERR_SIZE;
+  if (K <= 0 || (K & 31) || M > 16 || !x) return SX_ERR_SIZE;
   if (epi == EPI_SILU_MUL && (N & 1)) return SX_ERR_SIZE;
   if (ssq_in && n_in <= 0) return SX_ERR_SIZE;
   if (epi == EPI_RESID && (!h_io || !gain_next || !ssq_out)) return SX_ERR_SIZE;
@@ -486,317 +483,4 @@ extern "C" int sx_skinny_gemm_norm(const void* x, const void* W, void* out, int 
     case EPI_RESID: return skinny_pick_nt<EPI_RESID, false>(ks, xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, nrm, stream);
     default: return SX_ERR_DTYPE;
   }
-}
-
-// =======================================================================================
-// The same product with W brought in by bulk asynchronous copies through a ring of
-// shared-memory stages (cp.async.bulk + mbarrier), persistent over row tiles.
-//
-// The direct-load kernel above has only a few 16-byte loads per thread in flight, which is
-// too little for the small matrices of a layer (the 31 MB of a fused q/k/v matrix need
-// several MB in flight to run at HBM speed).  Here a producer warp keeps STAGES x 16 KB per
-// block in flight whatever the consumers do: a stage is 16 rows of W x 512 k-values, each row
-// one 1 KB bulk copy; 8 consumer warps split a stage's k between them (two 32-k steps each),
-// read their fragments from shared memory with the same "16 bytes of k per thread" map as
-// above, and add up through shared memory at the end of a row tile.  A block walks over row
-// tiles blockIdx.x, blockIdx.x + gridDim.x, ... with the ring running ahead across tiles.
-// Every wait on an mbarrier is bounded; a wait that runs out sets *status and the block ends.
-// =======================================================================================
-#define RG_CONSUMERS 8
-#define RG_THREADS (RG_CONSUMERS * 32 + 32)
-#define RG_STAGE_K 512
-#define RG_ROW_BYTES (RG_STAGE_K * 2 + 16)        // padded: rows land in different banks
-#define RG_STAGE_BYTES (16 * RG_ROW_BYTES)
-#define RG_SPIN_LIMIT (1u << 26)
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-// bounded wait: false if the phase did not complete within the limit
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < RG_SPIN_LIMIT; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ uint4 lds16(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
-
-template <int NT, int EPI, bool XS, int STAGES>
-__global__ void __launch_bounds__(RG_THREADS) ring_gemm_kernel(
-    const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int M, int N, int K,
-    const float* __restrict__ h_in, const bf16* __restrict__ delta, float* __restrict__ h_out,
-    const float* __restrict__ gain, float eps, int* __restrict__ status) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  unsigned char* stages = smem_raw;                                                   // STAGES * RG_STAGE_BYTES
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + STAGES * RG_STAGE_BYTES);   // full[STAGES], empty[STAGES]
-  float* red = reinterpret_cast<float*>(bars + 2 * STAGES);                           // [2][8][NT][4][32]
-  bf16* xs = reinterpret_cast<bf16*>(red + 2 * RG_CONSUMERS * NT * 4 * 32);           // [NT*8][K] (XS only)
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, t = lane & 3;
-  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, RG_CONSUMERS);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  }
-  __syncthreads();
-
-  const int n_rows_out = (EPI == EPI_SILU_MUL) ? N / 2 : N;
-  const int rows_per_tile = (EPI == EPI_SILU_MUL) ? 8 : 16;
-  const int tiles = (n_rows_out + rows_per_tile - 1) / rows_per_tile;
-  const int nk = (K + RG_STAGE_K - 1) / RG_STAGE_K;
-
-  if (warp == RG_CONSUMERS) {
-    // ------------------------------ producer ------------------------------
-    uint32_t it = 0;
-    bool alive = true;
-    for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
-      int row = 0;
-      if (lane < 16) {
-        if (EPI == EPI_SILU_MUL) {
-          const int i = min(tile * 8 + (lane & 7), N / 2 - 1);
-          row = (lane < 8) ? i : N / 2 + i;
-        } else {
-          row = min(tile * 16 + lane, N - 1);
-        }
-      }
-      const bf16* wrow = W + (size_t)row * K;
-      for (int kb = 0; kb < nk; ++kb, ++it) {
-        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-        bool ok = true;
-        if (lane == 0) ok = mbar_wait(empty0 + 8 * s, ph ^ 1);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) {
-          if (lane == 0) atomicExch(status, 1);
-          alive = false;
-          break;
-        }
-        const int k0 = kb * RG_STAGE_K;
-        const uint32_t row_bytes = (uint32_t)min(RG_STAGE_K, K - k0) * 2u;
-        if (lane == 0) mbar_expect_tx(full0 + 8 * s, row_bytes * 16u);
-        __syncwarp();
-        if (lane < 16)
-          bulk_copy_g2s(smem_u32(stages + (size_t)s * RG_STAGE_BYTES + lane * RG_ROW_BYTES), wrow + k0, row_bytes,
-                        full0 + 8 * s);
-      }
-    }
-    // copies in flight are waited for by the consumers; if they gave up, wait here (bounded)
-    return;
-  }
-
-  // ------------------------------ consumers ------------------------------
-  if (XS) {
-    for (int b = warp; b < NT * 8; b += RG_CONSUMERS) {
-      bf16* xr = xs + (size_t)b * K;
-      if (b < M) {
-        const float* hr = h_in + (size_t)b * K;
-        const bf16* dr = delta ? delta + (size_t)b * K : nullptr;
-        float ss = 0.f;
-        for (int k = lane; k < K; k += 32) {
-          const float v = hr[k] + (dr ? __bfloat162float(dr[k]) : 0.f);
-          ss += v * v;
-        }
-        ss = warp_sum(ss);
-        const float inv = rsqrtf(ss / (float)K + eps);
-        for (int k = lane; k < K; k += 32) {
-          const float v = hr[k] + (dr ? __bfloat162float(dr[k]) : 0.f);
-          if (blockIdx.x == 0 && h_out) h_out[(size_t)b * K + k] = v;
-          xr[k] = __float2bfloat16_rn(v * inv * gain[k]);
-        }
-      } else {
-        for (int k = lane; k < K; k += 32) xr[k] = __float2bfloat16_rn(0.f);
-      }
-    }
-    asm volatile("bar.sync 1, %0;\n" ::"n"(RG_CONSUMERS * 32) : "memory");
-  }
-
-  uint32_t it = 0;
-  int buf = 0;
-  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, buf ^= 1) {
-    float acc[NT][4];
-#pragma unroll
-    for (int i = 0; i < NT; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-
-    for (int kb = 0; kb < nk; ++kb, ++it) {
-      const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-      if (!mbar_wait(full0 + 8 * s, ph)) {
-        if (lane == 0) atomicExch(status, 2);
-        return;
-      }
-      const int k0 = kb * RG_STAGE_K;
-      const int steps = min(RG_STAGE_K, K - k0) >> 5;
-      const uint32_t base = smem_u32(stages + (size_t)s * RG_STAGE_BYTES) + t * 16;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int st = warp + h * RG_CONSUMERS;
-        if (st < steps) {
-          const uint4 va = lds16(base + g * RG_ROW_BYTES + st * 64);
-          const uint4 vb = lds16(base + (g + 8) * RG_ROW_BYTES + st * 64);
-          const int kk = k0 + st * 32 + t * 8;
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            const int b = nt * 8 + g;
-            uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-            if (XS) xv = *reinterpret_cast<const uint4*>(xs + (size_t)b * K + kk);
-            else if (b < M) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)b * K + kk));
-            mma_bf16_16816(acc[nt], va.x, vb.x, va.y, vb.y, xv.x, xv.y);
-            mma_bf16_16816(acc[nt], va.z, vb.z, va.w, vb.w, xv.z, xv.w);
-          }
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty0 + 8 * s);
-    }
-
-    // add up the 8 warps' partial sums in warp order
-    float* rb = red + (size_t)buf * RG_CONSUMERS * NT * 4 * 32;
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) rb[((warp * NT + nt) * 4 + j) * 32 + lane] = acc[nt][j];
-    asm volatile("bar.sync 1, %0;\n" ::"n"(RG_CONSUMERS * 32) : "memory");
-    if (warp != 0) continue;
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float v = acc[nt][j];
-        for (int w = 1; w < RG_CONSUMERS; ++w) v += rb[((w * NT + nt) * 4 + j) * 32 + lane];
-        acc[nt][j] = v;
-      }
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int b = nt * 8 + t * 2 + j;
-        if (b >= M) continue;
-        if (EPI == EPI_SILU_MUL) {
-          const int I = N / 2;
-          const int i = tile * 8 + g;
-          if (i < I) {
-            const float gate = acc[nt][j], up = acc[nt][2 + j];
-            reinterpret_cast<bf16*>(out)[(size_t)b * I + i] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
-          }
-        } else {
-          const int n0 = tile * 16 + g, n1 = n0 + 8;
-          if (EPI == EPI_F32) {
-            if (n0 < N) reinterpret_cast<float*>(out)[(size_t)b * N + n0] = acc[nt][j];
-            if (n1 < N) reinterpret_cast<float*>(out)[(size_t)b * N + n1] = acc[nt][2 + j];
-          } else {
-            if (n0 < N) reinterpret_cast<bf16*>(out)[(size_t)b * N + n0] = __float2bfloat16_rn(acc[nt][j]);
-            if (n1 < N) reinterpret_cast<bf16*>(out)[(size_t)b * N + n1] = __float2bfloat16_rn(acc[nt][2 + j]);
-          }
-        }
-      }
-    }
-  }
-}
-
-static int* rg_status_word() {
-  static int* p = nullptr;           // one word per process and device 0..; allocated at first use
-  static int dev_of = -1;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (p == nullptr || dev_of != dev) {
-    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
-    cudaMemset(p, 0, sizeof(int));
-    dev_of = dev;
-  }
-  return p;
-}
-
-template <int NT, int EPI, bool XS>
-static int ring_launch(const bf16* x, const bf16* W, void* out, int M, int N, int K, const float* h_in,
-                       const bf16* delta, float* h_out, const float* gain, float eps, int max_blocks,
-                       cudaStream_t stream) {
-  constexpr int STAGES = 6;
-  int* status = rg_status_word();
-  if (!status) return (int)cudaErrorMemoryAllocation;
-  const int rows_per_tile = (EPI == EPI_SILU_MUL) ? 8 : 16;
-  const int n_rows_out = (EPI == EPI_SILU_MUL) ? N / 2 : N;
-  const int tiles = (n_rows_out + rows_per_tile - 1) / rows_per_tile;
-  const int grid = tiles < max_blocks ? tiles : max_blocks;
-  const size_t smem = (size_t)STAGES * RG_STAGE_BYTES + 2 * STAGES * sizeof(uint64_t) +
-                      2 * (size_t)RG_CONSUMERS * NT * 4 * 32 * sizeof(float) + (XS ? (size_t)NT * 8 * K * sizeof(bf16) : 0);
-  if (smem > 227 * 1024) return SX_ERR_SIZE;
-  auto kern = ring_gemm_kernel<NT, EPI, XS, STAGES>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return (int)e;
-  kern<<<grid, RG_THREADS, smem, stream>>>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, status);
-  return sx_launch_status();
-}
-
-template <int EPI, bool XS>
-static int ring_pick_nt(const bf16* x, const bf16* W, void* out, int M, int N, int K, const float* h_in,
-                        const bf16* delta, float* h_out, const float* gain, float eps, int max_blocks,
-                        cudaStream_t stream) {
-  if (M <= 8) return ring_launch<1, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, max_blocks, stream);
-  if (M <= 16) return ring_launch<2, EPI, XS>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, max_blocks, stream);
-  if (XS) return SX_ERR_SIZE;
-  if (M <= 32) return ring_launch<4, EPI, false>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, max_blocks, stream);
-  if (M <= 64) return ring_launch<8, EPI, false>(x, W, out, M, N, K, h_in, delta, h_out, gain, eps, max_blocks, stream);
-  return SX_ERR_SIZE;
-}
-
-// Same contract as sx_skinny_gemm; max_blocks bounds the persistent grid (2 blocks per SM fit).
-extern "C" int sx_ring_gemm(const void* x, const void* W, void* out, int M, int N, int K, int epi, int max_blocks,
-                            const float* h_in, const void* delta, float* h_out, const float* gain, float eps,
-                            cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || (K & 31) || M > 64 || max_blocks <= 0) return SX_ERR_SIZE;
-  if (epi == EPI_SILU_MUL && (N & 1)) return SX_ERR_SIZE;
-  if (((uintptr_t)W & 15) || (x && ((uintptr_t)x & 15))) return SX_ERR_ALIGN;
-  const bf16* xb = (const bf16*)x;
-  const bf16* wb = (const bf16*)W;
-  const bf16* db = (const bf16*)delta;
-  if (h_in) {
-    switch (epi) {
-      case EPI_BF16: return ring_pick_nt<EPI_BF16, true>(xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, max_blocks, stream);
-      case EPI_F32: return ring_pick_nt<EPI_F32, true>(xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, max_blocks, stream);
-      case EPI_SILU_MUL: return ring_pick_nt<EPI_SILU_MUL, true>(xb, wb, out, M, N, K, h_in, db, h_out, gain, eps, max_blocks, stream);
-      default: return SX_ERR_DTYPE;
-    }
-  }
-  switch (epi) {
-    case EPI_BF16: return ring_pick_nt<EPI_BF16, false>(xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, max_blocks, stream);
-    case EPI_F32: return ring_pick_nt<EPI_F32, false>(xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, max_blocks, stream);
-    case EPI_SILU_MUL: return ring_pick_nt<EPI_SILU_MUL, false>(xb, wb, out, M, N, K, nullptr, nullptr, nullptr, nullptr, 0.f, max_blocks, stream);
-    default: return SX_ERR_DTYPE;
-  }
-}
-
-// the status word of the ring kernels: 0, or which wait ran out (1 producer, 2 consumer)
-extern "C" int sx_ring_status(int* host_value) {
-  int* p = rg_status_word();
-  if (!p) return (int)cudaErrorMemoryAllocation;
-  return (int)cudaMemcpy(host_value, p, sizeof(int), cudaMemcpyDeviceToHost);
 }

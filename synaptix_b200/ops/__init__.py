@@ -16,7 +16,7 @@ from ..csrc.build import KernelsUnavailable
 from ._lib import KernelError, set_launch_counter
 from .attention import (TC_TILE_ROWS, attn_decode, attn_decode_prep, attn_prefill, attn_prefill_tc, fast_supported, pick_splits,
                         query_tiles, tc_prefill_supported)
-from .decode import skinny_gemm, skinny_gemm_residual, skinny_gemm_scaled, skinny_supported
+from .decode import MAX_ROWS as SKINNY_MAX_ROWS, skinny_gemm, skinny_gemm_residual, skinny_gemm_scaled, skinny_supported
 from .gemm_tc import gemm_tc, tc_supported
 from .generic import (add_rmsnorm, attn_generic, decode_advance, embed_gather, gemm_generic, qkv_prepare,
                       residual_add,
@@ -28,7 +28,6 @@ __all__ = ["KernelsUnavailable", "KernelError", "set_launch_counter", "decode_ad
            "linear_into_residual", "linear_scaled"]
 
 
-SKINNY_MAX_ROWS = 16
 # Every block of a product that applies row factors fetches the partial sums; an output head has thousands of
 # blocks, and there one norm kernel before it is cheaper (132 against 122 us for 151,936 outputs of 8 rows).
 SCALED_MAX_OUT = 65536
@@ -44,8 +43,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if out_dtype is None:
         out_dtype = x.dtype
     # few rows: stream W once on mma.sync; more than SKINNY_MAX_ROWS: tcgen05 (split over K while rows are few)
-    if (skinny_supported(M, N, K, x.dtype, w.dtype) and out_dtype in (torch.bfloat16, torch.float32)
-            and (M <= SKINNY_MAX_ROWS or not tc_supported(M, N, K, x.dtype, w.dtype))):
+    if skinny_supported(M, N, K, x.dtype, w.dtype) and out_dtype in (torch.bfloat16, torch.float32):
         if epilogue == "silu_mul":
             if out_dtype == torch.bfloat16:
                 return skinny_gemm(x, w, epilogue="silu_mul")

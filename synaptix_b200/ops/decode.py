@@ -1,4 +1,4 @@
-"""Python face of the weight-streaming products in ``csrc/decode.cu`` (bfloat16, up to 64 rows)."""
+"""Python face of the weight-streaming products in ``csrc/decode.cu`` (bfloat16, up to 16 rows)."""
 from __future__ import annotations
 
 from typing import Optional
@@ -8,10 +8,11 @@ import torch
 from ._lib import KernelError, c_float, c_int, check, fn, ptr, require_cuda, stream
 
 _EPI = {None: 0, "f32": 1, "silu_mul": 2}
+MAX_ROWS = 16          # more rows go to the tcgen05 product, which takes every K this kernel takes
 
 
 def skinny_supported(M: int, N: int, K: int, x_dtype, w_dtype) -> bool:
-    return (x_dtype == torch.bfloat16 and w_dtype == torch.bfloat16 and 0 < M <= 64 and K % 32 == 0 and K > 0)
+    return (x_dtype == torch.bfloat16 and w_dtype == torch.bfloat16 and 0 < M <= MAX_ROWS and K % 32 == 0 and K > 0)
 
 
 def pick_ks(tiles: int, K: int = 0) -> int:
@@ -27,13 +28,13 @@ def skinny_gemm(x: Optional[torch.Tensor], w: torch.Tensor, *, epilogue: Optiona
                 norm_h: Optional[torch.Tensor] = None, norm_delta: Optional[torch.Tensor] = None,
                 norm_h_out: Optional[torch.Tensor] = None, norm_gain: Optional[torch.Tensor] = None,
                 norm_eps: float = 0.0) -> torch.Tensor:
-    """``x[M, K] @ w[N, K].T`` for ``M <= 64`` rows, reading ``w`` once.
+    """``x[M, K] @ w[N, K].T`` for ``M <= 16`` rows, reading ``w`` once (``ks``: 8 or 16 warps split K).
 
     ``epilogue``: ``None`` -> bfloat16 ``[M, N]``; ``"f32"`` -> float32 ``[M, N]``;
     ``"silu_mul"`` -> ``w`` is ``[gate; up]`` stacked, result bfloat16 ``[M, N/2]``.
     With ``norm_h`` (float32 ``[M, K]``) the activations are computed inside the kernel as
     ``rmsnorm(norm_h + norm_delta) * norm_gain`` and ``norm_h + norm_delta`` is written to
-    ``norm_h_out`` (which must not alias ``norm_h``); then ``M <= 16`` and ``x`` is ``None``.
+    ``norm_h_out`` (which must not alias ``norm_h``); then ``M <= 2`` and ``x`` is ``None``.
     """
     require_cuda(x, w, out, norm_h, norm_delta, norm_h_out, norm_gain)
     N, K = w.shape
@@ -113,42 +114,3 @@ def sm_count(device) -> int:
     if i not in _SM_COUNT:
         _SM_COUNT[i] = torch.cuda.get_device_properties(i).multi_processor_count
     return _SM_COUNT[i]
-
-
-def ring_gemm(x: Optional[torch.Tensor], w: torch.Tensor, *, epilogue: Optional[str] = None,
-              max_blocks: Optional[int] = None, out: Optional[torch.Tensor] = None,
-              norm_h: Optional[torch.Tensor] = None, norm_delta: Optional[torch.Tensor] = None,
-              norm_h_out: Optional[torch.Tensor] = None, norm_gain: Optional[torch.Tensor] = None,
-              norm_eps: float = 0.0) -> torch.Tensor:
-    """The same product as ``skinny_gemm`` with ``w`` streamed by bulk asynchronous copies through
-    a ring of shared-memory stages, persistent over row tiles (see ``csrc/decode.cu``)."""
-    require_cuda(x, w, out, norm_h, norm_delta, norm_h_out, norm_gain)
-    N, K = w.shape
-    src = x if x is not None else norm_h
-    M = src.shape[0]
-    if src.shape[1] != K:
-        raise KernelError("ring_gemm: inner sizes differ")
-    if epilogue not in _EPI:
-        raise KernelError(f"ring_gemm: unknown epilogue {epilogue!r}")
-    if norm_h is not None:
-        if norm_h.dtype != torch.float32 or norm_gain is None or norm_gain.dtype != torch.float32:
-            raise KernelError("ring_gemm: the norm prologue takes float32 h and gain")
-        if norm_h_out is not None and norm_h_out.data_ptr() == norm_h.data_ptr():
-            raise KernelError("ring_gemm: norm_h_out must not alias norm_h")
-    n_out = N // 2 if epilogue == "silu_mul" else N
-    if out is None:
-        out = torch.empty((M, n_out), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=w.device)
-    if max_blocks is None:
-        max_blocks = 2 * sm_count(w.device)
-    check(fn("decode", "sx_ring_gemm")(ptr(x), ptr(w), ptr(out), c_int(M), c_int(N), c_int(K), c_int(_EPI[epilogue]),
-                                       c_int(max_blocks), ptr(norm_h), ptr(norm_delta), ptr(norm_h_out),
-                                       ptr(norm_gain), c_float(norm_eps), stream()), "ring_gemm")
-    return out
-
-
-def ring_status() -> int:
-    """0, or which bounded wait of a ring kernel ran out (1 producer, 2 consumer); synchronises."""
-    import ctypes
-    v = ctypes.c_int(0)
-    check(fn("decode", "sx_ring_status")(ctypes.byref(v)), "ring_status", launches=0)
-    return v.value

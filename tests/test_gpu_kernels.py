@@ -332,7 +332,7 @@ def test_sampling_does_not_depend_on_batch_composition():
         assert one[0] == whole[r]
 
 
-@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("N,K", [(389, 32), (100, 256), (2560, 2560), (48, 9728), (16, 64)])
 def test_skinny_gemm(M, N, K):
     from synaptix_b200.ops.decode import skinny_gemm
@@ -340,7 +340,7 @@ def test_skinny_gemm(M, N, K):
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
     ref = x.double() @ w.double().T
-    for ks in (1, 2, 4, 8, 16):
+    for ks in (8, 16):
         out = skinny_gemm(x.cuda(), w.cuda(), epilogue="f32", ks=ks)
         assert out.shape == (M, N)
         assert torch.allclose(out.cpu().double(), ref, atol=2e-5 * math.sqrt(K), rtol=1e-5), f"ks={ks}"
@@ -348,7 +348,7 @@ def test_skinny_gemm(M, N, K):
     assert out.dtype == torch.bfloat16 and torch.allclose(out.float().cpu().double(), ref, atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("M", [1, 8, 13, 64])
+@pytest.mark.parametrize("M", [1, 8, 13, 16])
 @pytest.mark.parametrize("I,K", [(9, 64), (160, 96), (1000, 2560)])
 def test_skinny_gemm_silu_mul_epilogue(M, I, K):
     from synaptix_b200.ops.decode import skinny_gemm
@@ -357,18 +357,23 @@ def test_skinny_gemm_silu_mul_epilogue(M, I, K):
     y = x.double() @ w.double().T
     gate, up = y[:, :I], y[:, I:]
     ref = gate / (1 + torch.exp(-gate)) * up
-    for ks in (1, 4, 8):
+    for ks in (8, 16):
         out = skinny_gemm(x.cuda(), w.cuda(), epilogue="silu_mul", ks=ks)
         assert out.shape == (M, I)
         assert torch.allclose(out.float().cpu().double(), ref, atol=3e-2, rtol=2e-2), f"ks={ks}"
 
 
-def test_skinny_gemm_norm_prologue_refuses_many_rows():
+def test_skinny_gemm_refuses_what_it_does_not_take():
     from synaptix_b200.ops import KernelError
-    from synaptix_b200.ops.decode import skinny_gemm
+    from synaptix_b200.ops.decode import skinny_gemm, skinny_supported
     w = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(KernelError, match="size"):
+    with pytest.raises(KernelError, match="size"):               # the norm prologue: one or two rows
         skinny_gemm(None, w, norm_h=torch.zeros(3, 64, device="cuda"), norm_gain=torch.ones(64, device="cuda"))
+    assert not skinny_supported(17, 64, 64, torch.bfloat16, torch.bfloat16)
+    with pytest.raises(KernelError, match="size"):               # more than 16 rows
+        skinny_gemm(torch.zeros(17, 64, dtype=torch.bfloat16, device="cuda"), w)
+    with pytest.raises(KernelError, match="size"):               # 4 warps splitting K is not built
+        skinny_gemm(torch.zeros(4, 64, dtype=torch.bfloat16, device="cuda"), w, ks=4)
 
 
 @pytest.mark.parametrize("M", [1, 2])
@@ -399,7 +404,7 @@ def test_skinny_gemm_with_norm_prologue(M, epilogue, N, K):
     assert torch.allclose(out.float().cpu().double(), y2, atol=3e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("M", [1, 2, 5, 8, 13, 16, 40])
+@pytest.mark.parametrize("M", [1, 2, 5, 8, 13, 16])
 @pytest.mark.parametrize("N,K", [(2560, 4096), (176, 96), (100, 320), (24, 9728)])
 def test_skinny_gemm_adds_into_the_residual_and_prepares_the_norm(M, N, K):
     """h += x W^T in place, x~ = bf16(h * gain) and partial sums of squares of h; then a second product takes x~
@@ -412,7 +417,7 @@ def test_skinny_gemm_adds_into_the_residual_and_prepares_the_norm(M, N, K):
     gain = 1 + 0.3 * torch.randn(N, generator=g)
     eps = 1e-5
     h_ref = h0.double() + x.double() @ w.double().T
-    for ks in (1, 4, 8, 16):
+    for ks in (8, 16):
         h = h0.clone().cuda()
         xt, ssq = skinny_gemm_residual(x.cuda(), w.cuda(), h, gain.cuda(), ks=ks)
         assert torch.allclose(h.cpu().double(), h_ref, atol=2e-5 * math.sqrt(K), rtol=1e-5), f"ks={ks}"
@@ -428,62 +433,11 @@ def test_skinny_gemm_adds_into_the_residual_and_prepares_the_norm(M, N, K):
         y = xn.double() @ w2.double().T
         if epilogue == "silu_mul":
             y = y[:, :N2 // 2] / (1 + torch.exp(-y[:, :N2 // 2])) * y[:, N2 // 2:]
-        for ks in (1, 8):
+        for ks in (8, 16):
             out = skinny_gemm_scaled(xt, w2.cuda(), ssq, eps, epilogue=epilogue, ks=ks)
             assert torch.allclose(out.float().cpu().double(), y, atol=3e-2, rtol=2e-2), f"{epilogue} ks={ks}"
     out = skinny_gemm_scaled(xt, w2.cuda(), None, 0.0, epilogue="f32")          # without partial sums: a plain product
     assert torch.allclose(out.cpu().double(), xt.float().cpu().double() @ w2.double().T, atol=2e-5 * math.sqrt(N) * 30, rtol=1e-4)
-
-
-@pytest.mark.parametrize("M", [1, 8, 9, 16, 40, 64])
-@pytest.mark.parametrize("N,K", [(389, 32), (100, 544), (2560, 2560), (48, 9728), (16, 512), (700, 1056)])
-def test_ring_gemm(M, N, K):
-    from synaptix_b200.ops.decode import ring_gemm, ring_status
-    g = torch.Generator().manual_seed(M * 1000 + N)
-    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
-    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
-    ref = x.double() @ w.double().T
-    for max_blocks in (None, 3):              # 3 blocks: every block walks over many row tiles
-        out = ring_gemm(x.cuda(), w.cuda(), epilogue="f32", max_blocks=max_blocks)
-        assert torch.allclose(out.cpu().double(), ref, atol=2e-5 * math.sqrt(K), rtol=1e-5), f"max_blocks={max_blocks}"
-    out = ring_gemm(x.cuda(), w.cuda())
-    assert out.dtype == torch.bfloat16 and torch.allclose(out.float().cpu().double(), ref, atol=2e-2, rtol=2e-2)
-    assert ring_status() == 0
-
-
-@pytest.mark.parametrize("M", [1, 13, 64])
-@pytest.mark.parametrize("I,K", [(9, 64), (160, 96), (1000, 2560)])
-def test_ring_gemm_silu_mul_epilogue(M, I, K):
-    from synaptix_b200.ops.decode import ring_gemm, ring_status
-    x = torch.randn(M, K).to(torch.bfloat16)
-    w = (torch.randn(2 * I, K) * 2 / math.sqrt(K)).to(torch.bfloat16)
-    y = x.double() @ w.double().T
-    ref = y[:, :I] / (1 + torch.exp(-y[:, :I])) * y[:, I:]
-    for max_blocks in (None, 2):
-        out = ring_gemm(x.cuda(), w.cuda(), epilogue="silu_mul", max_blocks=max_blocks)
-        assert out.shape == (M, I) and torch.allclose(out.float().cpu().double(), ref, atol=3e-2, rtol=2e-2)
-    assert ring_status() == 0
-
-
-@pytest.mark.parametrize("M", [1, 5, 16])
-@pytest.mark.parametrize("epilogue,N", [(None, 200), ("silu_mul", 144)])
-def test_ring_gemm_with_norm_prologue(M, epilogue, N):
-    from synaptix_b200.ops.decode import ring_gemm, ring_status
-    K = 1056
-    h = torch.randn(M, K) * 2
-    d = torch.randn(M, K).to(torch.bfloat16)
-    gain = 1 + 0.2 * torch.randn(K)
-    w = (torch.randn(N, K) / math.sqrt(K)).to(torch.bfloat16)
-    s = h + d.float()
-    y = P.rms_norm(s, gain, 1e-5).to(torch.bfloat16).double() @ w.double().T
-    if epilogue == "silu_mul":
-        y = y[:, :N // 2] / (1 + torch.exp(-y[:, :N // 2])) * y[:, N // 2:]
-    h_out = torch.full((M, K), float("nan"), device="cuda")
-    out = ring_gemm(None, w.cuda(), epilogue=epilogue, norm_h=h.cuda(), norm_delta=d.cuda(), norm_h_out=h_out,
-                    norm_gain=gain.cuda(), norm_eps=1e-5)
-    assert torch.allclose(h_out.cpu(), s, atol=1e-6)
-    assert torch.allclose(out.float().cpu().double(), y, atol=3e-2, rtol=2e-2)
-    assert ring_status() == 0
 
 
 def fast_attention_case(nh, nkv, hd, window, past, new, seed, scale=None):
