@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the Qwen3-4B shape with random weights on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--shape 4b|8b|32b] [--batch B] [--context C]
 
 A step is one decode step of the whole batch (default batch 8, context 4,096: every
 sequence holds a prompt and decodes up to 4,096 tokens, the timed steps being the last K).
@@ -30,7 +30,13 @@ QWEN3_4B = dict(
     num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=9728, vocab_size=151936,
     rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=40960,
     hidden_act="silu", attention_bias=False, use_sliding_window=False)
-FULL_LAYERS = 36
+# the other shapes the measurement targets name (--shape); the default run is the 4B shape
+SHAPES = {
+    "4b": QWEN3_4B,
+    "8b": dict(QWEN3_4B, hidden_size=4096, intermediate_size=12288, tie_word_embeddings=False),
+    "32b": dict(QWEN3_4B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600,
+                tie_word_embeddings=False),
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -125,7 +131,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration has (named in config)")
+    ap.add_argument("--shape", default="4b", choices=sorted(SHAPES), help="layer sizes: Qwen3-4B (the default), 8B or 32B")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1/64 points, the prefill and the e2e run")
     ap.add_argument("--phase", default="all", choices=["all", "prefill"],
                     help="prefill: time only the 2,048-token prompt step (small cases for profilers)")
@@ -150,7 +157,12 @@ def main():
     from synaptix_b200.parts import Runtime
     from synaptix_b200.weights import RandomSource
 
-    cfgd = dict(QWEN3_4B, num_hidden_layers=a.layers)
+    shape = SHAPES[a.shape]
+    full_layers = shape["num_hidden_layers"]
+    name = f"Qwen3-{a.shape.upper()} shape"
+    if a.layers is None:
+        a.layers = full_layers
+    cfgd = dict(shape, num_hidden_layers=a.layers)
     cfg = Qwen3Config.from_dict(cfgd)
     dev = torch.device("cuda:0")
     model = model_skeleton(cfg)
@@ -190,8 +202,8 @@ def main():
                 "tflops": round(fl / (pms / 1e3) / 1e12, 1)}
 
     if a.phase == "prefill":
-        print(json.dumps({"metric": "prefill tok/s at 2,048 tokens (Qwen3-4B shape, bf16, random weights)", "impl": "ours",
-                          "layers": a.layers, "layers_of_config": FULL_LAYERS, "prefill": time_prefill()}))
+        print(json.dumps({"metric": f"prefill tok/s at 2,048 tokens ({name}, bf16, random weights)", "impl": "ours",
+                          "layers": a.layers, "layers_of_config": full_layers, "prefill": time_prefill()}))
         return 0
 
     def fill(B):
@@ -234,16 +246,16 @@ def main():
     nbytes = decode_bytes(cfgd, a.layers, a.batch, mean_ctx)
     achieved = nbytes / (main_r["ms_per_step"] / 1e3) / 1e9
     line = {
-        "metric": "decode tok/s (Qwen3-4B shape, bf16, random weights)", "value": round(main_r["tok_s"], 2),
+        "metric": f"decode tok/s ({name}, bf16, random weights)", "value": round(main_r["tok_s"], 2),
         "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(main_r["ms_per_step"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
-        "config": {"model": "Qwen3-4B shape, random weights", "global_batch": a.batch, "seq_len": a.context,
-                   "parallelism": "1 GPU", "layers": a.layers, "layers_of_config": FULL_LAYERS,
+        "config": {"model": f"{name}, random weights", "global_batch": a.batch, "seq_len": a.context,
+                   "parallelism": "1 GPU", "layers": a.layers, "layers_of_config": full_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-                   "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_norm_eps, "tied_head": True,
-                   "prefill_tokens": 2048, "l2": "inputs larger than L2 (a step streams ~8 GB of weights)"},
+                   "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_norm_eps, "tied_head": bool(shape["tie_word_embeddings"]),
+                   "prefill_tokens": 2048, "l2": "inputs larger than L2 (a step streams all weights, 8 GB or more)"},
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
