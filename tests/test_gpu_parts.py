@@ -330,3 +330,160 @@ def test_toy_architecture_with_a_stateful_mixer(tmp_path, dtype):
             assert_close(got, torch.stack([refs[i][cut[i] + j] for i in batch]), dtype, f"toy decode {j}")
         for i in batch:
             eng.close(slots[i])
+
+
+# ---------------------------------------------------------------------------------------------
+# a second toy architecture defined here: a feed-forward with routing (a router picks one of three
+# experts per token) and a position encoding of another law (half of every head rotated, with
+# frequencies that fall off as 1 / (1 + i)); layer 1's attention also has a window, so the two
+# layers' keys live in storage groups of their own
+# ---------------------------------------------------------------------------------------------
+def make_routed_toy():
+    from synaptix_b200 import ops
+    from synaptix_b200.config import ModelConfig, register_architecture, take
+    from synaptix_b200.models import DecoderModel
+    from synaptix_b200.parts import (Attention, Embedding, FeedForward, Linear, OutputHead, PositionEncoding,
+                                     PreNormBlock, RMSNorm, SwiGLU)
+
+    @dataclasses.dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        architectures: ClassVar[Tuple[str, ...]] = ("ToyRoutedLM",)
+        model_types: ClassVar[Tuple[str, ...]] = ("toy_routed",)
+        vocab: int = 0
+        width: int = 0
+        eps: float = 0.0
+        experts: int = 0
+        inner: int = 0
+        base: float = 0.0
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(vocab=take(d, "vocab", int), width=take(d, "width", int), eps=take(d, "eps", float),
+                       experts=take(d, "experts", int), inner=take(d, "inner", int), base=take(d, "base", float))
+
+        def to_dict(self):
+            return {"architectures": ["ToyRoutedLM"], "vocab": self.vocab, "width": self.width, "eps": self.eps,
+                    "experts": self.experts, "inner": self.inner, "base": self.base}
+
+        def validate(self):
+            pass
+
+    class HarmonicHalfRotary(PositionEncoding):
+        """The first ``rotary_dim`` elements of a head are rotated by ``position * base / (1 + i)``."""
+
+        def __init__(self, rotary_dim, base):
+            self.rotary_dim, self.base = rotary_dim, base
+            self.inv_freq = None
+
+        def bind(self, tensors, rt):
+            self.inv_freq = (self.base / (1.0 + torch.arange(self.rotary_dim // 2, dtype=torch.float32))).to(rt.device)
+
+        def rotation(self):
+            return self.inv_freq, self.rotary_dim
+
+    class OneOfExperts(FeedForward):
+        """``out_t = p_t[e_t] * expert_{e_t}(x_t)`` with ``p_t = softmax(router x_t)`` in float32 and ``e_t`` its
+        largest entry.  The router and the experts are the framework's ``Linear`` and ``SwiGLU``; picking the
+        tokens of an expert is this part's own business."""
+        graph_safe = False            # the number of tokens per expert is read on the host
+
+        def __init__(self, prefix, width, experts, inner):
+            self.router = Linear(prefix + "router.weight", width, experts)
+            self.experts = [SwiGLU(prefix + f"e{e}.", width, inner) for e in range(experts)]
+
+        def children(self):
+            return [self.router] + self.experts
+
+        def forward(self, x, ctx):
+            logits = self.router.forward(x, out_dtype=torch.float32)
+            p = torch.softmax(logits, dim=-1)
+            top = logits.argmax(dim=-1)
+            out = torch.zeros_like(x)
+            for e, expert in enumerate(self.experts):
+                idx = (top == e).nonzero().squeeze(1)
+                if idx.numel():
+                    y = expert.forward(x.index_select(0, idx).contiguous(), ctx)
+                    out.index_copy_(0, idx, (y.float() * p[idx, e][:, None]).to(x.dtype))
+            return out
+
+    def build(cfg):
+        emb = Embedding("emb.weight", cfg.vocab, cfg.width)
+        layers = []
+        for i, window in enumerate((None, 9)):
+            layers.append(PreNormBlock(
+                RMSNorm(f"l{i}.n1.weight", cfg.width, cfg.eps),
+                Attention(f"l{i}.att.", cfg.width, 3, 1, 32, position=HarmonicHalfRotary(16, cfg.base), window=window),
+                RMSNorm(f"l{i}.n2.weight", cfg.width, cfg.eps),
+                OneOfExperts(f"l{i}.ff.", cfg.width, cfg.experts, cfg.inner)))
+        return DecoderModel(cfg, emb, layers, RMSNorm("norm.weight", cfg.width, cfg.eps),
+                            OutputHead("head.weight", cfg.vocab, cfg.width, False, emb))
+
+    register_architecture(RoutedConfig, build)
+    return RoutedConfig
+
+
+def routed_toy_plain(cfg, W, tokens):
+    """The routed toy model on one whole sequence, plain float32."""
+    T = len(tokens)
+    h = W["emb.weight"][torch.tensor(tokens)]
+    pos = torch.arange(T)
+    freqs = cfg["base"] / (1.0 + torch.arange(8, dtype=torch.float32))
+
+    def rotate(x):                                                  # the first 16 of 32 elements
+        return torch.cat([P.rope_rotate_half(x[..., :16], pos, freqs), x[..., 16:]], dim=-1)
+
+    for i, window in enumerate((None, 9)):
+        x = P.rms_norm(h, W[f"l{i}.n1.weight"], cfg["eps"])
+        q = rotate((x @ W[f"l{i}.att.q_proj.weight"].T).view(T, 3, 32))
+        k = rotate((x @ W[f"l{i}.att.k_proj.weight"].T).view(T, 1, 32))
+        v = (x @ W[f"l{i}.att.v_proj.weight"].T).view(T, 1, 32)
+        a = P.causal_gqa_attention(q, k, v, 1.0 / math.sqrt(32), window).reshape(T, 96)
+        h = h + a @ W[f"l{i}.att.o_proj.weight"].T
+        x = P.rms_norm(h, W[f"l{i}.n2.weight"], cfg["eps"])
+        logits = x @ W[f"l{i}.ff.router.weight"].T
+        p = torch.softmax(logits, dim=-1)
+        out = torch.zeros_like(x)
+        for t in range(T):
+            e = int(logits[t].argmax())
+            pre = f"l{i}.ff.e{e}."
+            out[t] = p[t, e] * P.swiglu(x[t:t + 1], W[pre + "gate_proj.weight"], W[pre + "up_proj.weight"],
+                                        W[pre + "down_proj.weight"])[0]
+        h = h + out
+    return P.rms_norm(h, W["norm.weight"], cfg["eps"]) @ W["head.weight"].T
+
+
+def test_toy_architecture_with_routed_experts_and_another_rotation(tmp_path):
+    """Registered, built, loaded and stepped without a change to the framework's files.  In float32 only: the
+    choice of an expert is a step function of the router's logits, and a near-tie flipped by bfloat16 rounding
+    changes a token's output wholesale, which says nothing about the parts under test."""
+    from helpers import assert_close
+    from synaptix_b200.engine import Engine, Entry
+    from synaptix_b200.models import load_model
+    from synaptix_b200.weights import write_model_folder
+    RoutedConfig = make_routed_toy()
+    cfg = RoutedConfig(vocab=83, width=40, eps=2e-5, experts=3, inner=56, base=0.7)
+    d = write_model_folder(cfg, str(tmp_path / "routed"), 5, std_matrix=0.2, std_embedding=0.5, std_gain=0.1)
+    model = load_model(d, dtype="float32")
+    assert type(model.config).__name__ == "RoutedConfig" and not model.all_graph_safe()
+    eng = Engine(model, max_tokens=1024, max_seqs=3)
+    assert len(eng.cache.kv_groups) == 2                           # all keys, and a window of them
+    cfgd, W = P.load_folder(d)
+    g = torch.Generator().manual_seed(2)
+    seqs = [torch.randint(0, 83, (n,), generator=g).tolist() for n in (41, 90, 7, 26)]
+    refs = [routed_toy_plain(cfgd, W, s) for s in seqs]
+    used = set()
+    for s in seqs:                                                   # every expert is used by some token
+        x = P.rms_norm(W["emb.weight"][torch.tensor(s)], W["l0.n1.weight"], cfgd["eps"])
+        used |= set((x @ W["l0.ff.router.weight"].T).argmax(-1).tolist())
+    assert len(used) >= 2
+    for batch in ([0, 1, 2], [3, 1]):
+        slots = {i: eng.open() for i in batch}
+        cut = {i: len(seqs[i]) - 5 for i in batch}
+        got = eng.step([Entry(slots[i], seqs[i][:cut[i]], [0, cut[i] - 1]) for i in batch])
+        want = torch.stack([refs[i][j] for i in batch for j in (0, cut[i] - 1)])
+        assert_close(got, want, "float32", "routed prompts")
+        for j in range(5):
+            got = eng.step([Entry(slots[i], [seqs[i][cut[i] + j]], [0]) for i in batch])
+            assert_close(got, torch.stack([refs[i][cut[i] + j] for i in batch]), "float32", f"routed decode {j}")
+        for i in batch:
+            eng.close(slots[i])
