@@ -82,8 +82,6 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
     // launches ago, and a kernel behind a programmatic launch starts only when the one before its predecessor
     // has ended.
     first_pages();
-    pdl_wait();
-    pdl_trigger();
     constexpr int half = HD / 2;
     const int heads = nh + 2 * nkv;
     const bf16* tok = q + (size_t)seq * heads * HD;
@@ -92,6 +90,12 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
     if (prep.inv_freq && p < half) {
       sincosf((float)pos * prep.inv_freq[p], &sn[0], &cs[0]);
       sincosf((float)pos * prep.inv_freq[p + 1], &sn[1], &cs[1]);
+    }
+    // the gains of the two norms at this lane's four places: weights, like the angles fetched before the wait
+    float gq[4] = {1.f, 1.f, 1.f, 1.f}, gk[4] = {1.f, 1.f, 1.f, 1.f};
+    if (p < half) {
+      if (prep.wq) { gq[0] = prep.wq[p]; gq[1] = prep.wq[p + 1]; gq[2] = prep.wq[p + half]; gq[3] = prep.wq[p + 1 + half]; }
+      if (prep.wk) { gk[0] = prep.wk[p]; gk[1] = prep.wk[p + 1]; gk[2] = prep.wk[p + half]; gk[3] = prep.wk[p + 1 + half]; }
     }
     bf16* k_row = nullptr;
     bf16* v_row = nullptr;
@@ -103,6 +107,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
         v_row = v_pages + at;
       }
     }
+    pdl_wait();                                               // the projection comes from the kernel before
+    pdl_trigger();
     // jobs: the G query heads of the group, then (has_last) the key head and the value head
     const int jobs = G + (has_last ? 2 : 0);
     for (int j = warp; j < jobs; j += AT_THREADS / 32) {
@@ -125,8 +131,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
       float inv = 1.f;
       if (w) inv = rsqrtf(warp_sum(x1.x * x1.x + x1.y * x1.y + x2.x * x2.x + x2.y * x2.y) / (float)HD + prep.eps);
       if (p < half) {
-        const float a0 = x1.x * inv * (w ? w[p] : 1.f), a1 = x1.y * inv * (w ? w[p + 1] : 1.f);
-        const float b0 = x2.x * inv * (w ? w[p + half] : 1.f), b1 = x2.y * inv * (w ? w[p + 1 + half] : 1.f);
+        const float a0 = x1.x * inv * (is_q ? gq[0] : gk[0]), a1 = x1.y * inv * (is_q ? gq[1] : gk[1]);
+        const float b0 = x2.x * inv * (is_q ? gq[2] : gk[2]), b1 = x2.y * inv * (is_q ? gq[3] : gk[3]);
         const __nv_bfloat162 lo = __floats2bfloat162_rn(a0 * cs[0] - b0 * sn[0], a1 * cs[1] - b1 * sn[1]);
         const __nv_bfloat162 hi = __floats2bfloat162_rn(a0 * sn[0] + b0 * cs[0], a1 * sn[1] + b1 * cs[1]);
         bf16* dst = is_q ? q_s + j * HD : kv_new;
@@ -303,6 +309,12 @@ __global__ void __launch_bounds__(HD) attn_merge_kernel(const float* __restrict_
   pdl_trigger();
   const size_t row = blockIdx.x;
   const int d = threadIdx.x;
+  // the first splits' outputs are asked for together with the maxima and sums, not after the weights are known
+  constexpr int EARLY = 32;
+  const float* po = part_o + row * n_splits * HD + d;
+  float pv[EARLY];
+#pragma unroll
+  for (int i = 0; i < EARLY; ++i) pv[i] = i < n_splits ? po[(size_t)i * HD] : 0.f;
   for (int i = d; i < n_splits; i += HD) {
     const float2 ml = reinterpret_cast<const float2*>(part_ml)[row * n_splits + i];
     fac[i] = ml.x;
@@ -326,9 +338,10 @@ __global__ void __launch_bounds__(HD) attn_merge_kernel(const float* __restrict_
   }
   __syncthreads();
   float O = 0.f;
-  const float* po = part_o + row * n_splits * HD + d;
+#pragma unroll
+  for (int i = 0; i < EARLY; ++i) if (i < n_splits) O += pv[i] * fac[i];
 #pragma unroll 8
-  for (int i = 0; i < n_splits; ++i) O += po[(size_t)i * HD] * fac[i];
+  for (int i = EARLY; i < n_splits; ++i) O += po[(size_t)i * HD] * fac[i];
   const float L = s_L;
   out[row * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
 }
