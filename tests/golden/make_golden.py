@@ -39,7 +39,9 @@ def load(path):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <checkout of the reference project>")
+    ref = sys.argv[1]
     here = os.path.dirname(os.path.abspath(__file__))
     out = {}
     with tempfile.TemporaryDirectory() as tmp:
