@@ -1,6 +1,6 @@
 // Device code shared by the attention kernels: fragment helpers, the shared-memory layout of a
 // staged cache page, the page loader and the tile routine (scores, masking, online softmax, P*V).
-// Included by attention.cu and decode_stream.cu.
+// Included by attention.cu.
 #pragma once
 #include "common.cuh"
 

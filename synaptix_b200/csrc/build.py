@@ -41,7 +41,6 @@ LIBRARIES: Dict[str, tuple] = {
     "sampling": ("sampling.cu", []),
     "decode": ("decode.cu", []),
     "attention": ("attention.cu", []),
-    "decode_stream": ("decode_stream.cu", []),
     "attn_tc": ("attn_tc.cu", []),
     "gemm_tc": ("gemm_tc.cu", []),
 }
@@ -52,12 +51,12 @@ class KernelsUnavailable(RuntimeError):
 
 
 def find_nvcc() -> str:
-    for cand in (os.environ.get("SYNAPTIX_NVCC"), shutil.which("nvcc"),
+    for cand in (shutil.which("nvcc"),
                  os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc"),
                  "/usr/local/cuda/bin/nvcc"):
         if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
             return cand
-    raise KernelsUnavailable("nvcc was not found (looked at $SYNAPTIX_NVCC, PATH, $CUDA_HOME/bin, "
+    raise KernelsUnavailable("nvcc was not found (looked at PATH, $CUDA_HOME/bin, "
                              "/usr/local/cuda/bin); the kernels of this package must be compiled for sm_100a")
 
 

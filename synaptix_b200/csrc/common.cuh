@@ -82,20 +82,14 @@ static inline int sx_launch_status() { return (int)cudaGetLastError(); }
 // NEXT kernel be scheduled; it is called only AFTER pdl_wait(), so that at most one kernel waits
 // behind the running one (a kernel that triggered before waiting would let the whole chain of
 // later kernels pile up on the SMs, spinning).  Both are no-ops for a kernel launched normally.
-// SYNAPTIX_PDL=0 in the environment turns the launch attribute off.
+// sx_set_pdl(0), exported by every library, turns the launch attribute off for that library.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-#include <stdlib.h>
-static inline bool sx_pdl_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("SYNAPTIX_PDL");
-    v = (e && e[0] == '0') ? 0 : 1;
-  }
-  return v != 0;
-}
+static int g_sx_pdl = 1;
+extern "C" void sx_set_pdl(int on) { g_sx_pdl = on ? 1 : 0; }
+static inline bool sx_pdl_enabled() { return g_sx_pdl != 0; }
 
 template <typename... KArgs, typename... Args>
 static inline int sx_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {

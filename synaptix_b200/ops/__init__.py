@@ -7,7 +7,6 @@ the kernels, every call raises ``KernelsUnavailable``.
 """
 from __future__ import annotations
 
-import os
 from typing import Optional
 
 import torch
@@ -18,11 +17,12 @@ from .attention import (TC_TILE_ROWS, attn_decode, attn_decode_prep, attn_prefil
                         query_tiles, tc_prefill_supported)
 from .decode import MAX_ROWS as SKINNY_MAX_ROWS, skinny_gemm, skinny_gemm_residual, skinny_gemm_scaled, skinny_supported
 from .gemm_tc import gemm_tc, tc_supported
+from .options import OPTIONS, KernelOptions, options, set_options
 from .generic import (add_rmsnorm, attn_generic, decode_advance, embed_gather, gemm_generic, qkv_prepare,
                       residual_add,
                       silu_mul)
 
-__all__ = ["KernelsUnavailable", "KernelError", "set_launch_counter", "decode_advance", "add_rmsnorm", "attn_generic", "embed_gather",
+__all__ = ["OPTIONS", "KernelOptions", "options", "set_options", "KernelsUnavailable", "KernelError", "set_launch_counter", "decode_advance", "add_rmsnorm", "attn_generic", "embed_gather",
            "gemm_generic", "qkv_prepare", "residual_add", "silu_mul", "linear", "linear_normed", "norm_fusable", "attention",
            "attention_from_projection", "decode_attention_takes_projection", "residual_product_fusable",
            "linear_into_residual", "linear_scaled"]
@@ -89,10 +89,10 @@ def linear_normed(pn, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
 
 def residual_product_fusable(M: int, N: int, K: int, dtype) -> bool:
     """Can the product ``x[M, K] @ w[N, K].T`` add itself into the residual stream and prepare the norm after the
-    sum (``linear_into_residual``)?  3 to 16 rows in bfloat16; ``SYNAPTIX_RESID=0`` turns it off."""
+    sum (``linear_into_residual``)?  3 to 16 rows in bfloat16 (option ``fused_residual``)."""
     # one or two rows: the norm in the consumer's prologue (norm_fusable) measured faster (489 against 471 tok/s)
     return (dtype == torch.bfloat16 and 2 < M <= SKINNY_MAX_ROWS and K % 32 == 0 and K > 0
-            and os.environ.get("SYNAPTIX_RESID", "1") != "0")
+            and OPTIONS.fused_residual)
 
 
 def linear_into_residual(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, gain: torch.Tensor):
@@ -126,9 +126,9 @@ def linear_scaled(x: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tenso
 
 def decode_attention_takes_projection(dtype, nh: int, nkv: int, hd: int, rotary_dim: Optional[int], ctx) -> bool:
     """Can the attention kernel of a single-token step prepare the heads itself (norm, rotation, cache write) from
-    the fused projection?  (``SYNAPTIX_ATTN_PREP=0`` turns it off.)"""
+    the fused projection?  (Option ``attn_prep``.)"""
     return (fast_supported(dtype, nh, nkv, hd) and rotary_dim in (None, 0, hd) and ctx.all_single
-            and os.environ.get("SYNAPTIX_ATTN_PREP", "1") != "0")
+            and OPTIONS.attn_prep)
 
 
 def attention_from_projection(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx,

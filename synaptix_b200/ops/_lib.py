@@ -79,13 +79,36 @@ def check(code: int, what: str, launches: int = 1) -> None:
 
 
 _FN_CACHE = {}
+_LIBS = {}
+
+
+def _library(lib: str):
+    """The loaded library; the launch options of this process are handed to it when it is loaded."""
+    h = _LIBS.get(lib)
+    if h is None:
+        h = _LIBS[lib] = load_library(lib)
+        _set_pdl(h)
+    return h
+
+
+def _set_pdl(handle) -> None:
+    from .options import OPTIONS
+    f = getattr(handle, "sx_set_pdl", None)
+    if f is not None:
+        f(ctypes.c_int(1 if OPTIONS.pdl else 0))
+
+
+def apply_pdl() -> None:
+    """Tell every loaded library whether kernels are launched with programmatic dependent launch."""
+    for h in _LIBS.values():
+        _set_pdl(h)
 
 
 def fn(lib: str, name: str):
     key = (lib, name)
     f = _FN_CACHE.get(key)
     if f is None:
-        f = getattr(load_library(lib), name)
+        f = getattr(_library(lib), name)
         f.restype = ctypes.c_int
         _FN_CACHE[key] = f
     return f

@@ -7,10 +7,10 @@ import numpy as np
 import torch
 
 import ctypes
-import os
 
 from ._lib import KernelError, c_float, c_int, c_longlong, check, fn, ptr, require_cuda, stream
 from .decode import sm_count
+from .options import OPTIONS
 
 FAST_HEAD_DIMS = (32, 64, 128)
 
@@ -147,9 +147,8 @@ TC_TILE_ROWS = 128
 
 
 def tc_prefill_supported(dtype, nh: int, nkv: int, hd: int) -> bool:
-    """The tcgen05 prompt-attention kernel takes bfloat16 and head size 128 (``SYNAPTIX_ATTN_TC=0`` turns it off)."""
-    return (dtype == torch.bfloat16 and hd == TC_HEAD_DIM and nkv > 0 and nh % nkv == 0
-            and os.environ.get("SYNAPTIX_ATTN_TC", "1") != "0")
+    """The tcgen05 prompt-attention kernel takes bfloat16 and head size 128 (option ``attn_tc``)."""
+    return dtype == torch.bfloat16 and hd == TC_HEAD_DIM and nkv > 0 and nh % nkv == 0 and OPTIONS.attn_tc
 
 
 def attn_prefill_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, tile_seq: torch.Tensor,

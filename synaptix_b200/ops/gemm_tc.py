@@ -2,13 +2,13 @@
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import Optional
 
 import torch
 
 from ._lib import KernelError, c_int, check, fn, ptr, require_cuda, stream
 from .decode import sm_count
+from .options import OPTIONS
 
 _EPI = {None: 0, "f32": 1, "silu_mul": 2}
 
@@ -80,8 +80,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None,
         out = torch.empty((M, n_out), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=x.device)
     ws = counts = None
     n_cut = zmax = 0
-    if cut is None and os.environ.get("SYNAPTIX_GEMM_CUT", "1") == "0":      # a switch for measurements
-        cut = False
+    if cut is None:
+        cut = OPTIONS.gemm_cut
     if splits is None and cut is not False:
         _, n_cut, zmax, _ = plan_stream(M, N, K, epilogue)
     if splits is None:

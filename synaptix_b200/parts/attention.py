@@ -64,16 +64,6 @@ class Attention(Mixer):
     def cache_request(self):
         return KVRequest(self.nkv, self.hd, self.window)
 
-    def stream_fields(self, cache_view: KVView, write_cache: bool = True):
-        rot = self.position.rotation()
-        if rot is not None and rot[1] != self.hd:          # the fused kernel rotates the whole head or nothing
-            return None
-        return {"kind": "attention", "w_qkv": self.qkv.weight, "w_o": self.o.weight, "g_q": self.wq, "g_k": self.wk,
-                "eps_qk": self.qk_norm_eps, "inv_freq": None if rot is None else rot[0], "scale": self.scale,
-                "window": self.window, "H": self.width, "nh": self.nh, "nkv": self.nkv, "hd": self.hd,
-                "k_pages": cache_view.k, "v_pages": cache_view.v, "group": cache_view.group,
-                "write_cache": write_cache}
-
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_view: KVView, write_cache: bool = True,
                 defer_output: bool = False) -> torch.Tensor:
         out = self.o.deferred if defer_output else self.o.forward

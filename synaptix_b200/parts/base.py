@@ -197,12 +197,6 @@ class Part:
                 out[n] = s
         return out
 
-    def stream_fields(self, *args, **kw) -> Optional[dict]:
-        """What a fused multi-layer kernel needs to know of this part (its tensors and constants),
-        or ``None`` (the default) if the part can only run through ``forward``.  A block offers
-        itself to such a kernel only if all its parts answer."""
-        return None
-
     def all_graph_safe(self) -> bool:
         return self.graph_safe and all(c.all_graph_safe() for c in self.children())
 

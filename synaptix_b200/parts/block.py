@@ -26,24 +26,6 @@ class PreNormBlock(Part):
     def cache_request(self):
         return self.mixer.cache_request()
 
-    def stream_fields(self, cache_view, write_cache: bool = True):
-        """This block as one entry of a fused multi-layer kernel's table: pre-norm, attention over
-        the paged cache, pre-norm, gated feed-forward; ``None`` if a part is of another kind."""
-        n1, n2 = self.norm1.stream_fields(), self.norm2.stream_fields()
-        if cache_view is None or not hasattr(cache_view, "k"):
-            return None
-        mx, ff = self.mixer.stream_fields(cache_view, write_cache), self.ffn.stream_fields()
-        if None in (n1, n2, mx, ff):
-            return None
-        if (n1["kind"], n2["kind"], mx["kind"], ff["kind"]) != ("rmsnorm", "rmsnorm", "attention", "swiglu"):
-            return None
-        if not (n1["width"] == n2["width"] == mx["H"] == ff["H"]):
-            return None
-        d = dict(mx)
-        d.update(w_gu=ff["w_gu"], w_down=ff["w_down"], I=ff["I"], g_in=n1["gain"], eps_in=n1["eps"],
-                 g_post=n2["gain"], eps_post=n2["eps"])
-        return d
-
     def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
                 cache_view, write_cache: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
         """``pending`` and the second result may be a ``PendingLinear``: a branch's last product handed on unrun,

@@ -27,10 +27,6 @@ class SwiGLU(FeedForward):
     def children(self) -> List[Part]:
         return [self.gate_up, self.down]
 
-    def stream_fields(self):
-        return {"kind": "swiglu", "w_gu": self.gate_up.weight, "w_down": self.down.weight,
-                "H": self.width, "I": self.intermediate}
-
     def forward(self, x: torch.Tensor, ctx: StepContext, defer_output: bool = False) -> torch.Tensor:
         z = self.gate_up.forward(x, epilogue="silu_mul")
         return self.down.deferred(z) if defer_output else self.down.forward(z)

@@ -32,11 +32,6 @@ class RMSNorm(Norm):
         self.weight = to_device_f32(tensors[self.weight_name], rt)
         self._dtype = rt.dtype
 
-    def stream_fields(self) -> Optional[dict]:
-        if self._dtype != torch.bfloat16:
-            return None
-        return {"kind": "rmsnorm", "gain": self.weight, "eps": self.eps, "width": self.width}
-
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return ops.add_rmsnorm(h, None, self.weight, self.eps, self._dtype)
 
