@@ -4,10 +4,12 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--shape 4b|8b|32b] [--batch B] [--context C]
 
 A step is one decode step of the whole batch (default batch 8, context 4,096: every
-sequence holds a prompt and decodes up to 4,096 tokens, the timed steps being the last K).
+sequence holds a prompt and decodes up to 4,096 tokens, the timed steps being the last 5 x K).
 One JSON line is printed: ``value`` = decoded tokens per second timed on the device over K
-graph-replayed steps whose sampled tokens feed the next step on the device; ``e2e`` = the same
-through the Python entry point (``LLM.generate``), host tokens in and out every step;
+steps of a decode session (the loop ``LLM.generate`` runs: one CUDA graph a step, sampling and
+the next token kept on the device), median of 5 such regions back to back; ``e2e`` = the same
+steps from the same prompts through the Python entry point (``LLM.generate``), host tokens in
+and out, and its greedy tokens must equal the timed run's;
 ``prefill`` = one 2,048-token prompt; ``points`` = decoding at batch 1 and 64; ``roofline`` =
 bytes a decode step has to read (every weight once, the cache of the live sequences) over
 its time, against the measured copy bandwidth.  Inputs are larger than L2 (a step streams
@@ -152,7 +154,7 @@ def main():
     import torch
     from synaptix_b200.api import LLM
     from synaptix_b200.config import Qwen3Config
-    from synaptix_b200.engine import DecodeRun, Engine, Entry
+    from synaptix_b200.engine import DecodeRow, Entry
     from synaptix_b200.models import model_skeleton
     from synaptix_b200.parts import Runtime
     from synaptix_b200.weights import RandomSource
@@ -172,11 +174,12 @@ def main():
 
     batches = [a.batch] if a.no_points else sorted({a.batch, 1, 64})
     K, W = a.steps, a.warmup
-    start_len = a.context - (K + W) - 1          # the timed steps end at the context length
+    start_len = a.context - (5 * K + W) - 1      # the timed steps (5 regions of K) end at the context length
     if start_len < 1:
-        raise SystemExit("--context is too short for --steps + --warmup")
-    engine = Engine(model, max_tokens=max(batches) * (a.context + 64) if a.phase == "all" else 4096,
-                    use_graphs=not a.no_graph)
+        raise SystemExit("--context is too short for 5 x --steps + --warmup")
+    llm = LLM.from_model(model, max_tokens=max(batches) * (a.context + 64) if a.phase == "all" else 4096,
+                         graph=not a.no_graph)
+    engine = llm.engine
     g = torch.Generator().manual_seed(1)
 
     def time_prefill():
@@ -206,43 +209,60 @@ def main():
                           "layers": a.layers, "layers_of_config": full_layers, "prefill": time_prefill()}))
         return 0
 
-    def fill(B):
-        """Open B sequences and run their prompts (a few sequences a step)."""
-        slots = [engine.open() for _ in range(B)]
+    REGIONS = 5                                   # the K-step region is timed this many times, back to back
+    total_steps = W + REGIONS * K
+
+    def prompts_for(B):
+        return [torch.randint(0, cfg.vocab_size, (start_len,), generator=g).tolist() for _ in range(B)]
+
+    def fill(prompts, whole):
+        """Open a slot per prompt and run the prompts: all in one step as ``LLM.generate`` does (``whole``), or a
+        few sequences a step."""
+        slots = [engine.open() for _ in prompts]
         first = []
-        for i in range(0, B, 4):
-            part = slots[i:i + 4]
-            prompts = [torch.randint(0, cfg.vocab_size, (start_len,), generator=g).tolist() for _ in part]
-            lg = engine.step([Entry(s, p, [start_len - 1]) for s, p in zip(part, prompts)], keep=False)
+        per = len(prompts) if whole else 4
+        for i in range(0, len(prompts), per):
+            lg = engine.step([Entry(s, p, [len(p) - 1]) for s, p in zip(slots[i:i + per], prompts[i:i + per])], keep=False)
             first += lg.argmax(-1).tolist()
         return slots, first
 
     results = {}
     clocks = None
     launches = 0
+    device_tokens = main_prompts = None
     for B in batches:
-        slots, first = fill(B)
-        run = DecodeRun(engine, slots, first, W + K)
-        run.steps(W)
+        prompts = prompts_for(B)
+        slots, first = fill(prompts, whole=(B == a.batch))
+        session = engine.start_decode([DecodeRow(s, t, i, 1) for i, (s, t) in enumerate(zip(slots, first))])
+        for _ in range(W):
+            session.launch()
         torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(REGIONS + 1)]
         l0 = engine.kernel_launches
         with ClockSampler() as cs:
             torch.cuda.synchronize()
-            e0.record()
-            run.steps(K)
-            e1.record()
+            events[0].record()
+            for r in range(REGIONS):
+                for _ in range(K):
+                    session.launch()
+                events[r + 1].record()
             torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
-        results[B] = {"ms_per_step": ms / K, "tok_s": B * K / (ms / 1e3)}
+        region_ms = sorted(events[r].elapsed_time(events[r + 1]) for r in range(REGIONS))
+        ms = region_ms[REGIONS // 2]
+        results[B] = {"ms_per_step": ms / K, "tok_s": B * K / (ms / 1e3), "best_tok_s": B * K / (region_ms[0] / 1e3),
+                      "region_ms": [round(x, 3) for x in region_ms]}
+        toks = [session.collect() for _ in range(total_steps)]
         if B == a.batch:
             clocks = cs.summary()
-            launches = engine.kernel_launches - l0
+            launches = (engine.kernel_launches - l0) // REGIONS
+            device_tokens = [[first[i]] + [t[i] for t in toks] for i in range(B)]
+            main_prompts = prompts
+        session.drop(list(range(B)))
         for s in slots:
             engine.close(s)
 
     main_r = results[a.batch]
-    mean_ctx = a.context - K / 2.0
+    mean_ctx = a.context - REGIONS * K / 2.0
     nbytes = decode_bytes(cfgd, a.layers, a.batch, mean_ctx)
     achieved = nbytes / (main_r["ms_per_step"] / 1e3) / 1e9
     line = {
@@ -258,6 +278,8 @@ def main():
                    "prefill_tokens": 2048, "l2": "inputs larger than L2 (a step streams all weights, 8 GB or more)"},
         "gpu_launches": launches,
         "clocks": clocks,
+        "timing": {"regions": REGIONS, "steps_per_region": K, "value_is": "median region",
+                   "best": round(main_r["best_tok_s"], 2), "region_ms": main_r["region_ms"]},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"], "bytes_per_step": int(nbytes)},
     }
@@ -265,25 +287,27 @@ def main():
     if not a.no_points:
         line["points"] = {f"decode_b{B}": round(r["tok_s"], 2) for B, r in results.items() if B != a.batch}
         line["points"][f"decode_b{a.batch}"] = round(main_r["tok_s"], 2)
+        line["points_hbm_frac"] = {
+            f"decode_b{B}": round(decode_bytes(cfgd, a.layers, B, mean_ctx) / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+            for B, r in results.items()}
         line["prefill"] = time_prefill()
-        # end to end through the Python entry point: host tokens in and out every step
-        del engine
-        torch.cuda.empty_cache()
-        llm = LLM.__new__(LLM)
-        llm.model = model
-        llm.engine = Engine(model, max_tokens=a.batch * (a.context + 64), use_graphs=not a.no_graph)
-        llm.last_stats = None
-        e2e_steps = K
-        prompts = [torch.randint(0, cfg.vocab_size, (a.context - e2e_steps - 1,), generator=g).tolist()
-                   for _ in range(a.batch)]
-        llm.generate(prompts[:1], max_new_tokens=W + 1, eos_token_ids=[])          # warm-up, captures nothing reused
-        llm.generate(prompts, max_new_tokens=W + 1, eos_token_ids=[], max_batch_size=a.batch)
-        llm.generate(prompts, max_new_tokens=e2e_steps + 1, eos_token_ids=[], max_batch_size=a.batch)
+        # end to end through the Python entry point, from the same prompts: host tokens in, every step's control
+        # words up from pinned memory and its tokens back down; greedy, so the tokens must be the timed run's
+        llm.generate(main_prompts[:1], max_new_tokens=W + 1, eos_token_ids=[])
+        llm.generate(main_prompts, max_new_tokens=W + 1, eos_token_ids=[], max_batch_size=a.batch)
+        outs = llm.generate(main_prompts, max_new_tokens=total_steps + 1, eos_token_ids=[], max_batch_size=a.batch)
         st = llm.last_stats
+        same = outs == device_tokens
         line["e2e"] = {"value": round(a.batch * st.decode_steps / (st.decode_ms / 1e3), 2), "unit": "tokens/s",
                        "h2d_bytes_per_step": st.decode_h2d_bytes // max(st.decode_steps, 1),
                        "d2h_bytes_per_step": st.decode_d2h_bytes // max(st.decode_steps, 1),
-                       "steps": st.decode_steps}
+                       "steps": st.decode_steps, "tokens_equal_device_timed_run": same}
+        if not same:
+            bad = next(i for i in range(a.batch) if outs[i] != device_tokens[i])
+            k = next(k for k, (x, y) in enumerate(zip(outs[bad], device_tokens[bad])) if x != y)
+            print(json.dumps(line))
+            raise SystemExit(f"LLM.generate and the device-timed decode run disagree: request {bad}, token {k}: "
+                             f"{outs[bad][k]} against {device_tokens[bad][k]}")
     print(json.dumps(line))
     return 0
 

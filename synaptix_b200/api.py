@@ -30,7 +30,19 @@ class LLM:
     def __init__(self, model_dir: str, compute_dtype="bf16", device: str = "cuda:0",
                  max_tokens: Optional[int] = None, max_seq: Optional[int] = None, max_batch: int = 8,
                  graph: bool = True, source=None):
-        self.model = load_model(model_dir, dtype=compute_dtype, device=device, source=source)
+        self._setup(load_model(model_dir, dtype=compute_dtype, device=device, source=source),
+                    max_tokens, max_seq, max_batch, graph)
+
+    @classmethod
+    def from_model(cls, model, max_tokens: Optional[int] = None, max_seq: Optional[int] = None,
+                   max_batch: int = 8, graph: bool = True) -> "LLM":
+        """An ``LLM`` around a model that already has its weights bound (``DecoderModel.load``)."""
+        self = cls.__new__(cls)
+        self._setup(model, max_tokens, max_seq, max_batch, graph)
+        return self
+
+    def _setup(self, model, max_tokens, max_seq, max_batch, graph) -> None:
+        self.model = model
         cfg = self.model.config
         if max_tokens is None:
             per_seq = max_seq or getattr(cfg, "max_position_embeddings", None) or 4096

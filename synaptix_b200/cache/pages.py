@@ -144,6 +144,12 @@ class SequenceSlots:
         self._check(slot)
         return self._pages[slot][group].table
 
+    def table_shape(self, slot: int) -> tuple:
+        """Per group ``(pages in the table, leading pages given back)``: it changes exactly when
+        the slot's page tables do."""
+        self._check(slot)
+        return tuple((len(gp.table), gp.released) for gp in self._pages[slot])
+
     def reserve(self, slot: int, n_new: int) -> None:
         """Make sure pages exist for ``n_new`` more tokens; on ``CacheFull`` nothing changes."""
         self._check(slot)

@@ -10,9 +10,14 @@ each group storage of its own:
   separate page pools, and a windowed group gives pages back while the
   sequence is still running.
 * ``StateRequest(shape, dtype)``: state of fixed size per sequence,
-  ``[max_seqs, *shape]`` per entry, zeroed when a slot is opened.  The Qwen3
-  dense decoder has none; it exists for mixers that carry a running state
-  (the reference's GatedDeltaNetState, model.rs:377-492, is such a thing).
+  ``[max_seqs + 1, *shape]`` per entry, zeroed when a slot is opened.  The last
+  row belongs to no sequence (``Cache.spare_slot``): rows that pad a step up to
+  a captured graph's size carry that slot number, so a mixer that updates
+  ``state[ctx.seq_slots]`` on the device never touches a live sequence's state
+  from a padding row (as page 0 of every K/V group takes their cache writes).
+  The Qwen3 dense decoder has no such state; it exists for mixers that carry a
+  running state (the reference's GatedDeltaNetState, model.rs:377-492, is such
+  a thing).
 
 The reference's equivalent is ``KvCache``/``LayerCache``
 (crates/synaptix-models/llm/common/src/model.rs:349-368,1021-1046).
@@ -105,7 +110,7 @@ class Cache:
             self._v.append(torch.zeros(shape, dtype=dtype, device=self.device))
         self._state: List[torch.Tensor] = []
         for r, n in zip(st_keys, st_counts):
-            self._state.append(torch.zeros((n, self.max_seqs) + tuple(r.shape),
+            self._state.append(torch.zeros((n, self.max_seqs + 1) + tuple(r.shape),
                                            dtype=r.dtype, device=self.device))
 
         pools = [PagePool(self.n_pages - 1, first=1) for _ in kv_keys]
@@ -120,6 +125,11 @@ class Cache:
     @property
     def n_block_tables(self) -> int:
         return len(self.slots.pools)
+
+    @property
+    def spare_slot(self) -> int:
+        """The slot number of rows that belong to no sequence (padding of a captured step)."""
+        return self.max_seqs
 
     def view(self, entry: int):
         e = self._entry[entry]

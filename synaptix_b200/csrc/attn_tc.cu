@@ -241,8 +241,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
       ft_tma_2d(ft_smem(q_s + FT_CHUNK), &map_q, h * FT_HD + 64, t_begin + q0, bar(FT_B_QFULL));
       for (int j = 0; j < nb; ++j) {
         const int s = j % FT_KV_STAGES, u = j / FT_KV_STAGES;
-        if (!ft_mbar_wait(bar(FT_B_KVEMPTY + s), (u & 1) ^ 1)) { atomicExch(status, 1); break; }
-        if (j == FT_KV_STAGES - 1 && !ft_mbar_wait(bar(FT_B_QREADY), 0)) { atomicExch(status, 1); break; }      // Q has left this stage
+        if (!ft_mbar_wait(bar(FT_B_KVEMPTY + s), (u & 1) ^ 1)) { sx_set_status(status, 1); break; }
+        if (j == FT_KV_STAGES - 1 && !ft_mbar_wait(bar(FT_B_QREADY), 0)) { sx_set_status(status, 1); break; }      // Q has left this stage
         ft_mbar_expect_tx(bar(FT_B_KVFULL + s), FT_STAGE);
         const uint32_t k_dst = ft_smem(kv_s + s * FT_STAGE), v_dst = k_dst + FT_TILE;
         const int key0 = kb0 + j * FT_BN;
@@ -267,13 +267,13 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
       constexpr uint32_t idesc_pv = ft_idesc(FT_BM, FT_HD, true);
       // Q is in tensor memory once the softmax threads have copied it there
       bool ok = ft_mbar_wait(bar(FT_B_QREADY), 0);
-      if (!ok) atomicExch(status, 2);
+      if (!ok) sx_set_status(status, 2);
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       // MMAs run in the order they are issued, so S(j+2) = Q K(j+2)^T, issued after P(j) V(j), does not
       // overwrite P(j), which lies over S(j)
       auto issue_qk = [&](int j) -> bool {
         const int ks = j % FT_KV_STAGES, ku = j / FT_KV_STAGES, s = j & 1;
-        if (!ft_mbar_wait(bar(FT_B_KVFULL + ks), ku & 1)) { atomicExch(status, 3); return false; }
+        if (!ft_mbar_wait(bar(FT_B_KVFULL + ks), ku & 1)) { sx_set_status(status, 3); return false; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t ka = ft_smem(kv_s + ks * FT_STAGE);
         const uint32_t d = tmem_base + (s ? FT_COL_S1 : FT_COL_S0);
@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
       for (int j = 0; j < nb && ok; ++j) {
         if (j + 1 < nb) ok = issue_qk(j + 1);
         if (!ok) break;
-        if (!ft_mbar_wait(bar(FT_B_PREADY), j & 1)) { atomicExch(status, 5); ok = false; break; }
+        if (!ft_mbar_wait(bar(FT_B_PREADY), j & 1)) { sx_set_status(status, 5); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t pa = tmem_base + ((j & 1) ? FT_COL_S1 : FT_COL_S0), va = ft_smem(kv_s + (j % FT_KV_STAGES) * FT_STAGE + FT_TILE);
 #pragma unroll
@@ -308,7 +308,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
     float m = -INFINITY, l = 0.f;                                 // l: this thread's columns only
     bool ok = true;
     // this thread's half row of Q (64 values = one swizzled chunk row) from shared into tensor memory
-    if (!ft_mbar_wait(bar(FT_B_QFULL), 0)) { atomicExch(status, 6); ok = false; }
+    if (!ft_mbar_wait(bar(FT_B_QFULL), 0)) { sx_set_status(status, 6); ok = false; }
     {
       uint32_t qv[32];
 #pragma unroll
@@ -324,7 +324,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
     }
     for (int j = 0; j < nb && ok; ++j) {
       const int s = j & 1, u = j >> 1;
-      if (!ft_mbar_wait(bar(FT_B_SFULL + s), u & 1)) { atomicExch(status, 6); ok = false; break; }
+      if (!ft_mbar_wait(bar(FT_B_SFULL + s), u & 1)) { sx_set_status(status, 6); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       float sc[FT_HALF];
 #pragma unroll
@@ -351,7 +351,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
       xch[(s * 2 + hf) * FT_BM + r] = hmax;
       __syncwarp();                                // (a bounded wait instead of a named barrier: a warp that gave up does not hang its partner)
       if (lane == 0) ft_mbar_arrive(bar(FT_B_XCH + s * 4 + (warp & 3)));
-      if (!ft_mbar_wait(bar(FT_B_XCH + s * 4 + (warp & 3)), u & 1)) { atomicExch(status, 9); ok = false; break; }
+      if (!ft_mbar_wait(bar(FT_B_XCH + s * 4 + (warp & 3)), u & 1)) { sx_set_status(status, 9); ok = false; break; }
       const float bmax = fmaxf(hmax, xch[(s * 2 + (hf ^ 1)) * FT_BM + r]);
       // The reference point m moves only when the maximum has grown by more than FT_LAZY (in the exponent's
       // units): until then p = 2^(s*c - m*c) may exceed 1 by at most 2^FT_LAZY, which float32 sums and
@@ -377,7 +377,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
       // P goes over the scores of this block (every thread of the row has read its scores: the
       // exchange of the maxima came after the loads); O is free once the previous block's P V is done
       ft_st32u(t_row + (s ? FT_COL_S1 : FT_COL_S0) + hf * 32, pk);
-      if (j > 0 && !ft_mbar_wait(bar(FT_B_PVDONE), (j - 1) & 1)) { atomicExch(status, 7); ok = false; break; }
+      if (j > 0 && !ft_mbar_wait(bar(FT_B_PVDONE), (j - 1) & 1)) { sx_set_status(status, 7); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       // rows of V at or beyond the sequence's length (thread r stands for key r of the block here,
       // and hf for the half of the head's values)
@@ -408,9 +408,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
     xch[(4 + hf) * FT_BM + r] = l;
     __syncwarp();
     if (lane == 0) ft_mbar_arrive(bar(FT_B_XCH + 8 + (warp & 3)));
-    if (ok && !ft_mbar_wait(bar(FT_B_XCH + 8 + (warp & 3)), 0)) { atomicExch(status, 9); ok = false; }
+    if (ok && !ft_mbar_wait(bar(FT_B_XCH + 8 + (warp & 3)), 0)) { sx_set_status(status, 9); ok = false; }
     l += xch[(4 + (hf ^ 1)) * FT_BM + r];
-    if (ok && !ft_mbar_wait(bar(FT_B_PVDONE), (nb - 1) & 1)) { atomicExch(status, 8); ok = false; }
+    if (ok && !ft_mbar_wait(bar(FT_B_PVDONE), (nb - 1) & 1)) { sx_set_status(status, 8); ok = false; }
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -491,10 +491,7 @@ static int ft_map_pages(CUtensorMap* map, const void* pages, long long n_pages, 
 
 static int* ft_status_word() {
   static int* p = nullptr;
-  if (!p) {
-    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
-    cudaMemset(p, 0, sizeof(int));
-  }
+  if (!p) p = sx_status_word_alloc();
   return p;
 }
 
@@ -523,8 +520,12 @@ extern "C" int sx_attn_prefill_tc(const void* q, const void* k_pages, const void
 }
 
 // 0, or which bounded wait ran out (1 producer, 2-5 MMA issuer, 6-9 softmax)
-extern "C" int sx_attn_tc_status(int* host_value) {
+// Reads the word in host memory: no device call.  It tells of kernels the host has already waited for.
+// With reset != 0 the word goes back to 0.
+extern "C" int sx_attn_tc_status(int* host_value, int reset) {
   int* p = ft_status_word();
   if (!p) return (int)cudaErrorMemoryAllocation;
-  return (int)cudaMemcpy(host_value, p, sizeof(int), cudaMemcpyDeviceToHost);
+  *host_value = *(volatile int*)p;
+  if (reset) *(volatile int*)p = 0;
+  return 0;
 }

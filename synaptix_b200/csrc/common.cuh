@@ -75,6 +75,22 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 static inline int sx_launch_status() { return (int)cudaGetLastError(); }
 
 // ---------------------------------------------------------------------------------------
+// Status words of kernels with bounded waits.  A word lives in pinned host memory that the
+// device can write (one per library): a kernel whose wait ran out stores a code there, and the
+// host reads it without a device call once it has waited for the kernel by any means.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void sx_set_status(int* status, int code) {
+  *(volatile int*)status = code;
+  __threadfence_system();
+}
+static inline int* sx_status_word_alloc() {
+  int* h = nullptr;
+  if (cudaHostAlloc((void**)&h, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) return nullptr;
+  *h = 0;
+  return h;          // unified addressing: the same pointer is valid on the device
+}
+
+// ---------------------------------------------------------------------------------------
 // Programmatic dependent launch.  A kernel launched through sx_launch may be scheduled while its
 // predecessor in the stream is still running.  It must call pdl_wait() before it reads anything
 // an earlier kernel wrote or writes anything an earlier kernel may still read; what it does

@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     if (lane == 0) {
       for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % TC_STAGES;
-        if (!tc_mbar_wait(empty0 + 8 * s, ((kb / TC_STAGES) & 1) ^ 1)) { atomicExch(status, 1); break; }
+        if (!tc_mbar_wait(empty0 + 8 * s, ((kb / TC_STAGES) & 1) ^ 1)) { sx_set_status(status, 1); break; }
         tc_mbar_expect_tx(full0 + 8 * s, TC_STAGE_BYTES);
         const uint32_t a_dst = tc_smem(tiles + s * TC_STAGE_BYTES), b_dst = a_dst + TC_A_BYTES;
         const int kx = (kb0 + kb) * TC_BK;
@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
       bool ok = true;
       for (int kb = 0; kb < nkb && ok; ++kb) {
         const int s = kb % TC_STAGES;
-        if (!tc_mbar_wait(full0 + 8 * s, (kb / TC_STAGES) & 1)) { atomicExch(status, 2); ok = false; break; }
+        if (!tc_mbar_wait(full0 + 8 * s, (kb / TC_STAGES) & 1)) { sx_set_status(status, 2); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t a_addr = tc_smem(tiles + s * TC_STAGE_BYTES), b_addr = a_addr + TC_A_BYTES;
 #pragma unroll
@@ -224,7 +224,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         }
       }
     } else {
-      if (lane == 0) atomicExch(status, 3);
+      if (lane == 0) sx_set_status(status, 3);
     }
   }
 
@@ -414,7 +414,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
         const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * tile_n;
         for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const uint32_t s = it % STAGES;
-          if (!tc_mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) { atomicExch(status, 1); ok = false; break; }
+          if (!tc_mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) { sx_set_status(status, 1); ok = false; break; }
           tc_mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
           const uint32_t a_dst = tc_smem(tiles + s * STAGE_BYTES), b_dst = a_dst + TC_A_BYTES;
           tc_tma_load_2d(a_dst, &map_a, kb * TC_BK, m0, full0 + 8 * s);
@@ -434,12 +434,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
         int tile, kb_lo, kb_hi;
         work_of(w, tile, kb_lo, kb_hi);
         const uint32_t buf = w & 1, use = w >> 1;
-        if (!tc_mbar_wait(acc_empty0 + 8 * buf, (use & 1) ^ 1)) { atomicExch(status, 4); ok = false; break; }
+        if (!tc_mbar_wait(acc_empty0 + 8 * buf, (use & 1) ^ 1)) { sx_set_status(status, 4); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const uint32_t s = it % STAGES;
-          if (!tc_mbar_wait(full0 + 8 * s, (it / STAGES) & 1)) { atomicExch(status, 2); ok = false; break; }
+          if (!tc_mbar_wait(full0 + 8 * s, (it / STAGES) & 1)) { sx_set_status(status, 2); ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
           const uint32_t a_addr = tc_smem(tiles + s * STAGE_BYTES), b_addr = a_addr + TC_A_BYTES;
 #pragma unroll
@@ -462,7 +462,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
       const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * tile_n;
       const int row = m0 + quarter * 32 + lane;
       if (!tc_mbar_wait(acc_full0 + 8 * buf, use & 1)) {
-        if (lane == 0) atomicExch(status, 3);
+        if (lane == 0) sx_set_status(status, 3);
         return false;
       }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -494,7 +494,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
       const int m0 = (tile % tiles_m) * TC_BM;
       const int row = m0 + quarter * 32 + lane;
       if (!tc_mbar_wait(acc_full0 + 8 * buf, use & 1)) {
-        if (lane == 0) atomicExch(status, 3);
+        if (lane == 0) sx_set_status(status, 3);
         alive = false;
         break;
       }
@@ -545,7 +545,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
           asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(cnt) : "memory");
           if (v >= nz) { all = true; break; }
         }
-        if (!all) atomicExch(status, 5);
+        if (!all) sx_set_status(status, 5);
         *piece_ok = all;
       }
       asm volatile("bar.sync 1, 128;\n" ::: "memory");
@@ -673,10 +673,7 @@ static int tc_make_map(CUtensorMap* map, const void* base, int rows, int K) {
 
 static int* tc_status_word() {
   static int* p = nullptr;
-  if (!p) {
-    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
-    cudaMemset(p, 0, sizeof(int));
-  }
+  if (!p) p = sx_status_word_alloc();
   return p;
 }
 
@@ -925,8 +922,12 @@ extern "C" int sx_gemm_tc(const void* A, const void* W, void* out, int M, int N,
 }
 
 // 0, or which bounded wait ran out (1 producer, 2 and 4 MMA issuer, 3 epilogue, 5 the blocks of a cut tile waiting for one another)
-extern "C" int sx_gemm_tc_status(int* host_value) {
+// Reads the word in host memory: no device call.  It tells of kernels the host has already waited for.
+// With reset != 0 the word goes back to 0.
+extern "C" int sx_gemm_tc_status(int* host_value, int reset) {
   int* p = tc_status_word();
   if (!p) return (int)cudaErrorMemoryAllocation;
-  return (int)cudaMemcpy(host_value, p, sizeof(int), cudaMemcpyDeviceToHost);
+  *host_value = *(volatile int*)p;
+  if (reset) *(volatile int*)p = 0;
+  return 0;
 }

@@ -729,24 +729,62 @@ extern "C" int sx_silu_mul(const void* gu, void* out, int n_tokens, int I, int d
 }
 
 // ---------------------------------------------------------------------------------------
-// after a decode step, on the device: every sequence takes its sampled token as the next
-// input and moves one position on (used by decode runs that never come back to the host)
+// Decoding that stays on the device.  Before a step: a row whose control word is not negative
+// runs that token instead of the one sampled for it in the step before (and its history of
+// tokens, if kept for the penalties, ends with that token).  After a step: every live row
+// (advance_by = 1) takes its sampled token as the next input, appends it to its history, and
+// moves one position and one word of its random stream on; rows that pad the batch stay put.
 // ---------------------------------------------------------------------------------------
-__global__ void decode_advance_kernel(int* __restrict__ token_ids, const int* __restrict__ sampled,
-                                      int* __restrict__ positions, int* __restrict__ seq_past,
-                                      int* __restrict__ seq_lens, int S) {
+__global__ void decode_begin_kernel(int* __restrict__ token_ids, const int* __restrict__ control,
+                                    int* __restrict__ history, const int* __restrict__ hist_len, int hist_cap, int S) {
   pdl_wait();
   pdl_trigger();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= S) return;
-  token_ids[i] = sampled[i];
+  const int t = control[i];
+  if (t < 0) return;
+  token_ids[i] = t;
+  if (history != nullptr) {
+    const int n = hist_len[i];
+    if (n > 0 && n <= hist_cap) history[(size_t)i * hist_cap + n - 1] = t;
+  }
+}
+extern "C" int sx_decode_begin(int* token_ids, const int* control, int* history, const int* hist_len, int hist_cap,
+                               int S, cudaStream_t stream) {
+  if (S <= 0) return 0;
+  return sx_launch(decode_begin_kernel, dim3((S + 127) / 128), dim3(128), 0, stream, token_ids, control, history,
+                   hist_len, hist_cap, S);
+}
+
+__global__ void decode_advance_kernel(int* __restrict__ token_ids, const int* __restrict__ sampled,
+                                      int* __restrict__ positions, int* __restrict__ seq_past,
+                                      int* __restrict__ seq_lens, int* __restrict__ rng_step,
+                                      const int* __restrict__ advance_by, int* __restrict__ history,
+                                      int* __restrict__ hist_len, int hist_cap, int S) {
+  pdl_wait();
+  pdl_trigger();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= S) return;
+  const int by = advance_by != nullptr ? advance_by[i] : 1;
+  if (by == 0) return;
+  const int t = sampled[i];
+  token_ids[i] = t;
   positions[i] += 1;
   seq_past[i] += 1;
   seq_lens[i] += 1;
+  if (rng_step != nullptr) rng_step[i] += 1;
+  if (history != nullptr) {
+    const int n = hist_len[i];
+    if (n < hist_cap) {
+      history[(size_t)i * hist_cap + n] = t;
+      hist_len[i] = n + 1;
+    }
+  }
 }
-extern "C" int sx_decode_advance(int* token_ids, const int* sampled, int* positions, int* seq_past,
-                                 int* seq_lens, int S, cudaStream_t stream) {
+extern "C" int sx_decode_advance(int* token_ids, const int* sampled, int* positions, int* seq_past, int* seq_lens,
+                                 int* rng_step, const int* advance_by, int* history, int* hist_len, int hist_cap,
+                                 int S, cudaStream_t stream) {
   if (S <= 0) return 0;
   return sx_launch(decode_advance_kernel, dim3((S + 127) / 128), dim3(128), 0, stream, token_ids, sampled, positions,
-                   seq_past, seq_lens, S);
+                   seq_past, seq_lens, rng_step, advance_by, history, hist_len, hist_cap, S);
 }

@@ -1,6 +1,6 @@
 from .generate import (GenerationOptions, GenerationResult, GenerationStats, plan_batches,
                        run_generation)
-from .step import DecodeRun, Engine, Entry, StepError
+from .step import DecodeRow, DecodeSession, Engine, Entry, StepError
 
-__all__ = ["DecodeRun", "Engine", "Entry", "StepError", "GenerationOptions", "GenerationResult", "GenerationStats",
-           "plan_batches", "run_generation"]
+__all__ = ["DecodeRow", "DecodeSession", "Engine", "Entry", "StepError", "GenerationOptions", "GenerationResult",
+           "GenerationStats", "plan_batches", "run_generation"]

@@ -8,12 +8,20 @@ token counts), or when the cache cannot hold another token; its slot is given
 back at once and the later steps shrink.  Requests beyond one batch run as
 further batches, one after another, in the slots the earlier ones gave back.
 
+The single-token steps run as a decode session of the engine: sampling and the move
+to the next token stay on the device, the loop enqueues a step and reads the tokens of
+the step before while it runs.  A stop token is therefore seen when the next step is
+already on its way; that step's token for the stopped sequence is dropped (the
+sequence ends with the stop token, exactly as without the lookahead), and a sequence
+that ends by its length never runs a step too many, since the loop counts.
+
 Single-sequence semantics follow the reference's loop
 (crates/synaptix-models/llm/common/src/generate.rs:237-302: the stop check is on
 the last emitted token before the next model call, :281-285; ``eos_set`` :202-208).
-The loop knows the engine only as ``open() / close(slot) / step(entries) ->
-logits`` and the sampler only as a function of logits, so its decisions are
-tested on the CPU with a fake of both.
+The loop knows the engine only as ``open() / close(slot) / step(entries) -> logits /
+start_decode(rows, sampling) -> session`` (``launch``, ``collect``, ``drop``,
+``in_flight``) and ``check_kernels()`` and the sampler of the prompt step only as a function of logits, so
+its decisions are tested on the CPU with fakes of all of them.
 """
 from __future__ import annotations
 
@@ -23,7 +31,7 @@ from typing import Callable, List, Optional, Sequence, Tuple
 
 from ..cache.pages import PAGE_TOKENS, CacheFull, pages_for
 from ..sampling.params import SamplingParams
-from .step import Entry
+from .step import DecodeRow, Entry
 
 
 @dataclasses.dataclass(frozen=True)
@@ -32,6 +40,7 @@ class GenerationOptions:
     stop_token_ids: Tuple[int, ...] = ()
     sampling: SamplingParams = SamplingParams()
     max_batch_size: Optional[int] = None      # None: as many as the cache holds
+    lookahead: int = 2                        # decode steps enqueued before the oldest one's tokens are read
 
 
 @dataclasses.dataclass
@@ -133,26 +142,51 @@ def run_generation(engine, sample: Callable, prompts: Sequence[Sequence[int]], o
         logits = engine.step([Entry(s.slot, s.prompt, [len(s.prompt) - 1]) for s in live], keep=False)
         toks = sample(logits, [s.request for s in live], [0] * len(live),
                       [s.prompt for s in live] if need_ctx else None)
+        engine.check_kernels()            # the host has waited for the prompt step: did all of it run?
         stats.prefill_ms += (clock() - t0) * 1e3
         stats.prompt_tokens += sum(len(s.prompt) for s in live)
         live = [s for s, t in zip(live, toks) if take(s, int(t))]
 
         t0 = clock()
         up0 = getattr(engine, "h2d_bytes", 0)
-        while live:
-            stats.decode_d2h_bytes += 4 * len(live)
-            try:
-                logits = engine.step([Entry(s.slot, [s.out[-1]], [0]) for s in live], keep=False)
-            except CacheFull:
-                # no page for everyone: the longest sequence ends, the others go on
-                victim = max(live, key=lambda s: len(s.prompt) + len(s.out))
-                finish(victim, "capacity")
-                live = [s for s in live if s is not victim]
-                continue
-            stats.decode_steps += 1
-            toks = sample(logits, [s.request for s in live], [len(s.out) for s in live],
-                          [s.prompt + s.out for s in live] if need_ctx else None)
-            live = [s for s, t in zip(live, toks) if take(s, int(t))]
+        if live:
+            session = engine.start_decode(
+                [DecodeRow(s.slot, s.out[-1], s.request, len(s.out), (s.prompt + s.out) if need_ctx else None)
+                 for s in live], options.sampling)
+            depth = max(1, options.lookahead)
+            full = False
+            while live:       # (the session gives its captured step back when its last row is dropped)
+                # all live sequences of a batch have the same number of tokens so far: they started together
+                room = options.max_new_tokens - len(live[0].out) - session.in_flight
+                if not full and room > 0 and session.in_flight < depth:
+                    try:
+                        session.launch()
+                        stats.decode_steps += 1
+                        continue
+                    except CacheFull:
+                        full = True
+                if session.in_flight == 0:
+                    # no page for everyone: the longest sequence ends, the others go on
+                    victim = max(range(len(live)), key=lambda i: len(live[i].prompt) + len(live[i].out))
+                    finish(live[victim], "capacity")
+                    session.drop([victim])
+                    del live[victim]
+                    full = False
+                    continue
+                toks = session.collect()
+                stats.decode_d2h_bytes += 4 * len(toks)
+                gone = [i for i, (s, t) in enumerate(zip(live, toks)) if not take(s, int(t))]
+                if gone:
+                    # the steps already launched ran the ended sequences too; those tokens are dropped
+                    while session.in_flight:
+                        toks = session.collect()
+                        stats.decode_d2h_bytes += 4 * len(toks)
+                        for i, (s, t) in enumerate(zip(live, toks)):
+                            if i not in gone and not take(s, int(t)):
+                                gone.append(i)
+                    session.drop(gone)
+                    live = [s for i, s in enumerate(live) if i not in gone]
+                full = False
         stats.decode_ms += (clock() - t0) * 1e3
         stats.decode_h2d_bytes += getattr(engine, "h2d_bytes", 0) - up0
     return results, stats

@@ -64,25 +64,41 @@ def _capture(graph: "torch.cuda.CUDAGraph"):
 
 
 class _Layout:
-    """Where each index array of a step lies in the one int32 buffer that is uploaded."""
-    NAMES = ("token_ids", "positions", "seq_of_token", "cu_seqlens", "seq_past", "seq_lens", "seq_slots",
-             "want_rows")
+    """Where each index array of a step lies in the one int32 buffer that is uploaded.
 
-    def __init__(self, T: int, S: int, R: int, maxp: int, ngroups: int):
+    ``decode=True`` is the layout of a decode session: the arrays that the device itself moves on
+    after every step (tokens, positions, lengths, the random stream's step, the length of the
+    penalties' history) come first, and everything from ``fixed_start`` on is written by the host
+    alone, so it can be uploaded again (a sequence reached a new page) while steps are in flight.
+    """
+    MOVING = ("token_ids", "positions", "seq_past", "seq_lens", "rng_step", "hist_len")
+
+    def __init__(self, T: int, S: int, R: int, maxp: int, ngroups: int, decode: bool = False):
         self.T, self.S, self.R, self.maxp, self.ngroups = T, S, R, maxp, ngroups
-        sizes = [T, T, T, S + 1, S, S, S, R] + [S * maxp] * ngroups
-        self.sizes = sizes
-        self.offs = [0]
-        for s in sizes:
-            self.offs.append(self.offs[-1] + _align4(s))
-        self.total = self.offs[-1]
+        if decode:
+            arrays = [("token_ids", T), ("positions", T), ("seq_past", S), ("seq_lens", S), ("rng_step", S),
+                      ("hist_len", S), ("seq_of_token", T), ("cu_seqlens", S + 1), ("seq_slots", S),
+                      ("want_rows", R), ("advance_by", S), ("request", S)]
+        else:
+            arrays = [("token_ids", T), ("positions", T), ("seq_of_token", T), ("cu_seqlens", S + 1),
+                      ("seq_past", S), ("seq_lens", S), ("seq_slots", S), ("want_rows", R)]
+        arrays += [(("block_table", g), S * maxp) for g in range(ngroups)]
+        self.where = {}
+        off = 0
+        self.fixed_start = 0
+        for name, size in arrays:
+            if decode and name == "seq_of_token":
+                self.fixed_start = off
+            self.where[name] = (off, size)
+            off += _align4(size)
+        self.total = off
 
     def views(self, flat):
         """name -> view of ``flat`` (numpy or torch), block tables as a list under 'block_tables'."""
-        out = {n: flat[self.offs[i]:self.offs[i] + self.sizes[i]] for i, n in enumerate(self.NAMES)}
+        out = {n: flat[o:o + z] for n, (o, z) in self.where.items() if isinstance(n, str)}
         out["block_tables"] = [
-            flat[self.offs[8 + g]:self.offs[8 + g] + self.S * self.maxp].reshape(self.S, self.maxp)
-            for g in range(self.ngroups)]
+            flat[self.where[("block_table", g)][0]:self.where[("block_table", g)][0] + self.S * self.maxp].reshape(
+                self.S, self.maxp) for g in range(self.ngroups)]
         return out
 
 
@@ -98,6 +114,7 @@ class _Staging:
         self.bytes_uploaded = 0
 
     def upload(self, flat: np.ndarray, into: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Copy ``flat`` to the device (into ``into[:len(flat)]`` if given), asynchronously."""
         n = flat.shape[0]
         i = self.i
         self.i = (i + 1) % len(self.bufs)
@@ -110,9 +127,10 @@ class _Staging:
         buf[:n].numpy()[:] = flat
         dev = into if into is not None else torch.empty(n, dtype=torch.int32, device=self.device)
         dev[:n].copy_(buf[:n], non_blocking=True)
-        ev = torch.cuda.Event()
+        ev = self.events[i]
+        if ev is None:
+            ev = self.events[i] = torch.cuda.Event()
         ev.record()
-        self.events[i] = ev
         self.bytes_uploaded += n * 4
         return dev
 
@@ -136,39 +154,87 @@ def _bucket_pages(n: int) -> int:
     return b
 
 
-class _CapturedStep:
-    """A single-token step of ``S`` rows with block tables ``maxp`` pages wide, with its index
-    arrays at fixed addresses, run eagerly the first time and replayed as a graph afterwards."""
+class _Captured:
+    """Single-token steps of ``S`` rows with block tables ``maxp`` pages wide, with their index
+    arrays at fixed addresses: ``body()`` is run eagerly the first time and replayed as a CUDA
+    graph afterwards (or run eagerly every time when the engine does not use graphs)."""
 
-    def __init__(self, engine: "Engine", S: int, maxp: int):
+    def __init__(self, engine: "Engine", S: int, maxp: int, decode: bool = False):
         self.engine = engine
-        self.layout = _Layout(S, S, S, maxp, engine.cache.n_block_tables)
+        self.layout = _Layout(S, S, S, maxp, engine.cache.n_block_tables, decode=decode)
         self.flat = torch.zeros(self.layout.total, dtype=torch.int32, device=engine.device)
-        v = self.layout.views(self.flat)
+        self.arrays = v = self.layout.views(self.flat)
         self.ctx = StepContext(
             token_ids=v["token_ids"], positions=v["positions"], seq_of_token=v["seq_of_token"],
             cu_seqlens=v["cu_seqlens"], seq_past=v["seq_past"], seq_lens=v["seq_lens"], seq_slots=v["seq_slots"],
             want_rows=v["want_rows"], block_tables=v["block_tables"], n_tokens=S, n_seqs=S, n_want=S, max_new=1,
             max_len=maxp * PAGE_TOKENS, all_single=True, runtime=engine.runtime, want_all=True)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
-        self.logits: Optional[torch.Tensor] = None
+        self.result: Optional[torch.Tensor] = None
         self.launches = 0
+        self.in_use = False
+
+    def body(self) -> torch.Tensor:
+        return self.engine._forward(self.ctx)
 
     def run(self) -> torch.Tensor:
         eng = self.engine
         if self.graph is not None:
             self.graph.replay()
             eng.kernel_launches += self.launches
-            return self.logits
+            return self.result
         before = eng.kernel_launches
-        out = eng._forward(self.ctx)                    # eager: the real result of this step
+        out = self.body()                               # eager: the real result of this step
         self.launches = eng.kernel_launches - before
-        g = torch.cuda.CUDAGraph()
-        with _capture(g):                               # recorded, not run: the cache is untouched
-            self.logits = eng._forward(self.ctx)
-        eng.kernel_launches = before + self.launches
-        self.graph = g
+        if eng.use_graphs:
+            g = torch.cuda.CUDAGraph()
+            with _capture(g):                           # recorded, not run: nothing is touched
+                self.result = self.body()
+            eng.kernel_launches = before + self.launches
+            self.graph = g
         return out
+
+
+class _CapturedDecode(_Captured):
+    """A captured step that also samples and moves on, all on the device: the model, the sampler
+    (``params``), and the advance of tokens, positions, lengths and the random stream's step.
+
+    ``control [S]`` is written by the host before every step: ``-1`` lets a row take the token the
+    device sampled for it in the step before, any other value is the token the row runs instead.
+    ``sampled [S]`` holds the step's tokens afterwards.  ``history [S, hist_cap]`` (only when
+    ``params`` has penalties) is each row's context, which the advance appends to.
+    """
+
+    def __init__(self, engine: "Engine", S: int, maxp: int, params):
+        super().__init__(engine, S, maxp, decode=True)
+        self.params = params
+        dev = engine.device
+        self.control = torch.full((S,), -1, dtype=torch.int32, device=dev)
+        self.sampled = torch.zeros(S, dtype=torch.int32, device=dev)
+        self.hist_cap = maxp * PAGE_TOKENS + 1 if params.penalties_on else 0
+        self.history = torch.zeros((S, self.hist_cap), dtype=torch.int32, device=dev) if self.hist_cap else None
+
+    def body(self) -> torch.Tensor:
+        from ..sampling.sampler import sample_on_device
+        a = self.arrays
+        ops.decode_begin(a["token_ids"], self.control)
+        logits = self.engine._forward(self.ctx)
+        sample_on_device(self.params, logits, a["request"], a["rng_step"], self.history, a["hist_len"],
+                         out=self.sampled)
+        ops.decode_advance(a["token_ids"], self.sampled, a["positions"], a["seq_past"], a["seq_lens"],
+                           a["rng_step"], a["advance_by"], self.history, a["hist_len"])
+        return self.sampled
+
+
+class DecodeRow(NamedTuple):
+    """One sequence of a decode session: its slot, the token it runs next, and what the sampler
+    needs: the request's index and how many tokens it has sampled so far (they pick the word of
+    its random stream), and its context (prompt and output so far) if penalties are on."""
+    slot: int
+    token: int
+    request: int = 0
+    sampled_so_far: int = 0
+    context: Optional[Sequence[int]] = None
 
 
 class Engine:
@@ -188,8 +254,8 @@ class Engine:
                            dtype=rt.dtype, device=rt.device)
         self._staging = _Staging(rt.device)
         self.use_graphs = bool(use_graphs) and model.all_graph_safe()
-        self._captured: Dict[Tuple[int, int], _CapturedStep] = {}
-        self._last_decode = None
+        self._captured: Dict[Tuple[int, int], _Captured] = {}
+        self._captured_decode: Dict[tuple, _CapturedDecode] = {}
         self.kernel_launches = 0         # kernels of this package launched (graph replays counted by content)
         ops.set_launch_counter(self)
 
@@ -211,11 +277,15 @@ class Engine:
         return self.cache.open()
 
     def close(self, slot: int) -> None:
-        self._last_decode = None
         self.cache.close(slot)
 
     def length(self, slot: int) -> int:
         return self.cache.slots.length(slot)
+
+    def check_kernels(self) -> None:
+        """Raise ``KernelError`` if a bounded wait inside one of the tensor-memory kernels ran out
+        since the last call (their results are then not to be trusted).  Costs no device call."""
+        ops.check_status()
 
     # -- a step ------------------------------------------------------------------
     def _forward(self, ctx: StepContext) -> torch.Tensor:
@@ -249,7 +319,6 @@ class Engine:
 
     def _fill(self, lay: _Layout, entries: Sequence[Entry], past: List[int], new: List[int]) -> np.ndarray:
         """The step's index arrays; rows of ``lay`` beyond the entries are dummy single tokens."""
-        slots = self.cache.slots
         flat = np.zeros(lay.total, dtype=np.int32)
         v = lay.views(flat)
         tok, pos, sot, cu = v["token_ids"], v["positions"], v["seq_of_token"], v["cu_seqlens"]
@@ -267,21 +336,26 @@ class Engine:
                 v["want_rows"][r0] = t0 + w
                 r0 += 1
             t0 += n
-        for i in range(len(entries), lay.S):          # dummy rows: token 0 at position 0 of the unowned page 0
+        # dummy rows: token 0 at position 0 of page 0, which no sequence owns, in the state row no sequence owns
+        spare = self.cache.spare_slot
+        for i in range(len(entries), lay.S):
             sot[t0] = i
             cu[i] = t0
             v["seq_lens"][i] = 1
-            v["seq_slots"][i] = 0
+            v["seq_slots"][i] = spare
             v["want_rows"][r0] = t0
             r0 += 1
             t0 += 1
         cu[lay.S] = t0
-        for g in range(lay.ngroups):
-            bt = v["block_tables"][g]
-            for i, e in enumerate(entries):
-                row = np.asarray(slots.table(e.slot, g)[:lay.maxp], dtype=np.int32)
-                bt[i, :row.shape[0]] = np.maximum(row, 0)
+        self._fill_tables(v, [e.slot for e in entries], lay.maxp)
         return flat
+
+    def _fill_tables(self, v, slot_ids: Sequence[int], maxp: int) -> None:
+        slots = self.cache.slots
+        for g, bt in enumerate(v["block_tables"]):
+            for i, s in enumerate(slot_ids):
+                row = np.asarray(slots.table(s, g)[:maxp], dtype=np.int32)
+                bt[i, :row.shape[0]] = np.maximum(row, 0)       # pages given back (-1) read as page 0
 
     def plan(self, entries: Sequence[Entry], past: List[int], new: List[int]) -> StepContext:
         """Upload the step's index arrays and wrap them."""
@@ -305,12 +379,8 @@ class Engine:
         """Run one step; returns float32 logits ``[n_wanted, vocab]`` on the device.
 
         With ``keep=False`` the result may be a buffer that the next step overwrites
-        (the generation loop samples from it at once and needs no copy)."""
+        (a caller that samples from it at once needs no copy)."""
         entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
-        if self.use_graphs:
-            logits = self._step_again(entries)
-            if logits is not None:
-                return logits.clone() if keep else logits
         past, new = self._check(entries)
         single = all(n == 1 and tuple(e.want) == (0,) for n, e in zip(new, entries))
         if single and self.use_graphs:
@@ -318,129 +388,265 @@ class Engine:
             maxp = _bucket_pages(max(pages_for(p + 1) for p in past))
             cap = self._captured.get((S, maxp))
             if cap is None:
-                cap = self._captured[(S, maxp)] = _CapturedStep(self, S, maxp)
+                cap = self._captured[(S, maxp)] = _Captured(self, S, maxp)
             flat = self._fill(cap.layout, entries, past, new)
             self._staging.upload(flat, into=cap.flat)
             logits = cap.run()[:len(entries)]
-            # remembered for the next step of the same sequences (see _step_again)
-            self._last_decode = (tuple(e.slot for e in entries), [p + 1 for p in past], cap, flat)
             if keep:
                 logits = logits.clone()
         else:
-            self._last_decode = None
             ctx = self.plan(entries, past, new)
             logits = self._forward(ctx)
         for e in entries:
             self.cache.slots.advance(e.slot, len(e.tokens))
         return logits
 
-    def _step_again(self, entries: Sequence[Entry]) -> Optional[torch.Tensor]:
-        """The common case of decoding: the same sequences as in the last step, one more token
-        each, and nobody crosses into a new page.  Then the index arrays of the last step are
-        still right but for the tokens and the positions, which move on by one: no planning."""
-        last = self._last_decode
-        if last is None:
-            return None
-        key, lens, cap, flat = last
-        n = len(entries)
-        if n != len(key):
-            return None
-        vocab = self.model.embedding.vocab
-        slots = self.cache.slots
-        toks = []
-        for e, s, ln in zip(entries, key, lens):
-            if e.slot != s or len(e.tokens) != 1 or tuple(e.want) != (0,) or ln % PAGE_TOKENS == 0:
-                return None
-            t = e.tokens[0]
-            if not (0 <= t < vocab) or slots._len.get(s) != ln:
-                return None
-            toks.append(t)
-        v = cap.layout.views(flat)
-        v["token_ids"][:n] = toks
-        v["positions"][:n] += 1
-        v["seq_past"][:n] += 1
-        v["seq_lens"][:n] += 1
-        self._staging.upload(flat, into=cap.flat)
-        logits = cap.run()[:n]
-        for i, s in enumerate(key):
-            slots.advance(s, 1)
-            lens[i] += 1
-        return logits
-
-    # -- decoding without coming back to the host ------------------------------------
-    def decode_run(self, slots: Sequence[int], tokens: Sequence[int], n_steps: int, sampler=None) -> torch.Tensor:
-        """``n_steps`` single-token steps for ``slots`` starting from ``tokens``, each step's
-        sampled token fed to the next on the device; returns the sampled tokens int32
-        ``[n_steps, len(slots)]`` (on the device).  See ``DecodeRun``."""
-        if n_steps <= 0:
-            return torch.empty((0, len(slots)), dtype=torch.int32, device=self.device)
-        return DecodeRun(self, slots, tokens, n_steps, sampler).steps(n_steps)
+    # -- decoding -------------------------------------------------------------------
+    def start_decode(self, rows: Sequence[DecodeRow], sampling=None) -> "DecodeSession":
+        """A decode session for sequences that have run their prompts: see ``DecodeSession``."""
+        return DecodeSession(self, rows, sampling)
 
 
-class DecodeRun:
-    """Single-token steps of a fixed set of sequences that never come back to the host: each
-    step's sampled token is the next step's input, positions advance on the device, and the
-    whole step (model, sampling, advance) is one CUDA graph after its first, eager run.
+class _Pending:
+    """A launched step whose tokens the host has not handed out yet."""
+    __slots__ = ("buf", "event", "n", "tokens")
 
-    Pages for ``max_steps`` more tokens are reserved up front, so block tables do not change.
-    ``sampler(logits) -> int32 [rows]`` runs on the device inside the step (default: argmax).
-    Stop tokens are not looked at; the generation loop is the place for that.
+    def __init__(self, buf, event, n):
+        self.buf, self.event, self.n, self.tokens = buf, event, n, None
+
+    def read(self) -> List[int]:
+        if self.tokens is None:
+            self.event.synchronize()
+            self.tokens = self.buf[:self.n].tolist()
+        return self.tokens
+
+
+class DecodeSession:
+    """Single-token steps of a set of sequences, with sampling and the move to the next token
+    kept on the device: a step's sampled tokens are the next step's input without passing
+    through the host.  The host only enqueues (``launch``) and reads tokens as they arrive
+    (``collect``), so it can enqueue step k+1 before it has seen the tokens of step k.
+
+    ``launch()`` reserves the cache pages the step needs (``CacheFull`` leaves everything as it
+    was), writes the step's control words (and, when a sequence reached a new page, its page
+    tables) and enqueues the step: one CUDA graph of model, sampler and advance once it has been
+    recorded.  ``collect()`` waits for the oldest step not yet read and returns its tokens, one per
+    live row.  ``drop(rows)`` takes sequences out; all launched steps must have been collected.
+    What a step computes is what ``Engine.step`` computes for the same tokens: both run the
+    model through ``Engine._forward`` on the same cache.
+
+    A generation loop that sees a stop token in step k's tokens has usually launched step k+1
+    already; that step then ran one token too many for the stopped row, into pages the row still
+    held, and its token for that row is dropped.  The reference's loop has the same shape without
+    the lookahead (crates/synaptix-models/llm/qwen3/src/pipeline.rs:279-302: graph replay, the
+    sampled token copied back each step).
     """
 
-    def __init__(self, engine: Engine, slots: Sequence[int], tokens: Sequence[int], max_steps: int, sampler=None):
-        from ..ops import sampling as K
+    def __init__(self, engine: Engine, rows: Sequence[DecodeRow], sampling=None):
+        from ..sampling.params import SamplingParams
         self.engine = engine
-        self.slots = list(slots)
-        self.max_steps = max_steps
-        self.done = 0
-        entries = [Entry(s, [t], [0]) for s, t in zip(slots, tokens)]
-        past, _ = engine._check(entries)
-        engine.cache.slots.reserve_many(self.slots, [max_steps] * len(self.slots))
-        S = len(entries)
-        maxp = max(pages_for(p + max_steps) for p in past)
-        lay = _Layout(S, S, S, maxp, engine.cache.n_block_tables)
-        flat = engine._staging.upload(engine._fill(lay, entries, past, [1] * S)).clone()
-        v = lay.views(flat)
-        self.ctx = ctx = StepContext(
-            token_ids=v["token_ids"], positions=v["positions"], seq_of_token=v["seq_of_token"],
-            cu_seqlens=v["cu_seqlens"], seq_past=v["seq_past"], seq_lens=v["seq_lens"], seq_slots=v["seq_slots"],
-            want_rows=v["want_rows"], block_tables=v["block_tables"], n_tokens=S, n_seqs=S, n_want=S, max_new=1,
-            max_len=maxp * PAGE_TOKENS, all_single=True, runtime=engine.runtime, want_all=True)
-        self.sampled = sampled = torch.empty(S, dtype=torch.int32, device=engine.device)
+        self.params = sampling if sampling is not None else SamplingParams()
+        self.params.validate()
+        self.rows: List[DecodeRow] = []
+        self.lens: List[int] = []             # tokens each row holds after the steps launched so far
+        self.sampled: List[int] = []          # tokens each row has sampled, launched steps included
+        self.last: List[Optional[int]] = []   # the token each row runs next, if the host knows it
+        self.contexts: List[Optional[List[int]]] = []
+        self.pending: List[_Pending] = []
+        self.cap: Optional[_CapturedDecode] = None
+        self._stale = True                    # the device arrays must be written anew before the next step
+        self._tables: List[tuple] = []
+        self._free: List[tuple] = []          # (pinned buffer, event) pairs not in use
+        self.d2h_bytes = 0
+        vocab = engine.model.embedding.vocab
+        seen = set()
+        for r in rows:
+            r = r if isinstance(r, DecodeRow) else DecodeRow(*r)
+            if r.slot in seen:
+                raise StepError(f"slot {r.slot} appears twice in one decode session")
+            seen.add(r.slot)
+            if not (0 <= r.token < vocab):
+                raise StepError(f"slot {r.slot}: token ids must lie in [0, {vocab})")
+            if self.params.penalties_on and r.context is None:
+                raise StepError("penalties need each row's context")
+            self.rows.append(r)
+            self.lens.append(engine.cache.slots.length(r.slot))
+            self.sampled.append(r.sampled_so_far)
+            self.last.append(int(r.token))
+            self.contexts.append(list(r.context) if r.context is not None else None)
+        if not self.rows:
+            raise StepError("a decode session needs at least one row")
 
-        def one():
-            logits = engine._forward(ctx)
-            tok = K.argmax_rows(logits, out=sampled) if sampler is None else sampler(logits)
-            if tok is not sampled:
-                sampled.copy_(tok)
-            ops.decode_advance(ctx.token_ids, sampled, ctx.positions, ctx.seq_past, ctx.seq_lens)
+    # -- state ------------------------------------------------------------------------
+    @property
+    def in_flight(self) -> int:
+        return len(self.pending)
 
-        self._one = one
-        self.graph: Optional[torch.cuda.CUDAGraph] = None
-        self.launches_per_step = 0
+    @property
+    def n_rows(self) -> int:
+        return len(self.rows)
 
-    def steps(self, n: int) -> torch.Tensor:
-        """Run ``n`` more steps; returns their sampled tokens int32 ``[n, rows]`` on the device."""
+    def _release(self) -> None:
+        if self.cap is not None:
+            self.cap.in_use = False
+            self.cap = None
+
+    def close(self) -> None:
+        """Give the captured step back to the engine (``drop`` of the last rows does it too)."""
+        self._read_all()
+        self._release()
+
+    def _read_all(self) -> None:
+        """Wait for every launched step and keep its tokens for ``collect``; afterwards the host
+        knows the token each row runs next."""
+        for p in self.pending:
+            p.read()
+        if self.pending:
+            self.last = list(self.pending[-1].tokens)
+
+    def _table_lens(self) -> List[tuple]:
+        slots = self.engine.cache.slots
+        return [slots.table_shape(r.slot) for r in self.rows]
+
+    def _acquire(self, S: int, maxp: int) -> _CapturedDecode:
         eng = self.engine
-        if self.done + n > self.max_steps:
-            raise StepError(f"this run reserved {self.max_steps} steps, {self.done} are done, {n} more asked")
-        out = torch.empty((n, len(self.slots)), dtype=torch.int32, device=eng.device)
-        for k in range(n):
-            if self.graph is None:
-                before = eng.kernel_launches
-                self._one()                                   # eager: the real step
-                self.launches_per_step = eng.kernel_launches - before
-                if eng.use_graphs:
-                    g = torch.cuda.CUDAGraph()
-                    with _capture(g):
-                        self._one()                           # recorded, not run
-                    eng.kernel_launches = before + self.launches_per_step
-                    self.graph = g
-            elif self.graph is not None:
-                self.graph.replay()
-                eng.kernel_launches += self.launches_per_step
-            out[k].copy_(self.sampled)
-        self.done += n
-        for s in self.slots:
-            eng.cache.slots.advance(s, n)
-        return out
+        key = (S, maxp, self.params)
+        cap = eng._captured_decode.get(key)
+        if cap is None:
+            cap = eng._captured_decode[key] = _CapturedDecode(eng, S, maxp, self.params)
+        elif cap.in_use:                       # another session is on it: one of our own, not kept
+            cap = _CapturedDecode(eng, S, maxp, self.params)
+        cap.in_use = True
+        return cap
+
+    def _write_all(self, S: int, maxp: int) -> None:
+        """Everything the device holds of this session, from what the host knows."""
+        eng = self.engine
+        self._read_all()
+        if self.cap is None or (self.cap.layout.S, self.cap.layout.maxp) != (S, maxp):
+            self._release()
+            self.cap = self._acquire(S, maxp)
+        cap = self.cap
+        n = len(self.rows)
+        # a step of one token each for the live rows, dummy rows behind them
+        entries = [Entry(r.slot, [t], [0]) for r, t in zip(self.rows, self.last)]
+        flat = eng._fill(cap.layout, entries, self.lens, [1] * n)
+        v = cap.layout.views(flat)
+        v["advance_by"][:n] = 1
+        v["request"][:n] = [r.request for r in self.rows]
+        v["rng_step"][:n] = self.sampled
+        if cap.history is not None:
+            hist = np.zeros((cap.layout.S, cap.hist_cap), dtype=np.int32)
+            for i, c in enumerate(self.contexts):
+                c = c + [p.tokens[i] for p in self.pending]        # launched steps the caller has not collected
+                m = min(len(c), cap.hist_cap)
+                hist[i, :m] = c[len(c) - m:]
+                v["hist_len"][i] = m
+            cap.history.copy_(torch.from_numpy(hist).pin_memory(), non_blocking=True)
+            eng._staging.bytes_uploaded += hist.size * 4
+        eng._staging.upload(flat, into=cap.flat)
+        if not eng.use_graphs:
+            cap.ctx.host = {"cu_seqlens": list(range(n + 1)), "seq_slots": [r.slot for r in self.rows]}
+        self._tables = self._table_lens()
+        self._stale = False
+
+    def _write_tables(self) -> None:
+        """The host-owned part of the device arrays again (page tables changed); the arrays the
+        device moves on by itself are left alone, so steps may be in flight."""
+        eng, cap = self.engine, self.cap
+        lay = cap.layout
+        n = len(self.rows)
+        entries = [Entry(r.slot, [0], [0]) for r in self.rows]
+        flat = eng._fill(lay, entries, self.lens, [1] * n)
+        v = lay.views(flat)
+        v["advance_by"][:n] = 1
+        v["request"][:n] = [r.request for r in self.rows]
+        eng._staging.upload(flat[lay.fixed_start:], into=cap.flat[lay.fixed_start:])
+        self._tables = self._table_lens()
+
+    # -- steps -------------------------------------------------------------------------
+    def launch(self, tokens: Optional[Sequence[Optional[int]]] = None) -> None:
+        """Enqueue one step.  ``tokens[i]``, if given and not ``None``, is the token row ``i`` runs
+        in this step instead of the one sampled for it in the step before."""
+        eng = self.engine
+        slots = eng.cache.slots
+        n = len(self.rows)
+        if n == 0:
+            raise StepError("the decode session has no rows left")
+        vocab = eng.model.embedding.vocab
+        if tokens is not None:
+            if len(tokens) != n:
+                raise StepError(f"{len(tokens)} tokens for {n} rows")
+            for t in tokens:
+                if t is not None and not (0 <= t < vocab):
+                    raise StepError(f"token ids must lie in [0, {vocab})")
+            if self.params.penalties_on:
+                if self.pending:
+                    raise StepError("with penalties on, tokens are put in only when no step is in flight")
+                for c, t in zip(self.contexts, tokens):
+                    if t is not None:
+                        c[-1] = int(t)
+        for r, ln in zip(self.rows, self.lens):
+            if slots.length(r.slot) != ln:
+                raise StepError(f"slot {r.slot} was stepped outside its decode session")
+        slots.reserve_many([r.slot for r in self.rows], [1] * n)          # CacheFull: nothing has changed
+        need_p = max(pages_for(ln + 1) for ln in self.lens)
+        # a captured step has dummy rows up to a bucket; an eager one runs the live rows alone, since
+        # parts that loop over sequences on the host see exactly those
+        S = _bucket_rows(n) if eng.use_graphs else n
+        cap = self.cap
+        if self._stale or cap is None or cap.layout.S != S or cap.layout.maxp < need_p:
+            self._write_all(S, _bucket_pages(need_p))
+            cap = self.cap
+        elif self._table_lens() != self._tables:
+            self._write_tables()
+        if not eng.use_graphs:              # parts that loop on the host get this step's lengths
+            cap.ctx.host.update(seq_past=list(self.lens), seq_lens=[ln + 1 for ln in self.lens])
+            cap.ctx.max_len = max(self.lens) + 1
+        # control words: -1, or the token the host puts in
+        ctl = np.full(cap.layout.S, -1, dtype=np.int32)
+        if tokens is not None:
+            for i, t in enumerate(tokens):
+                if t is not None:
+                    ctl[i] = t
+        eng._staging.upload(ctl, into=cap.control)
+        cap.run()
+        buf, event = self._free.pop() if self._free else (
+            torch.empty(max(eng.max_seqs, 64), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+        buf[:n].copy_(cap.sampled[:n], non_blocking=True)
+        event.record()
+        self.pending.append(_Pending(buf, event, n))
+        self.d2h_bytes += 4 * n
+        for i, r in enumerate(self.rows):
+            slots.advance(r.slot, 1)
+            self.lens[i] += 1
+            self.sampled[i] += 1
+        self.last = [None] * n
+
+    def collect(self) -> List[int]:
+        """The tokens of the oldest launched step not yet collected, one per row."""
+        if not self.pending:
+            raise StepError("no step is in flight")
+        p = self.pending.pop(0)
+        tokens = p.read()
+        if not self.pending:
+            self.last = list(tokens)
+        self._free.append((p.buf, p.event))
+        if self.contexts and self.contexts[0] is not None:
+            for c, t in zip(self.contexts, tokens):
+                c.append(t)
+        self.engine.check_kernels()
+        return tokens
+
+    def drop(self, rows: Sequence[int]) -> None:
+        """Rows (indices into the live rows) leave the session; their slots are the caller's to close."""
+        if self.pending:
+            raise StepError("collect every launched step before rows are dropped")
+        gone = set(rows)
+        keep = [i for i in range(len(self.rows)) if i not in gone]
+        for name in ("rows", "lens", "sampled", "last", "contexts"):
+            old = getattr(self, name)
+            setattr(self, name, [old[i] for i in keep])
+        self._stale = True
+        if not self.rows:
+            self._release()

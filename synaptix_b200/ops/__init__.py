@@ -18,14 +18,42 @@ from .attention import (TC_TILE_ROWS, attn_decode, attn_decode_prep, attn_prefil
 from .decode import MAX_ROWS as SKINNY_MAX_ROWS, skinny_gemm, skinny_gemm_residual, skinny_gemm_scaled, skinny_supported
 from .gemm_tc import gemm_tc, tc_supported
 from .options import OPTIONS, KernelOptions, options, set_options
-from .generic import (add_rmsnorm, attn_generic, decode_advance, embed_gather, gemm_generic, qkv_prepare,
+from .generic import (add_rmsnorm, attn_generic, decode_advance, decode_begin, embed_gather, gemm_generic, qkv_prepare,
                       residual_add,
                       silu_mul)
 
-__all__ = ["OPTIONS", "KernelOptions", "options", "set_options", "KernelsUnavailable", "KernelError", "set_launch_counter", "decode_advance", "add_rmsnorm", "attn_generic", "embed_gather",
+__all__ = ["OPTIONS", "KernelOptions", "options", "set_options", "KernelsUnavailable", "KernelError", "set_launch_counter", "decode_advance", "decode_begin", "check_status", "add_rmsnorm", "attn_generic", "embed_gather",
            "gemm_generic", "qkv_prepare", "residual_add", "silu_mul", "linear", "linear_normed", "norm_fusable", "attention",
            "attention_from_projection", "decode_attention_takes_projection", "residual_product_fusable",
            "linear_into_residual", "linear_scaled"]
+
+
+_STATUS_READERS = {"gemm_tc": ("the tcgen05 matrix product (gemm_tc)", "gemm_tc_status"),
+                   "attn_tc": ("the tcgen05 prompt attention (attn_tc)", "attn_tc_status")}
+
+
+def check_status(readers=None) -> None:
+    """Raise ``KernelError`` if a bounded wait inside a tensor-memory kernel ran out in a launch the host has
+    since waited for: that kernel returned without writing (all of) its output.  The status word is put back to
+    0 (and the product's cut-tile counters are zeroed) so that later launches start clean.  Libraries that were
+    never loaded have launched nothing and are not looked at; reading costs no device call.
+
+    ``readers``: ``{name: (description, function(reset) -> code)}`` to look at instead (tests)."""
+    if readers is None:
+        from ._lib import loaded
+        from .attention import attn_tc_status
+        from .gemm_tc import gemm_tc_status
+        fns = {"gemm_tc_status": gemm_tc_status, "attn_tc_status": attn_tc_status}
+        readers = {}
+        for lib, (what, fname) in _STATUS_READERS.items():
+            if loaded(lib):
+                readers[lib] = (what, fns[fname])
+    for lib, (what, read) in readers.items():
+        code = read(False)
+        if code:
+            read(True)
+            raise KernelError(f"{what}: a bounded wait inside the kernel ran out (status {code}); "
+                              "its output is incomplete and the step's results must not be used")
 
 
 # Every block of a product that applies row factors fetches the partial sums; an output head has thousands of

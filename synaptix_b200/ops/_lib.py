@@ -91,6 +91,10 @@ def _library(lib: str):
     return h
 
 
+def loaded(lib: str) -> bool:
+    return lib in _LIBS
+
+
 def _set_pdl(handle) -> None:
     from .options import OPTIONS
     f = getattr(handle, "sx_set_pdl", None)

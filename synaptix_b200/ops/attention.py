@@ -171,8 +171,10 @@ def attn_prefill_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
     return out
 
 
-def attn_tc_status() -> int:
-    """0, or which bounded wait of the tcgen05 attention kernel ran out.  Synchronises the device."""
+def attn_tc_status(reset: bool = False) -> int:
+    """0, or which bounded wait of the tcgen05 attention kernel ran out (1 producer, 2-5 MMA issuer, 6-9
+    softmax).  No device call (the word lies in host memory the device writes to); it tells of launches the host
+    has already waited for.  ``reset`` puts it back to 0."""
     v = ctypes.c_int(0)
-    check(fn("attn_tc", "sx_attn_tc_status")(ctypes.byref(v)), "attn_tc_status", launches=0)
+    check(fn("attn_tc", "sx_attn_tc_status")(ctypes.byref(v), c_int(1 if reset else 0)), "attn_tc_status", launches=0)
     return int(v.value)

@@ -98,8 +98,14 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None,
     return out
 
 
-def gemm_tc_status() -> int:
-    """0, or which bounded wait of the kernel ran out (1 producer, 2 MMA issuer, 3 epilogue); synchronises."""
+def gemm_tc_status(reset: bool = False) -> int:
+    """0, or which bounded wait of the kernel ran out (1 producer, 2 and 4 MMA issuer, 3 epilogue, 5 the blocks
+    of a cut tile waiting for one another).  The word lies in host memory the device writes to, so this is no
+    device call; it tells of launches the host has already waited for.  ``reset`` puts it back to 0 and zeroes
+    the counters of cut tiles, which a wait that ran out may have left non-zero."""
     v = ctypes.c_int(0)
-    check(fn("gemm_tc", "sx_gemm_tc_status")(ctypes.byref(v)), "gemm_tc_status", launches=0)
+    check(fn("gemm_tc", "sx_gemm_tc_status")(ctypes.byref(v), c_int(1 if reset else 0)), "gemm_tc_status", launches=0)
+    if reset and v.value:
+        for t in _COUNTS.values():
+            t.zero_()
     return v.value

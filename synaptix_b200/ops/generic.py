@@ -141,9 +141,25 @@ def silu_mul(gu: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tens
     return out
 
 
+def decode_begin(token_ids: torch.Tensor, control: torch.Tensor, history: Optional[torch.Tensor] = None,
+                 hist_len: Optional[torch.Tensor] = None) -> None:
+    """On the device, before a decode step: ``token_ids[i] = control[i]`` where ``control[i] >= 0``
+    (and the last entry of row ``i``'s history becomes that token)."""
+    require_cuda(token_ids, control, history, hist_len)
+    check(fn("generic", "sx_decode_begin")(ptr(token_ids), ptr(control), ptr(history), ptr(hist_len),
+                                           c_int(0 if history is None else history.shape[1]),
+                                           c_int(token_ids.numel()), stream()), "decode_begin")
+
+
 def decode_advance(token_ids: torch.Tensor, sampled: torch.Tensor, positions: torch.Tensor,
-                   seq_past: torch.Tensor, seq_lens: torch.Tensor) -> None:
-    """On the device: ``token_ids = sampled`` and every position and length grows by one."""
-    require_cuda(token_ids, sampled, positions, seq_past, seq_lens)
+                   seq_past: torch.Tensor, seq_lens: torch.Tensor, rng_step: Optional[torch.Tensor] = None,
+                   advance_by: Optional[torch.Tensor] = None, history: Optional[torch.Tensor] = None,
+                   hist_len: Optional[torch.Tensor] = None) -> None:
+    """On the device, after a decode step: for every row with ``advance_by[i] != 0`` (all rows if absent)
+    ``token_ids = sampled``, position, lengths and ``rng_step`` grow by one, and the sampled token is
+    appended to the row's ``history [S, cap]`` (``hist_len`` grows)."""
+    require_cuda(token_ids, sampled, positions, seq_past, seq_lens, rng_step, advance_by, history, hist_len)
     check(fn("generic", "sx_decode_advance")(ptr(token_ids), ptr(sampled), ptr(positions), ptr(seq_past),
-                                             ptr(seq_lens), c_int(token_ids.numel()), stream()), "decode_advance")
+                                             ptr(seq_lens), ptr(rng_step), ptr(advance_by), ptr(history),
+                                             ptr(hist_len), c_int(0 if history is None else history.shape[1]),
+                                             c_int(token_ids.numel()), stream()), "decode_advance")

@@ -165,22 +165,33 @@ def block(h: torch.Tensor, W, layer: int, cfg, positions: torch.Tensor) -> torch
     return h + m
 
 
-def forward(cfg, W, tokens: Sequence[int]) -> torch.Tensor:
-    """Logits [T, vocab] at every position of one whole sequence: embedding -> blocks -> final
-    norm -> output head (tied to the embedding unless lm_head.weight is there and
-    tie_word_embeddings is not true) (crates/synaptix-models/llm/common/src/model.rs:757-772,
-    1057-1117)."""
+def hidden_states(cfg, W, tokens: Sequence[int]) -> torch.Tensor:
+    """The residual stream [T, width] after the last block of one whole sequence: embedding -> blocks
+    (crates/synaptix-models/llm/common/src/model.rs:1057-1066)."""
     with torch.no_grad():
         h = embedding(W["model.embed_tokens.weight"], tokens)
         positions = torch.arange(len(tokens))
         for layer in range(cfg["num_hidden_layers"]):
             h = block(h, W, layer, cfg, positions)
+        return h
+
+
+def logits_of(cfg, W, h: torch.Tensor) -> torch.Tensor:
+    """Final norm -> output head on the rows of ``h`` (the head is tied to the embedding unless
+    lm_head.weight is there and tie_word_embeddings is not true)
+    (crates/synaptix-models/llm/common/src/model.rs:757-772, 1068-1117)."""
+    with torch.no_grad():
         n = rms_norm(h, W["model.norm.weight"], cfg["rms_norm_eps"])
         tied = cfg.get("tie_word_embeddings")
         if tied is None:
             tied = "lm_head.weight" not in W
         head = W["model.embed_tokens.weight"] if tied else W["lm_head.weight"]
         return n @ head.T
+
+
+def forward(cfg, W, tokens: Sequence[int]) -> torch.Tensor:
+    """Logits [T, vocab] at every position of one whole sequence."""
+    return logits_of(cfg, W, hidden_states(cfg, W, tokens))
 
 
 # ----------------------------------------------------------------------------------------

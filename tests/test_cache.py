@@ -136,7 +136,11 @@ def test_cache_groups_requests_and_resets_state():
     assert v0.k.data_ptr() != v2.k.data_ptr() and v0.k.data_ptr() != v1.k.data_ptr()
     assert c.view(4) is None
     st = c.view(3)
-    assert st.shape == (3, 3, 4)
+    # a row per slot and one more that no sequence owns (rows that pad a captured step carry that slot number)
+    assert st.shape == (4, 3, 4) and c.spare_slot == 3
+    assert c.spare_slot not in [c.slots.open() for _ in range(3)]
+    for x in (0, 1, 2):
+        c.slots.close(x)
     s = c.open()
     st[s] += 5.0
     c.close(s)

@@ -16,6 +16,7 @@ class CounterEngine:
         self.slots = SequenceSlots(max_seqs, [PagePool(pages_for(max_tokens))])
         self.steps = []          # per step: list of (slot, n_tokens)
         self.opened, self.closed = [], []
+        self.sessions = []
 
     def open(self):
         s = self.slots.open()
@@ -33,6 +34,48 @@ class CounterEngine:
         self.steps.append([(e.slot, len(e.tokens)) for e in entries])
         # "logits": the next token for each wanted place
         return [e.tokens[w] + 1 for e in entries for w in e.want]
+
+    def check_kernels(self):
+        self.checks = getattr(self, "checks", 0) + 1
+
+    def start_decode(self, rows, sampling=None):
+        self.sessions.append(CounterSession(self, rows, sampling))
+        return self.sessions[-1]
+
+
+class CounterSession:
+    """The engine's decode session, faked: the token after ``t`` is ``t + 1``; a step's tokens are
+    known when it is launched but handed out only by ``collect``, in order."""
+
+    def __init__(self, engine, rows, sampling):
+        self.engine, self.sampling = engine, sampling
+        self.rows = list(rows)
+        self.next = [r.token for r in rows]
+        self.queue = []
+        self.most_in_flight = 0
+
+    @property
+    def in_flight(self):
+        return len(self.queue)
+
+    def launch(self):
+        eng = self.engine
+        eng.slots.reserve_many([r.slot for r in self.rows], [1] * len(self.rows))
+        for r in self.rows:
+            eng.slots.advance(r.slot, 1)
+        eng.steps.append([(r.slot, 1) for r in self.rows])
+        self.next = [t + 1 for t in self.next]
+        self.queue.append(list(self.next))
+        self.most_in_flight = max(self.most_in_flight, len(self.queue))
+
+    def collect(self):
+        return self.queue.pop(0)
+
+    def drop(self, rows):
+        assert not self.queue, "rows dropped while steps are in flight"
+        gone = set(rows)
+        self.rows = [r for i, r in enumerate(self.rows) if i not in gone]
+        self.next = [t for i, t in enumerate(self.next) if i not in gone]
 
 
 def counter_sample(logits, request_index, step, contexts):
@@ -66,7 +109,9 @@ def test_unequal_batch_shrinks_as_sequences_end():
     assert res[0].tokens == [11, 12] and res[1].tokens == [22, 23, 24, 25]
     assert res[2].tokens == list(range(33, 43)) and res[2].finish_reason == "length"
     assert eng.steps[0] == [(0, 1), (1, 2), (2, 3)]
-    assert [len(s) for s in eng.steps[1:]] == [3, 2, 2, 1, 1, 1, 1, 1, 1]
+    # a stop token is seen when the next step is already launched: that step still has the stopped row
+    assert [len(s) for s in eng.steps[1:]] == [3, 3, 2, 2, 1, 1, 1, 1, 1]
+    assert eng.sessions[0].most_in_flight == 2
     assert eng.slots.n_live == 0 and sorted(eng.closed) == [0, 1, 2]
     # slots are given back as soon as a sequence ends, not at the batch's end
     assert eng.closed[0] == 0
@@ -109,7 +154,7 @@ def test_zero_new_tokens_and_empty_prompt():
         run_generation(eng, counter_sample, [[]], GenerationOptions())
 
 
-def test_sampler_gets_request_index_step_and_context():
+def test_sampler_and_session_get_request_index_step_and_context():
     eng = CounterEngine()
     seen = []
 
@@ -117,11 +162,73 @@ def test_sampler_gets_request_index_step_and_context():
         seen.append((list(request_index), list(step), None if contexts is None else [list(c) for c in contexts]))
         return list(logits)
 
-    opts = GenerationOptions(max_new_tokens=3, sampling=SamplingParams(repetition_penalty=1.5), stop_token_ids=(7,))
-    run_generation(eng, spy, [[5], [8, 9]], opts)
-    assert seen[0] == ([0, 1], [0, 0], [[5], [8, 9]])
-    assert seen[1] == ([0, 1], [1, 1], [[5, 6], [8, 9, 10]])
-    assert seen[2] == ([1], [2], [[8, 9, 10, 11]])           # request 0 stopped at token 7
+    params = SamplingParams(repetition_penalty=1.5)
+    opts = GenerationOptions(max_new_tokens=3, sampling=params, stop_token_ids=(7,))
+    res, _ = run_generation(eng, spy, [[5], [6], [8, 9]], opts)
+    # the prompt step is sampled by the function; request 1 stops at once (token 7)
+    assert seen == [([0, 1, 2], [0, 0, 0], [[5], [6], [8, 9]])]
+    assert [r.tokens for r in res] == [[6, 7], [7], [10, 11, 12]]
+    # the session samples the rest: it is told each row's request, how many tokens it has, and its context
+    sess = eng.sessions[0]
+    assert sess.sampling == params
+    assert len(eng.sessions) == 1
+
+
+def test_session_rows_carry_what_the_sampler_needs():
+    eng = CounterEngine()
+    opts = GenerationOptions(max_new_tokens=2, sampling=SamplingParams(presence_penalty=0.5))
+    rows = []
+    real = eng.start_decode
+
+    def spy(r, sampling=None):
+        rows.extend(r)
+        return real(r, sampling)
+
+    eng.start_decode = spy
+    run_generation(eng, counter_sample, [[5], [8, 9]], opts)
+    assert [(r.slot, r.token, r.request, r.sampled_so_far, list(r.context)) for r in rows] == [
+        (0, 6, 0, 1, [5, 6]), (1, 10, 1, 1, [8, 9, 10])]
+    # without penalties no context is carried
+    eng, rows[:] = CounterEngine(), []
+    real = eng.start_decode
+    eng.start_decode = spy
+    run_generation(eng, counter_sample, [[5]], GenerationOptions(max_new_tokens=2))
+    assert rows[0].context is None
+
+
+def test_a_sequence_that_ends_by_length_runs_no_step_too_many():
+    eng = CounterEngine()
+    run_generation(eng, counter_sample, [[1], [2]], GenerationOptions(max_new_tokens=5))
+    assert len(eng.steps) == 1 + 4 and all(len(s) == 2 for s in eng.steps)
+    # lookahead 1: every step's tokens are read before the next is launched
+    eng = CounterEngine()
+    res, _ = run_generation(eng, counter_sample, [[1]], GenerationOptions(max_new_tokens=4, stop_token_ids=(3,), lookahead=1))
+    assert res[0].tokens == [2, 3] and len(eng.steps) == 2 and eng.sessions[0].most_in_flight == 1
+
+
+def test_the_step_after_a_stop_token_is_dropped():
+    eng = CounterEngine()
+    got = []
+    res, st = run_generation(eng, counter_sample, [[1], [10]], GenerationOptions(max_new_tokens=6, stop_token_ids=(4,)),
+                             on_token=lambda i, t: got.append((i, t)))
+    assert res[0].tokens == [2, 3, 4] and res[0].finish_reason == "stop"
+    assert res[1].tokens == [11, 12, 13, 14, 15, 16]
+    assert (0, 5) not in got                      # the extra step's token never reaches the caller
+    assert st.new_tokens == 9
+    assert eng.slots.n_live == 0 and eng.slots.pools[0].n_free == eng.slots.pools[0].n_pages
+
+
+def test_kernel_status_is_checked_and_stops_generation():
+    eng = CounterEngine()
+    run_generation(eng, counter_sample, [[1]], GenerationOptions(max_new_tokens=2))
+    assert eng.checks >= 1
+
+    class Broken(CounterEngine):
+        def check_kernels(self):
+            raise RuntimeError("a bounded wait inside the kernel ran out")
+
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        run_generation(Broken(), counter_sample, [[1]], GenerationOptions(max_new_tokens=2))
 
 
 def test_on_token_streams_in_order():

@@ -206,7 +206,9 @@ def test_embedding_and_output_head(tied):
 # a toy architecture defined here: a mixer with a running state of its own in layer 0, attention
 # in layer 1, and a schedule that runs layer 1 twice
 # ---------------------------------------------------------------------------------------------
-def make_toy():
+def make_toy(device_state: bool = False):
+    """``device_state``: the mixer updates its state on the device from ``ctx.seq_slots`` in single-token steps,
+    so those steps can be captured as CUDA graphs (registered under a name of its own)."""
     from synaptix_b200.cache import StateRequest
     from synaptix_b200.config import ModelConfig, register_architecture, take
     from synaptix_b200.models import DecoderModel, LayerRun
@@ -215,8 +217,8 @@ def make_toy():
 
     @dataclasses.dataclass(frozen=True)
     class ToyConfig(ModelConfig):
-        architectures: ClassVar[Tuple[str, ...]] = ("ToyRunningMeanLM",)
-        model_types: ClassVar[Tuple[str, ...]] = ("toy_running_mean",)
+        architectures: ClassVar[Tuple[str, ...]] = ("ToyRunningMeanGraphLM" if device_state else "ToyRunningMeanLM",)
+        model_types: ClassVar[Tuple[str, ...]] = ("toy_running_mean_graph" if device_state else "toy_running_mean",)
         vocab: int = 0
         width: int = 0
         eps: float = 0.0
@@ -228,7 +230,7 @@ def make_toy():
                        decay=take(d, "decay", float))
 
         def to_dict(self):
-            return {"architectures": ["ToyRunningMeanLM"], "vocab": self.vocab, "width": self.width,
+            return {"architectures": list(self.architectures), "vocab": self.vocab, "width": self.width,
                     "eps": self.eps, "decay": self.decay}
 
         def validate(self):
@@ -237,7 +239,7 @@ def make_toy():
     class DecayedSum(Mixer):
         """state <- decay * state + x_t ; out_t = W state.  The state [width] lives in the
         cache's per-sequence state region and goes on across steps."""
-        graph_safe = False
+        graph_safe = device_state
 
         def __init__(self, prefix, width, decay):
             self.width, self.decay = width, decay
@@ -250,6 +252,13 @@ def make_toy():
             return StateRequest((self.width,), torch.float32)
 
         def forward(self, x, ctx, state, write_cache=True):
+            if device_state and ctx.all_single:
+                # one token per sequence: the state rows of the step's slots, read and written on the device
+                # (rows that pad a captured step carry the cache's spare slot, which no sequence owns)
+                idx = ctx.seq_slots.long()
+                s = self.decay * state.index_select(0, idx) + x.float()
+                state.index_copy_(0, idx, s)
+                return self.proj.forward(s.to(x.dtype))
             out = torch.empty_like(x)
             cu, slots = ctx.host["cu_seqlens"], ctx.host["seq_slots"]
             for i, slot in enumerate(slots):
@@ -300,6 +309,45 @@ def toy_plain(cfg, W, tokens):
         h = h + P.causal_gqa_attention(q, k, v, 0.25, None).reshape(T, 32) @ W["l1.att.o_proj.weight"].T
         h = h + ff(P.rms_norm(h, W["l1.n2.weight"], cfg["eps"]), "l1.ff.")
     return P.rms_norm(h, W["norm.weight"], cfg["eps"]) @ W["head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_stateful_mixer_with_state_on_the_device_under_captured_steps(tmp_path, dtype):
+    """Three live sequences run in a captured step of four rows: the padding row must not touch any live
+    sequence's state (it carries the cache's spare slot).  Through the step function and through a decode session."""
+    from helpers import assert_close
+    from synaptix_b200.engine import DecodeRow, Engine, Entry
+    from synaptix_b200.models import load_model
+    from synaptix_b200.weights import write_model_folder
+    ToyConfig = make_toy(device_state=True)
+    cfg = ToyConfig(vocab=71, width=24, eps=1e-5, decay=0.9)
+    d = write_model_folder(cfg, str(tmp_path / "toyg"), 4, std_matrix=0.2, std_embedding=0.5, std_gain=0.1)
+    model = load_model(d, dtype=dtype)
+    assert model.all_graph_safe()
+    eng = Engine(model, max_tokens=1024, max_seqs=3)          # slots 0, 1, 2 are all in use
+    assert eng.use_graphs and eng.cache.spare_slot == 3
+    cfgd, W = P.load_folder(d)
+    g = torch.Generator().manual_seed(2)
+    n_dec = 40
+    seqs = [torch.randint(0, 71, (n + n_dec,), generator=g).tolist() for n in (30, 75, 9)]
+    refs = [toy_plain(cfgd, W, s) for s in seqs]
+    slots = [eng.open() for _ in seqs]
+    cut = [len(s) - n_dec for s in seqs]
+    got = eng.step([Entry(sl, s[:c], [c - 1]) for sl, s, c in zip(slots, seqs, cut)])
+    assert_close(got, torch.stack([r[c - 1] for r, c in zip(refs, cut)]), dtype, "prompts")
+    half = n_dec // 2
+    for j in range(half):                                     # captured steps of the step function (3 rows in 4)
+        got = eng.step([Entry(sl, [s[c + j]], [0]) for sl, s, c in zip(slots, seqs, cut)])
+        assert_close(got, torch.stack([r[c + j] for r, c in zip(refs, cut)]), dtype, f"step {j}")
+    assert any(c.graph is not None for c in eng._captured.values())
+    # the rest through a decode session, fed the sequences' own tokens; its choices are the plain model's
+    sess = eng.start_decode([DecodeRow(sl, s[c + half], i, 0) for i, (sl, s, c) in enumerate(zip(slots, seqs, cut))])
+    for j in range(half, n_dec):
+        sess.launch(tokens=[s[c + j] for s, c in zip(seqs, cut)])
+        got = sess.collect()
+        if dtype == "float32":
+            assert got == [int(r[c + j].argmax()) for r, c in zip(refs, cut)], f"session step {j}"
+    assert sess.cap.graph is not None and sess.cap.layout.S == 4
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
