@@ -295,13 +295,20 @@ def main():
         # words up from pinned memory and its tokens back down; greedy, so the tokens must be the timed run's
         llm.generate(main_prompts[:1], max_new_tokens=W + 1, eos_token_ids=[])
         llm.generate(main_prompts, max_new_tokens=W + 1, eos_token_ids=[], max_batch_size=a.batch)
-        outs = llm.generate(main_prompts, max_new_tokens=total_steps + 1, eos_token_ids=[], max_batch_size=a.batch)
-        st = llm.last_stats
-        same = outs == device_tokens
+        runs = []
+        same = True
+        for _ in range(3):                       # the whole generation three times; the median run is reported
+            outs = llm.generate(main_prompts, max_new_tokens=total_steps + 1, eos_token_ids=[], max_batch_size=a.batch)
+            runs.append(llm.last_stats)
+            same = same and outs == device_tokens
+        runs.sort(key=lambda st: st.decode_ms / max(st.decode_steps, 1))
+        st = runs[1]
         line["e2e"] = {"value": round(a.batch * st.decode_steps / (st.decode_ms / 1e3), 2), "unit": "tokens/s",
                        "h2d_bytes_per_step": st.decode_h2d_bytes // max(st.decode_steps, 1),
                        "d2h_bytes_per_step": st.decode_d2h_bytes // max(st.decode_steps, 1),
-                       "steps": st.decode_steps, "tokens_equal_device_timed_run": same}
+                       "steps": st.decode_steps, "runs": 3, "value_is": "median run",
+                       "best": round(a.batch * runs[0].decode_steps / (runs[0].decode_ms / 1e3), 2),
+                       "tokens_equal_device_timed_run": same}
         if not same:
             bad = next(i for i in range(a.batch) if outs[i] != device_tokens[i])
             k = next(k for k, (x, y) in enumerate(zip(outs[bad], device_tokens[bad])) if x != y)

@@ -298,6 +298,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(
 // merge of the splits: grid (S * nh), HD threads.  Maxima and sums of all splits are fetched at
 // once into shared memory and reduced by one warp; the weighted sum over splits then runs with
 // independent loads.
+#define AT_MAX_SPLITS 4096      // 32 KB of shared memory in the merge
+
 template <int HD>
 __global__ void __launch_bounds__(HD) attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                         bf16* __restrict__ out, int n_splits) {
@@ -473,6 +475,8 @@ static int attn_decode_any(const void* q, const void* k_pages, const void* v_pag
                            cudaStream_t stream) {
   if (S <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || n_splits < 1 || nkv > 65535 || S > 65535) return SX_ERR_SIZE;
+  // the merge keeps two floats a split in shared memory: refused before anything is launched
+  if (n_splits > AT_MAX_SPLITS) return SX_ERR_SIZE;
   if (n_splits > 1 && (!part_o || !part_ml)) return SX_ERR_SIZE;
   const float sl = scale * 1.4426950408889634f;
   const bf16* qb = (const bf16*)q;
@@ -528,26 +532,30 @@ extern "C" int sx_attn_decode_fused(const void* q, const void* k_pages, const vo
 // kernels and the launch path are the ones sx_attn_decode uses.
 // ---------------------------------------------------------------------------------------
 #include "no_alloc.h"
+#include <atomic>
 
 // In host code this name is only a handle for cudaGetSymbolAddress, never a pointer a kernel can use.
 static __device__ __align__(256) unsigned char sx_noalloc_scratch[SX_NOALLOC_SCRATCH_BYTES];
 
 #define SX_NOALLOC_MAX_DEVICES 64
 
-// the array's device address on the current device, looked up once per device
+// the array's device address on the current device, looked up once per device; host threads that make
+// their first call at the same time both look it up and store the same value
 static int noalloc_scratch_address(float** out_ptr) {
-  static float* addr[SX_NOALLOC_MAX_DEVICES] = {nullptr};
+  static std::atomic<float*> addr[SX_NOALLOC_MAX_DEVICES];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= SX_NOALLOC_MAX_DEVICES) return SX_ERR_SIZE;
-  if (!addr[dev]) {
+  float* a = addr[dev].load(std::memory_order_acquire);
+  if (!a) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, sx_noalloc_scratch);      // the copy of the array that lives on `dev`
     if (e != cudaSuccess) return (int)e;
-    addr[dev] = reinterpret_cast<float*>(p);
+    a = reinterpret_cast<float*>(p);
+    addr[dev].store(a, std::memory_order_release);
   }
-  *out_ptr = addr[dev];
+  *out_ptr = a;
   return 0;
 }
 
@@ -559,6 +567,7 @@ extern "C" int sx_attn_decode_noalloc(const void* q, const void* k_pages, const 
   if (S <= 0) return 0;
   if (nkv <= 0 || nh <= 0 || nh % nkv != 0 || nh / nkv > 16 || n_splits < 1 || nkv > 65535 || S > 65535) return SX_ERR_SIZE;
   if (hd != 128 && hd != 64 && hd != 32) return SX_ERR_SIZE;
+  if (n_splits > AT_MAX_SPLITS) return SX_ERR_SIZE;
   float* part_o = nullptr;
   float* part_ml = nullptr;
   if (n_splits > 1) {

@@ -16,9 +16,11 @@
 //     paged K/V, out [S, nh*hd] bfloat16, seq_lens and block_table int32 on the device).
 //   * S * nh * n_splits * (hd + 2) * 4 bytes must fit into SX_NOALLOC_SCRATCH_BYTES; a larger
 //     problem is refused with SX_ERR_NOALLOC_TOO_LARGE (10005) and nothing is launched.  With
-//     n_splits == 1 no scratch is used and any size that sx_attn_decode takes is taken.
+//     n_splits == 1 no scratch is used and any size that sx_attn_decode takes is taken.  More than
+//     4,096 splits are refused (10002) by both entry points, also before anything is launched.
 //   * The first call on a device looks up the array's device address (cudaGetSymbolAddress) with
 //     that device current and remembers it; make that first call outside any stream capture.
+//     Host threads may make their first calls at the same time.
 //     No call allocates or frees memory, on the device or through any library.
 //   * All calls share the one array and it keeps what the last call left.  Nothing in it has to
 //     start at zero: every slot a merge reads is written by the split kernel of the same call.

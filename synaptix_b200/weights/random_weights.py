@@ -10,6 +10,12 @@ drawn.
 ``RandomSource`` serves tensors straight to a model (on any device, which is
 how the benchmark avoids writing gigabytes to disk); ``write_model_folder``
 writes ``config.json`` and ``model.safetensors`` for a typed configuration.
+
+One seed gives one set of values PER DEVICE KIND: torch's CPU and CUDA generators
+draw different normal numbers from the same seed, so ``device="cuda:0"`` and
+``device="cpu"`` give two different (equally valid) random models.  A model folder is
+always written from the CPU generator, so the same seed writes the same bytes on any
+machine; whoever needs an engine and an oracle to agree loads both from one folder.
 """
 from __future__ import annotations
 

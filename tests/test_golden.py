@@ -14,18 +14,15 @@ import numpy as np
 import torch
 
 import plain_qwen3 as P
-from synaptix_b200.weights.safetensors_io import SafetensorsFile
+from safetensors import safe_open          # the package's reader: this anchor shares no code with the product
 
 TOL = 1e-5
 _PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_ops.safetensors")
 
 
 def _golden():
-    f = SafetensorsFile(_PATH)
-    try:
-        return {name: f.get(name).clone() for name in f.names()}
-    finally:
-        f.close()
+    with safe_open(_PATH, framework="pt") as f:
+        return {name: f.get_tensor(name).clone() for name in f.keys()}
 
 
 def _close(got, want):

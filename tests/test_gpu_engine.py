@@ -158,3 +158,30 @@ def test_step_errors_change_nothing(engines):
         eng.step([Entry(s + 1, [1], [0])])
     assert eng.length(s) == 0
     eng.close(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["W", "S", "G"])
+def test_prompt_in_portions_across_a_window_whose_pages_were_given_back(name, dtype):
+    """Layers with a window give pages back while the sequence runs; their table entries then read as page 0,
+    which no sequence owns.  A later portion of several tokens loads such an entry as part of a key block whose
+    other keys are visible: the keys of page 0 must count for nothing, whatever finite values lie there.  Every
+    other page starts as NaN, page 0 as large numbers."""
+    from synaptix_b200.engine import Engine, Entry
+    from synaptix_b200.models import load_model
+    eng = Engine(load_model(folder(name), dtype=dtype), max_tokens=1024)
+    poison_cache(eng)
+    g = torch.Generator().manual_seed(5)
+    for t in eng.cache._k + eng.cache._v:
+        t[:, 0] = (torch.randn(t[:, 0].shape, generator=g) * 1e4).to(t.dtype).to(t.device)
+    portions = [100, 2, 1, 90, 70, 3]
+    toks = random_tokens(vocab(name), sum(portions), 3100)
+    ref = oracle_logits(name, tuple(toks))
+    s = eng.open()
+    at = 0
+    for n in portions:
+        got = eng.step([Entry(s, toks[at:at + n], list(range(n)))])
+        assert_close(got, ref[at:at + n], dtype, f"{name} {dtype} portion of {n} at {at}")
+        at += n
+    assert any(-1 in eng.cache.slots.table(s, g_) for g_ in range(eng.cache.n_block_tables)), "no page was given back"
+    eng.close(s)

@@ -58,7 +58,7 @@ def test_greedy_generation_bfloat16_follows_the_oracle(name):
         if margin_ok(name, p, ref, 0.06 * scale):       # twice the bfloat16 logit tolerance
             assert o == ref
             checked += 1
-    assert len(outs) == 4
+    assert len(outs) == 4 and checked >= 1, "no prompt whose greedy choices are all clear: pick other seeds"
 
 
 def test_stop_tokens_end_sequences_early():
@@ -130,3 +130,31 @@ def test_command_line_run(tmp_path):
     out = json.loads(r.stdout.strip().splitlines()[-1])
     assert out["outputs"][0]["tokens"] == P.greedy_generate(cfg, W, prompt, 6)
     assert out["prompt_tokens"] == 9 and out["new_tokens"] == 6
+
+
+def test_penalties_in_a_batch_whose_sequences_end_at_different_times():
+    """Penalties look at each sequence's own context, which a decode session keeps on the device and writes
+    anew when a sequence leaves the batch.  Three prompts, one of which stops early."""
+    import synaptix_b200
+    cfg, W = oracle("B")
+    prompts = [random_tokens(389, n, 1400 + n) for n in (6, 20, 3)]
+    kw = dict(repetition_penalty=1.6, presence_penalty=0.4, frequency_penalty=0.3, repeat_last_n=12)
+
+    def plain(prompt, n, stop=()):
+        seq, out = list(prompt), []
+        while len(out) < n and not (out and out[-1] in stop):
+            v = P.processed_logits(oracle_logits("B", tuple(seq))[-1].numpy(), context=seq, repetition_penalty=1.6,
+                                   presence_penalty=0.4, frequency_penalty=0.3, repeat_last_n=12)
+            t = P.greedy(torch.from_numpy(v))
+            out.append(t)
+            seq.append(t)
+        return out
+
+    free = [plain(p, 14) for p in prompts]
+    stop = free[1][4]                         # request 1 ends with its fifth token (or earlier)
+    llm = synaptix_b200.LLM(folder("B"), compute_dtype="f32", max_tokens=512)
+    res = llm.generate(prompts, max_new_tokens=14, eos_token_ids=[stop], return_details=True, **kw)
+    for r, p in zip(res, prompts):
+        assert r.tokens == plain(p, 14, stop=(stop,))
+    assert res[1].finish_reason == "stop" and len(res[1].tokens) <= 5
+    assert any(len(r.tokens) == 14 for r in res)
