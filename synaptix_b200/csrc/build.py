@@ -41,6 +41,7 @@ LIBRARIES: Dict[str, tuple] = {
     "sampling": ("sampling.cu", []),
     "decode": ("decode.cu", []),
     "attention": ("attention.cu", []),
+    "attn_decode": ("attn_decode.cu", []),
     "attn_tc": ("attn_tc.cu", []),
     "gemm_tc": ("gemm_tc.cu", []),
 }

@@ -13,8 +13,8 @@ import torch
 
 from ..csrc.build import KernelsUnavailable
 from ._lib import KernelError, set_launch_counter
-from .attention import (TC_TILE_ROWS, attn_decode, attn_decode_prep, attn_prefill, attn_prefill_tc, fast_supported, pick_splits,
-                        query_tiles, tc_prefill_supported)
+from .attention import (TC_TILE_ROWS, attn_decode, attn_decode_prep, attn_decode_tma, attn_prefill, attn_prefill_tc,
+                        fast_supported, pick_splits, query_tiles, tc_prefill_supported, tma_decode_supported)
 from .decode import MAX_ROWS as SKINNY_MAX_ROWS, skinny_gemm, skinny_gemm_residual, skinny_gemm_scaled, skinny_supported
 from .gemm_tc import gemm_tc, tc_supported
 from .options import OPTIONS, KernelOptions, options, set_options
@@ -29,7 +29,8 @@ __all__ = ["OPTIONS", "KernelOptions", "options", "set_options", "KernelsUnavail
 
 
 _STATUS_READERS = {"gemm_tc": ("the tcgen05 matrix product (gemm_tc)", "gemm_tc_status"),
-                   "attn_tc": ("the tcgen05 prompt attention (attn_tc)", "attn_tc_status")}
+                   "attn_tc": ("the tcgen05 prompt attention (attn_tc)", "attn_tc_status"),
+                   "attn_decode": ("the TMA-fed decode attention (attn_decode)", "attn_decode_status")}
 
 
 def check_status(readers=None) -> None:
@@ -41,9 +42,9 @@ def check_status(readers=None) -> None:
     ``readers``: ``{name: (description, function(reset) -> code)}`` to look at instead (tests)."""
     if readers is None:
         from ._lib import loaded
-        from .attention import attn_tc_status
+        from .attention import attn_decode_status, attn_tc_status
         from .gemm_tc import gemm_tc_status
-        fns = {"gemm_tc_status": gemm_tc_status, "attn_tc_status": attn_tc_status}
+        fns = {"gemm_tc_status": gemm_tc_status, "attn_tc_status": attn_tc_status, "attn_decode_status": attn_decode_status}
         readers = {}
         for lib, (what, fname) in _STATUS_READERS.items():
             if loaded(lib):
@@ -164,6 +165,10 @@ def attention_from_projection(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages:
                               window: Optional[int], wq, wk, inv_freq, eps: float, write_cache: bool) -> torch.Tensor:
     """Single-token steps: head preparation and attention in one kernel (see ``attn_decode_prep``)."""
     max_pages = (ctx.max_len + 63) // 64
+    if OPTIONS.attn_tma and tma_decode_supported(qkv.dtype, nh, nkv, hd):
+        return attn_decode_tma(qkv, k_pages, v_pages, ctx.seq_lens, block_table, nh, nkv, hd, scale, window,
+                               pick_splits(ctx.n_seqs, nkv, max_pages, qkv.device), prep=True, wq=wq, wk=wk,
+                               inv_freq=inv_freq, eps=eps, write_cache=write_cache)
     return attn_decode_prep(qkv, k_pages, v_pages, ctx.seq_lens, block_table, nh, nkv, hd, scale, window,
                             pick_splits(ctx.n_seqs, nkv, max_pages, qkv.device), wq, wk, inv_freq, eps, write_cache)
 
@@ -175,6 +180,9 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx
     if fast_supported(q.dtype, nh, nkv, hd):
         if ctx.all_single:
             max_pages = (ctx.max_len + 63) // 64
+            if OPTIONS.attn_tma and tma_decode_supported(q.dtype, nh, nkv, hd):
+                return attn_decode_tma(q, k_pages, v_pages, ctx.seq_lens, block_table, nh, nkv, hd, scale, window,
+                                       pick_splits(ctx.n_seqs, nkv, max_pages, q.device))
             return attn_decode(q, k_pages, v_pages, ctx.seq_lens, block_table, nh, nkv, hd, scale, window,
                                pick_splits(ctx.n_seqs, nkv, max_pages, q.device))
         if ctx.host is not None:

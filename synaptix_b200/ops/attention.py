@@ -112,6 +112,59 @@ def attn_decode_prep(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Te
     return out
 
 
+TMA_HEAD_DIMS = (64, 128)
+
+
+def tma_decode_supported(dtype, nh: int, nkv: int, hd: int) -> bool:
+    """The TMA-fed decode attention takes bfloat16, head size 64 or 128, at most 16 query heads per kv head."""
+    return fast_supported(dtype, nh, nkv, hd) and hd in TMA_HEAD_DIMS
+
+
+def attn_decode_tma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, seq_lens: torch.Tensor,
+                    block_table: torch.Tensor, nh: int, nkv: int, hd: int, scale: float, window: Optional[int],
+                    n_splits: int, *, prep: bool = False, wq: Optional[torch.Tensor] = None,
+                    wk: Optional[torch.Tensor] = None, inv_freq: Optional[torch.Tensor] = None, eps: float = 0.0,
+                    write_cache: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Single-token attention with pages brought by TMA and a warp per page (``csrc/attn_decode.cu``).
+
+    ``q`` is ``[S, nh * hd]`` prepared queries against a cache that already holds the step's keys and values;
+    or, with ``prep``, the step's fused projection ``[S, (nh + 2 nkv) hd]``: the kernel then normalises (gains
+    ``wq``/``wk``, ``eps``) and rotates (``inv_freq``: the whole head, or ``None``) the query heads and the new
+    key itself and, with ``write_cache``, stores the new key and value.  ``n_splits`` blocks share a
+    sequence's pages; their partial results are added up by a second kernel."""
+    require_cuda(q, k_pages, v_pages, seq_lens, block_table, out, wq, wk, inv_freq)
+    S = q.shape[0]
+    if not tma_decode_supported(q.dtype, nh, nkv, hd) or k_pages.dtype != q.dtype:
+        raise KernelError("attn_decode_tma: bfloat16, head size 64 or 128 and at most 16 query heads per kv head")
+    if q.shape[1] != ((nh + 2 * nkv) * hd if prep else nh * hd):
+        raise KernelError("attn_decode_tma: q has the wrong width")
+    if inv_freq is not None and inv_freq.numel() != hd // 2:
+        raise KernelError("attn_decode_tma: the rotation must cover the whole head")
+    if out is None:
+        out = torch.empty((S, nh * hd), dtype=q.dtype, device=q.device)
+    n_splits = max(1, int(n_splits))
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty(S * nh * n_splits * hd, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(S * nh * n_splits * 2, dtype=torch.float32, device=q.device)
+    check(fn("attn_decode", "sx_attn_decode_tma")(
+        ptr(q), ptr(k_pages), ptr(v_pages), ptr(out), ptr(part_o), ptr(part_ml), c_int(1 if prep else 0), ptr(wq),
+        ptr(wk), ptr(inv_freq), c_float(eps), c_int(1 if write_cache else 0), c_longlong(k_pages.shape[0]),
+        ptr(seq_lens), ptr(block_table), c_int(block_table.shape[1]), c_int(S), c_int(nh), c_int(nkv), c_int(hd),
+        c_float(scale), c_int(0 if window is None else int(window)), c_int(n_splits), stream()), "attn_decode_tma",
+        launches=2 if n_splits > 1 else 1)
+    return out
+
+
+def attn_decode_status(reset: bool = False) -> int:
+    """0, or which bounded wait of the TMA-fed decode attention ran out (1 the producer's, 2 a compute warp's).
+    No device call; it tells of launches the host has already waited for.  ``reset`` puts it back to 0."""
+    v = ctypes.c_int(0)
+    check(fn("attn_decode", "sx_attn_decode_status")(ctypes.byref(v), c_int(1 if reset else 0)), "attn_decode_status",
+          launches=0)
+    return int(v.value)
+
+
 def query_tiles(cu_seqlens: Sequence[int], rows: int = 64):
     """Lists (sequence, first row) of the ``rows``-row query tiles of a packed batch."""
     seqs, q0s = [], []

@@ -9,6 +9,8 @@ switches in its runtime options (crates/synaptix-config/src/runtime.rs, ``AttnBa
 ``attn_tc``         prompt attention at head size 128 on tcgen05 (else ``mma.sync``)
 ``attn_prep``       single-token steps: the attention kernel norms, rotates and stores the new
                     heads itself (else a separate head-preparation launch)
+``attn_tma``        single-token steps at head size 64 / 128: pages by TMA, a warp per page (else the
+                    cp.async kernel, four warps a page)
 ``gemm_cut``        the persistent tcgen05 product cuts tiles over K where whole tiles would
                     leave SMs idle
 ``fused_residual``  3 to 16 rows: the o / down product adds itself into the residual stream and
@@ -25,6 +27,7 @@ import dataclasses
 class KernelOptions:
     attn_tc: bool = True
     attn_prep: bool = True
+    attn_tma: bool = True
     gemm_cut: bool = True
     fused_residual: bool = True
     pdl: bool = True

@@ -470,6 +470,27 @@ def test_attention_decode_kernel(nh, nkv, hd, window):
             assert err < 2e-2, f"n_splits={n_splits} fused={fused}: {err}"
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 128, None), (32, 8, 128, None), (6, 2, 32, None), (5, 1, 64, 24),
+                                               (8, 8, 64, None), (16, 1, 128, 100), (3, 3, 32, 65)])
+def test_attention_decode_kernel_with_pages_by_tma(nh, nkv, hd, window):
+    """Split counts from one (a block sees all pages, its warps take them in turn) to more splits than pages; the
+    cache's unused places hold NaN and the output starts as NaN, so that a value read from a place nobody wrote, or
+    a row nobody wrote, shows."""
+    from synaptix_b200.ops.attention import attn_decode_status, attn_decode_tma
+    if hd == 32:
+        pytest.skip("head size 32 stays on the cp.async kernel")
+    past, new = [0, 130, 1000, 63, 64, 255, 4, 700], [1] * 8
+    q, kp, vp, bt, pos, sot, scale, ref = fast_attention_case(nh, nkv, hd, window, past, new, 3)
+    lens = torch.tensor([p + 1 for p in past], dtype=torch.int32).cuda()
+    for n_splits in (1, 2, 3, 5, 16, 37):
+        out = torch.full((8, nh * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+        attn_decode_tma(q.view(8, nh * hd).cuda(), kp, vp, lens, bt, nh, nkv, hd, scale, window, n_splits, out=out)
+        err = (out.float().cpu().view(8, nh, hd) - ref).abs().max().item()
+        assert err < 2e-2, f"splits={n_splits}: {err}"
+    torch.cuda.synchronize()
+    assert attn_decode_status() == 0
+
+
 @pytest.mark.parametrize("nh,nkv,hd,window,rot,norm", [(4, 2, 128, None, True, True), (32, 8, 128, None, True, True),
                                                         (6, 2, 32, None, True, False), (5, 1, 64, 24, False, True),
                                                         (8, 8, 64, None, True, True), (16, 1, 128, 100, False, False),
@@ -531,51 +552,35 @@ def test_attention_decode_kernel_that_prepares_the_heads(nh, nkv, hd, window, ro
         # the cache now holds the tokens: a pass that writes nothing must see them there
         again = attn_decode_prep(qkv.cuda(), kp, vp, lens, bt, nh, nkv, hd, scale, window, n_splits, gq, gk, inv, eps, False)
         assert (again.float() - out.float()).abs().max().item() < 1e-2
+    # the same through the kernel that brings pages by TMA (head size 64 and 128)
+    if hd == 32:
+        return
+    from synaptix_b200.ops.attention import attn_decode_tma
+    for n_splits in (1, 3, 16):
+        kp.copy_(before_k); vp.copy_(before_v)
+        out = attn_decode_tma(qkv.cuda(), kp, vp, lens, bt, nh, nkv, hd, scale, window, n_splits, prep=True, wq=gq, wk=gk,
+                              inv_freq=inv, eps=eps, write_cache=True)
+        err = (out.float().cpu().view(S, nh, hd) - ref).abs().max().item()
+        assert err < 2e-2, f"tma splits={n_splits}: {err}"
+        kc, vc, bc = kp.float().cpu(), vp.float().cpu(), bt.cpu()
+        changed = torch.zeros(kc.shape[0], 64, dtype=torch.bool)
+        for i, p in enumerate(past):
+            page = int(bc[i, p // 64])
+            assert torch.allclose(kc[page, :, p % 64], k_new[i], atol=2e-2, rtol=2e-2)
+            assert torch.equal(vc[page, :, p % 64], v_new[i])
+            changed[page, p % 64] = True
+        keep = ~changed[:, None, :, None].expand_as(kc)
+        assert same(torch.where(keep, kp.float().cpu(), torch.zeros(())), torch.where(keep, before_k.float().cpu(), torch.zeros(())))
+        assert same(torch.where(keep, vp.float().cpu(), torch.zeros(())), torch.where(keep, before_v.float().cpu(), torch.zeros(())))
+        again = attn_decode_tma(qkv.cuda(), kp, vp, lens, bt, nh, nkv, hd, scale, window, n_splits, prep=True, wq=gq, wk=gk,
+                                inv_freq=inv, eps=eps, write_cache=False)
+        assert (again.float() - out.float()).abs().max().item() < 1e-2
 
 
-@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 128, None), (6, 2, 32, None), (5, 1, 64, 24), (8, 8, 64, None),
-                                               (2, 1, 128, 100), (32, 8, 128, None)])
-def test_attention_prefill_kernel(nh, nkv, hd, window):
-    from synaptix_b200.ops.attention import attn_prefill, query_tiles
-    past, new = [0, 130, 200, 64, 0], [67, 1, 3, 130, 64]
-    q, kp, vp, bt, pos, sot, scale, ref = fast_attention_case(nh, nkv, hd, window, past, new, 4)
-    cu = [0]
-    for n in new:
-        cu.append(cu[-1] + n)
-    ts, t0 = query_tiles(cu)
-    dev = lambda x: torch.tensor(x, dtype=torch.int32).cuda()
-    T = sum(new)
-    out = attn_prefill(q.view(T, nh * hd).cuda(), kp, vp, dev(ts), dev(t0), dev(cu), dev(past),
-                       dev([p + n for p, n in zip(past, new)]), bt, nh, nkv, hd, scale, window)
-    err = (out.float().cpu().view(T, nh, hd) - ref).abs().max().item()
-    assert err < 2e-2, err
-
-
-@pytest.mark.parametrize("nh,nkv,window", [(4, 2, None), (2, 1, 100), (32, 8, None), (6, 6, 200), (5, 1, 129)])
-def test_attention_prefill_tcgen05_kernel(nh, nkv, window):
-    """Prompts of unequal lengths, with and without keys held before the step, tiles that end inside a page,
-    sequences longer than one 128-key block; pages are scrambled and unwritten places hold NaN."""
-    from synaptix_b200.ops.attention import attn_prefill_tc, attn_tc_status, query_tiles
-    hd = 128
-    past, new = [0, 130, 200, 64, 0, 700, 5], [67, 1, 3, 130, 64, 300, 129]
-    q, kp, vp, bt, pos, sot, scale, ref = fast_attention_case(nh, nkv, hd, window, past, new, 4)
-    cu = [0]
-    for n in new:
-        cu.append(cu[-1] + n)
-    ts, t0 = query_tiles(cu, 128)
-    dev = lambda x: torch.tensor(x, dtype=torch.int32).cuda()
-    T = sum(new)
-    out = attn_prefill_tc(q.view(T, nh * hd).cuda(), kp, vp, dev(ts), dev(t0), dev(cu), dev(past),
-                          dev([p + n for p, n in zip(past, new)]), bt, nh, nkv, hd, scale, window)
-    assert attn_tc_status() == 0
-    got = out.float().cpu().view(T, nh, hd)
-    assert torch.isfinite(got).all()
-    err = (got - ref).abs().max().item()
-    assert err < 2e-2, err
 
 
 def test_fast_attention_finds_one_far_key_and_respects_the_window_edge():
-    from synaptix_b200.ops.attention import attn_decode, attn_prefill, query_tiles
+    from synaptix_b200.ops.attention import attn_decode, attn_decode_tma, attn_prefill, query_tiles
     nh, nkv, hd = 4, 2, 64
     dt = torch.bfloat16
     dev = lambda x: torch.tensor(x, dtype=torch.int32).cuda()
@@ -597,6 +602,9 @@ def test_fast_attention_finds_one_far_key_and_respects_the_window_edge():
         for n_splits in (1, 3):
             out = attn_decode(qd, kp, vp, dev([L]), bt, nh, nkv, hd, 1.0, W, n_splits).float().cpu().view(nh, hd)
             assert torch.allclose(out, want, atol=2e-2), f"decode L={L} far={far} W={W} splits={n_splits}"
+        for n_splits in (1, 3):
+            out = attn_decode_tma(qd, kp, vp, dev([L]), bt, nh, nkv, hd, 1.0, W, n_splits).float().cpu().view(nh, hd)
+            assert torch.allclose(out, want, atol=2e-2), f"decode, pages by TMA, L={L} far={far} W={W} splits={n_splits}"
         out = attn_prefill(qd, kp, vp, dev([0]), dev([0]), dev([0, 1]), dev([L - 1]), dev([L]), bt, nh, nkv, hd, 1.0, W)
         assert torch.allclose(out.float().cpu().view(nh, hd), want, atol=2e-2), f"prefill L={L} far={far} W={W}"
 
