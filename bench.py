@@ -174,7 +174,12 @@ def main():
 
     batches = [a.batch] if a.no_points else sorted({a.batch, 1, 64})
     K, W = a.steps, a.warmup
-    start_len = a.context - (5 * K + W) - 1      # the timed steps (5 regions of K) end at the context length
+    # Every sequence decodes at least 255 tokens, the timed steps (5 regions of K) being the last ones, which end at
+    # the context length.  A generation that short would be mostly the GPU coming back from the prompt step: the
+    # first 15 to 20 single-token steps after a long prompt step run about a quarter slower (measured; the SM clock
+    # is still low from the power cap of the prompt step's products), and the end-to-end figure below has them all.
+    total_steps = max(5 * K + W, 255)
+    start_len = a.context - total_steps - 1
     if start_len < 1:
         raise SystemExit("--context is too short for 5 x --steps + --warmup")
     llm = LLM.from_model(model, max_tokens=max(batches) * (a.context + 64) if a.phase == "all" else 4096,
@@ -210,7 +215,7 @@ def main():
         return 0
 
     REGIONS = 5                                   # the K-step region is timed this many times, back to back
-    total_steps = W + REGIONS * K
+    settle = total_steps - REGIONS * K            # untimed steps before them (at least the W warm-up steps)
 
     def prompts_for(B):
         return [torch.randint(0, cfg.vocab_size, (start_len,), generator=g).tolist() for _ in range(B)]
@@ -234,7 +239,7 @@ def main():
         prompts = prompts_for(B)
         slots, first = fill(prompts, whole=(B == a.batch))
         session = engine.start_decode([DecodeRow(s, t, i, 1) for i, (s, t) in enumerate(zip(slots, first))])
-        for _ in range(W):
+        for _ in range(settle):
             session.launch()
         torch.cuda.synchronize()
         events = [torch.cuda.Event(enable_timing=True) for _ in range(REGIONS + 1)]
