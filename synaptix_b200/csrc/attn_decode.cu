@@ -18,8 +18,12 @@
 //   * the output is rescaled only when a row's maximum moved.
 // The G = nh / nkv query heads that share the kv head are the rows of one fragment, so every cache byte
 // is read once for all of them.  grid (splits, kv heads, sequences): a block takes a contiguous share of
-// the sequence's visible pages, leaves un-normalised sums with maximum and denominator in scratch, and a
-// second kernel (attn_merge.cuh) adds the splits up; with one split the block writes the result itself.
+// the sequence's visible pages.  With one split the block writes the result itself.  With 2, 4, 8 or 16 splits
+// the blocks of a (sequence, kv head) form a thread-block cluster (CLUSTER): each leaves its un-normalised sums
+// with maximum and denominator in its own shared memory, and after a barrier over the cluster every block
+// merges a share of the outputs, reading the others' shared memory (distributed shared memory): no scratch in
+// global memory, no second kernel, one kernel boundary less in a decode step.  Any other number of splits goes
+// through scratch and a second kernel (attn_merge.cuh) that adds the splits up.
 //
 // With PREP the kernel takes the step's fused q/k/v projection as it left the product and does what head
 // preparation does on the way: per-head RMSNorm of q and k, rotate-half rotation by the token's position,
@@ -216,7 +220,7 @@ __device__ __forceinline__ void ad_attend_page(const uint32_t (&qf)[HD / 16][4],
   }
 }
 
-template <int HD, bool PREP>
+template <int HD, bool PREP, bool CLUSTER>
 __global__ void __launch_bounds__(AD_THREADS, 2) attn_decode_tma_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     const bf16* __restrict__ q, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, bf16* __restrict__ out,
@@ -280,6 +284,10 @@ __global__ void __launch_bounds__(AD_THREADS, 2) attn_decode_tma_kernel(
           ad_tma_4d(dst + L::TILE + h * AD_CHUNK, &map_v, h * 64, 0, kvh, page, full(st));
         }
       }
+    }
+    if (CLUSTER) {                  // every thread of the cluster takes part in its two barriers
+      cluster_sync_all();
+      cluster_sync_all();
     }
     return;
   }
@@ -433,6 +441,9 @@ __global__ void __launch_bounds__(AD_THREADS, 2) attn_decode_tma_kernel(
     wml[(warp * 16 + g + 8) * 2 + 1] = l[1];
   }
   asm volatile("bar.sync 1, %0;\n" ::"n"(AD_COMPUTE_WARPS * 32) : "memory");
+  // this block's result: O [G][HD], then (M, L) [G][2], behind the warps' results in the ring
+  float* res = wml + AD_COMPUTE_WARPS * 16 * 2;
+  float* res_ml = res + 16 * HD;
   for (int idx = threadIdx.x; idx < G * HD; idx += AD_COMPUTE_WARPS * 32) {
     const int r = idx / HD, d = idx % HD;
     float M = -INFINITY;
@@ -449,11 +460,34 @@ __global__ void __launch_bounds__(AD_THREADS, 2) attn_decode_tma_kernel(
     const int head = kvh * G + r;
     if (n_splits == 1) {
       out[((size_t)seq * nh + head) * HD + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
+    } else if (CLUSTER) {
+      res[r * HD + d] = O;
+      if (d == 0) { res_ml[r * 2] = M; res_ml[r * 2 + 1] = Lsum; }
     } else {
       const size_t pi = ((size_t)seq * nh + head) * n_splits + split;
       part_o[pi * HD + d] = O;
       if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = Lsum; }
     }
+  }
+  if (CLUSTER && n_splits > 1) {
+    // The cluster is the n_splits blocks of this (sequence, kv head); its rank is the split.  After the barrier
+    // every block's result lies in its shared memory; block k merges outputs k, k + n_splits, ... of the G * HD
+    // (head, value) pairs, in rank order, reading the others' results from afar.
+    cluster_sync_all();
+    for (int idx = split + n_splits * (int)threadIdx.x; idx < G * HD; idx += n_splits * AD_COMPUTE_WARPS * 32) {
+      const int r = idx / HD, d = idx % HD;
+      float M = -INFINITY;
+      for (int k = 0; k < n_splits; ++k) M = fmaxf(M, cluster_load_f32(res_ml + r * 2, k));
+      float Lsum = 0.f, O = 0.f;
+      for (int k = 0; k < n_splits; ++k) {
+        const float mk = cluster_load_f32(res_ml + r * 2, k);
+        const float f = (mk == -INFINITY) ? 0.f : exp2f(mk - M);
+        Lsum += cluster_load_f32(res_ml + r * 2 + 1, k) * f;
+        if (f != 0.f) O += cluster_load_f32(res + r * HD + d, k) * f;
+      }
+      out[((size_t)seq * nh + kvh * G + r) * HD + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
+    }
+    cluster_sync_all();             // nobody leaves while its shared memory may still be read
   }
 }
 
@@ -501,8 +535,17 @@ static int ad_launch(const CUtensorMap& mk, const CUtensorMap& mv, const bf16* q
                      int window, int n_splits, const AdPrep& prep, int* status, cudaStream_t stream) {
   using L = AdLayout<HD>;
   static_assert(AD_STAGES == AD_COMPUTE_WARPS, "a stage has one consumer");
-  static_assert(AD_STAGES * L::STAGE >= AD_COMPUTE_WARPS * (16 * HD + 16 * 2) * (int)sizeof(float), "the ring holds the warps' results");
-  auto kern = attn_decode_tma_kernel<HD, PREP>;
+  static_assert(AD_STAGES * L::STAGE >= (AD_COMPUTE_WARPS + 1) * (16 * HD + 16 * 2) * (int)sizeof(float),
+                "the ring holds the warps' results and the block's");
+  // 2, 4, 8 or 16 splits: the splits of a (sequence, kv head) are a cluster and merge among themselves
+  if (part_o == nullptr && n_splits > 1) {
+    auto kern = attn_decode_tma_kernel<HD, PREP, true>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    return sx_launch_cluster(kern, dim3(n_splits, nkv, S), dim3(AD_THREADS), (size_t)L::SMEM, stream, n_splits, mk, mv, q, k,
+                             v, out, part_o, part_ml, seq_lens, bt, maxp, nh, nkv, scale_log2, window, n_splits, prep, status);
+  }
+  auto kern = attn_decode_tma_kernel<HD, PREP, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM);
   if (e != cudaSuccess) return (int)e;
   int rc = sx_launch(kern, dim3(n_splits, nkv, S), dim3(AD_THREADS), (size_t)L::SMEM, stream, mk, mv, q, k, v, out, part_o,
@@ -517,7 +560,8 @@ static int ad_launch(const CUtensorMap& mk, const CUtensorMap& mv, const bf16* q
 // rotate-half rotation of the whole head by seq_lens[s] - 1 (inv_freq [hd / 2], or null), and (write != 0) the new
 // key and value into the cache happen inside the kernel.  k_pages / v_pages [n_pages, nkv, 64, hd]; out [S, nh * hd];
 // part_o f32 [S * nh * n_splits * hd] and part_ml f32 [S * nh * n_splits * 2] are scratch (unused with one split).
-// Head size 64 or 128.
+// Without scratch (both null) and 2, 4, 8 or 16 splits, the splits of a (sequence, kv head) run as a thread-block
+// cluster and merge through one another's shared memory; other split counts need the scratch.  Head size 64 or 128.
 extern "C" int sx_attn_decode_tma(const void* q, void* k_pages, void* v_pages, void* out, float* part_o, float* part_ml,
                                   int prep_on, const float* wq, const float* wk, const float* inv_freq, float eps,
                                   int write, long long n_pages, const int* seq_lens, const int* block_table, int maxp,
@@ -527,7 +571,8 @@ extern "C" int sx_attn_decode_tma(const void* q, void* k_pages, void* v_pages, v
   if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || n_splits < 1 || nkv > 65535 || S > 65535) return SX_ERR_SIZE;
   if (hd != 64 && hd != 128) return SX_ERR_SIZE;
   if (n_splits > AT_MAX_SPLITS) return SX_ERR_SIZE;
-  if (n_splits > 1 && (!part_o || !part_ml)) return SX_ERR_SIZE;
+  const bool clustered = n_splits == 2 || n_splits == 4 || n_splits == 8 || n_splits == 16;
+  if (n_splits > 1 && (!part_o || !part_ml) && !(clustered && !part_o && !part_ml)) return SX_ERR_SIZE;
   if (n_pages <= 0 || n_pages > 0x7fffffffLL) return SX_ERR_SIZE;
   if (((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15)) return SX_ERR_ALIGN;
   int* status = ad_status_word();

@@ -122,4 +122,49 @@ static inline int sx_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_
   return (int)cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
+// The same launch for a kernel whose blocks form clusters of `cluster` consecutive blocks along x
+// (thread-block clusters: the blocks of a cluster run at the same time and may read one another's
+// shared memory).  More than 8 blocks a cluster is a size the kernel has to be opted into.
+template <typename... KArgs, typename... Args>
+static inline int sx_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    int cluster, Args... args) {
+  if (cluster > 8) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return (int)e;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = sx_pdl_enabled() ? 2 : 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+// rank of this block in its cluster; a barrier over all threads of the cluster (release / acquire); a load from
+// the shared memory of the cluster's block `rank` at the place that `local` names in this block's own
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ float cluster_load_f32(const float* local, uint32_t rank) {
+  uint32_t a = (uint32_t)__cvta_generic_to_shared(local), r;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(r) : "memory");
+  return v;
+}
+
 #define SX_PAGE 64

@@ -113,6 +113,17 @@ def attn_decode_prep(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Te
 
 
 TMA_HEAD_DIMS = (64, 128)
+CLUSTER_SPLITS = (2, 4, 8, 16)          # split counts whose blocks can merge among themselves as a thread-block cluster
+CLUSTER_SPLITS_USED = (2, 4)            # ... and those for which that measured faster than scratch and a second kernel
+
+
+def use_cluster(n_splits: int) -> bool:
+    """Should the splits of a (sequence, kv head) merge among themselves as a thread-block cluster?  Measured at
+    32 query heads over 8 kv heads of 128, context 4,096, us a layer: 8 sequences, 4 splits 27.3 against 29.0 with
+    the second kernel; but 1 sequence, 8 or 16 blocks a cluster 11.3 / 11.9 against 8.9 for 32 splits and a
+    second kernel (a large cluster waits for as many free SMs of one GPC at once, and fewer splits mean more
+    pages one after another in a block): only small clusters are used."""
+    return n_splits in CLUSTER_SPLITS_USED
 
 
 def tma_decode_supported(dtype, nh: int, nkv: int, hd: int) -> bool:
@@ -124,14 +135,17 @@ def attn_decode_tma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
                     block_table: torch.Tensor, nh: int, nkv: int, hd: int, scale: float, window: Optional[int],
                     n_splits: int, *, prep: bool = False, wq: Optional[torch.Tensor] = None,
                     wk: Optional[torch.Tensor] = None, inv_freq: Optional[torch.Tensor] = None, eps: float = 0.0,
-                    write_cache: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    write_cache: bool = True, out: Optional[torch.Tensor] = None,
+                    cluster: Optional[bool] = None) -> torch.Tensor:
     """Single-token attention with pages brought by TMA and a warp per page (``csrc/attn_decode.cu``).
 
     ``q`` is ``[S, nh * hd]`` prepared queries against a cache that already holds the step's keys and values;
     or, with ``prep``, the step's fused projection ``[S, (nh + 2 nkv) hd]``: the kernel then normalises (gains
     ``wq``/``wk``, ``eps``) and rotates (``inv_freq``: the whole head, or ``None``) the query heads and the new
     key itself and, with ``write_cache``, stores the new key and value.  ``n_splits`` blocks share a
-    sequence's pages; their partial results are added up by a second kernel."""
+    sequence's pages; with 2, 4, 8 or 16 of them and ``cluster`` they merge their partial results among
+    themselves as a thread-block cluster, otherwise through scratch memory and a second kernel.  ``cluster=None``
+    decides by ``use_cluster``."""
     require_cuda(q, k_pages, v_pages, seq_lens, block_table, out, wq, wk, inv_freq)
     S = q.shape[0]
     if not tma_decode_supported(q.dtype, nh, nkv, hd) or k_pages.dtype != q.dtype:
@@ -144,7 +158,8 @@ def attn_decode_tma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         out = torch.empty((S, nh * hd), dtype=q.dtype, device=q.device)
     n_splits = max(1, int(n_splits))
     part_o = part_ml = None
-    if n_splits > 1:
+    clustered = (use_cluster(n_splits) if cluster is None else bool(cluster)) and n_splits in CLUSTER_SPLITS
+    if n_splits > 1 and not clustered:
         part_o = torch.empty(S * nh * n_splits * hd, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(S * nh * n_splits * 2, dtype=torch.float32, device=q.device)
     check(fn("attn_decode", "sx_attn_decode_tma")(
@@ -152,7 +167,7 @@ def attn_decode_tma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         ptr(wk), ptr(inv_freq), c_float(eps), c_int(1 if write_cache else 0), c_longlong(k_pages.shape[0]),
         ptr(seq_lens), ptr(block_table), c_int(block_table.shape[1]), c_int(S), c_int(nh), c_int(nkv), c_int(hd),
         c_float(scale), c_int(0 if window is None else int(window)), c_int(n_splits), stream()), "attn_decode_tma",
-        launches=2 if n_splits > 1 else 1)
+        launches=2 if n_splits > 1 and not clustered else 1)
     return out
 
 

@@ -482,11 +482,14 @@ def test_attention_decode_kernel_with_pages_by_tma(nh, nkv, hd, window):
     past, new = [0, 130, 1000, 63, 64, 255, 4, 700], [1] * 8
     q, kp, vp, bt, pos, sot, scale, ref = fast_attention_case(nh, nkv, hd, window, past, new, 3)
     lens = torch.tensor([p + 1 for p in past], dtype=torch.int32).cuda()
-    for n_splits in (1, 2, 3, 5, 16, 37):
+    # 2, 4, 8, 16 splits merge among themselves as a cluster; the others, and those with cluster=False, through scratch
+    for n_splits, cluster in [(1, None), (2, True), (3, None), (4, True), (5, None), (8, True), (16, True), (37, None),
+                              (4, False), (16, False)]:
         out = torch.full((8, nh * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
-        attn_decode_tma(q.view(8, nh * hd).cuda(), kp, vp, lens, bt, nh, nkv, hd, scale, window, n_splits, out=out)
+        attn_decode_tma(q.view(8, nh * hd).cuda(), kp, vp, lens, bt, nh, nkv, hd, scale, window, n_splits, out=out,
+                        cluster=cluster)
         err = (out.float().cpu().view(8, nh, hd) - ref).abs().max().item()
-        assert err < 2e-2, f"splits={n_splits}: {err}"
+        assert err < 2e-2, f"splits={n_splits} cluster={cluster}: {err}"
     torch.cuda.synchronize()
     assert attn_decode_status() == 0
 
@@ -556,7 +559,7 @@ def test_attention_decode_kernel_that_prepares_the_heads(nh, nkv, hd, window, ro
     if hd == 32:
         return
     from synaptix_b200.ops.attention import attn_decode_tma
-    for n_splits in (1, 3, 16):
+    for n_splits in (1, 3, 4, 16):                         # 4: the splits merge as a cluster
         kp.copy_(before_k); vp.copy_(before_v)
         out = attn_decode_tma(qkv.cuda(), kp, vp, lens, bt, nh, nkv, hd, scale, window, n_splits, prep=True, wq=gq, wk=gk,
                               inv_freq=inv, eps=eps, write_cache=True)
