@@ -29,25 +29,25 @@ class LLM:
 
     def __init__(self, model_dir: str, compute_dtype="bf16", device: str = "cuda:0",
                  max_tokens: Optional[int] = None, max_seq: Optional[int] = None, max_batch: int = 8,
-                 graph: bool = True, source=None):
+                 graph: bool = True, source=None, nvtx: bool = False):
         self._setup(load_model(model_dir, dtype=compute_dtype, device=device, source=source),
-                    max_tokens, max_seq, max_batch, graph)
+                    max_tokens, max_seq, max_batch, graph, nvtx)
 
     @classmethod
     def from_model(cls, model, max_tokens: Optional[int] = None, max_seq: Optional[int] = None,
-                   max_batch: int = 8, graph: bool = True) -> "LLM":
+                   max_batch: int = 8, graph: bool = True, nvtx: bool = False) -> "LLM":
         """An ``LLM`` around a model that already has its weights bound (``DecoderModel.load``)."""
         self = cls.__new__(cls)
-        self._setup(model, max_tokens, max_seq, max_batch, graph)
+        self._setup(model, max_tokens, max_seq, max_batch, graph, nvtx)
         return self
 
-    def _setup(self, model, max_tokens, max_seq, max_batch, graph) -> None:
+    def _setup(self, model, max_tokens, max_seq, max_batch, graph, nvtx=False) -> None:
         self.model = model
         cfg = self.model.config
         if max_tokens is None:
             per_seq = max_seq or getattr(cfg, "max_position_embeddings", None) or 4096
             max_tokens = max_batch * per_seq
-        self.engine = Engine(self.model, max_tokens=max_tokens, use_graphs=graph)
+        self.engine = Engine(self.model, max_tokens=max_tokens, use_graphs=graph, nvtx=nvtx)
         self.last_stats: Optional[GenerationStats] = None
 
     @property

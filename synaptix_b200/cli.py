@@ -60,6 +60,7 @@ def build_parser() -> argparse.ArgumentParser:
                      help="cache capacity per sequence; default prompt + max-tokens")
     run.add_argument("--compute-dtype", default="bf16", help="bf16 or f32 (f32: everything in true 32-bit)")
     run.add_argument("--no-graph", action="store_true", help="do not replay decode steps as CUDA graphs")
+    run.add_argument("--nvtx", action="store_true", help="name every step for a profiler's timeline (NVTX ranges)")
     run.add_argument("--warmup", action="store_true", help="run one prompt step and one token before timing")
     run.add_argument("--stop-ids", default=None, help="stop token ids; default: the model's eos_token_id")
     run.add_argument("--json", action="store_true", help="print one JSON object instead of text")
@@ -104,7 +105,7 @@ def cmd_run(a) -> int:
     max_tokens = sum(((min(per_seq, len(p) + a.max_tokens) + 63) // 64) * 64 for p in prompts)
     t0 = time.perf_counter()
     llm = LLM(a.model, compute_dtype=_dtype_arg(a.compute_dtype), device=_device(a.device),
-              max_tokens=max_tokens, graph=not a.no_graph)
+              max_tokens=max_tokens, graph=not a.no_graph, nvtx=a.nvtx)
     load_s = time.perf_counter() - t0
     kw = dict(max_new_tokens=a.max_tokens, temperature=a.temperature, top_k=a.top_k, top_p=a.top_p,
               min_p=a.min_p, repetition_penalty=a.repetition_penalty, repeat_last_n=a.repeat_last_n,

@@ -240,7 +240,11 @@ class DecodeRow(NamedTuple):
 class Engine:
     """A loaded model with its cache: slots are opened, stepped and closed here."""
 
-    def __init__(self, model, *, max_tokens: int, max_seqs: Optional[int] = None, use_graphs: bool = True):
+    def __init__(self, model, *, max_tokens: int, max_seqs: Optional[int] = None, use_graphs: bool = True,
+                 nvtx: bool = False):
+        """``nvtx``: name every step for a profiler's timeline (NVTX ranges ``prompt step`` / ``decode step`` with
+        the number of sequences and tokens), as the reference's telemetry does
+        (crates/synaptix-runtime/src/telemetry/nvtx.rs); off by default, it costs two calls a step."""
         if model.runtime is None:
             raise ValueError("the model has no weights bound")
         rt = model.runtime
@@ -254,6 +258,7 @@ class Engine:
                            dtype=rt.dtype, device=rt.device)
         self._staging = _Staging(rt.device)
         self.use_graphs = bool(use_graphs) and model.all_graph_safe()
+        self.nvtx = bool(nvtx)
         self._captured: Dict[Tuple[int, int], _Captured] = {}
         self._captured_decode: Dict[tuple, _CapturedDecode] = {}
         self.kernel_launches = 0         # kernels of this package launched (graph replays counted by content)
@@ -281,6 +286,14 @@ class Engine:
 
     def length(self, slot: int) -> int:
         return self.cache.slots.length(slot)
+
+    @contextlib.contextmanager
+    def _range(self, name: str):
+        torch.cuda.nvtx.range_push(name)
+        try:
+            yield
+        finally:
+            torch.cuda.nvtx.range_pop()
 
     def check_kernels(self) -> None:
         """Raise ``KernelError`` if a bounded wait inside one of the tensor-memory kernels ran out
@@ -383,6 +396,12 @@ class Engine:
         entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
         past, new = self._check(entries)
         single = all(n == 1 and tuple(e.want) == (0,) for n, e in zip(new, entries))
+        if not self.nvtx:
+            return self._run_step(entries, past, new, single, keep)
+        with self._range(f"{'decode' if max(new) == 1 else 'prompt'} step: {len(entries)} sequences, {sum(new)} tokens"):
+            return self._run_step(entries, past, new, single, keep)
+
+    def _run_step(self, entries, past, new, single, keep) -> torch.Tensor:
         if single and self.use_graphs:
             S = _bucket_rows(len(entries))
             maxp = _bucket_pages(max(pages_for(p + 1) for p in past))
@@ -610,7 +629,11 @@ class DecodeSession:
                 if t is not None:
                     ctl[i] = t
         eng._staging.upload(ctl, into=cap.control)
-        cap.run()
+        if eng.nvtx:
+            with eng._range(f"decode step: {n} sequences"):
+                cap.run()
+        else:
+            cap.run()
         buf, event = self._free.pop() if self._free else (
             torch.empty(max(eng.max_seqs, 64), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
         buf[:n].copy_(cap.sampled[:n], non_blocking=True)
