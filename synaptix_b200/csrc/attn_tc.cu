@@ -132,6 +132,12 @@ __device__ __forceinline__ void ft_st32u(uint32_t taddr, const uint32_t* r) {
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// one lane of the (converged) warp
+__device__ __forceinline__ bool ft_elect_one() {
+  uint32_t is_leader;
+  asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(is_leader));
+  return is_leader != 0;
+}
 __device__ __forceinline__ void ft_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
@@ -262,42 +268,59 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attn_tc_prefill_kernel(
     __syncwarp();
   } else if (warp == FT_MMA_WARP) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = ft_idesc(FT_BM, FT_BN, false);
-      constexpr uint32_t idesc_pv = ft_idesc(FT_BM, FT_HD, true);
-      // Q is in tensor memory once the softmax threads have copied it there
-      bool ok = ft_mbar_wait(bar(FT_B_QREADY), 0);
-      if (!ok) sx_set_status(status, 2);
+    // The WHOLE warp walks the key blocks, so that addresses and descriptors are computed in uniform control
+    // flow and stay in uniform registers, and one elected lane issues.  (With one lane branching off alone every
+    // tcgen05.mma cost tens of nanoseconds to issue, more than the instruction takes to run.)
+    constexpr uint32_t idesc_qk = ft_idesc(FT_BM, FT_BN, false);
+    constexpr uint32_t idesc_pv = ft_idesc(FT_BM, FT_HD, true);
+    const bool leader = ft_elect_one();
+    const uint32_t kv_addr = ft_smem(kv_s);
+    // Q is in tensor memory once the softmax threads have copied it there
+    bool ok = __all_sync(0xffffffffu, ft_mbar_wait(bar(FT_B_QREADY), 0));
+    if (!ok && leader) sx_set_status(status, 2);
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    // MMAs run in the order they are issued, so S(j+2) = Q K(j+2)^T, issued after P(j) V(j), does not
+    // overwrite P(j), which lies over S(j)
+    auto issue_qk = [&](int j) -> bool {
+      const int ks = j % FT_KV_STAGES, ku = j / FT_KV_STAGES, s = j & 1;
+      if (!__all_sync(0xffffffffu, ft_mbar_wait(bar(FT_B_KVFULL + ks), ku & 1))) {
+        if (leader) sx_set_status(status, 3);
+        return false;
+      }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      // MMAs run in the order they are issued, so S(j+2) = Q K(j+2)^T, issued after P(j) V(j), does not
-      // overwrite P(j), which lies over S(j)
-      auto issue_qk = [&](int j) -> bool {
-        const int ks = j % FT_KV_STAGES, ku = j / FT_KV_STAGES, s = j & 1;
-        if (!ft_mbar_wait(bar(FT_B_KVFULL + ks), ku & 1)) { sx_set_status(status, 3); return false; }
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t ka = ft_smem(kv_s + ks * FT_STAGE);
-        const uint32_t d = tmem_base + (s ? FT_COL_S1 : FT_COL_S0);
+      const uint64_t dk = ft_desc_kmajor(kv_addr + ks * FT_STAGE);
+      const uint32_t d = tmem_base + (s ? FT_COL_S1 : FT_COL_S0), qa = tmem_base + FT_COL_Q;
+      if (leader) {
 #pragma unroll
-        for (int k = 0; k < FT_HD / 16; ++k) {
-          const uint32_t off = (k >> 2) * FT_CHUNK + (k & 3) * 32;
-          ft_mma_ta(d, tmem_base + FT_COL_Q + k * 8, ft_desc_kmajor(ka + off), idesc_qk, k != 0);
-        }
+        for (int k = 0; k < FT_HD / 16; ++k)       // the descriptor's address counts 16-byte units
+          ft_mma_ta(d, qa + k * 8, dk + (((k >> 2) * FT_CHUNK + (k & 3) * 32) >> 4), idesc_qk, k != 0);
         ft_commit(bar(FT_B_SFULL + s));
-        return true;
-      };
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; j < nb && ok; ++j) {
-        if (j + 1 < nb) ok = issue_qk(j + 1);
-        if (!ok) break;
-        if (!ft_mbar_wait(bar(FT_B_PREADY), j & 1)) { sx_set_status(status, 5); ok = false; break; }
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t pa = tmem_base + ((j & 1) ? FT_COL_S1 : FT_COL_S0), va = ft_smem(kv_s + (j % FT_KV_STAGES) * FT_STAGE + FT_TILE);
+      }
+      __syncwarp();
+      return true;
+    };
+    if (ok) ok = issue_qk(0);
+    for (int j = 0; j < nb && ok; ++j) {
+      if (j + 1 < nb) ok = issue_qk(j + 1);
+      if (!ok) break;
+      ok = __all_sync(0xffffffffu, ft_mbar_wait(bar(FT_B_PREADY), j & 1));
+      if (!ok) {
+        if (leader) sx_set_status(status, 5);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const int ks = j % FT_KV_STAGES;
+      const uint32_t pa = tmem_base + ((j & 1) ? FT_COL_S1 : FT_COL_S0), o_acc = tmem_base + FT_COL_O;
+      const uint64_t dv = ft_desc_mnmajor(kv_addr + ks * FT_STAGE + FT_TILE);
+      const uint32_t acc = j != 0;
+      if (leader) {
 #pragma unroll
         for (int k = 0; k < FT_BN / 16; ++k)       // P: 8 columns (16 keys) further; V: 16 rows of 128 bytes further
-          ft_mma_ta(tmem_base + FT_COL_O, pa + k * 8, ft_desc_mnmajor(va + k * 2048), idesc_pv, (j | k) != 0);
+          ft_mma_ta(o_acc, pa + k * 8, dv + k * (2048 >> 4), idesc_pv, acc | (k != 0));
         ft_commit(bar(FT_B_PVDONE));
-        ft_commit(bar(FT_B_KVEMPTY + j % FT_KV_STAGES));
+        ft_commit(bar(FT_B_KVEMPTY + ks));
       }
+      __syncwarp();
     }
     __syncwarp();
   } else {

@@ -44,6 +44,7 @@ LIBRARIES: Dict[str, tuple] = {
     "attn_decode": ("attn_decode.cu", []),
     "attn_tc": ("attn_tc.cu", []),
     "gemm_tc": ("gemm_tc.cu", []),
+    "gemm_ws": ("gemm_ws.cu", []),
 }
 
 

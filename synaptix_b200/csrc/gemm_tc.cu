@@ -20,14 +20,12 @@
 // matching up rows, and the tile of C is 128 x 128).
 // Every wait on an mbarrier is bounded; a wait that runs out sets *status, and the block still
 // frees its tensor memory before it ends.
-#include <cuda.h>
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 #define TC_BM 128
 #define TC_BK 64
 #define TC_A_BYTES (TC_BM * TC_BK * 2)            // 16 KB
 #define TC_THREADS 192
-#define TC_SPIN_LIMIT (1u << 26)
 #define TC_RED_ROWS 6
 
 enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SILU_MUL = 2, TC_EPI_PARTIAL = 3 };
@@ -38,61 +36,6 @@ template <int BN> struct TcShape {
   static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
   static constexpr int STAGES = BN == 256 ? 4 : 6;
 };
-
-__device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void tc_mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void tc_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void tc_tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-// shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
-__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr >> 4) & 0x3FFF);          // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                         // leading byte offset (unused with swizzle)
-  d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                         // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
-  return d;
-}
-// instruction descriptor: D f32, A and B bf16, both K-major, N and M of the instruction
-__host__ __device__ constexpr uint32_t tc_instr_desc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
 
 template <int EPI, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -404,53 +347,76 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
   pdl_wait();          // barriers and tensor memory are set up; the operands may come from the kernel before
   pdl_trigger();
 
+  // Producer and MMA warp: the WHOLE warp walks the work (so that addresses and descriptors are computed in uniform
+  // control flow and stay in uniform registers; with one lane branching off alone each tcgen05.mma cost tens of
+  // nanoseconds to issue), and one elected lane issues.
   if (warp == 0) {
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int w = 0; w < n_work && ok; ++w) {
-        int tile, kb_lo, kb_hi;
-        work_of(w, tile, kb_lo, kb_hi);
-        const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * tile_n;
-        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
-          const uint32_t s = it % STAGES;
-          if (!tc_mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1)) { sx_set_status(status, 1); ok = false; break; }
-          tc_mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-          const uint32_t a_dst = tc_smem(tiles + s * STAGE_BYTES), b_dst = a_dst + TC_A_BYTES;
-          tc_tma_load_2d(a_dst, &map_a, kb * TC_BK, m0, full0 + 8 * s);
-          tc_tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, full0 + 8 * s);
-          if (BN == 256)
-            tc_tma_load_2d(b_dst + B_BYTES / 2, &map_w, kb * TC_BK, (EPI == TC_EPI_SILU_MUL) ? N / 2 + n0 : n0 + BN / 2, full0 + 8 * s);
+    const bool leader = tc_elect_one();
+    const uint32_t tiles_addr = tc_smem(tiles);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int w = 0; w < n_work && ok; ++w) {
+      int tile, kb_lo, kb_hi;
+      work_of(w, tile, kb_lo, kb_hi);
+      const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * tile_n;
+      for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+        const uint32_t s = it % STAGES;
+        ok = __all_sync(0xffffffffu, tc_mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1));
+        if (!ok) {
+          if (leader) sx_set_status(status, 1);
+          break;
         }
+        const uint32_t a_dst = tiles_addr + s * STAGE_BYTES, b_dst = a_dst + TC_A_BYTES, bar = full0 + 8 * s;
+        if (leader) {
+          tc_mbar_expect_tx(bar, STAGE_BYTES);
+          tc_tma_load_2d(a_dst, &map_a, kb * TC_BK, m0, bar);
+          tc_tma_load_2d(b_dst, &map_w, kb * TC_BK, n0, bar);
+          if (BN == 256)
+            tc_tma_load_2d(b_dst + B_BYTES / 2, &map_w, kb * TC_BK, (EPI == TC_EPI_SILU_MUL) ? N / 2 + n0 : n0 + BN / 2, bar);
+        }
+        __syncwarp();
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = tc_instr_desc(TC_BM, BN);
-      uint32_t it = 0;
-      bool ok = true;
-      for (int w = 0; w < n_work && ok; ++w) {
-        int tile, kb_lo, kb_hi;
-        work_of(w, tile, kb_lo, kb_hi);
-        const uint32_t buf = w & 1, use = w >> 1;
-        if (!tc_mbar_wait(acc_empty0 + 8 * buf, (use & 1) ^ 1)) { sx_set_status(status, 4); ok = false; break; }
+    constexpr uint32_t idesc = tc_instr_desc(TC_BM, BN);
+    const bool leader = tc_elect_one();
+    const uint32_t tiles_addr = tc_smem(tiles);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int w = 0; w < n_work && ok; ++w) {
+      int tile, kb_lo, kb_hi;
+      work_of(w, tile, kb_lo, kb_hi);
+      const uint32_t buf = w & 1, use = w >> 1;
+      ok = __all_sync(0xffffffffu, tc_mbar_wait(acc_empty0 + 8 * buf, (use & 1) ^ 1));
+      if (!ok) {
+        if (leader) sx_set_status(status, 4);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+        const uint32_t s = it % STAGES;
+        ok = __all_sync(0xffffffffu, tc_mbar_wait(full0 + 8 * s, (it / STAGES) & 1));
+        if (!ok) {
+          if (leader) sx_set_status(status, 2);
+          break;
+        }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
-          const uint32_t s = it % STAGES;
-          if (!tc_mbar_wait(full0 + 8 * s, (it / STAGES) & 1)) { sx_set_status(status, 2); ok = false; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-          const uint32_t a_addr = tc_smem(tiles + s * STAGE_BYTES), b_addr = a_addr + TC_A_BYTES;
+        const uint32_t a_addr = tiles_addr + s * STAGE_BYTES;
+        const uint64_t da = tc_smem_desc(a_addr), db = tc_smem_desc(a_addr + TC_A_BYTES);
+        const uint32_t acc = kb != kb_lo;
+        if (leader) {
 #pragma unroll
-          for (int k = 0; k < TC_BK / 16; ++k)
-            tc_mma(d_tmem, tc_smem_desc(a_addr + k * 32), tc_smem_desc(b_addr + k * 32), idesc, kb != kb_lo || k != 0);
+          for (int k = 0; k < TC_BK / 16; ++k)          // 32 bytes further along K: 2 in the descriptor's 16-byte units
+            tc_mma(d_tmem, da + 2 * k, db + 2 * k, idesc, acc | (k != 0));
           tc_commit(empty0 + 8 * s);
         }
-        tc_commit(acc_full0 + 8 * buf);
+        __syncwarp();
       }
+      if (leader) tc_commit(acc_full0 + 8 * buf);
+      __syncwarp();
     }
-    __syncwarp();
   } else {
     const int quarter = warp & 3;
     const int et = threadIdx.x - 64;                                    // 0..127 among the epilogue threads
@@ -640,36 +606,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
 // ---------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------
-typedef CUresult (*tc_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static tc_encode_fn tc_get_encode() {
-  static tc_encode_fn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return nullptr;
-    fn = (tc_encode_fn)p;
-  }
-  return fn;
-}
-
 // a [rows, K] row-major bfloat16 matrix as a 2-D tensor map with 128-row x 64-column boxes
-static int tc_make_map(CUtensorMap* map, const void* base, int rows, int K) {
-  tc_encode_fn enc = tc_get_encode();
-  if (!enc) return SX_ERR_SIZE;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  cuuint32_t box[2] = {TC_BK, 128};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : 20000 + (int)r;
-}
+static int tc_make_map(CUtensorMap* map, const void* base, int rows, int K) { return tc_make_map_rows(map, base, rows, K, 128); }
 
 static int* tc_status_word() {
   static int* p = nullptr;

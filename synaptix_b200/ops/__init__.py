@@ -17,6 +17,7 @@ from .attention import (TC_TILE_ROWS, attn_decode, attn_decode_prep, attn_decode
                         fast_supported, pick_splits, query_tiles, tc_prefill_supported, tma_decode_supported)
 from .decode import MAX_ROWS as SKINNY_MAX_ROWS, skinny_gemm, skinny_gemm_residual, skinny_gemm_scaled, skinny_supported
 from .gemm_tc import gemm_tc, tc_supported
+from .gemm_ws import MAX_ROWS as WS_MAX_ROWS, gemm_ws, gemm_ws_residual, ws_supported
 from .options import OPTIONS, KernelOptions, options, set_options
 from .generic import (add_rmsnorm, attn_generic, decode_advance, decode_begin, embed_gather, gemm_generic, qkv_prepare,
                       residual_add,
@@ -30,7 +31,8 @@ __all__ = ["OPTIONS", "KernelOptions", "options", "set_options", "KernelsUnavail
 
 _STATUS_READERS = {"gemm_tc": ("the tcgen05 matrix product (gemm_tc)", "gemm_tc_status"),
                    "attn_tc": ("the tcgen05 prompt attention (attn_tc)", "attn_tc_status"),
-                   "attn_decode": ("the TMA-fed decode attention (attn_decode)", "attn_decode_status")}
+                   "attn_decode": ("the TMA-fed decode attention (attn_decode)", "attn_decode_status"),
+                   "gemm_ws": ("the weight-streaming tcgen05 product (gemm_ws)", "gemm_ws_status")}
 
 
 def check_status(readers=None) -> None:
@@ -44,7 +46,9 @@ def check_status(readers=None) -> None:
         from ._lib import loaded
         from .attention import attn_decode_status, attn_tc_status
         from .gemm_tc import gemm_tc_status
-        fns = {"gemm_tc_status": gemm_tc_status, "attn_tc_status": attn_tc_status, "attn_decode_status": attn_decode_status}
+        from .gemm_ws import gemm_ws_status
+        fns = {"gemm_tc_status": gemm_tc_status, "attn_tc_status": attn_tc_status, "attn_decode_status": attn_decode_status,
+               "gemm_ws_status": gemm_ws_status}
         readers = {}
         for lib, (what, fname) in _STATUS_READERS.items():
             if loaded(lib):
@@ -71,13 +75,21 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     N = w.shape[0]
     if out_dtype is None:
         out_dtype = x.dtype
-    # few rows: stream W once on mma.sync; more than SKINNY_MAX_ROWS: tcgen05 (split over K while rows are few)
+    # up to 16 rows: stream W once on mma.sync; up to 128: tcgen05 with W as the M side, K shared by a cluster's
+    # blocks; more: the tcgen05 product of prompt steps
     if skinny_supported(M, N, K, x.dtype, w.dtype) and out_dtype in (torch.bfloat16, torch.float32):
         if epilogue == "silu_mul":
             if out_dtype == torch.bfloat16:
                 return skinny_gemm(x, w, epilogue="silu_mul")
         else:
             return skinny_gemm(x, w, epilogue="f32" if out_dtype == torch.float32 else None)
+    if (OPTIONS.gemm_ws and M > SKINNY_MAX_ROWS and ws_supported(M, N, K, x.dtype, w.dtype)
+            and out_dtype in (torch.bfloat16, torch.float32)):
+        if epilogue == "silu_mul":
+            if out_dtype == torch.bfloat16:
+                return gemm_ws(x, w, epilogue="silu_mul")
+        else:
+            return gemm_ws(x, w, epilogue="f32" if out_dtype == torch.float32 else None)
     if tc_supported(M, N, K, x.dtype, w.dtype) and out_dtype in (torch.bfloat16, torch.float32):
         if epilogue == "silu_mul":
             if out_dtype == torch.bfloat16:
@@ -118,17 +130,22 @@ def linear_normed(pn, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
 
 def residual_product_fusable(M: int, N: int, K: int, dtype) -> bool:
     """Can the product ``x[M, K] @ w[N, K].T`` add itself into the residual stream and prepare the norm after the
-    sum (``linear_into_residual``)?  3 to 16 rows in bfloat16 (option ``fused_residual``)."""
+    sum (``linear_into_residual``)?  3 to 128 rows in bfloat16 (option ``fused_residual``)."""
     # one or two rows: the norm in the consumer's prologue (norm_fusable) measured faster (489 against 471 tok/s)
-    return (dtype == torch.bfloat16 and 2 < M <= SKINNY_MAX_ROWS and K % 32 == 0 and K > 0
-            and OPTIONS.fused_residual)
+    if dtype != torch.bfloat16 or not OPTIONS.fused_residual or K <= 0:
+        return False
+    if 2 < M <= SKINNY_MAX_ROWS:
+        return K % 32 == 0
+    return OPTIONS.gemm_ws and SKINNY_MAX_ROWS < M <= WS_MAX_ROWS and K % 8 == 0
 
 
 def linear_into_residual(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, gain: torch.Tensor):
     """``h += x @ w.T`` (float32, in place); returns ``(bf16(h * gain), ssq)``: the rows of the RMSNorm after the
     sum without their factor ``rsqrt(mean(h^2) + eps)``, and partial sums of squares of ``h`` from which
     ``linear_scaled`` forms that factor."""
-    return skinny_gemm_residual(x, w, h, gain)
+    if x.shape[0] <= SKINNY_MAX_ROWS:
+        return skinny_gemm_residual(x, w, h, gain)
+    return gemm_ws_residual(x, w, h, gain)
 
 
 def linear_scaled(x: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tensor,
@@ -138,9 +155,9 @@ def linear_scaled(x: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tenso
     M, K = x.shape
     if out_dtype is None:
         out_dtype = x.dtype
-    if not (skinny_supported(M, w.shape[0], K, x.dtype, w.dtype) and M <= SKINNY_MAX_ROWS and w.shape[1] == K):
-        return None
-    if w.shape[0] > SCALED_MAX_OUT:
+    skinny = skinny_supported(M, w.shape[0], K, x.dtype, w.dtype) and M <= SKINNY_MAX_ROWS
+    ws = OPTIONS.gemm_ws and M > SKINNY_MAX_ROWS and ws_supported(M, w.shape[0], K, x.dtype, w.dtype)
+    if not (skinny or ws) or w.shape[1] != K or w.shape[0] > SCALED_MAX_OUT:
         return None
     if epilogue == "silu_mul":
         if out_dtype != torch.bfloat16:
@@ -150,7 +167,9 @@ def linear_scaled(x: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tenso
         epi = "f32" if out_dtype == torch.float32 else None
     else:
         return None
-    return skinny_gemm_scaled(x, w, ssq, eps, epilogue=epi)
+    if skinny:
+        return skinny_gemm_scaled(x, w, ssq, eps, epilogue=epi)
+    return gemm_ws(x, w, epilogue=epi, ssq=ssq, eps=eps)
 
 
 def decode_attention_takes_projection(dtype, nh: int, nkv: int, hd: int, rotary_dim: Optional[int], ctx) -> bool:

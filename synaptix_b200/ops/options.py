@@ -13,7 +13,9 @@ switches in its runtime options (crates/synaptix-config/src/runtime.rs, ``AttnBa
                     cp.async kernel, four warps a page)
 ``gemm_cut``        the persistent tcgen05 product cuts tiles over K where whole tiles would
                     leave SMs idle
-``fused_residual``  3 to 16 rows: the o / down product adds itself into the residual stream and
+``gemm_ws``         17 to 128 rows: the product with the weights as the tensor cores' M side, K shared by
+                    the blocks of a cluster (else the tcgen05 product of prompt steps, split over K)
+``fused_residual``  3 to 128 rows: the o / down product adds itself into the residual stream and
                     prepares the next norm
 ``pdl``             kernels are launched with programmatic dependent launch
 """
@@ -29,6 +31,7 @@ class KernelOptions:
     attn_prep: bool = True
     attn_tma: bool = True
     gemm_cut: bool = True
+    gemm_ws: bool = True
     fused_residual: bool = True
     pdl: bool = True
 

@@ -719,3 +719,86 @@ def test_gemm_tc_split_k(M, N, K, epilogue):
     again = gemm_tc(x.cuda(), w.cuda(), epilogue=epilogue, splits=3)
     assert torch.equal(again, outs[2])                  # the order of addition is fixed
     assert gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 17, 40, 64, 100, 128])
+@pytest.mark.parametrize("N,K", [(2560, 4096), (389, 96), (264, 72), (130, 64), (1000, 1224)])
+def test_gemm_ws(M, N, K):
+    """The weight-streaming tcgen05 product (weights as the M side, K shared by a cluster's blocks) against
+    float64: ragged M, N and K, every number of blocks a cluster may have, all plain epilogues, with and without
+    row factors; and the same bits twice (the blocks add up in a fixed order)."""
+    from synaptix_b200.ops.gemm_ws import gemm_ws, gemm_ws_status, plan_ws
+    g = torch.Generator().manual_seed(M * 31 + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 2 / math.sqrt(K)).to(torch.bfloat16)
+    ssq = torch.rand(M, 5, generator=g) * K * torch.logspace(-1, 1, M)[:, None]
+    eps = 1e-5
+    rf = torch.rsqrt(ssq.double().sum(1) / K + eps)[:, None]
+    ref = x.double() @ w.double().T
+    tiles, auto = plan_ws(M, N, K)
+    assert tiles == (N + 127) // 128 and auto in (1, 2, 4, 8)
+    xd, wd, sd = x.cuda(), w.cuda(), ssq.cuda()
+    for splits in (None, 1, 2, 4, 8):
+        out = gemm_ws(xd, wd, epilogue="f32", splits=splits)
+        assert torch.allclose(out.cpu().double(), ref, atol=2e-5 * math.sqrt(K), rtol=1e-5), f"splits={splits}"
+        assert torch.equal(out, gemm_ws(xd, wd, epilogue="f32", splits=splits))
+        out = gemm_ws(xd, wd, splits=splits)
+        assert out.dtype == torch.bfloat16 and torch.allclose(out.float().cpu().double(), ref, atol=3e-2, rtol=2e-2)
+        out = gemm_ws(xd, wd, epilogue="f32", ssq=sd, eps=eps, splits=splits)
+        assert torch.allclose(out.cpu().double(), ref * rf, atol=2e-5 * math.sqrt(K) * rf.max().item(), rtol=1e-4), f"splits={splits}"
+        if N % 2 == 0:
+            for s_, f_ in ((None, 1.0), (sd, rf)):
+                y = ref * f_
+                want = y[:, :N // 2] / (1 + torch.exp(-y[:, :N // 2])) * y[:, N // 2:]
+                out = gemm_ws(xd, wd, epilogue="silu_mul", ssq=s_, eps=eps, splits=splits)
+                assert out.shape == (M, N // 2)
+                assert torch.allclose(out.float().cpu().double(), want, atol=3e-2, rtol=2e-2), f"silu splits={splits}"
+    assert gemm_ws_status() == 0
+
+
+@pytest.mark.parametrize("M", [3, 17, 64, 128])
+@pytest.mark.parametrize("N,K", [(2560, 4096), (176, 96), (100, 320), (24, 9728)])
+def test_gemm_ws_adds_into_the_residual_and_prepares_the_norm(M, N, K):
+    """h += x W^T in place, x~ = bf16(h * gain) and partial sums of squares of h; then a second product takes x~
+    and the partial sums and must give what it gives for the plain rmsnorm(h) * gain."""
+    from synaptix_b200.ops.gemm_ws import gemm_ws, gemm_ws_residual, gemm_ws_status
+    g = torch.Generator().manual_seed(M * 7919 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    h0 = torch.randn(M, N, generator=g) * torch.logspace(-1, 1, M)[:, None]      # rows of very different size
+    gain = 1 + 0.3 * torch.randn(N, generator=g)
+    eps = 1e-5
+    h_ref = h0.double() + x.double() @ w.double().T
+    for splits in (None, 1, 2, 8):
+        h = h0.clone().cuda()
+        xt, ssq = gemm_ws_residual(x.cuda(), w.cuda(), h, gain.cuda(), splits=splits)
+        assert torch.allclose(h.cpu().double(), h_ref, atol=2e-5 * math.sqrt(K), rtol=1e-5), f"splits={splits}"
+        assert ssq.shape[0] == M and torch.isfinite(ssq).all()
+        assert torch.allclose(ssq.sum(1).cpu().double(), (h_ref ** 2).sum(1), rtol=1e-4), f"splits={splits}"
+        assert torch.allclose(xt.float().cpu().double(), h_ref * gain.double(), atol=1e-3, rtol=1e-2), f"splits={splits}"
+    if N % 8:
+        return
+    xn = P.rms_norm(h.cpu(), gain, eps)
+    for epilogue, N2 in ((None, 200), ("f32", 389), ("silu_mul", 144)):
+        w2 = (torch.randn(N2, N, generator=g) / math.sqrt(N)).to(torch.bfloat16)
+        y = xn.double() @ w2.double().T
+        if epilogue == "silu_mul":
+            y = y[:, :N2 // 2] / (1 + torch.exp(-y[:, :N2 // 2])) * y[:, N2 // 2:]
+        out = gemm_ws(xt, w2.cuda(), epilogue=epilogue, ssq=ssq, eps=eps)
+        assert torch.allclose(out.float().cpu().double(), y, atol=3e-2, rtol=2e-2), f"{epilogue}"
+    assert gemm_ws_status() == 0
+
+
+def test_gemm_ws_refuses_what_it_does_not_take():
+    from synaptix_b200.ops import KernelError
+    from synaptix_b200.ops.gemm_ws import gemm_ws
+    x = torch.zeros(129, 64, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(32, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(KernelError):
+        gemm_ws(x, w)                                           # more than 128 rows
+    with pytest.raises(KernelError):
+        gemm_ws(x[:8, :60].contiguous(), w[:, :60].contiguous())   # K no multiple of 8
+    with pytest.raises(KernelError):
+        gemm_ws(x[:8], w, splits=3)
+    with pytest.raises(KernelError):
+        gemm_ws(x[:8].float(), w)
