@@ -65,6 +65,12 @@ class ClockSampler:
     def __init__(self):
         self.rows = []
         self.proc = None
+        self.first = 0
+
+    def mark(self):
+        """The timed region begins: only what is sampled from here on counts.  (The sampler is started before the
+        untimed steps, because nvidia-smi's own start-up can hold the GPU up for tens of milliseconds.)"""
+        self.first = len(self.rows)
 
     def __enter__(self):
         try:
@@ -92,7 +98,7 @@ class ClockSampler:
     def summary(self):
         mhz, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in (self.rows[self.first:] or self.rows):
             try:
                 mhz.append(float(r[0]))
                 mx.append(float(r[1]))
@@ -239,13 +245,13 @@ def main():
         prompts = prompts_for(B)
         slots, first = fill(prompts, whole=(B == a.batch))
         session = engine.start_decode([DecodeRow(s, t, i, 1) for i, (s, t) in enumerate(zip(slots, first))])
-        for _ in range(settle):
-            session.launch()
-        torch.cuda.synchronize()
         events = [torch.cuda.Event(enable_timing=True) for _ in range(REGIONS + 1)]
-        l0 = engine.kernel_launches
         with ClockSampler() as cs:
+            for _ in range(settle):
+                session.launch()
             torch.cuda.synchronize()
+            l0 = engine.kernel_launches
+            cs.mark()
             events[0].record()
             for r in range(REGIONS):
                 for _ in range(K):
@@ -255,7 +261,7 @@ def main():
         region_ms = sorted(events[r].elapsed_time(events[r + 1]) for r in range(REGIONS))
         ms = region_ms[REGIONS // 2]
         results[B] = {"ms_per_step": ms / K, "tok_s": B * K / (ms / 1e3), "best_tok_s": B * K / (region_ms[0] / 1e3),
-                      "region_ms": [round(x, 3) for x in region_ms]}
+                      "region_ms": [round(events[r].elapsed_time(events[r + 1]), 3) for r in range(REGIONS)]}
         toks = [session.collect() for _ in range(total_steps)]
         if B == a.batch:
             clocks = cs.summary()

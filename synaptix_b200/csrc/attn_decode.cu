@@ -6,7 +6,7 @@
 // 16-byte copies with their addresses per page) and on bookkeeping that it repeats for every 16 keys
 // (four warps split a page), and with two blocks of four warps an SM that is what bounds it: measured
 // 486 instructions a warp a page, 1.6 us a page a block, whatever HBM could deliver.  Here
-//   * one lane of a producer warp brings a page with 2 (head size 64) or 4 (128) TMA copies
+//   * one elected lane of a producer warp (the whole warp walks the pages) brings a page with 2 (head size 64) or 4 (128) TMA copies
 //     (cp.async.bulk.tensor.4d over the cache [pages, kv heads, 64, head size], 128-byte swizzle)
 //     into 3 stages; full/empty mbarriers per stage, no block-wide barrier in the loop;
 //   * each of the 3 compute warps takes WHOLE pages (page i of the block's range goes to warp i % 3, through
@@ -83,6 +83,12 @@ __device__ __forceinline__ bool ad_mbar_wait(uint32_t bar, uint32_t parity) {
     if (ok) return true;
   }
   return false;
+}
+// one lane of the (converged) warp
+__device__ __forceinline__ bool ad_elect_one() {
+  uint32_t is_leader;
+  asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(is_leader));
+  return is_leader != 0;
 }
 __device__ __forceinline__ void ad_tma_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
   asm volatile(
@@ -271,19 +277,26 @@ __global__ void __launch_bounds__(AD_THREADS, 2) attn_decode_tma_kernel(
     // but the token's own, which this kernel makes) and the lengths and block tables were written at least two
     // launches ago, and a kernel behind a programmatic launch starts only when the one before its predecessor
     // has ended.
-    if (lane == 0) {
-      for (int i = 0; i < npages; ++i) {
-        const int st = i % AD_STAGES, use = i / AD_STAGES;
-        if (use > 0 && !ad_mbar_wait(empty(st), (use - 1) & 1)) { sx_set_status(status, 1); break; }
-        const int page = bt[p0 + i];
-        const uint32_t dst = ring_a + st * L::STAGE;
-        ad_mbar_expect_tx(full(st), L::STAGE);
+    // (The whole warp walks the pages and one elected lane issues: addresses computed in uniform control flow
+    // stay in uniform registers, which the copy instruction takes its operands from.)
+    const bool leader = ad_elect_one();
+    for (int i = 0; i < npages; ++i) {
+      const int st = i % AD_STAGES, use = i / AD_STAGES;
+      if (use > 0 && !__all_sync(0xffffffffu, ad_mbar_wait(empty(st), (use - 1) & 1))) {
+        if (leader) sx_set_status(status, 1);
+        break;
+      }
+      const int page = bt[p0 + i];
+      const uint32_t dst = ring_a + st * L::STAGE, bar = full(st);
+      if (leader) {
+        ad_mbar_expect_tx(bar, L::STAGE);
 #pragma unroll
         for (int h = 0; h < L::HALVES; ++h) {
-          ad_tma_4d(dst + h * AD_CHUNK, &map_k, h * 64, 0, kvh, page, full(st));
-          ad_tma_4d(dst + L::TILE + h * AD_CHUNK, &map_v, h * 64, 0, kvh, page, full(st));
+          ad_tma_4d(dst + h * AD_CHUNK, &map_k, h * 64, 0, kvh, page, bar);
+          ad_tma_4d(dst + L::TILE + h * AD_CHUNK, &map_v, h * 64, 0, kvh, page, bar);
         }
       }
+      __syncwarp();
     }
     if (CLUSTER) {                  // every thread of the cluster takes part in its two barriers
       cluster_sync_all();

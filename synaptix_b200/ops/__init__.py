@@ -61,6 +61,11 @@ def check_status(readers=None) -> None:
                               "its output is incomplete and the step's results must not be used")
 
 
+# The weight-streaming product of 17 to 128 rows makes one block per 128 outputs; an output head has a thousand of
+# them, and there the persistent product with its 256-wide tiles measured faster (142 against 158 us for 151,936
+# outputs of 64 rows).
+WS_MAX_OUT = 32768
+
 # Every block of a product that applies row factors fetches the partial sums; an output head has thousands of
 # blocks, and there one norm kernel before it is cheaper (132 against 122 us for 151,936 outputs of 8 rows).
 SCALED_MAX_OUT = 65536
@@ -83,7 +88,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
                 return skinny_gemm(x, w, epilogue="silu_mul")
         else:
             return skinny_gemm(x, w, epilogue="f32" if out_dtype == torch.float32 else None)
-    if (OPTIONS.gemm_ws and M > SKINNY_MAX_ROWS and ws_supported(M, N, K, x.dtype, w.dtype)
+    if (OPTIONS.gemm_ws and M > SKINNY_MAX_ROWS and N <= WS_MAX_OUT and ws_supported(M, N, K, x.dtype, w.dtype)
             and out_dtype in (torch.bfloat16, torch.float32)):
         if epilogue == "silu_mul":
             if out_dtype == torch.bfloat16:
@@ -156,7 +161,8 @@ def linear_scaled(x: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tenso
     if out_dtype is None:
         out_dtype = x.dtype
     skinny = skinny_supported(M, w.shape[0], K, x.dtype, w.dtype) and M <= SKINNY_MAX_ROWS
-    ws = OPTIONS.gemm_ws and M > SKINNY_MAX_ROWS and ws_supported(M, w.shape[0], K, x.dtype, w.dtype)
+    ws = (OPTIONS.gemm_ws and M > SKINNY_MAX_ROWS and w.shape[0] <= WS_MAX_OUT
+          and ws_supported(M, w.shape[0], K, x.dtype, w.dtype))
     if not (skinny or ws) or w.shape[1] != K or w.shape[0] > SCALED_MAX_OUT:
         return None
     if epilogue == "silu_mul":
