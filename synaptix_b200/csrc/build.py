@@ -48,6 +48,11 @@ LIBRARIES: Dict[str, tuple] = {
 }
 
 
+# host-only C++ (the kernels' plain counterparts for the CPU): library name -> source file, compiled with the C++ compiler
+HOST_LIBRARIES: Dict[str, str] = {"reference": "reference.cpp"}
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC"]
+
+
 class KernelsUnavailable(RuntimeError):
     """The CUDA kernels cannot be built or loaded; nothing falls back to anything else."""
 
@@ -177,8 +182,50 @@ def build_all(verbose: bool = True) -> List[str]:
     return [out[n] for n in names]
 
 
+def build_host_library(name: str, verbose: bool = True) -> str:
+    """Compile a host-only C++ library (no CUDA in it, no GPU needed to run it); return its path."""
+    src = HOST_LIBRARIES[name]
+    with open(os.path.join(CSRC_DIR, src), "rb") as f:
+        digest = hashlib.sha256(" ".join(HOST_FLAGS).encode() + f.read()).hexdigest()[:12]
+    out = os.path.join(_build_dir(), f"libsx_{name}-{digest}.so")
+    if os.path.isfile(out):
+        return out
+    cxx = shutil.which("g++") or shutil.which("c++") or shutil.which("clang++")
+    if cxx is None:
+        raise KernelsUnavailable(f"no C++ compiler (g++, c++, clang++) was found to build csrc/{src}")
+    tmp = f"{out}.{os.getpid()}.tmp"
+    cmd = [cxx] + HOST_FLAGS + ["-o", tmp, os.path.join(CSRC_DIR, src)]
+    if verbose:
+        _say(f"compiling csrc/{src} for the host ...")
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if proc.returncode != 0:
+        try:
+            os.remove(tmp)
+        except OSError:
+            pass
+        raise KernelsUnavailable(f"{cxx} failed on csrc/{src}:\n{' '.join(cmd)}\n{proc.stdout}")
+    os.replace(tmp, out)
+    prefix = f"libsx_{name}-"
+    for fn in os.listdir(os.path.dirname(out)):
+        if fn.startswith(prefix) and fn.endswith(".so") and os.path.join(os.path.dirname(out), fn) != out:
+            try:
+                os.remove(os.path.join(os.path.dirname(out), fn))
+            except OSError:
+                pass
+    return out
+
+
 _LOADED: Dict[str, ctypes.CDLL] = {}
 _LOCK = threading.Lock()
+
+
+def load_host_library(name: str) -> ctypes.CDLL:
+    with _LOCK:
+        key = "host:" + name
+        lib = _LOADED.get(key)
+        if lib is None:
+            lib = _LOADED[key] = ctypes.CDLL(build_host_library(name))
+        return lib
 
 
 def load_library(name: str) -> ctypes.CDLL:
