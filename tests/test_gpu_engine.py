@@ -8,7 +8,7 @@ from tiny import random_tokens
 
 pytestmark = pytest.mark.gpu
 
-NAMES = ["A", "B", "W", "F", "S", "G"]
+NAMES = ["A", "B", "W", "F", "S", "G", "O"]
 DTYPES = ["float32", "bfloat16"]
 
 

@@ -63,7 +63,17 @@ TINY_G = dict(
     use_sliding_window=True, sliding_window=70, max_window_layers=1)
 TINY_G_INIT = dict(seed=17, std_matrix=0.05, std_embedding=0.05, std_gain=0.1)
 
-CONFIGS = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "W": (TINY_W, TINY_W_INIT),
+# widths that are no multiples of 8 (100, 90, vocabulary 257) and head size 80: in bfloat16 too, every product and the
+# attention run on the plain kernels, which take every size
+TINY_O = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=100, num_attention_heads=3, num_key_value_heads=3, head_dim=80,
+    intermediate_size=90, vocab_size=257, rope_theta=20000.0, rms_norm_eps=3e-6,
+    max_position_embeddings=512, tie_word_embeddings=False, hidden_act="silu", attention_bias=False,
+    use_sliding_window=False, sliding_window=None)
+TINY_O_INIT = dict(seed=21, std_matrix=0.05, std_embedding=0.05, std_gain=0.1)
+
+CONFIGS = {"O": (TINY_O, TINY_O_INIT), "A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "W": (TINY_W, TINY_W_INIT),
            "F": (TINY_F, TINY_F_INIT), "S": (TINY_S, TINY_S_INIT), "G": (TINY_G, TINY_G_INIT)}
 
 
