@@ -173,13 +173,32 @@ __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_con
   } else {
     pdl_wait();
     pdl_trigger();
-    // the rows' factors, while the product runs
+    // The rows' factors, while the product runs.  The 128 threads share the rows (1, 2, 4 ... threads a row, neighbours
+    // in a warp), each adds its part of the row's partial sums with 16-byte loads, many on the way at once, and
+    // the parts are added by shuffles: a fixed order.  (One thread a row walking 160 partial sums one after the
+    // other cost 8 us at 64 rows, a warp a row as much: what counts is how many loads are on the way.)
     if (ep.ssq_in != nullptr) {
-      for (int m = threadIdx.x - 64; m < M; m += WS_THREADS - 64) {
-        float s = 0.f;
-        for (int j = 0; j < ep.n_ssq; ++j) s += ep.ssq_in[(size_t)m * ep.n_ssq + j];
-        row_factor[m] = rsqrtf(s / (float)K + ep.eps);
+      const int e = threadIdx.x - 64;
+      int tpr = 1;
+      while (tpr < 32 && 2 * tpr * M <= WS_THREADS - 64) tpr *= 2;
+      const int m = e / tpr, sub = e - m * tpr;
+      float s = 0.f;
+      if (m < M) {
+        const float* row = ep.ssq_in + (size_t)m * ep.n_ssq;
+        if ((ep.n_ssq & 3) == 0 && ((uintptr_t)ep.ssq_in & 15) == 0) {
+          const float4* r4 = reinterpret_cast<const float4*>(row);
+#pragma unroll 8
+          for (int j = sub; j < (ep.n_ssq >> 2); j += tpr) {
+            const float4 f = r4[j];
+            s += (f.x + f.y) + (f.z + f.w);
+          }
+        } else {
+#pragma unroll 8
+          for (int j = sub; j < ep.n_ssq; j += tpr) s += row[j];
+        }
       }
+      for (int d = tpr >> 1; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+      if (m < M && sub == 0) row_factor[m] = rsqrtf(s / (float)K + ep.eps);
     }
     const int quarter = warp & 3;                     // warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
     if (tc_mbar_wait(accum, 0)) {
