@@ -337,13 +337,40 @@ static int ws_sm_count() {
   return n[dev];
 }
 
-// blocks of a cluster that share a tile's K: the fewest of 1, 2, 4, 8 that give (nearly) every SM a block, each
+// Shared memory a block takes with a ring of `stages` (the partial tile lies over the ring), and how many blocks of
+// that size an SM holds (228 KB an SM, 1 KB of it per resident block).
+static size_t ws_smem_bytes(int M, int nmma, int stages) {
+  const size_t ring = (size_t)stages * (WS_W_BYTES + nmma * WS_BK * 2), p_bytes = (size_t)M * 128 * 4;
+  return 1024 + (ring > p_bytes ? ring : p_bytes) + (2 * WS_MAX_STAGES + 1) * sizeof(uint64_t) + 8 + 128 * sizeof(float) + 16;
+}
+static int ws_blocks_per_sm(int M, int nmma, int stages) { return (int)(233472 / (ws_smem_bytes(M, nmma, stages) + 1024)); }
+
+// The deepest ring (up to what lets two blocks share an SM) with which all `blocks` blocks are on the GPU at once;
+// 0 if there is none of at least 2 stages.  A block that has to wait for a place runs behind all the others.
+static int ws_pick_stages(int M, int nmma, long long blocks) {
+  const int sms = ws_sm_count();
+  int stages = (100 * 1024) / (WS_W_BYTES + nmma * WS_BK * 2);
+  if (stages > WS_MAX_STAGES) stages = WS_MAX_STAGES;
+  const long long per_sm = (blocks + sms - 1) / sms;
+  while (stages >= 2 && ws_blocks_per_sm(M, nmma, stages) < per_sm) --stages;
+  return stages >= 2 ? stages : 0;
+}
+
+// Blocks of a cluster that share a tile's K: the fewest of 1, 2, 4, 8 that give (nearly) every SM a block, each
 // block keeping at least two 64-wide slices.  (Measured at 64 rows: 6144 x 2560 best with 4, 2560 x 4096 and
-// 2560 x 9728 with 8, the stacked 19456 x 2560 with 1; more blocks than that cost more than they stream.)
-static int ws_pick_splits(int tiles, int nkb) {
-  const int want = ws_sm_count() * 7 / 8;
+// 2560 x 9728 with 8; more blocks than that cost more than they stream.)  Then, if that is more than one block an
+// SM (the stacked 19456 x 2560: 152 tiles on 148 SMs), twice as many blocks with shallower rings, as long as they
+// are all on the GPU at once and keep 16 slices each: most SMs would otherwise hold ONE block, whose ring of 3 or
+// 4 stages is too few bytes on the way for a loaded HBM (27.5 us with 1 block a tile and 4 stages, 23.9 with 2 and 3).
+static int ws_pick_splits(int M, int tiles, int nkb) {
+  const int sms = ws_sm_count(), want = sms * 7 / 8;
+  const int nmma = (M + 15) / 16 * 16;
   int s = 1;
   while (s < 8 && tiles * s < want && nkb / (2 * s) >= 2) s *= 2;
+  if (s < 8 && (long long)tiles * s > sms && nkb / (2 * s) >= 16) {
+    const int st = ws_pick_stages(M, nmma, (long long)tiles * 2 * s);
+    if (st >= (nmma <= 64 ? 3 : 2)) s *= 2;
+  }
   return s;
 }
 
@@ -353,7 +380,7 @@ extern "C" int sx_gemm_ws_plan(int M, int N, int K, int epi, int* out2) {
   const int tile_cols = epi == WS_EPI_SILU_MUL ? 64 : 128;
   const int tiles = (n_out + tile_cols - 1) / tile_cols;
   out2[0] = tiles;
-  out2[1] = ws_pick_splits(tiles, (K + WS_BK - 1) / WS_BK);
+  out2[1] = ws_pick_splits(M, tiles, (K + WS_BK - 1) / WS_BK);
   return 0;
 }
 
@@ -373,14 +400,14 @@ static int ws_launch(const void* X, const void* W, void* out, int M, int N, int 
   int rc = tc_make_map_rows(&mw, W, N, K, EPI == WS_EPI_SILU_MUL ? 64 : 128);
   if (rc) return rc;
   if ((rc = tc_make_map_rows(&mx, X, M, K, nmma))) return rc;
-  // two blocks an SM: a ring of up to 8 stages within ~100 KB, never smaller than the partial tile laid over it
+  // the ring: given, or the deepest with which every block is on the GPU at once (at most what lets two share an SM)
   const int stage_bytes = WS_W_BYTES + nmma * WS_BK * 2;
+  if (stages <= 0) stages = ws_pick_stages(M, nmma, tiles * splits);
   if (stages <= 0) stages = (100 * 1024) / stage_bytes;
   if (stages > WS_MAX_STAGES) stages = WS_MAX_STAGES;
   if (stages > (220 * 1024) / stage_bytes) stages = (220 * 1024) / stage_bytes;
   if (stages < 2) stages = 2;
-  const int ring = stages * stage_bytes, p_bytes = M * 128 * 4;
-  const size_t smem = 1024 + (size_t)(ring > p_bytes ? ring : p_bytes) + (2 * WS_MAX_STAGES + 1) * sizeof(uint64_t) + 8 + 128 * sizeof(float) + 16;
+  const size_t smem = ws_smem_bytes(M, nmma, stages);
   auto kern = gemm_ws_kernel<EPI>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
@@ -405,7 +432,7 @@ extern "C" int sx_gemm_ws(const void* X, const void* W, void* out, int M, int N,
   const int nkb = (K + WS_BK - 1) / WS_BK;
   const int n_out = epi == WS_EPI_SILU_MUL ? N / 2 : N;
   const int tile_cols = epi == WS_EPI_SILU_MUL ? 64 : 128;
-  if (splits == 0) splits = ws_pick_splits((n_out + tile_cols - 1) / tile_cols, nkb);
+  if (splits == 0) splits = ws_pick_splits(M, (n_out + tile_cols - 1) / tile_cols, nkb);
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return SX_ERR_SIZE;
   while (splits > nkb) splits /= 2;
   WsEpilogue ep;
