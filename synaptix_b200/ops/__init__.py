@@ -66,6 +66,25 @@ def check_status(readers=None) -> None:
 # outputs of 64 rows).
 WS_MAX_OUT = 32768
 
+# Up to 16 rows both weight-streaming products apply.  The tcgen05 one is the faster for the wide matrices (at 8 rows
+# gate/up 19.3 against 22.8 us, down 12.9 against 13.9) and for everything at 9 to 16 rows, where the mma.sync kernel
+# needs a second tile of rows (49.5 against 77.6 us a layer at 16 rows); the narrow ones (q/k/v, o) are faster on
+# mma.sync at up to 8 rows (o 6.9 against 7.5 us).
+WS_FEW_ROWS_MIN_ELEMENTS = 20_000_000
+
+
+def _weight_stream_kernel(M: int, N: int, K: int, x_dtype, w_dtype) -> Optional[str]:
+    """Which weight-streaming product takes ``M <= 128`` rows against ``w[N, K]``: ``"skinny"`` (mma.sync, up to 16
+    rows), ``"ws"`` (tcgen05, up to 128 rows and 32,768 outputs) or ``None``."""
+    skinny = skinny_supported(M, N, K, x_dtype, w_dtype)
+    ws = OPTIONS.gemm_ws and N <= WS_MAX_OUT and ws_supported(M, N, K, x_dtype, w_dtype)
+    if skinny and ws:
+        if M <= 2:          # (one or two rows: batch 1 measured 506 tok/s with mma.sync throughout, 494 with tcgen05 for down)
+            return "skinny"
+        return "ws" if (M > 8 or N * K >= WS_FEW_ROWS_MIN_ELEMENTS) else "skinny"
+    return "skinny" if skinny else ("ws" if ws else None)
+
+
 # Every block of a product that applies row factors fetches the partial sums; an output head has thousands of
 # blocks, and there one norm kernel before it is cheaper (132 against 122 us for 151,936 outputs of 8 rows).
 SCALED_MAX_OUT = 65536
@@ -80,21 +99,16 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     N = w.shape[0]
     if out_dtype is None:
         out_dtype = x.dtype
-    # up to 16 rows: stream W once on mma.sync; up to 128: tcgen05 with W as the M side, K shared by a cluster's
-    # blocks; more: the tcgen05 product of prompt steps
-    if skinny_supported(M, N, K, x.dtype, w.dtype) and out_dtype in (torch.bfloat16, torch.float32):
+    # up to 128 rows: stream W once (mma.sync or tcgen05 with W as the M side, see _weight_stream_kernel); more: the
+    # tcgen05 product of prompt steps
+    stream_k = _weight_stream_kernel(M, N, K, x.dtype, w.dtype) if out_dtype in (torch.bfloat16, torch.float32) else None
+    if stream_k is not None:
+        product = skinny_gemm if stream_k == "skinny" else gemm_ws
         if epilogue == "silu_mul":
             if out_dtype == torch.bfloat16:
-                return skinny_gemm(x, w, epilogue="silu_mul")
+                return product(x, w, epilogue="silu_mul")
         else:
-            return skinny_gemm(x, w, epilogue="f32" if out_dtype == torch.float32 else None)
-    if (OPTIONS.gemm_ws and M > SKINNY_MAX_ROWS and N <= WS_MAX_OUT and ws_supported(M, N, K, x.dtype, w.dtype)
-            and out_dtype in (torch.bfloat16, torch.float32)):
-        if epilogue == "silu_mul":
-            if out_dtype == torch.bfloat16:
-                return gemm_ws(x, w, epilogue="silu_mul")
-        else:
-            return gemm_ws(x, w, epilogue="f32" if out_dtype == torch.float32 else None)
+            return product(x, w, epilogue="f32" if out_dtype == torch.float32 else None)
     if tc_supported(M, N, K, x.dtype, w.dtype) and out_dtype in (torch.bfloat16, torch.float32):
         if epilogue == "silu_mul":
             if out_dtype == torch.bfloat16:
@@ -137,18 +151,16 @@ def residual_product_fusable(M: int, N: int, K: int, dtype) -> bool:
     """Can the product ``x[M, K] @ w[N, K].T`` add itself into the residual stream and prepare the norm after the
     sum (``linear_into_residual``)?  3 to 128 rows in bfloat16 (option ``fused_residual``)."""
     # one or two rows: the norm in the consumer's prologue (norm_fusable) measured faster (489 against 471 tok/s)
-    if dtype != torch.bfloat16 or not OPTIONS.fused_residual or K <= 0:
+    if dtype != torch.bfloat16 or not OPTIONS.fused_residual or K <= 0 or M <= 2:
         return False
-    if 2 < M <= SKINNY_MAX_ROWS:
-        return K % 32 == 0
-    return OPTIONS.gemm_ws and SKINNY_MAX_ROWS < M <= WS_MAX_ROWS and K % 8 == 0
+    return _weight_stream_kernel(M, N, K, dtype, dtype) is not None
 
 
 def linear_into_residual(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, gain: torch.Tensor):
     """``h += x @ w.T`` (float32, in place); returns ``(bf16(h * gain), ssq)``: the rows of the RMSNorm after the
     sum without their factor ``rsqrt(mean(h^2) + eps)``, and partial sums of squares of ``h`` from which
     ``linear_scaled`` forms that factor."""
-    if x.shape[0] <= SKINNY_MAX_ROWS:
+    if _weight_stream_kernel(x.shape[0], w.shape[0], w.shape[1], x.dtype, w.dtype) == "skinny":
         return skinny_gemm_residual(x, w, h, gain)
     return gemm_ws_residual(x, w, h, gain)
 
@@ -160,10 +172,8 @@ def linear_scaled(x: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tenso
     M, K = x.shape
     if out_dtype is None:
         out_dtype = x.dtype
-    skinny = skinny_supported(M, w.shape[0], K, x.dtype, w.dtype) and M <= SKINNY_MAX_ROWS
-    ws = (OPTIONS.gemm_ws and M > SKINNY_MAX_ROWS and w.shape[0] <= WS_MAX_OUT
-          and ws_supported(M, w.shape[0], K, x.dtype, w.dtype))
-    if not (skinny or ws) or w.shape[1] != K or w.shape[0] > SCALED_MAX_OUT:
+    stream_k = _weight_stream_kernel(M, w.shape[0], K, x.dtype, w.dtype)
+    if stream_k is None or w.shape[1] != K or w.shape[0] > SCALED_MAX_OUT:
         return None
     if epilogue == "silu_mul":
         if out_dtype != torch.bfloat16:
@@ -173,7 +183,7 @@ def linear_scaled(x: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tenso
         epi = "f32" if out_dtype == torch.float32 else None
     else:
         return None
-    if skinny:
+    if stream_k == "skinny":
         return skinny_gemm_scaled(x, w, ssq, eps, epilogue=epi)
     return gemm_ws(x, w, epilogue=epi, ssq=ssq, eps=eps)
 
