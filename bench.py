@@ -145,6 +145,9 @@ def main():
     ap.add_argument("--phase", default="all", choices=["all", "prefill"],
                     help="prefill: time only the 2,048-token prompt step (small cases for profilers)")
     ap.add_argument("--no-graph", action="store_true", help="run decode steps eagerly instead of replaying CUDA graphs")
+    ap.add_argument("--short", action="store_true",
+                    help="decode only 5 x --steps + --warmup tokens instead of at least 255 (small cases for profilers: "
+                         "every launch under a profiler costs a good part of a second)")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -184,7 +187,7 @@ def main():
     # the context length.  A generation that short would be mostly the GPU coming back from the prompt step: the
     # first 15 to 20 single-token steps after a long prompt step run about a quarter slower (measured; the SM clock
     # is still low from the power cap of the prompt step's products), and the end-to-end figure below has them all.
-    total_steps = max(5 * K + W, 255)
+    total_steps = 5 * K + W if a.short else max(5 * K + W, 255)
     start_len = a.context - total_steps - 1
     if start_len < 1:
         raise SystemExit("--context is too short for 5 x --steps + --warmup")
