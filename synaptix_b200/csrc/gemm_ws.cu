@@ -78,29 +78,23 @@ __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_con
   const int kb0 = (int)((long long)nkb_all * part / splits), kb1 = (int)((long long)nkb_all * (part + 1) / splits);
   const int nkb = kb1 - kb0;                                                // the host keeps splits <= nkb_all: >= 1
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) {
-      tc_mbar_init(full0 + 8 * s, 1);
-      tc_mbar_init(empty0 + 8 * s, 1);
-    }
-    tc_mbar_init(accum, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"((uint32_t)tmem_cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-  const uint32_t tmem_base = *tmem_slot;
-
+  // Warp 0 sets the barriers up and asks for the first ring of W at once: before the tensor memory is there, and
+  // before the wait for the kernel before (weights are nobody's result).
+  const bool leader = warp == 0 && tc_elect_one();
+  const uint32_t tiles_addr = tc_smem(tiles);
+  const int pre = nkb < stages ? nkb : stages;
   if (warp == 0) {
-    // (the whole warp walks the ring, one elected lane issues: see the MMA warp)
-    const bool leader = tc_elect_one();
-    const uint32_t tiles_addr = tc_smem(tiles);
-    const int pre = nkb < stages ? nkb : stages;
-    // the first ring of W, before the wait for the kernel before
+    if (lane == 0) {
+      for (int s = 0; s < stages; ++s) {
+        tc_mbar_init(full0 + 8 * s, 1);
+        tc_mbar_init(empty0 + 8 * s, 1);
+      }
+      tc_mbar_init(accum, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+      asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_x) : "memory");
+    }
+    __syncwarp();
     for (int kb = 0; kb < pre; ++kb) {
       const uint32_t w_dst = tiles_addr + kb * stage_bytes, bar = full0 + 8 * kb;
       const int kx = (kb0 + kb) * WS_BK;
@@ -115,6 +109,18 @@ __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_con
       }
     }
     __syncwarp();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem(tmem_slot)), "r"((uint32_t)tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // (the whole warp walks the ring, one elected lane issues: see the MMA warp)
     pdl_wait();
     pdl_trigger();
     for (int kb = 0; kb < pre; ++kb)
@@ -147,20 +153,19 @@ __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_con
     // The whole warp walks the ring (so that addresses and descriptors are computed in uniform control flow and
     // stay in uniform registers); one elected lane issues.
     const uint32_t idesc = tc_instr_desc(128, nmma);
-    const bool leader = tc_elect_one();
-    const uint32_t tiles_addr = tc_smem(tiles);
+    const bool issuer = tc_elect_one();
     for (int kb = 0; kb < nkb; ++kb) {
       const int s = kb % stages;
       const bool ok = __all_sync(0xffffffffu, tc_mbar_wait(full0 + 8 * s, (kb / stages) & 1));
       if (!ok) {
-        if (leader) sx_set_status(status, 2);
+        if (issuer) sx_set_status(status, 2);
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const uint32_t w_addr = tiles_addr + s * stage_bytes, x_addr = w_addr + WS_W_BYTES;
       const uint64_t dw = tc_smem_desc(w_addr), dx = tc_smem_desc(x_addr);
       const uint32_t acc = kb != 0;
-      if (leader) {
+      if (issuer) {
 #pragma unroll
         for (int k = 0; k < WS_BK / 16; ++k)          // 32 bytes further along K: 2 in the descriptor's 16-byte units
           tc_mma(tmem_base, dw + 2 * k, dx + 2 * k, idesc, acc | (k != 0));
@@ -168,7 +173,7 @@ __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_con
       }
       __syncwarp();
     }
-    if (leader) tc_commit(accum);
+    if (issuer) tc_commit(accum);
     __syncwarp();
   } else {
     pdl_wait();
@@ -219,7 +224,12 @@ __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_con
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-  cluster_sync_all();                                 // every block's P is complete and visible
+  if (splits > 1) cluster_sync_all();                 // every block's P is complete and visible
+  else __syncthreads();
+  if (warp == 1) {                                    // the accumulator has been read: the tensor memory goes back now
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)tmem_cols) : "memory");
+  }
 
   // the sum over the cluster's blocks and the epilogue: this block takes tile_cols / splits columns of every row
   {
@@ -311,11 +321,7 @@ __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_con
     }
   }
 
-  cluster_sync_all();                                 // nobody reads this block's P any more
-  if (warp == 1) {
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)tmem_cols) : "memory");
-  }
+  if (splits > 1) cluster_sync_all();                 // nobody reads this block's P any more
 }
 
 // ---------------------------------------------------------------------------------------
