@@ -7,8 +7,9 @@
 // of C, column = row of C.  K is cut over the blocks of a thread-block cluster (1, 2, 4 or 8), so that a narrow
 // matrix still gives every SM a block and each block streams its own part of W; the blocks of a cluster leave
 // their float32 partial tiles in their own shared memory and add them up, each block a share of the columns,
-// reading the others' through distributed shared memory, in block order.  No workspace in global memory and
-// no second kernel.  The reference's products for decode steps are mma.sync tiles
+// reading the others' through distributed shared memory, in block order (with up to 32 rows of X the blocks
+// send their parts to the block that adds them up instead: one cluster barrier less).  No workspace in global
+// memory and no second kernel.  The reference's products for decode steps are mma.sync tiles
 // (crates/synaptix-kernels-cuda/src/best_cu/gemm/gemm_bf16.cu:37-61); it has no such path.
 //
 //   warp 0   producer: per 64-wide slice of K one TMA load of W (128 rows x 64; for a stacked [gate; up] matrix 64
@@ -50,11 +51,20 @@ __device__ __forceinline__ float4 ws_cluster_load4(const float* local, uint32_t 
   return v;
 }
 
+__device__ __forceinline__ uint32_t ws_cluster_addr(const float* local, uint32_t rank) {
+  uint32_t a = (uint32_t)__cvta_generic_to_shared(local), r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(a), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void ws_cluster_store(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
+}
+
 template <int EPI>
 __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
                                                                 void* __restrict__ out, int M, int N, int K, int nmma,
-                                                                int stages, int splits, int tmem_cols, WsEpilogue ep,
+                                                                int stages, int splits, int tmem_cols, int push, WsEpilogue ep,
                                                                 int* __restrict__ status) {
   extern __shared__ unsigned char ws_smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(ws_smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -62,7 +72,9 @@ __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_con
   const int stage_bytes = WS_W_BYTES + x_bytes;
   const int ring_bytes = stages * stage_bytes;
   const int p_bytes = M * 128 * 4;
-  unsigned char* after = tiles + (ring_bytes > p_bytes ? ring_bytes : p_bytes);
+  // pull: the partial tile P lies over the ring; push: a buffer of its own behind the ring receives the cluster's parts
+  unsigned char* after = tiles + (push ? ring_bytes + p_bytes : (ring_bytes > p_bytes ? ring_bytes : p_bytes));
+  float* R = reinterpret_cast<float*>(tiles + ring_bytes);                  // [splits][M][128 / splits] (push)
   uint64_t* bars = reinterpret_cast<uint64_t*>(after);                      // full[S], empty[S], accum
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * WS_MAX_STAGES + 1);
   float* row_factor = reinterpret_cast<float*>(tmem_slot + 2);              // [128]
@@ -209,14 +221,38 @@ __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_con
     if (tc_mbar_wait(accum, 0)) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
-      float* dst = P + quarter * 32 + lane;
-      for (int c0 = 0; c0 < nmma; c0 += 16) {
-        uint32_t v[16];
-        tc_ld16(t_row + c0, v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+      const int n = quarter * 32 + lane;                 // this thread's row of the W tile
+      if (push) {
+        // every value goes straight into the shared memory of the block that will add this column up
+        const int cpo = 128 / splits;                    // values a row of C an owner receives from one block
+        int owner, j;
+        if (EPI == WS_EPI_SILU_MUL) {
+          const int half = cpo >> 1, c = n & 63;
+          owner = c / half;
+          j = (n >> 6) * half + c % half;                // gate values first, then up values
+        } else {
+          owner = n / cpo;
+          j = n % cpo;
+        }
+        const uint32_t dst = ws_cluster_addr(R + (size_t)part * M * cpo + j, (uint32_t)owner);
+        for (int c0 = 0; c0 < nmma; c0 += 16) {
+          uint32_t v[16];
+          tc_ld16(t_row + c0, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          if (c0 + i < M) dst[(size_t)(c0 + i) * 128] = __uint_as_float(v[i]);
+          for (int i = 0; i < 16; ++i)
+            if (c0 + i < M) ws_cluster_store(dst + (uint32_t)((c0 + i) * cpo * 4), __uint_as_float(v[i]));
+        }
+      } else {
+        float* dst = P + n;
+        for (int c0 = 0; c0 < nmma; c0 += 16) {
+          uint32_t v[16];
+          tc_ld16(t_row + c0, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (c0 + i < M) dst[(size_t)(c0 + i) * 128] = __uint_as_float(v[i]);
+        }
       }
     } else {
       if (lane == 0) sx_set_status(status, 3);
@@ -242,7 +278,18 @@ __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_con
       const int m = valid ? idx / g4 : 0;
       const int c = part * cols_per + (valid ? idx - m * g4 : 0) * 4;       // column within the tile
       float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-      if (valid) {
+      if (valid && push) {
+        const int cpo = 128 / splits, col4 = c - part * cols_per;
+        for (int z = 0; z < splits; ++z) {            // what every block sent, in block order
+          const float* src = R + ((size_t)z * M + m) * cpo + col4;
+          const float4 f = *reinterpret_cast<const float4*>(src);
+          a.x += f.x; a.y += f.y; a.z += f.z; a.w += f.w;
+          if (EPI == WS_EPI_SILU_MUL) {
+            const float4 u = *reinterpret_cast<const float4*>(src + cols_per);
+            b.x += u.x; b.y += u.y; b.z += u.z; b.w += u.w;
+          }
+        }
+      } else if (valid) {
         for (int z = 0; z < splits; ++z) {
           const float4 f = ws_cluster_load4(P + (size_t)m * 128 + c, (uint32_t)z);
           a.x += f.x; a.y += f.y; a.z += f.z; a.w += f.w;
@@ -321,7 +368,7 @@ __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_con
     }
   }
 
-  if (splits > 1) cluster_sync_all();                 // nobody reads this block's P any more
+  if (splits > 1 && !push) cluster_sync_all();        // nobody reads this block's P any more
 }
 
 // ---------------------------------------------------------------------------------------
@@ -345,11 +392,18 @@ static int ws_sm_count() {
 
 // Shared memory a block takes with a ring of `stages` (the partial tile lies over the ring), and how many blocks of
 // that size an SM holds (228 KB an SM, 1 KB of it per resident block).
-static size_t ws_smem_bytes(int M, int nmma, int stages) {
+// With few rows the blocks of a cluster SEND their partial results to the block that adds a column up (a buffer of
+// M x 128 floats behind the ring receives them): one cluster barrier and no remote loads.  With more rows that buffer
+// would cost ring stages, and the partial tile stays where it is (over the ring) for the others to fetch: two barriers.
+#define WS_PUSH_MAX_ROWS 32
+static size_t ws_smem_bytes(int M, int nmma, int stages, bool push) {
   const size_t ring = (size_t)stages * (WS_W_BYTES + nmma * WS_BK * 2), p_bytes = (size_t)M * 128 * 4;
-  return 1024 + (ring > p_bytes ? ring : p_bytes) + (2 * WS_MAX_STAGES + 1) * sizeof(uint64_t) + 8 + 128 * sizeof(float) + 16;
+  return 1024 + (push ? ring + p_bytes : (ring > p_bytes ? ring : p_bytes)) + (2 * WS_MAX_STAGES + 1) * sizeof(uint64_t) + 8 +
+         128 * sizeof(float) + 16;
 }
-static int ws_blocks_per_sm(int M, int nmma, int stages) { return (int)(233472 / (ws_smem_bytes(M, nmma, stages) + 1024)); }
+static int ws_blocks_per_sm(int M, int nmma, int stages) {
+  return (int)(233472 / (ws_smem_bytes(M, nmma, stages, M <= WS_PUSH_MAX_ROWS) + 1024));
+}
 
 // The deepest ring (up to what lets two blocks share an SM) with which all `blocks` blocks are on the GPU at once;
 // 0 if there is none of at least 2 stages.  A block that has to wait for a place runs behind all the others.
@@ -413,12 +467,13 @@ static int ws_launch(const void* X, const void* W, void* out, int M, int N, int 
   if (stages > WS_MAX_STAGES) stages = WS_MAX_STAGES;
   if (stages > (220 * 1024) / stage_bytes) stages = (220 * 1024) / stage_bytes;
   if (stages < 2) stages = 2;
-  const size_t smem = ws_smem_bytes(M, nmma, stages);
+  const int push = splits > 1 && M <= WS_PUSH_MAX_ROWS;
+  const size_t smem = ws_smem_bytes(M, nmma, stages, push != 0);
   auto kern = gemm_ws_kernel<EPI>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   return sx_launch_cluster(kern, dim3((unsigned)(tiles * splits)), dim3(WS_THREADS), smem, stream, splits, mw, mx, out, M, N, K, nmma,
-                           stages, splits, tmem_cols, ep, status);
+                           stages, splits, tmem_cols, push, ep, status);
 }
 
 // X [M, K], W [N, K] bfloat16 row-major, 16-byte aligned, K % 8 == 0, 1 <= M <= 128.

@@ -66,11 +66,13 @@ def check_status(readers=None) -> None:
 # outputs of 64 rows).
 WS_MAX_OUT = 32768
 
-# Up to 16 rows both weight-streaming products apply.  The tcgen05 one is the faster for the wide matrices (at 8 rows
-# gate/up 19.3 against 22.8 us, down 12.9 against 13.9) and for everything at 9 to 16 rows, where the mma.sync kernel
-# needs a second tile of rows (49.5 against 77.6 us a layer at 16 rows); the narrow ones (q/k/v, o) are faster on
-# mma.sync at up to 8 rows (o 6.9 against 7.5 us).
-WS_FEW_ROWS_MIN_ELEMENTS = 20_000_000
+# Up to 16 rows both weight-streaming products apply.  The tcgen05 one streams faster and has the longer beginning and
+# end, so it takes the matrices of 15 M elements and more (at 8 rows and Qwen3-4B sizes, us in replayed graphs: gate/up
+# 19.3 against 22.8, down 12.2 against 13.9, q/k/v 8.0 against 8.4) and everything at 9 to 16 rows, where the
+# mma.sync kernel needs a second tile of rows (a layer's four products at 16 rows: 47 against 77 us).  The 10 M
+# elements of the o product are faster there too when timed alone (6.7 against 6.8) but slower in a step, behind the
+# attention kernel (2,874 against 2,944 tok/s at batch 8).
+WS_FEW_ROWS_MIN_ELEMENTS = 15_000_000
 
 
 def _weight_stream_kernel(M: int, N: int, K: int, x_dtype, w_dtype) -> Optional[str]:
