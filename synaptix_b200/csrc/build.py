@@ -161,7 +161,7 @@ def build_library(name: str, verbose: bool = True, ptxas_info: bool = False) -> 
 
 
 def build_all(verbose: bool = True) -> List[str]:
-    """Compile every library of the package (in parallel)."""
+    """Compile every library of the package (in parallel), the host-only ones after them."""
     names = [n for n, (src, _) in LIBRARIES.items() if os.path.isfile(os.path.join(CSRC_DIR, src))]
     out: Dict[str, str] = {}
     errs: List[BaseException] = []
@@ -179,7 +179,7 @@ def build_all(verbose: bool = True) -> List[str]:
         t.join()
     if errs:
         raise errs[0]
-    return [out[n] for n in names]
+    return [out[n] for n in names] + [build_host_library(n, verbose=verbose) for n in HOST_LIBRARIES]
 
 
 def build_host_library(name: str, verbose: bool = True) -> str:
