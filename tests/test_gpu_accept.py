@@ -138,3 +138,47 @@ def test_decode_steps_at_context_4096(engines, dtype):
     check(got, ref_rows(seq, range(4070, 4080)), dtype, "1 row at context 4,070 to 4,080")
     eng.close(s)
     eng.close(slots[0])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_seqs", [20, 40])
+def test_a_few_dozen_rows_at_the_benchmark_sizes(engines, dtype, n_seqs):
+    """Steps of 17 to 128 rows at the real layer sizes: in bfloat16 these are the rows the weight-streaming tcgen05
+    product takes, with the split norm between the products.  Three short prompts in one step (a few dozen tokens),
+    then ``n_seqs`` sequences of unequal lengths decoding together for 5 steps, through ``Engine.step`` (eager) and,
+    in slots used again, through a decode session (one graph a step)."""
+    from synaptix_b200.engine import DecodeRow, Entry
+    eng = engines(dtype)
+    # a prompt step of 11 + 25 + 40 = 76 rows
+    short = [random_tokens(V, n, 900 + n) for n in (11, 25, 40)]
+    slots = [eng.open() for _ in short]
+    got = eng.step([Entry(sl, s, [len(s) - 1]) for sl, s in zip(slots, short)])
+    check(got, torch.cat([ref_rows(s, [len(s) - 1]) for s in short]), dtype, "three short prompts in one step")
+    for sl in slots:
+        eng.close(sl)
+    # n_seqs sequences: prompts of 3 to 70 tokens, then 5 single-token steps of n_seqs rows
+    n_dec = 5
+    lens = [3 + (7 * i) % 68 for i in range(n_seqs)]
+    seqs = [random_tokens(V, n + n_dec, 1300 + i) for i, n in enumerate(lens)]
+    slots = [eng.open() for _ in seqs]
+    eng.step([Entry(sl, s[:n], []) for sl, s, n in zip(slots, seqs, lens)])
+    for j in range(n_dec):
+        got = eng.step([Entry(sl, [s[n + j]], [0]) for sl, s, n in zip(slots, seqs, lens)])
+        check(got, torch.cat([ref_rows(s, [n + j]) for s, n in zip(seqs, lens)]), dtype, f"{n_seqs} rows, decode step {j}")
+    for sl in slots:
+        eng.close(sl)
+    # the same through a decode session with forced tokens: its greedy choices are those of the plain implementation
+    slots = [eng.open() for _ in seqs]
+    eng.step([Entry(sl, s[:n], []) for sl, s, n in zip(slots, seqs, lens)])
+    session = eng.start_decode([DecodeRow(sl, s[n], i, 0) for i, (sl, s, n) in enumerate(zip(slots, seqs, lens))])
+    for j in range(n_dec):
+        session.launch(tokens=None if j == 0 else [s[n + j] for s, n in zip(seqs, lens)])
+        picked = session.collect()
+        ref = torch.cat([ref_rows(s, [n + j]) for s, n in zip(seqs, lens)])
+        top = torch.topk(ref, 2, dim=-1).values
+        clear = (top[:, 0] - top[:, 1]) > (4e-4 if dtype == "float32" else 6e-2) * ref.abs().max()
+        assert clear.any()
+        assert [p for p, c in zip(picked, clear.tolist()) if c] == [int(t) for t, c in zip(ref.argmax(-1).tolist(), clear.tolist()) if c]
+    session.close()
+    for sl in slots:
+        eng.close(sl)
