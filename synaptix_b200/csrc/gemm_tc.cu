@@ -26,9 +26,31 @@
 #define TC_BK 64
 #define TC_A_BYTES (TC_BM * TC_BK * 2)            // 16 KB
 #define TC_THREADS 192
+// (the epilogue that prepares heads has eight epilogue warps, one group of four per head of the tile)
+template <int EPI> struct TcThreads { static constexpr int N = EPI == 4 ? 320 : TC_THREADS; };
 #define TC_RED_ROWS 6
 
-enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SILU_MUL = 2, TC_EPI_PARTIAL = 3 };
+enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SILU_MUL = 2, TC_EPI_PARTIAL = 3, TC_EPI_QKV = 4 };
+
+// TC_EPI_QKV: the product is the fused q/k/v projection of a prompt step with heads of 128, and its epilogue is the head
+// preparation (what sx_qkv_prepare does to the projection): a 128 x 256 tile holds two whole heads of 128 tokens, an
+// epilogue thread owns a token, so the RMSNorm over a head and the rotation of its halves stay inside a thread.  Query heads
+// go to q_out [M, nh * 128], keys and values into the token's place in its sequence's page.  Values are rounded to bfloat16
+// first, as the projection's own output would be.  cs / sn [M, 64]: cosines and sines of position * inv_freq (null: no rotation).
+struct TcQkv {
+  bf16* q_out;
+  bf16* k_pages;
+  bf16* v_pages;
+  const float* wq;
+  const float* wk;
+  const float* cs;
+  const float* sn;
+  const int* positions;
+  const int* seq_of_token;
+  const int* block_table;
+  int maxp, nh, nkv, n_pages;
+  float eps;
+};
 
 // BN: columns of W per block (256, or 128 for the split-K form); stages fill the shared memory
 template <int BN> struct TcShape {
@@ -287,13 +309,13 @@ __host__ __device__ inline bool tc_piece(const TcPlan& p, int c, int i, TcPiece&
 }
 
 template <int EPI, int BN>
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(TcThreads<EPI>::N, 1) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                            const __grid_constant__ CUtensorMap map_w,
                                                                            void* __restrict__ out, int M, int N, int K,
                                                                            int n_whole, int zmax, int sp,
                                                                            float* __restrict__ piece_ws,
                                                                            int* __restrict__ piece_count,
-                                                                           int* __restrict__ status) {
+                                                                           int* __restrict__ status, const TcQkv qk) {
   constexpr int STAGES = TcShape<BN>::STAGES, B_BYTES = TcShape<BN>::B_BYTES, STAGE_BYTES = TcShape<BN>::STAGE_BYTES;
   extern __shared__ unsigned char tc_smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -332,7 +354,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
     }
     for (int b = 0; b < 2; ++b) {
       tc_mbar_init(acc_full0 + 8 * b, 1);
-      tc_mbar_init(acc_empty0 + 8 * b, 4);          // one arrival per epilogue warp
+      tc_mbar_init(acc_empty0 + 8 * b, (TcThreads<EPI>::N - 64) / 32);          // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -427,25 +449,105 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_persistent_kernel(const
       const uint32_t buf = w & 1, use = w >> 1;
       const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * tile_n;
       const int row = m0 + quarter * 32 + lane;
+      // (head preparation: where this thread's token goes is looked up while the tile's MMAs still run)
+      const bool live = row < M;
+      int pos = 0, page = -1;
+      if (EPI == TC_EPI_QKV && live) {
+        pos = qk.positions[row];
+        page = qk.block_table[(size_t)qk.seq_of_token[row] * qk.maxp + (pos >> 6)];
+      }
       if (!tc_mbar_wait(acc_full0 + 8 * buf, use & 1)) {
         if (lane == 0) sx_set_status(status, 3);
         return false;
       }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const uint32_t t_row = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < tile_n; c0 += 32) {
-        uint32_t v[32], u[32];
-        tc_ld32(t_row + c0, v);
-        if (EPI == TC_EPI_SILU_MUL) tc_ld32(t_row + BN / 2 + c0, u);
-        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-        if (c0 + 32 >= tile_n) {
-          // everything of this accumulator is in registers: hand it back before the last stores
+      if (EPI == TC_EPI_QKV) {
+        // head preparation: this thread's token, the tile's two heads one after the other
+        const bool page_ok = page >= 0 && page < qk.n_pages;
+        {
+          const int hh = (warp - 2) >> 2;                 // warps 2-5 take the tile's first head, warps 6-9 its second
+          const int head = n0 / 128 + hh;
+          float x[128];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tc_ld32(t_row + hh * 128 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&x[c * 32]));
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < 128; ++i) x[i] = __bfloat162float(__float2bfloat16_rn(x[i]));
+          // this warp's part of the accumulator is in registers: hand it back
           asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
           __syncwarp();
           if (lane == 0) tc_mbar_arrive(acc_empty0 + 8 * buf);
+          const bool is_q = head < qk.nh, is_k = !is_q && head < qk.nh + qk.nkv, is_v = !is_q && !is_k && head < qk.nh + 2 * qk.nkv;
+          bf16* dst = nullptr;
+          if (live) {
+            if (is_q) {
+              dst = qk.q_out + ((size_t)row * qk.nh + head) * 128;
+            } else if (is_k || is_v) {
+              bf16* base = is_k ? qk.k_pages : qk.v_pages;
+              const int kvh = is_k ? head - qk.nh : head - qk.nh - qk.nkv;
+              if (base && page_ok) dst = base + (((size_t)page * qk.nkv + kvh) * SX_PAGE + (pos & 63)) * 128;
+            }
+          }
+          if (!dst) return true;
+          if (is_q || is_k) {
+            // (four sums side by side: this thread has no other warp to hide behind; every index a constant, so that
+            //  the head stays in registers)
+            const float* w = is_q ? qk.wq : qk.wk;
+            float inv = 1.f;
+            if (w) {
+              float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+              for (int i = 0; i < 128; i += 4) {
+                s0 += x[i] * x[i]; s1 += x[i + 1] * x[i + 1]; s2 += x[i + 2] * x[i + 2]; s3 += x[i + 3] * x[i + 3];
+              }
+              inv = rsqrtf(((s0 + s1) + (s2 + s3)) / 128.f + qk.eps);
+            }
+            const float4* cs4 = qk.cs ? reinterpret_cast<const float4*>(qk.cs + (size_t)row * 64) : nullptr;
+            const float4* sn4 = qk.cs ? reinterpret_cast<const float4*>(qk.sn + (size_t)row * 64) : nullptr;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float4 glo = make_float4(1.f, 1.f, 1.f, 1.f), ghi = glo, c4 = glo, s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (w) {
+                glo = *reinterpret_cast<const float4*>(w + 4 * i);
+                ghi = *reinterpret_cast<const float4*>(w + 64 + 4 * i);
+              }
+              if (cs4) { c4 = cs4[i]; s4 = sn4[i]; }
+              const float gl[4] = {glo.x, glo.y, glo.z, glo.w}, gh[4] = {ghi.x, ghi.y, ghi.z, ghi.w};
+              const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float a = x[4 * i + j] * inv * gl[j], bb = x[64 + 4 * i + j] * inv * gh[j];
+                x[4 * i + j] = a * cc[j] - bb * sv[j];
+                x[64 + 4 * i + j] = a * sv[j] + bb * cc[j];
+              }
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            uint4 pk;
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(x[8 * i], x[8 * i + 1]), t1 = __floats2bfloat162_rn(x[8 * i + 2], x[8 * i + 3]);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(x[8 * i + 4], x[8 * i + 5]), t3 = __floats2bfloat162_rn(x[8 * i + 6], x[8 * i + 7]);
+            pk.x = *reinterpret_cast<uint32_t*>(&t0); pk.y = *reinterpret_cast<uint32_t*>(&t1);
+            pk.z = *reinterpret_cast<uint32_t*>(&t2); pk.w = *reinterpret_cast<uint32_t*>(&t3);
+            reinterpret_cast<uint4*>(dst)[i] = pk;
+          }
         }
-        if (row < M && n0 + c0 < n_out) tc_store_chunk<EPI>(v, u, out, row, n0 + c0, n_out);
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < tile_n; c0 += 32) {
+          uint32_t v[32], u[32];
+          tc_ld32(t_row + c0, v);
+          if (EPI == TC_EPI_SILU_MUL) tc_ld32(t_row + BN / 2 + c0, u);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          if (c0 + 32 >= tile_n) {
+            // everything of this accumulator is in registers: hand it back before the last stores
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive(acc_empty0 + 8 * buf);
+          }
+          if (row < M && n0 + c0 < n_out) tc_store_chunk<EPI>(v, u, out, row, n0 + c0, n_out);
+        }
       }
       return true;
     };
@@ -758,7 +860,7 @@ extern "C" int sx_gemm_tc_plan(int M, int N, int K, int epi, int* out4) {
 
 template <int EPI, int BN>
 static int tc_launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K,
-                                const TcHostPlan& h, float* ws, int* counts, cudaStream_t stream) {
+                                const TcHostPlan& h, float* ws, int* counts, cudaStream_t stream, const TcQkv& qk = TcQkv()) {
   int* status = tc_status_word();
   if (!status) return (int)cudaErrorMemoryAllocation;
   if (h.n_whole < 0 || h.G <= 0) return SX_ERR_SIZE;
@@ -767,8 +869,8 @@ static int tc_launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, vo
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   // with whole tiles after them, the blocks of a cut tile add up inside the kernel; without, a second kernel does
-  int rc = sx_launch(kern, h.G, dim3(TC_THREADS), smem, stream, ma, mw, out, M, N, K, h.n_whole, h.zmax, h.sp, ws, counts, status);
-  if (rc || h.R == 0 || h.sp > 0) return rc;
+  int rc = sx_launch(kern, h.G, dim3(TcThreads<EPI>::N), smem, stream, ma, mw, out, M, N, K, h.n_whole, h.zmax, h.sp, ws, counts, status, qk);
+  if (rc || h.R == 0 || h.sp > 0 || EPI == TC_EPI_QKV) return rc;
   const int tile_n = (EPI == TC_EPI_SILU_MUL) ? BN / 2 : BN;
   const long long total = (long long)h.R * TC_BM * (tile_n / 4);
   return sx_launch(tc_pieces_reduce_kernel<EPI, BN>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const float*)ws, out,
@@ -857,6 +959,30 @@ extern "C" int sx_gemm_tc(const void* A, const void* W, void* out, int M, int N,
     case TC_EPI_SILU_MUL: return tc_launch_persistent<TC_EPI_SILU_MUL, 256>(ma, mw, out, M, N, K, h, workspace, counts, stream);
     default: return SX_ERR_DTYPE;
   }
+}
+
+// The fused q/k/v projection of a prompt step with its head preparation as the epilogue (see TcQkv): A [M, K], W [N, K] with
+// N = (nh + 2 nkv) * 128 a multiple of 256; q_out [M, nh * 128]; k_pages / v_pages [n_pages, nkv, 64, 128] (null: nothing is
+// written to the cache); wq / wk [128] (null: no norm); cs / sn [M, 64] (null: no rotation).  All tiles are computed whole.
+extern "C" int sx_gemm_tc_qkv(const void* A, const void* W, int M, int N, int K, void* q_out, void* k_pages, void* v_pages,
+                              const float* wq, const float* wk, const float* cs, const float* sn, const int* positions,
+                              const int* seq_of_token, const int* block_table, int maxp, int nh, int nkv, int n_pages,
+                              float eps, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (K <= 0 || (K & 7) || nh <= 0 || nkv <= 0 || N != (nh + 2 * nkv) * 128 || (N & 255) || !q_out || (!cs) != (!sn)) return SX_ERR_SIZE;
+  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)q_out & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) ||
+      ((uintptr_t)wq & 15) || ((uintptr_t)wk & 15) || ((uintptr_t)cs & 15) || ((uintptr_t)sn & 15))
+    return SX_ERR_ALIGN;
+  CUtensorMap ma, mw;
+  int rc = tc_make_map(&ma, A, M, K);
+  if (rc) return rc;
+  if ((rc = tc_make_map(&mw, W, N, K))) return rc;
+  const TcHostPlan h = tc_plan_stream(M, N, K, TC_EPI_BF16, false);
+  TcQkv qk;
+  qk.q_out = (bf16*)q_out; qk.k_pages = (bf16*)k_pages; qk.v_pages = (bf16*)v_pages; qk.wq = wq; qk.wk = wk; qk.cs = cs; qk.sn = sn;
+  qk.positions = positions; qk.seq_of_token = seq_of_token; qk.block_table = block_table;
+  qk.maxp = maxp; qk.nh = nh; qk.nkv = nkv; qk.n_pages = n_pages; qk.eps = eps;
+  return tc_launch_persistent<TC_EPI_QKV, 256>(ma, mw, nullptr, M, N, K, h, nullptr, nullptr, stream, qk);
 }
 
 // 0, or which bounded wait ran out (1 producer, 2 and 4 MMA issuer, 3 epilogue, 5 the blocks of a cut tile waiting for one another)

@@ -616,6 +616,30 @@ extern "C" int sx_qkv_prepare(const void* qkv, void* q_out, void* k_pages, void*
 }
 
 // ---------------------------------------------------------------------------------------
+// cosines and sines of position * inv_freq[i] for every token of a step, [n_tokens, pairs] each: what the head
+// preparation computes per token, made once for a product whose epilogue prepares the heads
+// ---------------------------------------------------------------------------------------
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int pairs,
+                                  float* __restrict__ cs, float* __restrict__ sn, size_t n) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n) return;
+  const size_t t = idx / pairs;
+  const int i = (int)(idx - t * pairs);
+  float s, c;
+  sincosf((float)positions[t] * inv_freq[i], &s, &c);
+  cs[idx] = c;
+  sn[idx] = s;
+}
+extern "C" int sx_rope_table(const int* positions, const float* inv_freq, int pairs, int n_tokens, float* cs, float* sn,
+                             cudaStream_t stream) {
+  if (n_tokens <= 0 || pairs <= 0) return 0;
+  const size_t n = (size_t)n_tokens * pairs;
+  return sx_launch(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, positions, inv_freq, pairs, cs, sn, n);
+}
+
+// ---------------------------------------------------------------------------------------
 // attention over the paged cache, one block per (token, query head): scores of the keys
 // lo..pos in tiles of 128, running maximum and sum (online softmax), all in 32-bit.
 //   lo = window > 0 ? max(0, pos - window + 1) : 0;  query head h reads kv head h / (nh/nkv).

@@ -16,17 +16,16 @@ from ._lib import KernelError, set_launch_counter
 from .attention import (TC_TILE_ROWS, attn_decode, attn_decode_prep, attn_decode_tma, attn_prefill, attn_prefill_tc,
                         fast_supported, pick_splits, query_tiles, tc_prefill_supported, tma_decode_supported)
 from .decode import MAX_ROWS as SKINNY_MAX_ROWS, skinny_gemm, skinny_gemm_residual, skinny_gemm_scaled, skinny_supported
-from .gemm_tc import gemm_tc, tc_supported
+from .gemm_tc import gemm_tc, gemm_tc_qkv, qkv_epilogue_supported, tc_supported
 from .gemm_ws import MAX_ROWS as WS_MAX_ROWS, gemm_ws, gemm_ws_residual, ws_supported
 from .options import OPTIONS, KernelOptions, options, set_options
 from .generic import (add_rmsnorm, attn_generic, decode_advance, decode_begin, embed_gather, gemm_generic, qkv_prepare,
-                      residual_add,
-                      silu_mul)
+                      residual_add, rope_table, silu_mul)
 
 __all__ = ["OPTIONS", "KernelOptions", "options", "set_options", "KernelsUnavailable", "KernelError", "set_launch_counter", "decode_advance", "decode_begin", "check_status", "add_rmsnorm", "attn_generic", "embed_gather",
            "gemm_generic", "qkv_prepare", "residual_add", "silu_mul", "linear", "linear_normed", "norm_fusable", "attention",
            "attention_from_projection", "decode_attention_takes_projection", "residual_product_fusable",
-           "linear_into_residual", "linear_scaled"]
+           "linear_into_residual", "linear_scaled", "projection_prepares_heads", "project_and_prepare", "rope_table"]
 
 
 _STATUS_READERS = {"gemm_tc": ("the tcgen05 matrix product (gemm_tc)", "gemm_tc_status"),
@@ -188,6 +187,35 @@ def linear_scaled(x: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tenso
     if stream_k == "skinny":
         return skinny_gemm_scaled(x, w, ssq, eps, epilogue=epi)
     return gemm_ws(x, w, epilogue=epi, ssq=ssq, eps=eps)
+
+
+# Fewer rows than this and the fused projection is one of the weight-streaming products, which have no such epilogue.
+QKV_EPILOGUE_MIN_ROWS = WS_MAX_ROWS + 1
+
+
+def projection_prepares_heads(M: int, K: int, x_dtype, w_dtype, nh: int, nkv: int, hd: int, rotary_dim: Optional[int]) -> bool:
+    """Can the q/k/v product of a prompt step prepare the heads in its epilogue (``project_and_prepare``)?  (Option
+    ``qkv_epilogue``.)"""
+    return (OPTIONS.qkv_epilogue and M >= QKV_EPILOGUE_MIN_ROWS and rotary_dim in (None, 0, hd)
+            and qkv_epilogue_supported(M, nh, nkv, hd, K, x_dtype, w_dtype))
+
+
+def project_and_prepare(x: torch.Tensor, w: torch.Tensor, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                        wq, wk, inv_freq, eps: float, ctx, block_table: torch.Tensor, nh: int, nkv: int, hd: int) -> torch.Tensor:
+    """The prepared queries ``[T, nh * hd]`` of a prompt step straight from the block's input: the fused q/k/v product
+    with the head preparation (per-head RMSNorm, rotation, cache write) as its epilogue.  The cosines and sines of the
+    step's angles are made once a step and rotation (``ctx.scratch``) and shared by the layers."""
+    cos = sin = None
+    if inv_freq is not None:
+        key = ("rope_table", inv_freq.data_ptr())
+        table = ctx.scratch.get(key)
+        if table is None:
+            table = ctx.scratch[key] = rope_table(ctx.positions[:x.shape[0]], inv_freq)
+        cos, sin = table
+    q = torch.empty((x.shape[0], nh * hd), dtype=x.dtype, device=x.device)
+    gemm_tc_qkv(x, w, q, k_pages, v_pages, wq, wk, cos, sin, eps, ctx.positions[:x.shape[0]], ctx.seq_of_token[:x.shape[0]],
+                block_table, nh, nkv)
+    return q
 
 
 def decode_attention_takes_projection(dtype, nh: int, nkv: int, hd: int, rotary_dim: Optional[int], ctx) -> bool:

@@ -98,6 +98,52 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None,
     return out
 
 
+QKV_HEAD_DIM = 128
+
+
+def qkv_epilogue_supported(M: int, nh: int, nkv: int, hd: int, K: int, x_dtype, w_dtype) -> bool:
+    """Can the fused q/k/v projection prepare the heads in its epilogue?  Heads of 128, an even number of them
+    (a 256-wide tile holds two), bfloat16."""
+    return (x_dtype == torch.bfloat16 and w_dtype == torch.bfloat16 and hd == QKV_HEAD_DIM and (nh + 2 * nkv) % 2 == 0
+            and K > 0 and K % 8 == 0 and M > 0)
+
+
+def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages: Optional[torch.Tensor],
+                v_pages: Optional[torch.Tensor], wq: Optional[torch.Tensor], wk: Optional[torch.Tensor],
+                cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], eps: float, positions: torch.Tensor,
+                seq_of_token: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int) -> None:
+    """``x @ w.T`` for the stacked q/k/v matrix with heads of 128, and what ``qkv_prepare`` does to the result, in
+    the product's epilogue: per-head RMSNorm of q and k (gains ``wq`` / ``wk``, skipped when ``None``), rotate-half
+    rotation by the angles whose cosines and sines are ``cos`` / ``sin [M, 64]`` (skipped when ``None``), q to
+    ``q_out [M, nh * 128]``, k and v into the pages (skipped when ``None``)."""
+    require_cuda(x, w, q_out, k_pages, v_pages, wq, wk, cos, sin, positions, seq_of_token, block_table)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or N != (nh + 2 * nkv) * QKV_HEAD_DIM or not qkv_epilogue_supported(M, nh, nkv, QKV_HEAD_DIM, K, x.dtype, w.dtype):
+        raise KernelError("gemm_tc_qkv: bfloat16, heads of 128, an even number of heads, K a multiple of 8")
+    if q_out.dtype != torch.bfloat16 or tuple(q_out.shape) != (M, nh * QKV_HEAD_DIM):
+        raise KernelError("gemm_tc_qkv: q_out must be bfloat16 [M, nh * 128]")
+    n_pages = 0
+    for pg in (k_pages, v_pages):
+        if pg is not None:
+            if pg.dtype != torch.bfloat16 or pg.dim() != 4 or tuple(pg.shape[1:]) != (nkv, 64, QKV_HEAD_DIM):
+                raise KernelError("gemm_tc_qkv: cache pages must be bfloat16 [n_pages, nkv, 64, 128]")
+            n_pages = pg.shape[0]
+    for t in (wq, wk):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != QKV_HEAD_DIM):
+            raise KernelError("gemm_tc_qkv: norm gains are float32 [128]")
+    if (cos is None) != (sin is None) or (cos is not None and (cos.dtype != torch.float32 or tuple(cos.shape) != (M, 64)
+                                                                 or tuple(sin.shape) != (M, 64))):
+        raise KernelError("gemm_tc_qkv: cos and sin are float32 [M, 64]")
+    for t in (positions, seq_of_token, block_table):
+        if t.dtype != torch.int32:
+            raise KernelError("gemm_tc_qkv: index tensors are int32")
+    check(fn("gemm_tc", "sx_gemm_tc_qkv")(
+        ptr(x), ptr(w), c_int(M), c_int(N), c_int(K), ptr(q_out), ptr(k_pages), ptr(v_pages), ptr(wq), ptr(wk), ptr(cos),
+        ptr(sin), ptr(positions), ptr(seq_of_token), ptr(block_table), c_int(block_table.shape[1]), c_int(nh), c_int(nkv),
+        c_int(n_pages), ctypes.c_float(eps), stream()), "gemm_tc_qkv")
+
+
 def gemm_tc_status(reset: bool = False) -> int:
     """0, or which bounded wait of the kernel ran out (1 producer, 2 and 4 MMA issuer, 3 epilogue, 5 the blocks
     of a cut tile waiting for one another).  The word lies in host memory the device writes to, so this is no

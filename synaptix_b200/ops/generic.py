@@ -114,6 +114,17 @@ def qkv_prepare(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: Optional[torch.
         stream()), "qkv_prepare")
 
 
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor):
+    """``(cos, sin)`` float32 ``[T, pairs]`` of ``position * inv_freq[i]`` (32-bit angles, ``sincosf``)."""
+    require_cuda(positions, inv_freq)
+    T, pairs = positions.numel(), inv_freq.numel()
+    cs = torch.empty((T, pairs), dtype=torch.float32, device=positions.device)
+    sn = torch.empty_like(cs)
+    check(fn("generic", "sx_rope_table")(ptr(positions), ptr(inv_freq), c_int(pairs), c_int(T), ptr(cs), ptr(sn), stream()),
+          "rope_table")
+    return cs, sn
+
+
 def attn_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, positions: torch.Tensor,
                  seq_of_token: torch.Tensor, block_table: torch.Tensor, nh: int, nkv: int, hd: int,
                  scale: float, window: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -68,10 +68,20 @@ class Attention(Mixer):
                 defer_output: bool = False) -> torch.Tensor:
         out = self.o.deferred if defer_output else self.o.forward
         T = x.shape[0]
-        qkv = self.qkv.forward(x)
         rot = self.position.rotation()
         inv_freq, rotary_dim = rot if rot is not None else (None, 0)
         bt = ctx.block_tables[cache_view.group]
+        eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
+        if (isinstance(x, torch.Tensor)
+                and ops.projection_prepares_heads(T, x.shape[1], x.dtype, self.qkv.weight.dtype, self.nh, self.nkv, self.hd,
+                                                  rotary_dim)
+                and not ctx.all_single):
+            # prompt steps: the projection's epilogue prepares the heads and writes the cache
+            q = ops.project_and_prepare(x, self.qkv.weight, cache_view.k if write_cache else None,
+                                        cache_view.v if write_cache else None, self.wq, self.wk, inv_freq, eps, ctx, bt,
+                                        self.nh, self.nkv, self.hd)
+            return out(ops.attention(q, cache_view.k, cache_view.v, ctx, bt, self.nh, self.nkv, self.hd, self.scale, self.window))
+        qkv = self.qkv.forward(x)
         if ops.decode_attention_takes_projection(qkv.dtype, self.nh, self.nkv, self.hd, rotary_dim, ctx):
             # single-token steps: the attention kernel prepares the heads and writes the cache itself
             a = ops.attention_from_projection(qkv, cache_view.k, cache_view.v, ctx, bt, self.nh, self.nkv, self.hd,

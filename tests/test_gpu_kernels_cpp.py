@@ -258,3 +258,61 @@ def test_decode_bookkeeping_kernels_against_the_cpp_loops():
     ops.decode_advance(gpu[0], samp.cuda(), gpu[3], gpu[4], gpu[5], gpu[6], adv.cuda(), gpu[1], gpu[2])
     for a, b in zip(cpu, gpu):
         assert torch.equal(a, b.cpu())
+
+
+@pytest.mark.parametrize("M", [129, 300, 1000])
+@pytest.mark.parametrize("nh,nkv,K,norm,rot", [(4, 2, 264, True, True), (6, 1, 1224, True, False), (2, 2, 96, False, True)])
+def test_projection_with_head_preparation_in_its_epilogue_against_the_cpp_loops(M, nh, nkv, K, norm, rot):
+    """The fused q/k/v product of a prompt step whose epilogue norms and rotates the heads and writes the cache: the C++
+    product (rounded to bfloat16, as the projection's output would be), then the C++ head preparation; and the two
+    kernels it replaces."""
+    from synaptix_b200 import ops
+    from synaptix_b200.ops.gemm_tc import gemm_tc, gemm_tc_qkv, gemm_tc_status
+    hd = 128
+    g = torch.Generator().manual_seed(M + K)
+    x = torch.randn(M, K, generator=g).to(BF)
+    w = (torch.randn((nh + 2 * nkv) * hd, K, generator=g) * 2 / math.sqrt(K)).to(BF)
+    wq = 1 + 0.3 * torch.randn(hd, generator=g) if norm else None
+    wk = 1 + 0.3 * torch.randn(hd, generator=g) if norm else None
+    inv = torch.rand(hd // 2, generator=g) * 0.3 if rot else None
+    # three sequences, the second with keys from before; pages in scrambled order
+    new = [M // 2, M // 3, M - M // 2 - M // 3]
+    past = [0, 70, 5]
+    positions = torch.cat([torch.arange(p, p + n) for p, n in zip(past, new)])
+    seq_of = torch.cat([torch.full((n,), s) for s, n in enumerate(new)])
+    need = [(p + n + 63) // 64 for p, n in zip(past, new)]
+    n_pages = sum(need) + 2
+    perm = torch.randperm(n_pages - 1, generator=g).add(1).tolist()
+    bt = torch.zeros((3, max(need)), dtype=torch.int32)
+    for s in range(3):
+        for i in range(need[s]):
+            bt[s, i] = perm.pop()
+    kp = torch.full((n_pages, nkv, 64, hd), float("nan"), dtype=BF)
+    vp = kp.clone()
+    want_q = R.qkv_prepare(R.gemm(x, w), kp, vp, wq, wk, inv, hd if rot else 0, 1e-6, positions, seq_of, bt, nh, nkv, hd)
+    dev = lambda t: None if t is None else t.cuda()
+    cos, sin = ops.rope_table(i32(positions), inv.cuda()) if rot else (None, None)
+    if rot:
+        ang = positions.float()[:, None] * inv[None, :]
+        assert torch.allclose(cos.cpu(), torch.cos(ang), atol=1e-6) and torch.allclose(sin.cpu(), torch.sin(ang), atol=1e-6)
+    kc, vc = torch.full_like(kp, float("nan")).cuda(), torch.full_like(vp, float("nan")).cuda()
+    q = torch.full((M, nh * hd), float("nan"), dtype=BF, device="cuda")
+    gemm_tc_qkv(x.cuda(), w.cuda(), q, kc, vc, dev(wq), dev(wk), cos, sin, 1e-6, i32(positions), i32(seq_of), bt.cuda(), nh, nkv)
+    t = dict(atol=3e-2, rtol=2e-2)
+    assert torch.allclose(q.float().cpu(), want_q.float(), **t)
+    assert torch.equal(torch.isnan(kc.float().cpu()), torch.isnan(kp.float()))          # the same places were written
+    assert torch.allclose(torch.nan_to_num(kc.float().cpu()), torch.nan_to_num(kp.float()), **t)
+    assert torch.allclose(torch.nan_to_num(vc.float().cpu()), torch.nan_to_num(vp.float()), **t)
+    # the two kernels it replaces give the same numbers but for the order of the sums (that product may split K)
+    k2, v2 = torch.full_like(kc, float("nan")), torch.full_like(vc, float("nan"))
+    q2 = torch.empty_like(q)
+    ops.qkv_prepare(gemm_tc(x.cuda(), w.cuda()), q2, k2, v2, dev(wq), dev(wk), dev(inv), hd if rot else 0, 1e-6, i32(positions),
+                    i32(seq_of), bt.cuda(), nh, nkv, hd)
+    assert torch.allclose(q.float(), q2.float(), atol=2e-2, rtol=1e-2)
+    assert torch.allclose(torch.nan_to_num(vc.float()), torch.nan_to_num(v2.float()), atol=2e-2, rtol=1e-2)
+    assert torch.allclose(torch.nan_to_num(kc.float()), torch.nan_to_num(k2.float()), atol=2e-2, rtol=1e-2)
+    # a layer that reads another layer's cache writes nothing
+    q3 = torch.empty_like(q)
+    gemm_tc_qkv(x.cuda(), w.cuda(), q3, None, None, dev(wq), dev(wk), cos, sin, 1e-6, i32(positions), i32(seq_of), bt.cuda(), nh, nkv)
+    assert torch.equal(q3, q)
+    assert gemm_tc_status() == 0
