@@ -26,6 +26,11 @@ def rotary_inv_freq(theta: float, rotary_dim: int) -> np.ndarray:
     return np.power(np.float32(theta), exponent).astype(np.float32)
 
 
+# one device tensor per (theta, rotary_dim, device): layers with the same rotation share it, and what a step derives
+# from it (a table of cosines and sines) is made once a step, not once a layer
+_INV_FREQ = {}
+
+
 class RotaryHalf(PositionEncoding):
     def __init__(self, head_dim: int, theta: float, rotary_dim: int = None):
         self.head_dim = head_dim
@@ -36,7 +41,10 @@ class RotaryHalf(PositionEncoding):
         self.inv_freq = None
 
     def bind(self, tensors, rt: Runtime) -> None:
-        self.inv_freq = torch.from_numpy(rotary_inv_freq(self.theta, self.rotary_dim)).to(rt.device)
+        key = (self.theta, self.rotary_dim, str(rt.device))
+        if key not in _INV_FREQ:
+            _INV_FREQ[key] = torch.from_numpy(rotary_inv_freq(self.theta, self.rotary_dim)).to(rt.device)
+        self.inv_freq = _INV_FREQ[key]
 
     def rotation(self):
         return self.inv_freq, self.rotary_dim
