@@ -25,11 +25,11 @@ The reference's equivalent is ``KvCache``/``LayerCache``
 from __future__ import annotations
 
 import dataclasses
-from typing import Dict, List, Optional, Sequence, Tuple, Union
+from typing import List, Optional, Sequence, Tuple, Union
 
 import torch
 
-from .pages import PAGE_TOKENS, CacheFull, PagePool, SequenceSlots, SlotError, pages_for
+from .pages import PAGE_TOKENS, PagePool, SequenceSlots, pages_for
 
 
 @dataclasses.dataclass(frozen=True)

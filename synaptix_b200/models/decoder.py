@@ -14,13 +14,12 @@ here only the wanted rows are normalised and projected.
 from __future__ import annotations
 
 import dataclasses
-from typing import Dict, List, Mapping, Optional, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
-from .. import ops
 from ..cache.store import CacheRequest
-from ..parts.base import Norm, Part, PendingLinear, Runtime, StepContext, plain
+from ..parts.base import Norm, Part, PendingLinear, Runtime, StepContext
 from ..parts.embedding import Embedding, OutputHead
 from ..weights.loader import TensorSpec, WeightSource, bind_tensors
 

@@ -3,7 +3,6 @@ from __future__ import annotations
 
 from typing import Optional, Sequence, Tuple
 
-import numpy as np
 import torch
 
 import ctypes

@@ -11,7 +11,7 @@ from typing import List, Optional, Tuple
 
 import torch
 
-from .base import FeedForward, Mixer, Norm, Part, PendingLinear, PendingNorm, ScaledRows, StepContext, plain
+from .base import FeedForward, Mixer, Norm, Part, PendingLinear, PendingNorm, ScaledRows, StepContext
 
 
 class PreNormBlock(Part):

@@ -9,7 +9,6 @@ from typing import List
 
 import torch
 
-from .. import ops
 from .base import FeedForward, Part, StepContext
 from .linear import Linear
 

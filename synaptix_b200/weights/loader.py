@@ -15,7 +15,7 @@ compute dtype, norm gains stay in 32-bit) is the part's business.
 """
 from __future__ import annotations
 
-from typing import Dict, Iterable, List, Mapping, NamedTuple, Optional, Set, Tuple
+from typing import Dict, List, Mapping, NamedTuple, Optional, Tuple
 
 import torch
 

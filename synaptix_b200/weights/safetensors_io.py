@@ -17,7 +17,7 @@ import json
 import mmap
 import os
 import struct
-from typing import Dict, Iterable, List, Mapping, NamedTuple, Optional, Tuple
+from typing import Dict, List, Mapping, NamedTuple, Optional, Tuple
 
 import torch
 
