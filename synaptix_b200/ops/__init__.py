@@ -73,6 +73,11 @@ WS_MAX_OUT = 32768
 # attention kernel (2,874 against 2,944 tok/s at batch 8).
 WS_FEW_ROWS_MIN_ELEMENTS = 15_000_000
 
+# A step of ONE row norms inside the next product's prologue (every block repeats the norm of the row) and keeps the
+# mma.sync kernels throughout; from two rows on the o / down product adds itself into the residual stream and the next
+# product applies the rows' factors (batch 2: 934 against 907 tok/s; batch 1: 492 against 506).
+PROLOGUE_NORM_MAX_ROWS = 1
+
 
 def _weight_stream_kernel(M: int, N: int, K: int, x_dtype, w_dtype) -> Optional[str]:
     """Which weight-streaming product takes ``M <= 128`` rows against ``w[N, K]``: ``"skinny"`` (mma.sync, up to 16
@@ -80,7 +85,7 @@ def _weight_stream_kernel(M: int, N: int, K: int, x_dtype, w_dtype) -> Optional[
     skinny = skinny_supported(M, N, K, x_dtype, w_dtype)
     ws = OPTIONS.gemm_ws and N <= WS_MAX_OUT and ws_supported(M, N, K, x_dtype, w_dtype)
     if skinny and ws:
-        if M <= 2:          # (one or two rows: batch 1 measured 506 tok/s with mma.sync throughout, 494 with tcgen05 for down)
+        if M <= PROLOGUE_NORM_MAX_ROWS:          # (one row: batch 1 measured 506 tok/s with mma.sync throughout, 494 with tcgen05 for down)
             return "skinny"
         return "ws" if (M > 8 or N * K >= WS_FEW_ROWS_MIN_ELEMENTS) else "skinny"
     return "skinny" if skinny else ("ws" if ws else None)
@@ -125,7 +130,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
 def norm_fusable(M: int, K: int, dtype) -> bool:
     """Can ``rmsnorm(h + delta)`` of ``M`` rows of width ``K`` run inside the next product's prologue?"""
     # every block repeats the norm, so it pays only while the rows are few
-    return dtype == torch.bfloat16 and 0 < M <= 2 and K % 32 == 0 and K <= 4096
+    return dtype == torch.bfloat16 and 0 < M <= PROLOGUE_NORM_MAX_ROWS and K % 32 == 0 and K <= 4096
 
 
 def linear_normed(pn, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
@@ -150,9 +155,9 @@ def linear_normed(pn, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
 
 def residual_product_fusable(M: int, N: int, K: int, dtype) -> bool:
     """Can the product ``x[M, K] @ w[N, K].T`` add itself into the residual stream and prepare the norm after the
-    sum (``linear_into_residual``)?  3 to 128 rows in bfloat16 (option ``fused_residual``)."""
-    # one or two rows: the norm in the consumer's prologue (norm_fusable) measured faster (489 against 471 tok/s)
-    if dtype != torch.bfloat16 or not OPTIONS.fused_residual or K <= 0 or M <= 2:
+    sum (``linear_into_residual``)?  2 to 128 rows in bfloat16 (option ``fused_residual``)."""
+    # one row: the norm in the consumer's prologue (norm_fusable) measured faster (506 against 492 tok/s)
+    if dtype != torch.bfloat16 or not OPTIONS.fused_residual or K <= 0 or M <= PROLOGUE_NORM_MAX_ROWS:
         return False
     return _weight_stream_kernel(M, N, K, dtype, dtype) is not None
 

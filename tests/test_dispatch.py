@@ -14,8 +14,8 @@ def pick(M, N, K, dtype=BF):
 def test_weight_streaming_kernel_by_rows_and_size():
     qkv, o, gate_up, down, head = (6144, 2560), (2560, 4096), (19456, 2560), (2560, 9728), (151936, 2560)
     for shape in (qkv, o, gate_up, down, head):
-        assert pick(1, *shape) == "skinny" and pick(2, *shape) == "skinny"       # one or two rows: mma.sync throughout
-    for M in (3, 8):
+        assert pick(1, *shape) == "skinny"                                        # one row: mma.sync throughout
+    for M in (2, 3, 8):
         assert pick(M, *qkv) == "ws" and pick(M, *gate_up) == "ws" and pick(M, *down) == "ws"
         assert pick(M, *o) == "skinny"                                            # under 15 M elements
         assert pick(M, *head) == "skinny"                                         # more outputs than the tcgen05 stream takes
@@ -31,15 +31,16 @@ def test_weight_streaming_kernel_by_rows_and_size():
 def test_sizes_and_dtypes_the_fast_products_refuse():
     assert pick(8, 64, 100) is None                      # K no multiple of 8: the plain product
     assert pick(8, 64, 72) == "ws"                       # K a multiple of 8 but not of 32: only the tcgen05 stream
-    assert pick(2, 64, 72) == "ws"
+    assert pick(1, 64, 72) == "ws"
     assert pick(8, 64, 64, torch.float32) is None        # the 32-bit path has its own kernels
     with ops.options(gemm_ws=False):
         assert pick(8, 19456, 2560) == "skinny" and pick(64, 19456, 2560) is None and pick(8, 64, 72) is None
 
 
 def test_which_products_add_themselves_into_the_residual_stream():
-    assert not ops.residual_product_fusable(1, 2560, 4096, BF) and not ops.residual_product_fusable(2, 2560, 9728, BF)
-    assert all(ops.residual_product_fusable(M, 2560, 4096, BF) for M in (3, 8, 16, 17, 64, 128))
+    assert not ops.residual_product_fusable(1, 2560, 4096, BF) and not ops.residual_product_fusable(1, 2560, 9728, BF)
+    assert all(ops.residual_product_fusable(M, 2560, 4096, BF) for M in (2, 3, 8, 16, 17, 64, 128))
+    assert ops.norm_fusable(1, 2560, BF) and not ops.norm_fusable(2, 2560, BF)
     assert not ops.residual_product_fusable(129, 2560, 4096, BF)
     assert not ops.residual_product_fusable(8, 2560, 4096, torch.float32)
     with ops.options(fused_residual=False):
