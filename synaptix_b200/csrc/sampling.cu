@@ -221,8 +221,132 @@ __device__ __forceinline__ uint32_t philox_word(uint32_t k0, uint32_t k1, uint32
 }
 
 // ---------------------------------------------------------------------------------------
-// temperature / top-k / top-p / min-p / multinomial, one block per row
+// temperature / top-k / top-p / min-p / multinomial, one block per row.
+//
+// Every cut-off is found by bisection on the values' keys, FOUR BITS a pass: a pass counts (top-k) or weighs
+// (top-p) the values against 15 thresholds at once, so a cut-off costs 8 passes over the row instead of 32, and a
+// pass reads the row 16 bytes a thread with several loads on the way (one 4-byte load at a time left a block at
+// 20 GB/s: a draw with top-k and top-p took 2 ms for 151,936 logits, whatever the number of rows).  When top-k
+// keeps few values (at most SAMPLE_LIST of them, ties included) they are gathered into shared memory in index
+// order and top-p, min-p and the draw work on that list.  Counts are integers and sums are added in a fixed
+// order (a thread's own elements, lanes by butterfly, warps in index order), so a row's result depends on
+// nothing but the row.
 // ---------------------------------------------------------------------------------------
+#define SAMPLE_LIST 2048
+#define SAMPLE_WARPS (SAMPLE_THREADS / 32)
+
+// f(i, x) for every element of the row, x = logit / temperature; 16-byte loads, four of them on the way
+template <typename F>
+__device__ __forceinline__ void sample_for_each(const float* __restrict__ row, int V, float temperature, bool divide, F f) {
+  const int tid = threadIdx.x;
+  if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const float4* r4 = reinterpret_cast<const float4*>(row);
+    const int n4 = V >> 2;
+    for (int j0 = tid; j0 < n4; j0 += 4 * SAMPLE_THREADS) {
+      float4 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = j0 + u * SAMPLE_THREADS;
+        q[u] = j < n4 ? r4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = j0 + u * SAMPLE_THREADS;
+        if (j < n4) {
+          const float e[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) f(4 * j + c, divide ? e[c] / temperature : e[c]);
+        }
+      }
+    }
+  } else {
+    for (int i = tid; i < V; i += SAMPLE_THREADS) f(i, divide ? row[i] / temperature : row[i]);
+  }
+}
+// the same over a list in shared memory
+template <typename F>
+__device__ __forceinline__ void sample_for_list(const float* xv, int n, F f) {
+  for (int i = threadIdx.x; i < n; i += SAMPLE_THREADS) f(i, xv[i]);
+}
+
+// 15 block-wide sums at once, each in a fixed order; every thread gets them in out[15].  red: [SAMPLE_WARPS][16] + [16]
+template <typename T>
+__device__ __forceinline__ void block_sum15(const T (&v)[15], T* red, T (&out)[15]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  T w[15];
+#pragma unroll
+  for (int j = 0; j < 15; ++j) {
+    w[j] = v[j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) w[j] += __shfl_xor_sync(0xffffffffu, w[j], o);
+  }
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int j = 0; j < 15; ++j) red[warp * 16 + j] = w[j];
+  }
+  __syncthreads();
+  if (threadIdx.x < 15) {
+    T sum = 0;
+    for (int i = 0; i < SAMPLE_WARPS; ++i) sum += red[i * 16 + threadIdx.x];
+    red[SAMPLE_WARPS * 16 + threadIdx.x] = sum;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 15; ++j) out[j] = red[SAMPLE_WARPS * 16 + j];
+}
+
+// Largest key t with count(key >= t) >= k over the elements the walk visits (0 if even key 1 has fewer), and that count
+template <typename W>
+__device__ __forceinline__ uint32_t sample_kth_key(W walk, int k, int* red, int& kept) {
+  uint32_t t = 0u;
+  kept = 0;
+  for (int shift = 28; shift >= 0; shift -= 4) {
+    int c[15];
+#pragma unroll
+    for (int j = 0; j < 15; ++j) c[j] = 0;
+    walk([&](int, float x) {
+      const uint32_t key = order_key(x);
+#pragma unroll
+      for (int j = 0; j < 15; ++j) c[j] += key >= (t | ((uint32_t)(j + 1) << shift));
+    });
+    int tot[15];
+    block_sum15(c, red, tot);
+    int best = 0;
+#pragma unroll
+    for (int j = 0; j < 15; ++j)
+      if (tot[j] >= k) { best = j + 1; kept = tot[j]; }
+    t |= (uint32_t)best << shift;
+  }
+  return t;
+}
+
+// Largest key t with mass(key > t) > thresh, the mass being sum of exp(x - mx) over visited elements with live(x)
+template <typename W, typename L>
+__device__ __forceinline__ uint32_t sample_mass_key(W walk, L live, float mx, float thresh, float* red) {
+  uint32_t t = 0u;
+  for (int shift = 28; shift >= 0; shift -= 4) {
+    float g[15];
+#pragma unroll
+    for (int j = 0; j < 15; ++j) g[j] = 0.f;
+    walk([&](int, float x) {
+      if (!live(x)) return;
+      const uint32_t key = order_key(x);
+      const float e = expf(x - mx);
+#pragma unroll
+      for (int j = 0; j < 15; ++j) g[j] += key > (t | ((uint32_t)(j + 1) << shift)) ? e : 0.f;
+    });
+    float tot[15];
+    block_sum15(g, red, tot);
+    int best = 0;
+#pragma unroll
+    for (int j = 0; j < 15; ++j)
+      if (tot[j] > thresh) best = j + 1;
+    t |= (uint32_t)best << shift;
+  }
+  return t;
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS) sample_rows_kernel(
     const float* __restrict__ logits, int* __restrict__ out, int V, float temperature, int top_k,
     float top_p, float min_p, uint32_t seed_lo, uint32_t seed_hi, const int* __restrict__ seq_index,
@@ -230,7 +354,11 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_rows_kernel(
   __shared__ float red[33];
   __shared__ float red_v[33];
   __shared__ int red_i[33];
+  __shared__ float red15f[SAMPLE_WARPS * 16 + 16];
+  __shared__ int red15i[SAMPLE_WARPS * 16 + 16];
   __shared__ float chunk_excl[SAMPLE_THREADS];
+  __shared__ float list_x[SAMPLE_LIST];
+  __shared__ int list_i[SAMPLE_LIST];
   __shared__ int found;
   const int r = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (size_t)r * V;
@@ -241,68 +369,145 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_rows_kernel(
     return;
   }
   const bool divide = temperature != 1.0f;
-#define XVAL(i) (divide ? row[i] / temperature : row[i])
+  auto walk_row = [&](auto f) { sample_for_each(row, V, temperature, divide, f); };
 
   // maximum
   float mx = -INFINITY;
-  for (int i = tid; i < V; i += SAMPLE_THREADS) {
-    float v = XVAL(i);
-    if (v == v) mx = fmaxf(mx, v);
-  }
+  walk_row([&](int, float v) { if (v == v) mx = fmaxf(mx, v); });
   mx = block_max(mx, red);
 
   // top-k: largest key tk with count(key >= tk) >= k
   uint32_t tk = 0u;
+  int n_list = -1;                  // >= 0: the kept values are in the list
   if (top_k > 0 && top_k < V) {
-    for (int bit = 31; bit >= 0; --bit) {
-      const uint32_t cand = tk | (1u << bit);
-      int c = 0;
-      for (int i = tid; i < V; i += SAMPLE_THREADS) c += order_key(XVAL(i)) >= cand;
-      c = block_sum_int(c, red_i);
-      if (c >= top_k) tk = cand;
+    int kept = 0;
+    tk = sample_kth_key(walk_row, top_k, red15i, kept);
+    if (kept > 0 && kept <= SAMPLE_LIST) {
+      // gather them in index order: every thread its own contiguous run of the row
+      const int chunk = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+      const int b0 = min(V, tid * chunk), e0 = min(V, b0 + chunk);
+      int mine = 0;
+      for (int i = b0; i < e0; ++i) {
+        const float v = divide ? row[i] / temperature : row[i];
+        mine += order_key(v) >= tk && v > -INFINITY;
+      }
+      // exclusive scan over the threads: lanes, then warps in order
+      const int lane = tid & 31, warp = tid >> 5;
+      int incl = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      __syncthreads();
+      if (lane == 31) red_i[warp] = incl;
+      __syncthreads();
+      if (tid == 0) {
+        int run = 0;
+        for (int w = 0; w < SAMPLE_WARPS; ++w) { const int c = red_i[w]; red_i[w] = run; run += c; }
+        red_i[32] = run;
+      }
+      __syncthreads();
+      int at = red_i[warp] + incl - mine;
+      n_list = red_i[32];           // <= kept: values equal to -inf are not listed
+      for (int i = b0; i < e0; ++i) {
+        const float v = divide ? row[i] / temperature : row[i];
+        if (order_key(v) >= tk && v > -INFINITY) { list_x[at] = v; list_i[at] = i; ++at; }
+      }
+      __syncthreads();
     }
   }
-  // top-p: largest key tp with mass(key > tp) > top_p * mass(all kept by top-k); keep key > tp
+
   bool use_tp = false;
   uint32_t tp = 0u;
+  const int chunk_row = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+  int pick_index = -1;              // thread 0 holds the result
+  if (n_list >= 0) {
+    // ------------------------------------------------------------ the kept values are few: work on the list
+    auto walk_list = [&](auto f) { sample_for_list(list_x, n_list, f); };
+    if (top_p < 1.0f) {
+      float sm = 0.f, g0 = 0.f;
+      walk_list([&](int, float v) { const float e = expf(v - mx); sm += e; if (order_key(v) > 0u) g0 += e; });
+      sm = block_sum(sm, red);
+      g0 = block_sum(g0, red);
+      const float thresh = top_p * sm;
+      if (g0 > thresh) {
+        use_tp = true;
+        tp = sample_mass_key(walk_list, [](float) { return true; }, mx, thresh, red15f);
+      }
+    }
+    auto kept_l = [&](float v) { return (!use_tp || order_key(v) > tp) && (!(min_p > 0.f) || expf(v - mx) >= min_p); };
+    const int chunk = (n_list + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+    const int b = min(n_list, tid * chunk), e = min(n_list, b + chunk);
+    float cs = 0.f;
+    for (int i = b; i < e; ++i)
+      if (kept_l(list_x[i])) cs += expf(list_x[i] - mx);
+    chunk_excl[tid] = cs;
+    if (tid == 0) found = -1;
+    __syncthreads();
+    if (tid == 0) {
+      float run = 0.f;
+      for (int t = 0; t < SAMPLE_THREADS; ++t) { const float c = chunk_excl[t]; chunk_excl[t] = run; run += c; }
+      red[32] = run;
+    }
+    __syncthreads();
+    const float total = red[32];
+    const uint32_t word = philox_word(seed_lo, seed_hi, (uint32_t)(step[r] >> 2), (uint32_t)seq_index[r], step[r] & 3);
+    const float u = (float)(double)word / 4294967296.0f;          // (multinomial.rs:30-32)
+    if (tid == 0 && u_out) u_out[r] = u;
+    const float target = u * total;
+    const float lo = chunk_excl[tid];
+    if (cs > 0.f && target >= lo && target < lo + cs) {
+      float run = lo;
+      int pick = -1, last = -1;
+      for (int i = b; i < e; ++i) {
+        if (!kept_l(list_x[i])) continue;
+        last = i;
+        run += expf(list_x[i] - mx);
+        if (target < run) { pick = i; break; }
+      }
+      atomicMax(&found, pick < 0 ? last : pick);      // at most one thread gets here with target in its range
+    }
+    __syncthreads();
+    const int first_try = found;
+    __syncthreads();
+    if (first_try < 0) {                // u == 1 or rounding past the end: the last kept value
+      int last = -1;
+      for (int i = b; i < e; ++i)
+        if (kept_l(list_x[i])) last = i;
+      if (last >= 0) atomicMax(&found, last);
+      __syncthreads();
+    }
+    if (tid == 0) pick_index = found < 0 ? V - 1 : list_i[found];
+    if (tid == 0) out[r] = pick_index;
+    return;
+  }
+
+  // -------------------------------------------------------------- no top-k, or it keeps many: work on the row
+  auto in_k = [&](float v) { return order_key(v) >= tk && v > -INFINITY; };
   if (top_p < 1.0f) {
-    float s = 0.f;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) {
-      const float v = XVAL(i);
-      if (order_key(v) >= tk && v > -INFINITY) s += expf(v - mx);
-    }
-    s = block_sum(s, red);
-    const float thresh = top_p * s;
-    // mass(key > 0) is everything except keys equal to 0 (never a finite value)
-    float g0 = 0.f;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) {
-      const float v = XVAL(i);
-      const uint32_t k = order_key(v);
-      if (k >= tk && k > 0u && v > -INFINITY) g0 += expf(v - mx);
-    }
+    float sm = 0.f, g0 = 0.f;
+    walk_row([&](int, float v) {
+      if (!in_k(v)) return;
+      const float e = expf(v - mx);
+      sm += e;
+      if (order_key(v) > 0u) g0 += e;       // mass(key > 0) is everything except keys equal to 0 (never a finite value)
+    });
+    sm = block_sum(sm, red);
     g0 = block_sum(g0, red);
+    const float thresh = top_p * sm;
     if (g0 > thresh) {
       use_tp = true;
-      for (int bit = 31; bit >= 0; --bit) {
-        const uint32_t cand = tp | (1u << bit);
-        float g = 0.f;
-        for (int i = tid; i < V; i += SAMPLE_THREADS) {
-          const float v = XVAL(i);
-          const uint32_t k = order_key(v);
-          if (k >= tk && k > cand && v > -INFINITY) g += expf(v - mx);
-        }
-        g = block_sum(g, red);
-        if (g > thresh) tp = cand;
-      }
+      tp = sample_mass_key(walk_row, in_k, mx, thresh, red15f);
     }
   }
   // min-p: with the maximum's probability as reference, keep exp(x - max) >= min_p
 #define KEPT(v) (order_key(v) >= tk && (!use_tp || order_key(v) > tp) && (v) > -INFINITY && \
                  (!(min_p > 0.f) || expf((v) - mx) >= min_p))
+#define XVAL(i) (divide ? row[i] / temperature : row[i])
 
   // multinomial over the kept values: contiguous chunks per thread, exclusive scan of chunk sums
-  const int chunk = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
-  const int b = tid * chunk, e = min(V, b + chunk);
+  const int b = min(V, tid * chunk_row), e = min(V, b + chunk_row);
   float cs = 0.f;
   for (int i = b; i < e; ++i) {
     const float v = XVAL(i);
