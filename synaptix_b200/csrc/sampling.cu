@@ -563,13 +563,340 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_rows_kernel(
 #undef KEPT
 }
 
-extern "C" int sx_sample_rows(const float* logits, int* out, int R, int V, float temperature, int top_k,
-                              float top_p, float min_p, unsigned long long seed, const int* seq_index,
-                              const int* step, float* u_out, cudaStream_t stream) {
+// ---------------------------------------------------------------------------------------
+// The same draw with a row spread over a CLUSTER of blocks, for wide vocabularies.
+//
+// One block per row leaves all but a few SMs idle and walks 150 thousand logits with one SM's issue rate: after
+// the loads were widened the passes were bound by instructions (a pass of 15 compare-and-adds per value took
+// 60 us a row).  Here the row is cut into contiguous parts, one per block of a cluster; a block turns its part
+// into keys ONCE (the division by the temperature included) and keeps them in shared memory, so every later pass
+// reads shared memory.  A pass sorts each value into one of 16 bins (its next four key bits relative to the
+// threshold found so far), a thread adding into bins of its own in shared memory, so a value costs a handful of
+// instructions instead of 15 compare-and-adds; suffix sums of the bins give the 15 counts or masses.  Blocks
+// exchange their partial results through one another's shared memory: every block writes its words, one
+// cluster barrier, every block reads all of them and combines them in rank order, so all blocks hold the same
+// bits and take the same branches.  Two buffers in turn make one barrier an exchange enough.
+// The draw walks the kept values in index order: rank by rank, and in a block thread by thread over contiguous runs.
+// ---------------------------------------------------------------------------------------
+#define SC_THREADS 512
+#define SC_WARPS (SC_THREADS / 32)
+#define SC_MAX_CLUSTER 8
+#define SC_KEY_NEG_INF 0x007fffffu      // order_key(-inf): no key is smaller
+
+__device__ __forceinline__ float key_value(uint32_t key) {     // order_key's inverse
+  return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+__device__ __forceinline__ uint32_t cluster_load_u32(const uint32_t* local, uint32_t rank) {
+  uint32_t a = (uint32_t)__cvta_generic_to_shared(local), r, v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];\n" : "=r"(v) : "r"(r) : "memory");
+  return v;
+}
+
+struct ScShared {
+  uint32_t xch[2][16];                    // this block's words of the running exchange, two buffers in turn
+  uint32_t gath[SC_MAX_CLUSTER][16];      // every block's words of the last exchange
+  uint32_t red[SC_WARPS * 16];
+  float excl[SC_THREADS];
+  int found[2];
+};
+
+// Every block has written n <= 16 words into sh.xch[parity]; afterwards sh.gath[c][j] holds block c's word j.
+__device__ __forceinline__ void sc_exchange(ScShared& sh, int& parity, int n, int C) {
+  cluster_sync_all();
+  const int tid = threadIdx.x;
+  if (tid < C * 16) {
+    const int c = tid >> 4, j = tid & 15;
+    if (j < n) sh.gath[c][j] = cluster_load_u32(&sh.xch[parity][j], (uint32_t)c);
+  }
+  __syncthreads();
+  parity ^= 1;
+}
+
+// 15 sums over the block, lanes by butterfly and warps in index order, left in sh.xch[parity][0..15)
+template <typename T>
+__device__ __forceinline__ void sc_block_sum15(const T (&v)[15], ScShared& sh, int parity) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  T* red = reinterpret_cast<T*>(sh.red);
+#pragma unroll
+  for (int j = 0; j < 15; ++j) {
+    T w = v[j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
+    if (lane == 0) red[warp * 16 + j] = w;
+  }
+  __syncthreads();
+  if (threadIdx.x < 15) {
+    T sum = 0;
+    for (int i = 0; i < SC_WARPS; ++i) sum += red[i * 16 + threadIdx.x];
+    reinterpret_cast<T*>(sh.xch[parity])[threadIdx.x] = sum;
+  }
+}
+
+// one float summed over the block and then over the cluster, the same bits in every block
+__device__ __forceinline__ float sc_cluster_sum(float v, ScShared& sh, int& parity, int C) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* red = reinterpret_cast<float*>(sh.red);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int i = 0; i < SC_WARPS; ++i) s += red[i];
+    sh.xch[parity][0] = __float_as_uint(s);
+  }
+  sc_exchange(sh, parity, 1, C);
+  float s = 0.f;
+  for (int c = 0; c < C; ++c) s += __uint_as_float(sh.gath[c][0]);
+  return s;
+}
+
+__global__ void __launch_bounds__(SC_THREADS) sample_rows_cluster_kernel(
+    const float* __restrict__ logits, int* __restrict__ out, int V, int part, float temperature, int top_k,
+    float top_p, float min_p, uint32_t seed_lo, uint32_t seed_hi, const int* __restrict__ seq_index,
+    const int* __restrict__ step, float* __restrict__ u_out) {
+  extern __shared__ __align__(16) uint32_t sc_dyn[];
+  __shared__ ScShared sh;
+  uint32_t* keys = sc_dyn;                                   // [part]
+  uint32_t* bins = sc_dyn + part;                            // [16][SC_THREADS]; part is a multiple of 4
+  float* bins_f = reinterpret_cast<float*>(bins);
+  const int tid = threadIdx.x;
+  const int C = (int)gridDim.x, rank = (int)cluster_rank(), r = blockIdx.y;
+  const float* row = logits + (size_t)r * V;
+  const int begin = min(V, rank * part), n = min(V, begin + part) - begin;
+  const bool divide = temperature != 1.0f;
+  int parity = 0;
+
+  // ---- this block's part as keys, and the row's maximum
+  uint32_t kmax = SC_KEY_NEG_INF;
+  if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const float4* r4 = reinterpret_cast<const float4*>(row + begin);
+    uint4* k4 = reinterpret_cast<uint4*>(keys);
+    const int n4 = n >> 2;
+#pragma unroll 4
+    for (int j = tid; j < n4; j += SC_THREADS) {
+      const float4 q = r4[j];
+      uint4 k;
+      k.x = order_key(divide ? q.x / temperature : q.x);
+      k.y = order_key(divide ? q.y / temperature : q.y);
+      k.z = order_key(divide ? q.z / temperature : q.z);
+      k.w = order_key(divide ? q.w / temperature : q.w);
+      k4[j] = k;
+      kmax = max(max(kmax, k.x), max(k.y, max(k.z, k.w)));
+    }
+  } else {
+    for (int i = tid; i < n; i += SC_THREADS) {
+      const float x = row[begin + i];
+      const uint32_t k = order_key(divide ? x / temperature : x);
+      keys[i] = k;
+      kmax = max(kmax, k);
+    }
+  }
+  {
+    const int lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+    if (lane == 0) sh.red[warp] = kmax;
+    __syncthreads();                                         // the keys are written, too
+    if (tid == 0) {
+      uint32_t m = sh.red[0];
+      for (int i = 1; i < SC_WARPS; ++i) m = max(m, sh.red[i]);
+      sh.xch[parity][0] = m;
+    }
+    sc_exchange(sh, parity, 1, C);
+    kmax = sh.gath[0][0];
+    for (int c = 1; c < C; ++c) kmax = max(kmax, sh.gath[c][0]);
+  }
+  const float mx = key_value(kmax);
+
+  // ---- top-k: the largest key tk with count(key >= tk) >= k
+  uint32_t tk = 0u;
+  if (top_k > 0 && top_k < V) {
+    for (int shift = 28; shift >= 0; shift -= 4) {
+#pragma unroll
+      for (int b = 1; b < 16; ++b) bins[b * SC_THREADS + tid] = 0u;
+      for (int i = tid; i < n; i += SC_THREADS) {
+        const uint32_t key = keys[i];
+        if (key >= tk) {
+          const uint32_t b = min((key - tk) >> shift, 15u);
+          if (b) bins[b * SC_THREADS + tid] += 1u;
+        }
+      }
+      int c[15];
+      int run = 0;
+#pragma unroll
+      for (int b = 15; b >= 1; --b) { run += (int)bins[b * SC_THREADS + tid]; c[b - 1] = run; }
+      sc_block_sum15(c, sh, parity);
+      sc_exchange(sh, parity, 15, C);
+      int best = 0;
+#pragma unroll
+      for (int j = 0; j < 15; ++j) {
+        int tot = 0;
+        for (int cc = 0; cc < C; ++cc) tot += (int)sh.gath[cc][j];
+        if (tot >= top_k) best = j + 1;
+      }
+      tk |= (uint32_t)best << shift;
+    }
+  }
+  const uint32_t low = max(tk, SC_KEY_NEG_INF + 1u);          // kept by top-k, and not -inf
+
+  // ---- top-p: the largest key tp with mass(key > tp) > top_p * mass(all kept by top-k)
+  bool use_tp = false;
+  uint32_t tp = 0u;
+  if (top_p < 1.0f) {
+    float sm = 0.f;
+    for (int i = tid; i < n; i += SC_THREADS) {
+      const uint32_t key = keys[i];
+      if (key >= low) sm += expf(key_value(key) - mx);
+    }
+    sm = sc_cluster_sum(sm, sh, parity, C);
+    const float thresh = top_p * sm;
+    if (sm > thresh) {
+      use_tp = true;
+      for (int shift = 28; shift >= 0; shift -= 4) {
+#pragma unroll
+        for (int b = 1; b < 16; ++b) bins_f[b * SC_THREADS + tid] = 0.f;
+        for (int i = tid; i < n; i += SC_THREADS) {
+          const uint32_t key = keys[i];
+          if (key >= low && key - 1u >= tp) {                // key > tp + j * 2^shift  <=>  bin of (key - 1) >= j
+            const uint32_t b = min((key - 1u - tp) >> shift, 15u);
+            if (b) bins_f[b * SC_THREADS + tid] += expf(key_value(key) - mx);
+          }
+        }
+        float g[15];
+        float run = 0.f;
+#pragma unroll
+        for (int b = 15; b >= 1; --b) { run += bins_f[b * SC_THREADS + tid]; g[b - 1] = run; }
+        sc_block_sum15(g, sh, parity);
+        sc_exchange(sh, parity, 15, C);
+        int best = 0;
+#pragma unroll
+        for (int j = 0; j < 15; ++j) {
+          float tot = 0.f;
+          for (int cc = 0; cc < C; ++cc) tot += __uint_as_float(sh.gath[cc][j]);
+          if (tot > thresh) best = j + 1;
+        }
+        tp |= (uint32_t)best << shift;
+      }
+    }
+  }
+
+  // ---- the draw over the kept values, in index order
+  auto kept = [&](uint32_t key) {
+    return key >= low && (!use_tp || key > tp) && (!(min_p > 0.f) || expf(key_value(key) - mx) >= min_p);
+  };
+  const int chunk = (n + SC_THREADS - 1) / SC_THREADS;
+  const int b0 = min(n, tid * chunk), e0 = min(n, b0 + chunk);
+  float cs = 0.f;
+  int last = -1;
+  for (int i = b0; i < e0; ++i) {
+    const uint32_t key = keys[i];
+    if (kept(key)) { cs += expf(key_value(key) - mx); last = i; }
+  }
+  sh.excl[tid] = cs;
+  if (tid == 0) { sh.found[0] = -1; sh.found[1] = -1; }
+  __syncthreads();
+  if (tid == 0) {
+    float run = 0.f;
+    for (int t = 0; t < SC_THREADS; ++t) { const float c = sh.excl[t]; sh.excl[t] = run; run += c; }
+    sh.xch[parity][0] = __float_as_uint(run);
+  }
+  sc_exchange(sh, parity, 1, C);
+  float base = 0.f, total = 0.f;
+  for (int c = 0; c < C; ++c) {
+    if (c == rank) base = total;
+    total += __uint_as_float(sh.gath[c][0]);
+  }
+  const uint32_t word = philox_word(seed_lo, seed_hi, (uint32_t)(step[r] >> 2), (uint32_t)seq_index[r], step[r] & 3);
+  const float u = (float)(double)word / 4294967296.0f;          // (multinomial.rs:30-32)
+  const float target = u * total;
+  const float lo = base + sh.excl[tid];
+  if (cs > 0.f && target >= lo) {
+    // the last kept value of every run that starts at or before the target: the answer if no run claims the
+    // target (u == 1, or rounding between two runs' ends)
+    atomicMax(&sh.found[1], begin + last);
+    if (target < lo + cs) {
+      float run = lo;
+      int pick = last;
+      for (int i = b0; i < e0; ++i) {
+        const uint32_t key = keys[i];
+        if (!kept(key)) continue;
+        run += expf(key_value(key) - mx);
+        if (target < run) { pick = i; break; }
+      }
+      atomicMax(&sh.found[0], begin + pick);
+    }
+  }
+  __syncthreads();
+  if (tid < 2) sh.xch[parity][tid] = (uint32_t)sh.found[tid];
+  sc_exchange(sh, parity, 2, C);
+  if (rank == 0 && tid == 0) {
+    int claim = -1, before = -1;
+    for (int c = 0; c < C; ++c) { claim = max(claim, (int)sh.gath[c][0]); before = max(before, (int)sh.gath[c][1]); }
+    out[r] = claim >= 0 ? claim : (before >= 0 ? before : V - 1);
+    if (u_out) u_out[r] = u;
+  }
+  // no block leaves while another may still read its words
+  cluster_sync_all();
+}
+
+static size_t sc_smem_bytes(int part) { return ((size_t)part + 16 * SC_THREADS) * sizeof(uint32_t); }
+
+// blocks a row: 0 = this row width goes to the one-block kernel
+static int sc_pick_cluster(int V) {
+  if (V < 8192) return 0;
+  const int part = (((V + SC_MAX_CLUSTER - 1) / SC_MAX_CLUSTER) + 3) & ~3;
+  return sc_smem_bytes(part) + sizeof(ScShared) + 1024 <= 227u * 1024u ? SC_MAX_CLUSTER : 0;
+}
+
+extern "C" int sx_sample_rows_cluster(const float* logits, int* out, int R, int V, float temperature, int top_k,
+                                      float top_p, float min_p, unsigned long long seed, const int* seq_index,
+                                      const int* step, float* u_out, int cluster, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (V <= 0 || !(temperature > 0.f) || R > 65535) return SX_ERR_SIZE;
+  if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return SX_ERR_SIZE;
+  const int part = (((V + cluster - 1) / cluster) + 3) & ~3;
+  const size_t smem = sc_smem_bytes(part);
+  if (smem + sizeof(ScShared) + 1024 > 227u * 1024u) return SX_ERR_SIZE;
+  auto kern = sample_rows_cluster_kernel;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)cluster, (unsigned)R);
+  cfg.blockDim = dim3(SC_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, logits, out, V, part, temperature, top_k, top_p, min_p,
+                                 (uint32_t)(seed & 0xffffffffull), (uint32_t)(seed >> 32), seq_index, step, u_out);
+}
+
+extern "C" int sx_sample_rows_block(const float* logits, int* out, int R, int V, float temperature, int top_k,
+                                    float top_p, float min_p, unsigned long long seed, const int* seq_index,
+                                    const int* step, float* u_out, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0) return SX_ERR_SIZE;
   sample_rows_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(
       logits, out, V, temperature, top_k, top_p, min_p, (uint32_t)(seed & 0xffffffffull),
       (uint32_t)(seed >> 32), seq_index, step, u_out);
   return sx_launch_status();
+}
+
+extern "C" int sx_sample_rows(const float* logits, int* out, int R, int V, float temperature, int top_k,
+                              float top_p, float min_p, unsigned long long seed, const int* seq_index,
+                              const int* step, float* u_out, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (V <= 0) return SX_ERR_SIZE;
+  if (temperature > 0.f && R <= 65535) {
+    const int cluster = sc_pick_cluster(V);
+    if (cluster) return sx_sample_rows_cluster(logits, out, R, V, temperature, top_k, top_p, min_p, seed, seq_index, step, u_out, cluster, stream);
+  }
+  return sx_sample_rows_block(logits, out, R, V, temperature, top_k, top_p, min_p, seed, seq_index, step, u_out, stream);
 }

@@ -48,15 +48,32 @@ def apply_penalties(logits: torch.Tensor, hist: torch.Tensor, hist_len: torch.Te
 
 def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float,
                 seed: int, seq_index: torch.Tensor, step: torch.Tensor,
-                out: Optional[torch.Tensor] = None, u_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, u_out: Optional[torch.Tensor] = None,
+                cluster: Optional[int] = None) -> torch.Tensor:
     """int32 ``[rows]``: argmax if ``temperature <= 0``; else temperature, top-k, top-p, min-p
-    and a multinomial draw with the Philox word (``seed``, ``seq_index[r]``, ``step[r]``)."""
+    and a multinomial draw with the Philox word (``seed``, ``seq_index[r]``, ``step[r]``).
+
+    ``cluster``: None lets the library choose between its two kernels by the row's width (one block a row, or a
+    row spread over a cluster of blocks); 0 asks for the one-block kernel, 1, 2, 4 or 8 for that many blocks a row."""
     R, V = _rows(logits)
     require_cuda(seq_index, step, out, u_out)
     if seq_index.dtype != torch.int32 or step.dtype != torch.int32:
         raise KernelError("sample_rows: seq_index and step are int32")
     if out is None:
         out = torch.empty(R, dtype=torch.int32, device=logits.device)
+    if cluster:
+        check(fn("sampling", "sx_sample_rows_cluster")(ptr(logits), ptr(out), c_int(R), c_int(V), c_float(temperature),
+                                                       c_int(top_k), c_float(top_p), c_float(min_p),
+                                                       c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), ptr(seq_index),
+                                                       ptr(step), ptr(u_out), c_int(cluster), stream()),
+              "sample_rows")
+        return out
+    if cluster == 0:
+        check(fn("sampling", "sx_sample_rows_block")(ptr(logits), ptr(out), c_int(R), c_int(V), c_float(temperature),
+                                                     c_int(top_k), c_float(top_p), c_float(min_p),
+                                                     c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), ptr(seq_index),
+                                                     ptr(step), ptr(u_out), stream()), "sample_rows")
+        return out
     check(fn("sampling", "sx_sample_rows")(ptr(logits), ptr(out), c_int(R), c_int(V), c_float(temperature),
                                            c_int(top_k), c_float(top_p), c_float(min_p),
                                            c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), ptr(seq_index), ptr(step),

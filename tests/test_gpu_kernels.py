@@ -285,15 +285,18 @@ def test_penalties_match_the_plain_processors():
 @pytest.mark.parametrize("kw", [dict(temperature=1.0), dict(temperature=0.7), dict(temperature=0.8, top_k=5),
                                 dict(temperature=1.2, top_p=0.6), dict(temperature=1.0, min_p=0.2),
                                 dict(temperature=0.9, top_k=40, top_p=0.8, min_p=0.05)])
-def test_sample_rows_draws_from_the_filtered_distribution(kw):
+@pytest.mark.parametrize("cluster,V", [(0, 3001), (1, 3001), (4, 3001), (8, 3002), (8, 3004), (None, 20012), (None, 20011)])
+def test_sample_rows_draws_from_the_filtered_distribution(kw, cluster, V):
+    """Both kernels (one block a row; a row over a cluster of 1 to 8 blocks), rows whose width is and is not a
+    multiple of four, and the library's own choice for a wide row."""
     from synaptix_b200.ops import sampling as K
-    V, R, seed = 3001, 64, 1234
+    R, seed = 64 if V < 8192 else 12, 1234
     x = torch.randn(R, V) * 2.5
     seq = torch.arange(R, dtype=torch.int32) % 7
     step = torch.arange(R, dtype=torch.int32)
     u_out = torch.empty(R, device="cuda")
     got = K.sample_rows(x.cuda(), kw.get("temperature", 1.0), kw.get("top_k", 0), kw.get("top_p", 1.0),
-                        kw.get("min_p", 0.0), seed, seq.cuda(), step.cuda(), u_out=u_out).tolist()
+                        kw.get("min_p", 0.0), seed, seq.cuda(), step.cuda(), u_out=u_out, cluster=cluster).tolist()
     us = u_out.cpu().tolist()
     for r in range(R):
         u_ref = float(P.uniform_from_u32(P.philox_u32(seed, int(step[r]), int(seq[r]))))
@@ -306,24 +309,38 @@ def test_sample_rows_draws_from_the_filtered_distribution(kw):
         assert lo - 1e-4 <= u_ref <= cum[got[r]] + 1e-4, f"row {r}: u={u_ref} outside [{lo}, {cum[got[r]]}]"
 
 
-def test_sample_rows_kept_sets_match_exactly():
+@pytest.mark.parametrize("cluster,V", [(0, 777), (2, 777), (8, 776), (None, 9000)])
+def test_sample_rows_kept_sets_match_exactly(cluster, V):
     """With a point mass the draw is forced; with top_k=1 it is the argmax, whatever u is."""
     from synaptix_b200.ops import sampling as K
-    x = torch.randn(8, 777)
+    x = torch.randn(8, V)
     z = torch.zeros(8, dtype=torch.int32).cuda()
-    got = K.sample_rows(x.cuda(), 1.0, 1, 1.0, 0.0, 5, z, z).tolist()
+    got = K.sample_rows(x.cuda(), 1.0, 1, 1.0, 0.0, 5, z, z, cluster=cluster).tolist()
     assert got == x.argmax(dim=1).tolist()
-    got = K.sample_rows(x.cuda(), 1.0, 0, 1e-6, 0.0, 5, z, z).tolist()
+    got = K.sample_rows(x.cuda(), 1.0, 0, 1e-6, 0.0, 5, z, z, cluster=cluster).tolist()
     assert got == x.argmax(dim=1).tolist()
-    got = K.sample_rows(x.cuda(), 1.0, 0, 1.0, 1.0, 5, z, z).tolist()
+    got = K.sample_rows(x.cuda(), 1.0, 0, 1.0, 1.0, 5, z, z, cluster=cluster).tolist()
     assert got == x.argmax(dim=1).tolist()
+    # ties at the cut-off are all kept, -inf and NaN never: 3 equal maxima far apart, top_k = 1
+    y = torch.randn(8, V)
+    y[:, 3] = y[:, V // 2] = y[:, V - 1] = 30.0
+    y[:, 5] = float("nan")
+    y[:, 7] = float("-inf")
+    seq = torch.arange(8, dtype=torch.int32).cuda()
+    seen = set()
+    for s in range(6):
+        got = K.sample_rows(y.cuda(), 0.5, 1, 1.0, 0.0, 11, seq, torch.full((8,), s, dtype=torch.int32).cuda(), cluster=cluster).tolist()
+        assert set(got) <= {3, V // 2, V - 1}
+        seen |= set(got)
+    assert seen == {3, V // 2, V - 1}
     got = K.sample_rows(x.cuda(), 0.0, 0, 1.0, 0.0, 5, z, z).tolist()       # temperature 0: greedy
     assert got == x.argmax(dim=1).tolist()
 
 
-def test_sampling_does_not_depend_on_batch_composition():
+@pytest.mark.parametrize("V", [1000, 151936])
+def test_sampling_does_not_depend_on_batch_composition(V):
     from synaptix_b200.ops import sampling as K
-    x = torch.randn(6, 1000) * 2
+    x = torch.randn(6, V) * 2
     seq = torch.tensor([3, 1, 4, 1, 5, 9], dtype=torch.int32)
     step = torch.tensor([2, 7, 1, 8, 2, 8], dtype=torch.int32)
     whole = K.sample_rows(x.cuda(), 0.8, 50, 0.9, 0.0, 99, seq.cuda(), step.cuda()).tolist()

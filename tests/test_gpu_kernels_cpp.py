@@ -222,21 +222,26 @@ def test_sampling_kernels_against_the_cpp_loops():
                dict(temperature=1.0, min_p=0.2), dict(temperature=0.9, top_k=40, top_p=0.8, min_p=0.05), dict(temperature=0.0)):
         args = (kw["temperature"], kw.get("top_k", 0), kw.get("top_p", 1.0), kw.get("min_p", 0.0), seed)
         u_gpu = torch.empty(rows, device="cuda")
-        got = K.sample_rows(x.cuda(), *args, i32(seq), i32(step), u_out=u_gpu).cpu()
         want, u, kept = R.sample_rows(x, *args, seq, step, want_kept=True)
         if kw["temperature"] == 0.0:
-            assert torch.equal(got, want)
+            assert torch.equal(K.sample_rows(x.cuda(), *args, i32(seq), i32(step)).cpu(), want)
             continue
-        assert torch.equal(u_gpu.cpu(), u)
-        # the same token, unless u lies within rounding of an interval's end (the kernel sums in another order)
-        xs = x.double() / kw["temperature"]
-        p = torch.exp(xs - xs.max(1, keepdim=True).values) * kept.double()
-        cum = torch.cumsum(p / p.sum(1, keepdim=True), 1)
-        for r in range(rows):
-            assert kept[r, got[r]] == 1, f"{kw} row {r}: the kernel drew a token the filters drop"
-            if got[r] != want[r]:
-                edge = cum[r, min(got[r], want[r])].item()
-                assert abs(edge - u[r].item()) < 1e-5, f"{kw} row {r}: {got[r]} vs {want[r]}"
+        for cluster in (0, 8):
+            _sampled_like_the_loops(K.sample_rows(x.cuda(), *args, i32(seq), i32(step), u_out=u_gpu, cluster=cluster).cpu(),
+                                    u_gpu, want, u, kept, x, kw)
+
+
+def _sampled_like_the_loops(got, u_gpu, want, u, kept, x, kw):
+    assert torch.equal(u_gpu.cpu(), u)
+    # the same token, unless u lies within rounding of an interval's end (the kernel sums in another order)
+    xs = x.double() / kw["temperature"]
+    p = torch.exp(xs - xs.max(1, keepdim=True).values) * kept.double()
+    cum = torch.cumsum(p / p.sum(1, keepdim=True), 1)
+    for r in range(x.shape[0]):
+        assert kept[r, got[r]] == 1, f"{kw} row {r}: the kernel drew a token the filters drop"
+        if got[r] != want[r]:
+            edge = cum[r, min(got[r], want[r])].item()
+            assert abs(edge - u[r].item()) < 1e-5, f"{kw} row {r}: {got[r]} vs {want[r]}"
 
 
 def test_decode_bookkeeping_kernels_against_the_cpp_loops():
