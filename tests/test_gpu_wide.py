@@ -1,6 +1,7 @@
 """The benchmark model's layer sizes (two layers of them) against the plain implementation, in
 32-bit and in bfloat16, whole and cut: this is where the tensor-core kernels, the split products
 and the fused prologues run at the shapes they were written for."""
+import numpy as np
 import pytest
 import torch
 
@@ -70,3 +71,28 @@ def test_wide_model_greedy_tokens_float32():
     llm = synaptix_b200.LLM(folder("WIDE"), compute_dtype="f32", max_tokens=512)
     outs = llm.generate(prompts, max_new_tokens=4, eos_token_ids=[])
     assert outs == [P.greedy_generate(cfg, W, p, 4) for p in prompts]
+
+
+def test_wide_vocabulary_sampling_in_a_replayed_step_equals_the_eager_one():
+    """At this vocabulary the draw runs in the kernel that spreads a row over a cluster of blocks; a decode session
+    records it into its graph.  Replayed and eager steps draw the same tokens, a request alone the same as in its
+    batch, and every drawn token passes the filters applied to the engine's own logits."""
+    import plain_qwen3 as P
+    import synaptix_b200
+    from synaptix_b200.engine import Entry
+    prompts = [random_tokens(V, n, 90 + n) for n in (3, 17, 66)]
+    kw = dict(max_new_tokens=6, temperature=0.9, top_k=30, top_p=0.85, seed=5, eos_token_ids=[])
+    outs = {}
+    for graphs in (True, False):
+        llm = synaptix_b200.LLM(folder("WIDE"), compute_dtype="f32", max_tokens=1024, graph=graphs)
+        outs[graphs] = llm.generate(prompts, **kw)
+        if graphs:
+            assert llm.generate([prompts[0]], **kw)[0] == outs[True][0]
+    assert outs[True] == outs[False]
+    eng = llm.engine
+    for p, o in zip(prompts, outs[True]):
+        s = eng.open()
+        lg = eng.step([Entry(s, p + o[:-1], list(range(len(p) - 1, len(p) + len(o) - 1)))]).float().cpu().numpy()
+        eng.close(s)
+        for row, t in zip(lg, o):
+            assert np.isfinite(P.processed_logits(row, temperature=0.9, top_k=30, top_p=0.85)[t])
