@@ -40,7 +40,7 @@ def apply_penalties(logits: torch.Tensor, hist: torch.Tensor, hist_len: torch.Te
     require_cuda(hist, hist_len)
     if hist.dtype != torch.int32 or hist_len.dtype != torch.int32 or hist.shape[0] != R:
         raise KernelError("penalties: hist int32 [rows, n], hist_len int32 [rows]")
-    counts = torch.empty((R, V), dtype=torch.int32, device=logits.device)
+    counts = torch.zeros((R, V), dtype=torch.int32, device=logits.device)     # the kernel wants zeros and leaves zeros
     check(fn("sampling", "sx_penalties")(ptr(logits), ptr(counts), ptr(hist), ptr(hist_len), c_int(hist.shape[1]),
                                          c_int(last_n), c_float(repetition), c_float(presence),
                                          c_float(frequency), c_int(R), c_int(V), stream()), "penalties")
