@@ -13,10 +13,12 @@ and out, and its greedy tokens must equal the timed run's;
 ``prefill`` = one 2,048-token prompt step (median of 5, timed before the decode runs and again after them: the
 faster of the two, with both times beside it); ``points`` = decoding at batch 1 and 64; ``roofline`` =
 bytes a decode step has to read (every weight once, the cache of the live sequences) over
-its time, against the measured copy bandwidth.  Inputs are larger than L2 (a step streams
+its time, against the measured copy bandwidth; ``further`` = short runs at contexts 8,192 and 16,384 and at
+the 8B and 32B shapes (all their layers), made after everything else.  Inputs are larger than L2 (a step streams
 all weights, ~8 GB), so L2 is not flushed between steps.
 """
 import argparse
+import gc
 import json
 import os
 import subprocess
@@ -132,6 +134,85 @@ def prefill_flops(cfg, layers, T):
     return layers * (mat + att) + 2 * V * H
 
 
+def further_points(torch, pk, graph):
+    """Decoding and the prompt step at further sizes, one short run each: the 4B shape at contexts 8,192 and 16,384
+    (batch 1 and 8), and the 8B and 32B shapes at context 4,096 (batch 8, all their layers).  Flat: name -> number;
+    ``*_hbm_frac`` is the decode step's bytes over its time over the copy bandwidth, ``*_prefill_frac`` the
+    2,048-token prompt step's flops over its time over the burst peak."""
+    from synaptix_b200.api import LLM
+    from synaptix_b200.config import Qwen3Config
+    from synaptix_b200.engine import DecodeRow, Entry
+    from synaptix_b200.models import model_skeleton
+    from synaptix_b200.parts import Runtime
+    from synaptix_b200.weights import RandomSource
+    out = {}
+    K, REGIONS, TOTAL = 20, 5, 255
+    g = torch.Generator().manual_seed(2)
+
+    def decode(llm, cfg, cfgd, B, context, key):
+        engine = llm.engine
+        prompts = [torch.randint(0, cfg.vocab_size, (context - TOTAL - 1,), generator=g).tolist() for _ in range(B)]
+        slots = [engine.open() for _ in prompts]
+        first = []
+        for i in range(0, B, 4):
+            lg = engine.step([Entry(s, p, [len(p) - 1]) for s, p in zip(slots[i:i + 4], prompts[i:i + 4])], keep=False)
+            first += lg.argmax(-1).tolist()
+        session = engine.start_decode([DecodeRow(s, t, i, 1) for i, (s, t) in enumerate(zip(slots, first))])
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(REGIONS + 1)]
+        for _ in range(TOTAL - REGIONS * K):
+            session.launch()
+        events[0].record()
+        for r in range(REGIONS):
+            for _ in range(K):
+                session.launch()
+            events[r + 1].record()
+        torch.cuda.synchronize()
+        ms = sorted(events[r].elapsed_time(events[r + 1]) for r in range(REGIONS))[REGIONS // 2] / K
+        for _ in range(TOTAL):
+            session.collect()
+        session.drop(list(range(B)))
+        for s in slots:
+            engine.close(s)
+        nbytes = decode_bytes(cfgd, cfgd["num_hidden_layers"], B, context - REGIONS * K / 2.0)
+        out[key] = round(B / (ms / 1e3), 1)
+        out[key + "_hbm_frac"] = round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+
+    def prefill(llm, cfg, cfgd, key):
+        engine, T = llm.engine, 2048
+        toks = torch.randint(0, cfg.vocab_size, (T,), generator=g).tolist()
+        times = []
+        for it in range(3 + 5):
+            s = engine.open()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            engine.step([Entry(s, toks, [T - 1])], keep=False)
+            e1.record()
+            torch.cuda.synchronize()
+            engine.close(s)
+            if it >= 3:
+                times.append(e0.elapsed_time(e1))
+        ms = sorted(times)[len(times) // 2]
+        out[key + "_ms"] = round(ms, 2)
+        out[key + "_frac"] = round(prefill_flops(cfgd, cfgd["num_hidden_layers"], T) / (ms / 1e3) / 1e12 / pk["bf16_tflops"], 4)
+
+    for shape_name, runs in (("4b", [(8192, 1), (8192, 8), (16384, 1), (16384, 8)]), ("8b", [(4096, 8)]), ("32b", [(4096, 8)])):
+        cfgd = dict(SHAPES[shape_name])
+        cfg = Qwen3Config.from_dict(cfgd)
+        model = model_skeleton(cfg)
+        src = RandomSource(model.all_tensor_specs(), seed=0, std_matrix=0.02, std_gain=0.05, device="cuda:0")
+        model.load(src, Runtime(torch.device("cuda:0"), torch.bfloat16), where="random weights")
+        llm = LLM.from_model(model, max_tokens=max(B * (c + 64) for c, B in runs), graph=graph)
+        if shape_name != "4b":
+            prefill(llm, cfg, cfgd, f"qwen3_{shape_name}_prefill_2048")
+        for context, B in runs:
+            decode(llm, cfg, cfgd, B, context, f"qwen3_{shape_name}_ctx{context}_decode_b{B}")
+        del llm, model, src
+        gc.collect()                             # engines and models hold reference cycles
+        torch.cuda.empty_cache()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -146,6 +227,8 @@ def main():
     ap.add_argument("--phase", default="all", choices=["all", "prefill"],
                     help="prefill: time only the 2,048-token prompt step (small cases for profilers)")
     ap.add_argument("--no-graph", action="store_true", help="run decode steps eagerly instead of replaying CUDA graphs")
+    ap.add_argument("--no-further", action="store_true",
+                    help="skip the short runs at further contexts and at the 8B and 32B shapes (the default run of the 4B shape makes them)")
     ap.add_argument("--short", action="store_true",
                     help="decode only 5 x --steps + --warmup tokens instead of at least 255 (small cases for profilers: "
                          "every launch under a profiler costs a good part of a second)")
@@ -337,6 +420,15 @@ def main():
             print(json.dumps(line))
             raise SystemExit(f"LLM.generate and the device-timed decode run disagree: request {bad}, token {k}: "
                              f"{outs[bad][k]} against {device_tokens[bad][k]}")
+    if not a.no_points and not a.no_further and a.shape == "4b" and a.layers == full_layers:
+        # after everything the line's other figures need; a failure here costs these figures alone
+        del session, llm, engine, model, src
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            line["further"] = further_points(torch, pk, not a.no_graph)
+        except Exception as e:                   # noqa: BLE001 - the line above is measured and is printed whatever happens here
+            line["further"] = {"error": f"{type(e).__name__}: {e}"[:300]}
     print(json.dumps(line))
     return 0
 
