@@ -43,7 +43,8 @@ inline void store(void* p, size_t i, int dt, float v) {
 inline bool known(int dt) { return dt == SX_F32 || dt == SX_BF16; }
 
 // the key that orders floats as unsigned integers (the sampling kernel cuts by it)
-inline uint32_t order_key(float f) {
+inline uint32_t order_key(float f) {     // larger float, larger key; a NaN counts as -inf
+  if (f != f) f = -INFINITY;
   uint32_t b;
   std::memcpy(&b, &f, 4);
   return (b & 0x80000000u) ? ~b : (b | 0x80000000u);

@@ -217,6 +217,9 @@ def test_sampling_kernels_against_the_cpp_loops():
         K.apply_penalties(a, hist.cuda(), hl.cuda(), last_n, 1.2, 0.4, 0.3)
         R.apply_penalties(b, hist, hl, last_n, 1.2, 0.4, 0.3)
         assert torch.allclose(a.cpu(), b, atol=1e-6)
+    x[0, 17] = x[1, 0] = float("nan")
+    x[2, :900] = float("-inf")
+    x[3] = (x[3] * 2).round() / 2
     seq, step = torch.arange(rows) % 6, torch.arange(rows) * 3
     for kw in (dict(temperature=1.0), dict(temperature=0.7, top_k=5), dict(temperature=1.2, top_p=0.6),
                dict(temperature=1.0, min_p=0.2), dict(temperature=0.9, top_k=40, top_p=0.8, min_p=0.05), dict(temperature=0.0)):

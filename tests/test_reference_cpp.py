@@ -160,6 +160,8 @@ def test_argmax_penalties_and_sampling_match_the_plain_processors():
             assert np.allclose(y[r].numpy(), ref, atol=1e-6)
     V, Rr, seed = 1001, 48, 4321
     z = torch.randn(Rr, V) * 2.5
+    z[0, 17] = z[1, 0] = float("nan")                           # a NaN is never kept and never the cut-off
+    z[2, :500] = float("-inf")
     seq, step = torch.arange(Rr) % 5, torch.arange(Rr)
     for kw in (dict(temperature=1.0), dict(temperature=0.7, top_k=5), dict(temperature=1.2, top_p=0.6),
                dict(temperature=1.0, min_p=0.2), dict(temperature=0.9, top_k=40, top_p=0.8, min_p=0.05)):
@@ -168,14 +170,15 @@ def test_argmax_penalties_and_sampling_match_the_plain_processors():
         for r in range(Rr):
             u_ref = float(P.uniform_from_u32(P.philox_u32(seed, int(step[r]), int(seq[r]))))
             assert float(u[r]) == u_ref
-            v = P.processed_logits(z[r].numpy(), **kw)
+            # what the reference does with a NaN depends on its sort; here a NaN counts as -inf everywhere
+            v = P.processed_logits(np.nan_to_num(z[r].numpy(), nan=-np.inf, posinf=np.inf, neginf=-np.inf), **kw)
             assert np.array_equal(np.isfinite(v), kept[r].numpy().astype(bool)), f"{kw} row {r}: kept sets differ"
             cum = P.multinomial_intervals(v)
             t = int(got[r])
             lo = cum[t - 1] if t > 0 else 0.0
             assert lo - 1e-5 <= u_ref <= cum[t] + 1e-5
     got, _, _ = R.sample_rows(z, 0.0, 0, 1.0, 0.0, seed, seq, step)
-    assert got.tolist() == z.argmax(1).tolist()
+    assert got.tolist() == torch.nan_to_num(z, nan=float("-inf")).argmax(1).tolist()
 
 
 def test_decode_bookkeeping():
