@@ -38,7 +38,11 @@ QWEN3_4B = dict(
 # the other shapes the measurement targets name (--shape); the default run is the 4B shape
 SHAPES = {
     "4b": QWEN3_4B,
+    "0.6b": dict(QWEN3_4B, num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, intermediate_size=3072),
+    "1.7b": dict(QWEN3_4B, num_hidden_layers=28, hidden_size=2048, num_attention_heads=16, intermediate_size=6144),
     "8b": dict(QWEN3_4B, hidden_size=4096, intermediate_size=12288, tie_word_embeddings=False),
+    "14b": dict(QWEN3_4B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408,
+                tie_word_embeddings=False),
     "32b": dict(QWEN3_4B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600,
                 tie_word_embeddings=False),
 }
@@ -221,12 +225,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--shape", default="4b", choices=sorted(SHAPES), help="layer sizes: Qwen3-4B (the default), 8B or 32B")
+    ap.add_argument("--shape", default="4b", choices=sorted(SHAPES), help="layer sizes: Qwen3-4B (the default) or another size of the family")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1/64 points, the prefill and the e2e run")
     ap.add_argument("--phase", default="all", choices=["all", "prefill"],
                     help="prefill: time only the 2,048-token prompt step (small cases for profilers)")
     ap.add_argument("--no-graph", action="store_true", help="run decode steps eagerly instead of replaying CUDA graphs")
+    ap.add_argument("--prefill-tokens", type=int, default=2048, help="length of the timed prompt step (the line's figure is for 2,048)")
     ap.add_argument("--no-further", action="store_true",
                     help="skip the short runs at further contexts and at the 8B and 32B shapes (the default run of the 4B shape makes them)")
     ap.add_argument("--short", action="store_true",
@@ -275,14 +280,14 @@ def main():
     start_len = a.context - total_steps - 1
     if start_len < 1:
         raise SystemExit("--context is too short for 5 x --steps + --warmup")
-    llm = LLM.from_model(model, max_tokens=max(batches) * (a.context + 64) if a.phase == "all" else 4096,
+    llm = LLM.from_model(model, max_tokens=max(max(batches) * (a.context + 64), a.prefill_tokens + 64) if a.phase == "all" else a.prefill_tokens + 2048,
                          graph=not a.no_graph)
     engine = llm.engine
     g = torch.Generator().manual_seed(1)
 
     def time_prefill():
         """Median time of a 2,048-token prompt step of one sequence, a fresh slot each time."""
-        T = 2048
+        T = a.prefill_tokens
         toks = torch.randint(0, cfg.vocab_size, (T,), generator=g).tolist()
         times = []
         for it in range(3 + 5):
@@ -303,7 +308,7 @@ def main():
                 "tflops": round(fl / (pms / 1e3) / 1e12, 1)}
 
     if a.phase == "prefill":
-        print(json.dumps({"metric": f"prefill tok/s at 2,048 tokens ({name}, bf16, random weights)", "impl": "ours",
+        print(json.dumps({"metric": f"prefill tok/s at {a.prefill_tokens:,} tokens ({name}, bf16, random weights)", "impl": "ours",
                           "layers": a.layers, "layers_of_config": full_layers, "prefill": time_prefill()}))
         return 0
 
@@ -377,7 +382,7 @@ def main():
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_norm_eps, "tied_head": bool(shape["tie_word_embeddings"]),
-                   "prefill_tokens": 2048, "l2": "inputs larger than L2 (a step streams all weights, 8 GB or more)"},
+                   "prefill_tokens": a.prefill_tokens, "l2": "inputs larger than L2 (a step streams all weights, 8 GB or more)"},
         "gpu_launches": launches,
         "clocks": clocks,
         "timing": {"regions": REGIONS, "steps_per_region": K, "value_is": "median region",

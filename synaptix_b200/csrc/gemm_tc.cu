@@ -808,6 +808,38 @@ __global__ void tc_pieces_reduce_kernel(const float* __restrict__ ws, void* __re
 // What the persistent kernel does for a product: how many tiles are computed whole, how many are cut, the most
 // pieces a cut tile has, and the grid.
 struct TcHostPlan { int n_whole, R, zmax, G, sp; };
+// Several rows of tiles that are fewer than the SMs (a prompt step of a few hundred rows: 512 x 2,560 has 40
+// tiles) can be cut over K as well.  Whole tiles leave most SMs idle and take 5 + 0.352 us x slices whatever their
+// number (a 128 x 256 tile with K = 4,096: 27.5 us, K = 9,728: 58.5 us), and the uniform split over K in 128-wide
+// tiles (sx_gemm_tc with splits > 1) took 40 us for 512 x 2,560 x 4,096 and 69 us for K = 9,728.  Cut into G
+// shares the same products take about 6.5 + 0.352 x slices / G + 0.07 G us (the last term: G partial tiles written
+// and read again by the second kernel): 23.5 and 37 us for the two products above.
+// The figures are measured on a B200 with the weights coming from HBM; a product is cut only when the estimate is
+// a tenth below the whole tiles'.  Not for a handful of tiles (the uniform split is faster up to a dozen).  The
+// pieces of the row tiles over one block of W run at different times, so W is read once per row of tiles, from HBM
+// when L2 cannot keep it (5,120 x 25,600 at 512 rows: 196 us cut, 153 us whole): for a matrix larger than half
+// of L2 the estimate is at least that traffic's time.
+static int g_tc_cut_few = 1;
+extern "C" void sx_gemm_tc_cut_few(int on) { g_tc_cut_few = on ? 1 : 0; }
+static bool tc_cut_few(int tiles_m, int n_tiles, int nkb, long long U, long long w_bytes, int sms, int* G) {
+  if (!g_tc_cut_few || tiles_m <= 1 || n_tiles >= sms || n_tiles <= 12) return false;
+  // a matrix larger than half of L2 comes from HBM once per row of tiles
+  const double t_hbm = w_bytes > (64LL << 20) ? (double)tiles_m * (double)w_bytes / 6.0e6 : 0.0;
+  // every tile into the same number of pieces, so that no block's share begins in one tile and ends in the next
+  // (a block with two pieces stores two partial tiles: 30 tiles in 97 shares took 24.4 us, in 120 shares 18.4 us)
+  const double t_whole = 5.0 + 0.352 * nkb;
+  double best = 0.9 * t_whole;
+  int pieces = 0;
+  for (int z = 2; z * n_tiles <= sms && z <= nkb; ++z) {
+    double t_cut = 6.5 + 0.352 * (double)nkb / z + 0.07 * z * n_tiles;
+    if (t_cut < t_hbm + 6.5) t_cut = t_hbm + 6.5;
+    if (t_cut < best) { best = t_cut; pieces = z; }
+  }
+  if (!pieces) return false;
+  *G = pieces * n_tiles;
+  return true;
+}
+
 static TcHostPlan tc_plan_stream(int M, int N, int K, int epi, bool allow_cut) {
   const int tile_n = epi == TC_EPI_SILU_MUL ? 128 : 256;
   const int n_out = epi == TC_EPI_SILU_MUL ? N / 2 : N;
@@ -829,10 +861,13 @@ static TcHostPlan tc_plan_stream(int M, int N, int K, int epi, bool allow_cut) {
   // splits > 1: 128-wide tiles, fewer and larger partial tiles) measured faster there.
   // Behind three or more rounds of whole tiles a short last round costs little, and cutting it did not pay
   // (gate/up at 2,048 rows: 1,216 tiles, 164 us cut against 155 us whole).
+  int G_few = 0;
+  const bool few = tc_cut_few(tiles_m, n_tiles, nkb, U, (long long)N * K * 2, sms, &G_few);
   const bool cut = allow_cut && R0 > 0 && nkb >= 2 && R0 < sms &&
-                   (n_tiles >= sms ? (2 * R0 <= sms && U >= sms && n_tiles < 3 * sms) : (tiles_m == 1 && 2 * R0 >= sms));
+                   (n_tiles >= sms ? (2 * R0 <= sms && U >= sms && n_tiles < 3 * sms) : ((tiles_m == 1 && 2 * R0 >= sms) || few));
   if (!cut) { h.n_whole = n_tiles; h.R = 0; h.zmax = 0; h.G = n_tiles < sms ? n_tiles : sms; return h; }
   h.n_whole = n_tiles - R0; h.R = R0; h.G = U < sms ? (int)U : sms;
+  if (few && n_tiles < sms && tiles_m > 1 && G_few < h.G) h.G = G_few;
   if (h.n_whole > 0) {                               // equal pieces per tile, one piece a block
     h.sp = sms / R0;
     if (h.sp > nkb) h.sp = nkb;

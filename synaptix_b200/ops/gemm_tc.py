@@ -35,9 +35,24 @@ def plan_splits(M: int, N: int, K: int, n_sm: int) -> int:
     tiles_256 = ((N + 255) // 256) * ((M + 127) // 128)
     if tiles_256 >= (n_sm * 3) // 4:
         return 1
+    # several rows of tiles: beyond a dozen tiles whole ones measured faster than this form wherever the persistent
+    # kernel does not cut them itself (256 x 6,144 x 2,560: 20.5 against 35.1 us; 512 x 2,560 x 4,096: 27.7 against 40.3)
+    if M > 128 and tiles_256 > 12:
+        return 1
     tiles_128 = ((N + 127) // 128) * ((M + 127) // 128)
     nkb = (K + 63) // 64
     return max(1, min(nkb // 2, (n_sm + tiles_128 // 2) // tiles_128))
+
+
+_cut_few_applied = None
+
+
+def _apply_cut_few() -> None:
+    """Hand option ``gemm_cut_few`` to the library when it changed."""
+    global _cut_few_applied
+    if _cut_few_applied != OPTIONS.gemm_cut_few:
+        fn("gemm_tc", "sx_gemm_tc_cut_few")(c_int(1 if OPTIONS.gemm_cut_few else 0))
+        _cut_few_applied = OPTIONS.gemm_cut_few
 
 
 def plan_stream(M: int, N: int, K: int, epilogue: Optional[str] = None):
@@ -45,7 +60,10 @@ def plan_stream(M: int, N: int, K: int, epilogue: Optional[str] = None):
     device.  Tiles that would not fill a round of all SMs (a last round at most half full: 2,048 x 2,560 has
     160 tiles for 148 SMs; or all tiles of a step with at most 128 rows) are cut over K: their 64-wide slices
     of K form one sequence that is dealt out to the blocks in equal contiguous shares, the blocks of a tile
-    leave float32 partial tiles in a workspace and add them up together, in a fixed order."""
+    leave float32 partial tiles in a workspace and add them up together, in a fixed order.  Several rows of tiles
+    that are fewer than the SMs (a few hundred rows) are cut when an estimate from measured times says that pays
+    (option ``gemm_cut_few``)."""
+    _apply_cut_few()
     out = (ctypes.c_int * 4)()
     check(fn("gemm_tc", "sx_gemm_tc_plan")(c_int(M), c_int(N), c_int(K), c_int(_EPI[epilogue]), out), "gemm_tc_plan",
           launches=0)
@@ -84,6 +102,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None,
         cut = OPTIONS.gemm_cut
     if splits is None and cut is not False:
         _, n_cut, zmax, _ = plan_stream(M, N, K, epilogue)
+    _apply_cut_few()
     if splits is None:
         splits = 1 if n_cut else plan_splits(M, N, K, sm_count(x.device))
     splits = max(1, min(int(splits), (K + 63) // 64))

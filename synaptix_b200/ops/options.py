@@ -13,6 +13,8 @@ switches in its runtime options (crates/synaptix-config/src/runtime.rs, ``AttnBa
                     cp.async kernel, four warps a page)
 ``gemm_cut``        the persistent tcgen05 product cuts tiles over K where whole tiles would
                     leave SMs idle
+``gemm_cut_few``    a few hundred rows: tiles fewer than the SMs are cut over K too, where an estimate
+                    from measured times says that beats whole tiles
 ``gemm_ws``         17 to 128 rows: the product with the weights as the tensor cores' M side, K shared by
                     the blocks of a cluster (else the tcgen05 product of prompt steps, split over K)
 ``qkv_epilogue``    prompt steps at head size 128: the q/k/v product prepares the heads in its epilogue (norm,
@@ -33,6 +35,7 @@ class KernelOptions:
     attn_prep: bool = True
     attn_tma: bool = True
     gemm_cut: bool = True
+    gemm_cut_few: bool = True
     gemm_ws: bool = True
     qkv_epilogue: bool = True
     fused_residual: bool = True

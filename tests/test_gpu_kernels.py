@@ -677,6 +677,9 @@ def test_gemm_tc(M, N, K):
     (2048, 2560, 512, None, False),
     # one row of tiles, at least half as many as SMs: all tiles cut, a second kernel adds up
     (64, 19456, 2560, "silu_mul", True), (100, 20000, 136, None, True), (33, 30000, 264, "f32", True), (17, 25000, 200, "silu_mul", True),
+    # several rows of tiles, fewer than the SMs, long K: all tiles cut into shares that may begin and end inside a tile
+    (512, 2560, 4096, None, True), (300, 2560, 9728, "f32", True), (640, 2500, 4104, "f32", True), (400, 1024, 3080, None, True),
+    (384, 2048, 6144, "silu_mul", True), (512, 6144, 2560, None, False),
     # a handful of tiles: the two-kernel split form
     (64, 6144, 2560, None, False), (64, 2560, 4096, "f32", False), (17, 389, 96, "f32", False), (128, 256, 64, "f32", False),
     (200, 700, 1224, "silu_mul", False), (40, 24, 8, "f32", False)])
