@@ -1,4 +1,4 @@
-// C[M, N] = X[M, K] * W[N, K]^T for a few dozen rows of X (decode steps of 17 to 128 sequences): the weight
+// C[M, N] = X[M, K] * W[N, K]^T for a few dozen rows of X (decode steps of 17 to 256 sequences): the weight
 // matrix streams from HBM once, through TMA, and is the M side of the tcgen05 instruction.
 //
 // With so few rows the product is bound by reading W, and a 128-row tile of X would be mostly padding.  So the
@@ -29,7 +29,7 @@
 #define WS_THREADS 192
 #define WS_BK 64
 #define WS_W_BYTES (128 * WS_BK * 2)          // 16 KB of W per stage
-#define WS_MAX_ROWS 128
+#define WS_MAX_ROWS 256
 #define WS_MAX_STAGES 8
 
 enum { WS_EPI_BF16 = 0, WS_EPI_F32 = 1, WS_EPI_SILU_MUL = 2, WS_EPI_RESIDUAL = 3 };
@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_con
   float* R = reinterpret_cast<float*>(tiles + ring_bytes);                  // [splits][M][128 / splits] (push)
   uint64_t* bars = reinterpret_cast<uint64_t*>(after);                      // full[S], empty[S], accum
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * WS_MAX_STAGES + 1);
-  float* row_factor = reinterpret_cast<float*>(tmem_slot + 2);              // [128]
+  float* row_factor = reinterpret_cast<float*>(tmem_slot + 2);              // [WS_MAX_ROWS]
   float* P = reinterpret_cast<float*>(tiles);                               // [M][128] once the ring is done with
   const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + WS_MAX_STAGES), accum = tc_smem(bars + 2 * WS_MAX_STAGES);
 
@@ -198,24 +198,27 @@ __global__ void __launch_bounds__(WS_THREADS, 2) gemm_ws_kernel(const __grid_con
       const int e = threadIdx.x - 64;
       int tpr = 1;
       while (tpr < 32 && 2 * tpr * M <= WS_THREADS - 64) tpr *= 2;
-      const int m = e / tpr, sub = e - m * tpr;
-      float s = 0.f;
-      if (m < M) {
-        const float* row = ep.ssq_in + (size_t)m * ep.n_ssq;
-        if ((ep.n_ssq & 3) == 0 && ((uintptr_t)ep.ssq_in & 15) == 0) {
-          const float4* r4 = reinterpret_cast<const float4*>(row);
+      // (more rows than threads: a thread takes rows e, e + 128, ...)
+      const int rows_a_pass = (WS_THREADS - 64) / tpr, m_end = (M + rows_a_pass - 1) / rows_a_pass * rows_a_pass;
+      for (int m = e / tpr, sub = e - (e / tpr) * tpr; m < m_end; m += rows_a_pass) {
+        float s = 0.f;
+        if (m < M) {
+          const float* row = ep.ssq_in + (size_t)m * ep.n_ssq;
+          if ((ep.n_ssq & 3) == 0 && ((uintptr_t)ep.ssq_in & 15) == 0) {
+            const float4* r4 = reinterpret_cast<const float4*>(row);
 #pragma unroll 8
-          for (int j = sub; j < (ep.n_ssq >> 2); j += tpr) {
-            const float4 f = r4[j];
-            s += (f.x + f.y) + (f.z + f.w);
+            for (int j = sub; j < (ep.n_ssq >> 2); j += tpr) {
+              const float4 f = r4[j];
+              s += (f.x + f.y) + (f.z + f.w);
+            }
+          } else {
+#pragma unroll 8
+            for (int j = sub; j < ep.n_ssq; j += tpr) s += row[j];
           }
-        } else {
-#pragma unroll 8
-          for (int j = sub; j < ep.n_ssq; j += tpr) s += row[j];
         }
+        for (int d = tpr >> 1; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+        if (m < M && sub == 0) row_factor[m] = rsqrtf(s / (float)K + ep.eps);
       }
-      for (int d = tpr >> 1; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
-      if (m < M && sub == 0) row_factor[m] = rsqrtf(s / (float)K + ep.eps);
     }
     const int quarter = warp & 3;                     // warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31
     if (tc_mbar_wait(accum, 0)) {
@@ -399,7 +402,7 @@ static int ws_sm_count() {
 static size_t ws_smem_bytes(int M, int nmma, int stages, bool push) {
   const size_t ring = (size_t)stages * (WS_W_BYTES + nmma * WS_BK * 2), p_bytes = (size_t)M * 128 * 4;
   return 1024 + (push ? ring + p_bytes : (ring > p_bytes ? ring : p_bytes)) + (2 * WS_MAX_STAGES + 1) * sizeof(uint64_t) + 8 +
-         128 * sizeof(float) + 16;
+         WS_MAX_ROWS * sizeof(float) + 16;
 }
 static int ws_blocks_per_sm(int M, int nmma, int stages) {
   return (int)(233472 / (ws_smem_bytes(M, nmma, stages, M <= WS_PUSH_MAX_ROWS) + 1024));
@@ -409,7 +412,9 @@ static int ws_blocks_per_sm(int M, int nmma, int stages) {
 // 0 if there is none of at least 2 stages.  A block that has to wait for a place runs behind all the others.
 static int ws_pick_stages(int M, int nmma, long long blocks) {
   const int sms = ws_sm_count();
-  int stages = (100 * 1024) / (WS_W_BYTES + nmma * WS_BK * 2);
+  // (a partial tile of more than 100 KB leaves room for one block an SM whatever the ring: the ring may be as large)
+  const size_t room = (size_t)M * 128 * 4 > 100 * 1024 ? 200 * 1024 : 100 * 1024;
+  int stages = (int)(room / (WS_W_BYTES + nmma * WS_BK * 2));
   if (stages > WS_MAX_STAGES) stages = WS_MAX_STAGES;
   const long long per_sm = (blocks + sms - 1) / sms;
   while (stages >= 2 && ws_blocks_per_sm(M, nmma, stages) < per_sm) --stages;
@@ -463,7 +468,7 @@ static int ws_launch(const void* X, const void* W, void* out, int M, int N, int 
   // the ring: given, or the deepest with which every block is on the GPU at once (at most what lets two share an SM)
   const int stage_bytes = WS_W_BYTES + nmma * WS_BK * 2;
   if (stages <= 0) stages = ws_pick_stages(M, nmma, tiles * splits);
-  if (stages <= 0) stages = (100 * 1024) / stage_bytes;
+  if (stages <= 0) stages = (int)(((size_t)M * 128 * 4 > 100 * 1024 ? 200 * 1024 : 100 * 1024) / stage_bytes);
   if (stages > WS_MAX_STAGES) stages = WS_MAX_STAGES;
   if (stages > (220 * 1024) / stage_bytes) stages = (220 * 1024) / stage_bytes;
   if (stages < 2) stages = 2;
@@ -476,7 +481,7 @@ static int ws_launch(const void* X, const void* W, void* out, int M, int N, int 
                            stages, splits, tmem_cols, push, ep, status);
 }
 
-// X [M, K], W [N, K] bfloat16 row-major, 16-byte aligned, K % 8 == 0, 1 <= M <= 128.
+// X [M, K], W [N, K] bfloat16 row-major, 16-byte aligned, K % 8 == 0, 1 <= M <= 256.
 // epi 0: out bf16 [M, N]; 1: out f32 [M, N]; 2: W = [gate; up] stacked, out bf16 [M, N/2];
 // 3: h [M, N] float32 += the product in place, out bf16 [M, N] = bf16(h * gain), ssq_out [M, tiles * splits] the sums
 //    of squares of the new h over each block's columns (sx_gemm_ws_plan gives tiles and splits).

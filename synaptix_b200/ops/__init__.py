@@ -17,7 +17,7 @@ from .attention import (TC_TILE_ROWS, attn_decode, attn_decode_prep, attn_decode
                         fast_supported, pick_splits, query_tiles, tc_prefill_supported, tma_decode_supported)
 from .decode import MAX_ROWS as SKINNY_MAX_ROWS, skinny_gemm, skinny_gemm_residual, skinny_gemm_scaled, skinny_supported
 from .gemm_tc import gemm_tc, gemm_tc_qkv, qkv_epilogue_supported, tc_supported
-from .gemm_ws import MAX_ROWS as WS_MAX_ROWS, gemm_ws, gemm_ws_residual, ws_supported
+from .gemm_ws import gemm_ws, gemm_ws_residual, ws_supported
 from .options import OPTIONS, KernelOptions, options, set_options
 from .generic import (add_rmsnorm, attn_generic, decode_advance, decode_begin, embed_gather, gemm_generic, qkv_prepare,
                       residual_add, rope_table, silu_mul)
@@ -60,7 +60,13 @@ def check_status(readers=None) -> None:
                               "its output is incomplete and the step's results must not be used")
 
 
-# The weight-streaming product of 17 to 128 rows makes one block per 128 outputs; an output head has a thousand of
+# The weight-streaming tcgen05 product takes up to 256 rows; the step function gives it up to this many.  Measured at
+# Qwen3-4B sizes, us for q/k/v + o + gate/up + down in replayed graphs: 144 rows 90 against 100 with the tile product of
+# prompt steps, 192 rows 109 against 101, 256 rows 124 against 103 (one block of 256 rows of partial results fills an
+# SM's shared memory, and the 152 tiles of gate/up then take 62 us).
+WS_MAX_ROWS = 160
+
+# The weight-streaming product of 17 to 160 rows makes one block per 128 outputs; an output head has a thousand of
 # them, and there the persistent product with its 256-wide tiles measured faster (142 against 158 us for 151,936
 # outputs of 64 rows).
 WS_MAX_OUT = 32768
@@ -80,10 +86,10 @@ PROLOGUE_NORM_MAX_ROWS = 1
 
 
 def _weight_stream_kernel(M: int, N: int, K: int, x_dtype, w_dtype) -> Optional[str]:
-    """Which weight-streaming product takes ``M <= 128`` rows against ``w[N, K]``: ``"skinny"`` (mma.sync, up to 16
-    rows), ``"ws"`` (tcgen05, up to 128 rows and 32,768 outputs) or ``None``."""
+    """Which weight-streaming product takes ``M <= 160`` rows against ``w[N, K]``: ``"skinny"`` (mma.sync, up to 16
+    rows), ``"ws"`` (tcgen05, up to 160 rows and 32,768 outputs) or ``None``."""
     skinny = skinny_supported(M, N, K, x_dtype, w_dtype)
-    ws = OPTIONS.gemm_ws and N <= WS_MAX_OUT and ws_supported(M, N, K, x_dtype, w_dtype)
+    ws = OPTIONS.gemm_ws and N <= WS_MAX_OUT and M <= WS_MAX_ROWS and ws_supported(M, N, K, x_dtype, w_dtype)
     if skinny and ws:
         if M <= PROLOGUE_NORM_MAX_ROWS:          # (one row: batch 1 measured 506 tok/s with mma.sync throughout, 494 with tcgen05 for down)
             return "skinny"
@@ -105,7 +111,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     N = w.shape[0]
     if out_dtype is None:
         out_dtype = x.dtype
-    # up to 128 rows: stream W once (mma.sync or tcgen05 with W as the M side, see _weight_stream_kernel); more: the
+    # up to 160 rows: stream W once (mma.sync or tcgen05 with W as the M side, see _weight_stream_kernel); more: the
     # tcgen05 product of prompt steps
     stream_k = _weight_stream_kernel(M, N, K, x.dtype, w.dtype) if out_dtype in (torch.bfloat16, torch.float32) else None
     if stream_k is not None:
@@ -155,7 +161,7 @@ def linear_normed(pn, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
 
 def residual_product_fusable(M: int, N: int, K: int, dtype) -> bool:
     """Can the product ``x[M, K] @ w[N, K].T`` add itself into the residual stream and prepare the norm after the
-    sum (``linear_into_residual``)?  2 to 128 rows in bfloat16 (option ``fused_residual``)."""
+    sum (``linear_into_residual``)?  2 to 160 rows in bfloat16 (option ``fused_residual``)."""
     # one row: the norm in the consumer's prologue (norm_fusable) measured faster (506 against 492 tok/s)
     if dtype != torch.bfloat16 or not OPTIONS.fused_residual or K <= 0 or M <= PROLOGUE_NORM_MAX_ROWS:
         return False

@@ -1,4 +1,4 @@
-"""Python face of the weight-streaming tcgen05 product in ``csrc/gemm_ws.cu`` (bfloat16, up to 128 rows)."""
+"""Python face of the weight-streaming tcgen05 product in ``csrc/gemm_ws.cu`` (bfloat16, up to 256 rows)."""
 from __future__ import annotations
 
 import ctypes
@@ -9,7 +9,7 @@ import torch
 from ._lib import KernelError, c_float, c_int, check, fn, ptr, require_cuda, stream
 
 _EPI = {None: 0, "f32": 1, "silu_mul": 2, "residual": 3}
-MAX_ROWS = 128
+MAX_ROWS = 256
 
 
 def ws_supported(M: int, N: int, K: int, x_dtype, w_dtype) -> bool:
@@ -28,7 +28,7 @@ def plan_ws(M: int, N: int, K: int, epilogue: Optional[str] = None) -> Tuple[int
 def gemm_ws(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None, ssq: Optional[torch.Tensor] = None,
             eps: float = 0.0, splits: Optional[int] = None, stages: Optional[int] = None,
             out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``x[M, K] @ w[N, K].T`` for ``M <= 128`` rows with ``w`` as the tensor cores' M side, read once from HBM;
+    """``x[M, K] @ w[N, K].T`` for ``M <= 256`` rows with ``w`` as the tensor cores' M side, read once from HBM;
     K is shared by the ``splits`` (1, 2, 4, 8) blocks of a cluster, which add up through their shared memory.
 
     ``epilogue``: ``None`` -> bfloat16 ``[M, N]``; ``"f32"`` -> float32; ``"silu_mul"`` -> ``w`` is ``[gate; up]``
@@ -42,7 +42,7 @@ def gemm_ws(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None,
     if epilogue not in (None, "f32", "silu_mul"):
         raise KernelError(f"gemm_ws: unknown epilogue {epilogue!r}")
     if not ws_supported(M, N, K, x.dtype, w.dtype):
-        raise KernelError("gemm_ws: bfloat16 operands, at most 128 rows and K a multiple of 8")
+        raise KernelError("gemm_ws: bfloat16 operands, at most 256 rows and K a multiple of 8")
     if ssq is not None and (ssq.dtype != torch.float32 or ssq.dim() != 2 or ssq.shape[0] != M):
         raise KernelError("gemm_ws: ssq must be float32 [M, n]")
     n_out = N // 2 if epilogue == "silu_mul" else N
@@ -67,7 +67,7 @@ def gemm_ws_residual(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, gain: to
     if gain.dtype != torch.float32 or gain.numel() != N:
         raise KernelError("gemm_ws_residual: gain must be float32 [N]")
     if not ws_supported(M, N, K, x.dtype, w.dtype):
-        raise KernelError("gemm_ws_residual: bfloat16 operands, at most 128 rows and K a multiple of 8")
+        raise KernelError("gemm_ws_residual: bfloat16 operands, at most 256 rows and K a multiple of 8")
     tiles, auto = plan_ws(M, N, K, "residual")
     splits = splits or auto
     while splits > (K + 63) // 64:

@@ -22,10 +22,10 @@ def test_weight_streaming_kernel_by_rows_and_size():
     for M in (9, 16):
         assert all(pick(M, *s) == "ws" for s in (qkv, o, gate_up, down))
         assert pick(M, *head) == "skinny"
-    for M in (17, 64, 128):
+    for M in (17, 64, 128, 144, 160):
         assert all(pick(M, *s) == "ws" for s in (qkv, o, gate_up, down))
         assert pick(M, *head) is None                                             # the persistent tcgen05 product
-    assert pick(129, *qkv) is None
+    assert pick(161, *qkv) is None
 
 
 def test_sizes_and_dtypes_the_fast_products_refuse():
@@ -39,9 +39,9 @@ def test_sizes_and_dtypes_the_fast_products_refuse():
 
 def test_which_products_add_themselves_into_the_residual_stream():
     assert not ops.residual_product_fusable(1, 2560, 4096, BF) and not ops.residual_product_fusable(1, 2560, 9728, BF)
-    assert all(ops.residual_product_fusable(M, 2560, 4096, BF) for M in (2, 3, 8, 16, 17, 64, 128))
+    assert all(ops.residual_product_fusable(M, 2560, 4096, BF) for M in (2, 3, 8, 16, 17, 64, 128, 160))
     assert ops.norm_fusable(1, 2560, BF) and not ops.norm_fusable(2, 2560, BF)
-    assert not ops.residual_product_fusable(129, 2560, 4096, BF)
+    assert not ops.residual_product_fusable(161, 2560, 4096, BF)
     assert not ops.residual_product_fusable(8, 2560, 4096, torch.float32)
     with ops.options(fused_residual=False):
         assert not ops.residual_product_fusable(8, 2560, 4096, BF)

@@ -741,7 +741,7 @@ def test_gemm_tc_split_k(M, N, K, epilogue):
     assert gemm_tc_status() == 0
 
 
-@pytest.mark.parametrize("M", [1, 17, 40, 64, 100, 128])
+@pytest.mark.parametrize("M", [1, 17, 40, 64, 100, 128, 129, 150, 200, 256])
 @pytest.mark.parametrize("N,K", [(2560, 4096), (389, 96), (264, 72), (130, 64), (1000, 1224)])
 def test_gemm_ws(M, N, K):
     """The weight-streaming tcgen05 product (weights as the M side, K shared by a cluster's blocks) against
@@ -776,7 +776,7 @@ def test_gemm_ws(M, N, K):
     assert gemm_ws_status() == 0
 
 
-@pytest.mark.parametrize("M", [3, 17, 64, 128])
+@pytest.mark.parametrize("M", [3, 17, 64, 128, 144, 256])
 @pytest.mark.parametrize("N,K", [(2560, 4096), (176, 96), (100, 320), (24, 9728)])
 def test_gemm_ws_adds_into_the_residual_and_prepares_the_norm(M, N, K):
     """h += x W^T in place, x~ = bf16(h * gain) and partial sums of squares of h; then a second product takes x~
@@ -812,10 +812,10 @@ def test_gemm_ws_adds_into_the_residual_and_prepares_the_norm(M, N, K):
 def test_gemm_ws_refuses_what_it_does_not_take():
     from synaptix_b200.ops import KernelError
     from synaptix_b200.ops.gemm_ws import gemm_ws
-    x = torch.zeros(129, 64, dtype=torch.bfloat16, device="cuda")
+    x = torch.zeros(257, 64, dtype=torch.bfloat16, device="cuda")
     w = torch.zeros(32, 64, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(KernelError):
-        gemm_ws(x, w)                                           # more than 128 rows
+        gemm_ws(x, w)                                           # more than 256 rows
     with pytest.raises(KernelError):
         gemm_ws(x[:8, :60].contiguous(), w[:, :60].contiguous())   # K no multiple of 8
     with pytest.raises(KernelError):

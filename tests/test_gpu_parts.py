@@ -49,10 +49,10 @@ def test_rmsnorm_part(dtype):
     assert torch.allclose(n.forward(h).float().cpu(), P.rms_norm(ref_h, w.float(), 3e-5), **tol(dtype))
 
 
-@pytest.mark.parametrize("rows", [1, 2, 5, 16, 20, 128, 150])
+@pytest.mark.parametrize("rows", [1, 2, 5, 16, 20, 128, 150, 170])
 def test_a_deferred_product_through_the_norm_and_the_next_product(rows):
     """A branch's last product handed on unrun (PendingLinear): the norm lets it add itself into h and hands scaled
-    rows to the next product (2 to 128 rows), or runs it and norms as ever; either way the numbers are the plain ones.
+    rows to the next product (2 to 160 rows), or runs it and norms as ever; either way the numbers are the plain ones.
     A norm that does not say it takes such a thing never sees one (the block runs the product first)."""
     from synaptix_b200.parts import Linear, RMSNorm
     from synaptix_b200.parts.base import PendingLinear, ScaledRows
@@ -74,7 +74,7 @@ def test_a_deferred_product_through_the_norm_and_the_next_product(rows):
     for lazy in (True, False):
         h = h0.clone().cuda()
         x = n.add_forward(h, down.deferred(z.cuda()), lazy=lazy)
-        assert isinstance(x, ScaledRows) == (lazy and 1 < rows <= 128)
+        assert isinstance(x, ScaledRows) == (lazy and 1 < rows <= 160)
         y = nxt.forward(x, out_dtype=torch.float32)
         h_after = x.h_after() if hasattr(x, "h_after") else h        # a lazy norm says where the sum went
         assert torch.allclose(h_after.cpu().double(), ref_h, atol=3e-2, rtol=1e-2)          # the branch is rounded to bf16 when run alone
