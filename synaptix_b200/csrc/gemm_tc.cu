@@ -868,6 +868,8 @@ static TcHostPlan tc_plan_stream(int M, int N, int K, int epi, bool allow_cut) {
   if (!cut) { h.n_whole = n_tiles; h.R = 0; h.zmax = 0; h.G = n_tiles < sms ? n_tiles : sms; return h; }
   h.n_whole = n_tiles - R0; h.R = R0; h.G = U < sms ? (int)U : sms;
   if (few && n_tiles < sms && tiles_m > 1 && G_few < h.G) h.G = G_few;
+  // (a second kernel adds these up: the blocks of a tile adding up among themselves, as behind whole tiles, took 7 to
+  //  10 us longer here, 512 x 2,560 x 4,096: 30.4 against 20.5 us, with nothing to hide behind and 128 threads a block)
   if (h.n_whole > 0) {                               // equal pieces per tile, one piece a block
     h.sp = sms / R0;
     if (h.sp > nkb) h.sp = nkb;
