@@ -863,8 +863,19 @@ static TcHostPlan tc_plan_stream(int M, int N, int K, int epi, bool allow_cut) {
   // (gate/up at 2,048 rows: 1,216 tiles, 164 us cut against 155 us whole).
   int G_few = 0;
   const bool few = tc_cut_few(tiles_m, n_tiles, nkb, U, (long long)N * K * 2, sms, &G_few);
+  // Behind whole tiles a piece costs its share of a tile's slices and about 8.6 us for the partial tiles' trip and the
+  // adding up (by the four epilogue warps, before their whole tile's epilogue); that has to stay well under the
+  // round of whole tiles it saves (1,024 x 6,144 x 2,560, 44 tiles in three pieces each: 40.1 us cut, 34.7 whole;
+  // the same rows x 6,144 x 4,096: 48.2 cut, 52.3 whole).
+  bool last_round_pays = false;
+  if (n_tiles >= sms && R0 > 0) {
+    int sp = sms / R0;
+    if (sp > nkb) sp = nkb;
+    last_round_pays = 5.0 + 0.352 * nkb / sp + 8.6 < 0.8 * (5.0 + 0.352 * nkb);
+  }
   const bool cut = allow_cut && R0 > 0 && nkb >= 2 && R0 < sms &&
-                   (n_tiles >= sms ? (2 * R0 <= sms && U >= sms && n_tiles < 3 * sms) : ((tiles_m == 1 && 2 * R0 >= sms) || few));
+                   (n_tiles >= sms ? (2 * R0 <= sms && U >= sms && n_tiles < 3 * sms && last_round_pays)
+                                   : ((tiles_m == 1 && 2 * R0 >= sms) || few));
   if (!cut) { h.n_whole = n_tiles; h.R = 0; h.zmax = 0; h.G = n_tiles < sms ? n_tiles : sms; return h; }
   h.n_whole = n_tiles - R0; h.R = R0; h.G = U < sms ? (int)U : sms;
   if (few && n_tiles < sms && tiles_m > 1 && G_few < h.G) h.G = G_few;

@@ -673,8 +673,8 @@ def test_gemm_tc(M, N, K):
 
 @pytest.mark.parametrize("M,N,K,epilogue,is_cut", [
     # a nearly empty last round of whole tiles: its tiles are cut, the blocks add up inside the kernel
-    (2048, 2560, 4096, "f32", True), (2048, 2560, 9728, None, True), (2000, 2500, 1032, "f32", True), (1300, 3484, 1672, None, True),
-    (2048, 2560, 512, None, False),
+    (2048, 2560, 4096, "f32", True), (2048, 2560, 9728, None, True), (2000, 2500, 4104, "f32", True), (1300, 3484, 3656, None, True),
+    (2048, 2560, 512, None, False), (1024, 6144, 2560, None, False),
     # one row of tiles, at least half as many as SMs: all tiles cut, a second kernel adds up
     (64, 19456, 2560, "silu_mul", True), (100, 20000, 136, None, True), (33, 30000, 264, "f32", True), (17, 25000, 200, "silu_mul", True),
     # several rows of tiles, fewer than the SMs, long K: all tiles cut into shares that may begin and end inside a tile
