@@ -232,6 +232,7 @@ def main():
                     help="prefill: time only the 2,048-token prompt step (small cases for profilers)")
     ap.add_argument("--no-graph", action="store_true", help="run decode steps eagerly instead of replaying CUDA graphs")
     ap.add_argument("--prefill-tokens", type=int, default=2048, help="length of the timed prompt step (the line's figure is for 2,048)")
+    ap.add_argument("--further-only", action="store_true", help="only the short runs at further sizes, as a JSON object")
     ap.add_argument("--no-further", action="store_true",
                     help="skip the short runs at further contexts and at the 8B and 32B shapes (the default run of the 4B shape makes them)")
     ap.add_argument("--short", action="store_true",
@@ -250,6 +251,12 @@ def main():
     a.warmup = max(a.warmup, 3)
 
     import torch
+    if a.further_only:
+        try:
+            print(json.dumps(further_points(torch, peaks(), not a.no_graph)))
+        except Exception as e:                   # noqa: BLE001 - reported in the caller's line
+            print(json.dumps({"error": f"{type(e).__name__}: {e}"[:300]}))
+        return 0
     from synaptix_b200.api import LLM
     from synaptix_b200.config import Qwen3Config
     from synaptix_b200.engine import DecodeRow, Entry
@@ -426,12 +433,16 @@ def main():
             raise SystemExit(f"LLM.generate and the device-timed decode run disagree: request {bad}, token {k}: "
                              f"{outs[bad][k]} against {device_tokens[bad][k]}")
     if not a.no_points and not a.no_further and a.shape == "4b" and a.layers == full_layers:
-        # after everything the line's other figures need; a failure here costs these figures alone
+        # After everything the line's other figures need, and in a process of its own with a time limit: a failure
+        # there costs these figures alone.
         del session, llm, engine, model, src
         gc.collect()
         torch.cuda.empty_cache()
         try:
-            line["further"] = further_points(torch, pk, not a.no_graph)
+            r = subprocess.run([sys.executable, os.path.abspath(__file__), "--further-only"] + (["--no-graph"] if a.no_graph else []),
+                               capture_output=True, text=True, timeout=240)
+            line["further"] = json.loads(r.stdout.strip().splitlines()[-1]) if r.returncode == 0 and r.stdout.strip() else \
+                {"error": f"exit code {r.returncode}: {r.stderr.strip()[-200:]}"}
         except Exception as e:                   # noqa: BLE001 - the line above is measured and is printed whatever happens here
             line["further"] = {"error": f"{type(e).__name__}: {e}"[:300]}
     print(json.dumps(line))
