@@ -1,4 +1,5 @@
-// Sampling on the device: one block per row of logits [R, V] (float32).
+// Sampling on the device, over rows of logits [R, V] (float32): one block a row, or, for wide vocabularies, a row
+// spread over a thread-block cluster (argmax: over blocks of a first kernel, with a second to finish).
 //
 // What is computed follows the reference's host-side pipeline
 // (crates/synaptix-models/llm/common/src/generate.rs:304-340):
@@ -7,8 +8,10 @@
 // with the processors of crates/synaptix-infer/src/sampling/{repetition,logit_processor,top_k,
 // top_p,min_p,greedy,multinomial}.rs and the Philox4x32-10 generator of
 // crates/synaptix-ops/src/rng.rs:1-97.  The reference sorts on the host; here the top-k and
-// top-p cut-offs are found by bisection on the values' bit patterns, with block-wide
-// reductions in a fixed order, so a row's result depends on nothing but the row.
+// top-p cut-offs are found by bisection on the values' bit patterns, with reductions in a
+// fixed order, so a row's result depends on nothing but the row.  Where the reference's
+// result depends on its sort (a NaN among the logits; equal values at a cut-off), here a
+// NaN counts as -inf and all values equal to the cut-off are kept.
 #include "common.cuh"
 
 #define SAMPLE_THREADS 1024
