@@ -44,6 +44,23 @@ def plan_splits(M: int, N: int, K: int, n_sm: int) -> int:
     return max(1, min(nkb // 2, (n_sm + tiles_128 // 2) // tiles_128))
 
 
+_PLANS = {}
+_WORKSPACES = {}
+
+
+def _workspace(n_floats: int, device) -> torch.Tensor:
+    """Float32 scratch for partial tiles.  One buffer per device that only grows: the kernels of a stream run one
+    after the other, and a partial tile is read by the launch (or the second kernel) that wrote it.  While a CUDA
+    graph is being captured a fresh buffer is taken instead (it belongs to that graph's memory)."""
+    if torch.cuda.is_current_stream_capturing():
+        return torch.empty(n_floats, dtype=torch.float32, device=device)
+    key = torch.device(device).index or 0
+    buf = _WORKSPACES.get(key)
+    if buf is None or buf.numel() < n_floats:
+        buf = _WORKSPACES[key] = torch.empty(max(n_floats, 1 << 22), dtype=torch.float32, device=device)
+    return buf
+
+
 _cut_few_applied = None
 
 
@@ -97,20 +114,26 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, *, epilogue: Optional[str] = None,
     if out is None:
         out = torch.empty((M, n_out), dtype=torch.float32 if epilogue == "f32" else torch.bfloat16, device=x.device)
     ws = counts = None
-    n_cut = zmax = 0
     if cut is None:
         cut = OPTIONS.gemm_cut
-    if splits is None and cut is not False:
-        _, n_cut, zmax, _ = plan_stream(M, N, K, epilogue)
     _apply_cut_few()
-    if splits is None:
-        splits = 1 if n_cut else plan_splits(M, N, K, sm_count(x.device))
-    splits = max(1, min(int(splits), (K + 63) // 64))
-    if splits > 1:
-        ws = torch.empty(splits * M * N, dtype=torch.float32, device=x.device)
-    elif n_cut:
-        ws = torch.empty(n_cut * zmax * 128 * 256, dtype=torch.float32, device=x.device)
-        counts = _counts(x.device)
+    # what the library will do with this shape, remembered: a prompt step asks a hundred times for a handful of shapes
+    key = (M, N, K, epilogue, splits, bool(cut), OPTIONS.gemm_cut_few)
+    plan = _PLANS.get(key)
+    if plan is None:
+        n_cut = zmax = 0
+        if splits is None and cut is not False:
+            _, n_cut, zmax, _ = plan_stream(M, N, K, epilogue)
+        sp = splits
+        if sp is None:
+            sp = 1 if n_cut else plan_splits(M, N, K, sm_count(x.device))
+        sp = max(1, min(int(sp), (K + 63) // 64))
+        plan = _PLANS[key] = (sp, n_cut, sp * M * N if sp > 1 else n_cut * zmax * 128 * 256)
+    splits, n_cut, ws_floats = plan
+    if ws_floats:
+        ws = _workspace(ws_floats, x.device)
+        if splits == 1:
+            counts = _counts(x.device)
     check(fn("gemm_tc", "sx_gemm_tc")(ptr(x), ptr(w), ptr(out), c_int(M), c_int(N), c_int(K), c_int(_EPI[epilogue]),
                                       c_int(splits), ptr(ws), ctypes.c_ulonglong(0 if ws is None else ws.numel()),
                                       ptr(counts), stream()), "gemm_tc", launches=2 if splits > 1 else 1)

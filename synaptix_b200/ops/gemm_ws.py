@@ -12,6 +12,9 @@ _EPI = {None: 0, "f32": 1, "silu_mul": 2, "residual": 3}
 MAX_ROWS = 256
 
 
+_RESIDUAL_PLANS = {}
+
+
 def ws_supported(M: int, N: int, K: int, x_dtype, w_dtype) -> bool:
     return x_dtype == torch.bfloat16 and w_dtype == torch.bfloat16 and 0 < M <= MAX_ROWS and K > 0 and K % 8 == 0 and N > 0
 
@@ -68,7 +71,10 @@ def gemm_ws_residual(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, gain: to
         raise KernelError("gemm_ws_residual: gain must be float32 [N]")
     if not ws_supported(M, N, K, x.dtype, w.dtype):
         raise KernelError("gemm_ws_residual: bfloat16 operands, at most 256 rows and K a multiple of 8")
-    tiles, auto = plan_ws(M, N, K, "residual")
+    plan = _RESIDUAL_PLANS.get((M, N, K))          # (a step asks dozens of times for two shapes)
+    if plan is None:
+        plan = _RESIDUAL_PLANS[(M, N, K)] = plan_ws(M, N, K, "residual")
+    tiles, auto = plan
     splits = splits or auto
     while splits > (K + 63) // 64:
         splits //= 2
