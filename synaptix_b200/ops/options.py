@@ -15,11 +15,11 @@ switches in its runtime options (crates/synaptix-config/src/runtime.rs, ``AttnBa
                     leave SMs idle
 ``gemm_cut_few``    a few hundred rows: tiles fewer than the SMs are cut over K too, where an estimate
                     from measured times says that beats whole tiles
-``gemm_ws``         17 to 128 rows: the product with the weights as the tensor cores' M side, K shared by
+``gemm_ws``         2 to 160 rows: the product with the weights as the tensor cores' M side, K shared by
                     the blocks of a cluster (else the tcgen05 product of prompt steps, split over K)
 ``qkv_epilogue``    prompt steps at head size 128: the q/k/v product prepares the heads in its epilogue (norm,
                     rotation, cache write; else a head-preparation launch)
-``fused_residual``  3 to 128 rows: the o / down product adds itself into the residual stream and
+``fused_residual``  2 to 160 rows: the o / down product adds itself into the residual stream and
                     prepares the next norm
 ``pdl``             kernels are launched with programmatic dependent launch
 """
