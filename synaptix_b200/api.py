@@ -58,13 +58,14 @@ class LLM:
                  top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, repetition_penalty: float = 1.0,
                  repeat_last_n: int = 0, presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
                  seed: int = 0, eos_token_id: Optional[int] = None, eos_token_ids: Optional[Sequence[int]] = None,
-                 max_batch_size: Optional[int] = None,
+                 max_batch_size: Optional[int] = None, prefill_batch: int = 0,
                  on_token: Optional[Callable[[int, int], None]] = None,
                  return_details: bool = False):
         """Generate for each prompt (a list of token ids); returns the new tokens of each.
 
         Stop tokens: ``eos_token_ids`` together with ``eos_token_id``; if neither is given,
         the model configuration's.  A stop token ends its sequence and is part of the output.
+        ``prefill_batch``: prompts run in portions of that many tokens a sequence (0: whole, in one step).
         """
         single = len(prompts) > 0 and isinstance(prompts[0], int)
         if single:
@@ -79,7 +80,7 @@ class LLM:
                                 seed=seed)
         sampler = Sampler(params, self.engine.device)
         opts = GenerationOptions(max_new_tokens=max_new_tokens, stop_token_ids=stop, sampling=params,
-                                 max_batch_size=max_batch_size)
+                                 max_batch_size=max_batch_size, prefill_batch=prefill_batch)
         results, stats = run_generation(self.engine, sampler.sample_to_host, prompts, opts, on_token=on_token)
         self.last_stats = stats
         if return_details:

@@ -56,6 +56,8 @@ def build_parser() -> argparse.ArgumentParser:
     run.add_argument("--presence-penalty", type=float, default=0.0)
     run.add_argument("--frequency-penalty", type=float, default=0.0)
     run.add_argument("--device", default="cuda", help="cuda or cuda:N (there is no CPU path)")
+    run.add_argument("--prefill-batch", type=int, default=0,
+                     help="run the prompt in portions of N tokens (0: the whole prompt in one step)")
     run.add_argument("--max-seq", type=int, default=None,
                      help="cache capacity per sequence; default prompt + max-tokens")
     run.add_argument("--compute-dtype", default="bf16", help="bf16 or f32 (f32: everything in true 32-bit)")
@@ -109,7 +111,8 @@ def cmd_run(a) -> int:
     load_s = time.perf_counter() - t0
     kw = dict(max_new_tokens=a.max_tokens, temperature=a.temperature, top_k=a.top_k, top_p=a.top_p,
               min_p=a.min_p, repetition_penalty=a.repetition_penalty, repeat_last_n=a.repeat_last_n,
-              presence_penalty=a.presence_penalty, frequency_penalty=a.frequency_penalty, seed=a.seed)
+              presence_penalty=a.presence_penalty, frequency_penalty=a.frequency_penalty, seed=a.seed,
+              prefill_batch=a.prefill_batch)
     if a.stop_ids is not None:
         kw["eos_token_ids"] = parse_ids(a.stop_ids)
     if a.warmup:

@@ -40,6 +40,7 @@ class GenerationOptions:
     stop_token_ids: Tuple[int, ...] = ()
     sampling: SamplingParams = SamplingParams()
     max_batch_size: Optional[int] = None      # None: as many as the cache holds
+    prefill_batch: int = 0                    # prompts run in portions of this many tokens a sequence (0: whole, in one step)
     lookahead: int = 2                        # decode steps enqueued before the oldest one's tokens are read
 
 
@@ -97,6 +98,35 @@ def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, max_tokens: in
     return batches
 
 
+def _run_prompts(engine, live, portion: int):
+    """The prompts of a batch through the step function; returns the logits at every sequence's last prompt token,
+    in the order of ``live``.  ``portion`` 0: all prompts whole, in one step.  Otherwise (the reference's
+    ``prefill_batch``, generate.rs:255-271) in steps of at most ``portion`` tokens a sequence, which bounds a step's
+    activations whatever the prompts' lengths; a sequence's logits come from the step that holds its last token."""
+    if portion <= 0 or all(len(s.prompt) <= portion for s in live):
+        return engine.step([Entry(s.slot, s.prompt, [len(s.prompt) - 1]) for s in live], keep=False)
+    rows = [None] * len(live)
+    off = 0
+    longest = max(len(s.prompt) for s in live)
+    while off < longest:
+        part = [(i, s) for i, s in enumerate(live) if len(s.prompt) > off]
+        entries, ends = [], []
+        for i, s in part:
+            piece = s.prompt[off:off + portion]
+            last = off + len(piece) == len(s.prompt)
+            entries.append(Entry(s.slot, piece, [len(piece) - 1] if last else []))
+            if last:
+                ends.append(i)
+        logits = engine.step(entries, keep=True)
+        for k, i in enumerate(ends):
+            rows[i] = logits[k]
+        off += portion
+    if hasattr(rows[0], "dim"):          # tensors from the engine (the loop's tests drive it with plain lists)
+        import torch
+        return torch.stack(rows)
+    return rows
+
+
 def run_generation(engine, sample: Callable, prompts: Sequence[Sequence[int]], options: GenerationOptions,
                    on_token: Optional[Callable[[int, int], None]] = None,
                    clock: Callable[[], float] = time.perf_counter):
@@ -139,7 +169,7 @@ def run_generation(engine, sample: Callable, prompts: Sequence[Sequence[int]], o
         stats.batches += 1
         live = [_Live(i, engine.open(), prompts[i]) for i in batch]
         t0 = clock()
-        logits = engine.step([Entry(s.slot, s.prompt, [len(s.prompt) - 1]) for s in live], keep=False)
+        logits = _run_prompts(engine, live, options.prefill_batch)
         toks = sample(logits, [s.request for s in live], [0] * len(live),
                       [s.prompt for s in live] if need_ctx else None)
         engine.check_kernels()            # the host has waited for the prompt step: did all of it run?

@@ -237,3 +237,22 @@ def test_on_token_streams_in_order():
     run_generation(eng, counter_sample, [[1], [50]], GenerationOptions(max_new_tokens=2),
                    on_token=lambda i, t: got.append((i, t)))
     assert got == [(0, 2), (1, 51), (0, 3), (1, 52)]
+
+
+def test_prompts_in_portions_run_the_same_tokens_in_more_steps():
+    """``prefill_batch`` (the reference's name, generate.rs:255-271): prompts go through the step function in portions
+    of that many tokens a sequence; a sequence's first token comes from the step that holds its last prompt token."""
+    prompts = [[10, 11, 12], list(range(20, 29)), list(range(40, 50))]
+    def sample(logits, requests, steps, ctx):
+        return list(logits)
+    whole_eng, part_eng = CounterEngine(), CounterEngine()
+    whole, _ = run_generation(whole_eng, sample, prompts, GenerationOptions(max_new_tokens=3))
+    parts, stats = run_generation(part_eng, sample, prompts, GenerationOptions(max_new_tokens=3, prefill_batch=4))
+    assert [r.tokens for r in parts] == [r.tokens for r in whole] == [[13, 14, 15], [29, 30, 31], [50, 51, 52]]
+    assert [sorted(n for _, n in st) for st in whole_eng.steps[:1]] == [[3, 9, 10]]
+    assert [sorted(n for _, n in st) for st in part_eng.steps[:3]] == [[3, 4, 4], [4, 4], [1, 2]]
+    assert stats.prompt_tokens == 22
+    # a portion at least as long as every prompt: one step, as without it
+    eng = CounterEngine()
+    run_generation(eng, sample, prompts, GenerationOptions(max_new_tokens=2, prefill_batch=10))
+    assert sorted(n for _, n in eng.steps[0]) == [3, 9, 10]

@@ -158,3 +158,15 @@ def test_penalties_in_a_batch_whose_sequences_end_at_different_times():
         assert r.tokens == plain(p, 14, stop=(stop,))
     assert res[1].finish_reason == "stop" and len(res[1].tokens) <= 5
     assert any(len(r.tokens) == 14 for r in res)
+
+
+def test_prompts_in_portions_generate_the_same_tokens():
+    """``prefill_batch``: the prompts in portions of 50 tokens a sequence instead of one step; float32, so the
+    greedy tokens are the plain implementation's either way."""
+    import synaptix_b200
+    cfg, W = oracle("B")
+    prompts = [random_tokens(389, n, 1400 + n) for n in (3, 120, 51, 100)]
+    llm = synaptix_b200.LLM(folder("B"), compute_dtype="f32", max_tokens=1024)
+    want = [P.greedy_generate(cfg, W, p, 5) for p in prompts]
+    assert llm.generate(prompts, max_new_tokens=5, eos_token_ids=[], prefill_batch=50) == want
+    assert llm.generate(prompts, max_new_tokens=5, eos_token_ids=[]) == want
