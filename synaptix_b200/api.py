@@ -59,13 +59,15 @@ class LLM:
                  repeat_last_n: int = 0, presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
                  seed: int = 0, eos_token_id: Optional[int] = None, eos_token_ids: Optional[Sequence[int]] = None,
                  max_batch_size: Optional[int] = None, prefill_batch: int = 0,
-                 on_token: Optional[Callable[[int, int], None]] = None,
+                 on_token: Optional[Callable[[int, int], Optional[bool]]] = None,
                  return_details: bool = False):
         """Generate for each prompt (a list of token ids); returns the new tokens of each.
 
         Stop tokens: ``eos_token_ids`` together with ``eos_token_id``; if neither is given,
         the model configuration's.  A stop token ends its sequence and is part of the output.
         ``prefill_batch``: prompts run in portions of that many tokens a sequence (0: whole, in one step).
+        ``on_token(request, token)`` is called for every new token; if it returns ``False`` that sequence ends there
+        (``finish_reason`` "cancelled").
         """
         single = len(prompts) > 0 and isinstance(prompts[0], int)
         if single:

@@ -47,7 +47,7 @@ class GenerationOptions:
 @dataclasses.dataclass
 class GenerationResult:
     tokens: List[int]
-    finish_reason: str          # "stop", "length" or "capacity"
+    finish_reason: str          # "stop", "length", "capacity" or "cancelled" (the token callback returned False)
     prompt_tokens: int
 
 
@@ -154,8 +154,11 @@ def run_generation(engine, sample: Callable, prompts: Sequence[Sequence[int]], o
         """Record a token; True if the sequence goes on."""
         seq.out.append(token)
         stats.new_tokens += 1
-        if on_token is not None:
-            on_token(seq.request, token)
+        # (as the reference's StreamSink::on_token -> bool, generate.rs:67-75,279-291: a callback that returns False
+        #  ends its sequence after this token; anything else, None included, lets it go on)
+        if on_token is not None and on_token(seq.request, token) is False:
+            finish(seq, "cancelled")
+            return False
         if token in stop:
             finish(seq, "stop")
             return False

@@ -256,3 +256,18 @@ def test_prompts_in_portions_run_the_same_tokens_in_more_steps():
     eng = CounterEngine()
     run_generation(eng, sample, prompts, GenerationOptions(max_new_tokens=2, prefill_batch=10))
     assert sorted(n for _, n in eng.steps[0]) == [3, 9, 10]
+
+
+def test_a_token_callback_that_returns_false_ends_its_sequence():
+    """The reference's sink cancels by returning false from ``on_token`` (generate.rs:67-75); here per sequence."""
+    prompts = [[10], [20], [30]]
+    seen = []
+    def on_token(request, token):
+        seen.append((request, token))
+        return not (request == 1 and token == 22)          # None or True goes on; False ends request 1 at its second token
+    eng = CounterEngine()
+    results, _ = run_generation(eng, lambda logits, *a: list(logits), prompts, GenerationOptions(max_new_tokens=4), on_token=on_token)
+    assert [r.tokens for r in results] == [[11, 12, 13, 14], [21, 22], [31, 32, 33, 34]]
+    assert [r.finish_reason for r in results] == ["length", "cancelled", "length"]
+    assert sorted(eng.closed) == sorted(eng.opened) and eng.slots.n_live == 0
+    assert (1, 22) in seen and (1, 23) not in seen
