@@ -72,6 +72,24 @@ class LLM:
         single = len(prompts) > 0 and isinstance(prompts[0], int)
         if single:
             prompts = [prompts]
+        out = self._generate(prompts, self.engine, None, None, max_new_tokens=max_new_tokens, temperature=temperature,
+                             top_k=top_k, top_p=top_p, min_p=min_p, repetition_penalty=repetition_penalty,
+                             repeat_last_n=repeat_last_n, presence_penalty=presence_penalty,
+                             frequency_penalty=frequency_penalty, seed=seed, eos_token_id=eos_token_id,
+                             eos_token_ids=eos_token_ids, max_batch_size=max_batch_size, prefill_batch=prefill_batch,
+                             on_token=on_token, return_details=return_details)
+        return out[0] if single else out
+
+    def conversation(self) -> "Conversation":
+        """A sequence whose cache is kept between calls (see ``Conversation``); close it to give its slot back."""
+        return Conversation(self)
+
+    def _generate(self, prompts, engine, cached, lookahead, max_new_tokens: int = 64, temperature: float = 0.0,
+                  top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, repetition_penalty: float = 1.0,
+                  repeat_last_n: int = 0, presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
+                  seed: int = 0, eos_token_id: Optional[int] = None, eos_token_ids: Optional[Sequence[int]] = None,
+                  max_batch_size: Optional[int] = None, prefill_batch: int = 0, on_token=None,
+                  return_details: bool = False):
         if eos_token_id is None and eos_token_ids is None:
             stop: Tuple[int, ...] = tuple(self.model.stop_token_ids)
         else:
@@ -82,13 +100,69 @@ class LLM:
                                 seed=seed)
         sampler = Sampler(params, self.engine.device)
         opts = GenerationOptions(max_new_tokens=max_new_tokens, stop_token_ids=stop, sampling=params,
-                                 max_batch_size=max_batch_size, prefill_batch=prefill_batch)
-        results, stats = run_generation(self.engine, sampler.sample_to_host, prompts, opts, on_token=on_token)
+                                 max_batch_size=max_batch_size, prefill_batch=prefill_batch,
+                                 **({} if lookahead is None else {"lookahead": lookahead}))
+        results, stats = run_generation(engine, sampler.sample_to_host, prompts, opts, on_token=on_token, cached=cached)
         self.last_stats = stats
-        if return_details:
-            return results[0] if single else results
-        out = [r.tokens for r in results]
-        return out[0] if single else out
+        return results if return_details else [r.tokens for r in results]
+
+
+class _HeldSlot:
+    """The engine as the generation loop knows it, with ONE slot that is open already and stays open: ``open`` hands
+    that slot out, ``close`` leaves it alone.  Everything else is the engine's."""
+
+    def __init__(self, engine, slot: int):
+        self._engine, self._slot = engine, slot
+        self.max_seqs = 1
+
+    def open(self) -> int:
+        return self._slot
+
+    def close(self, slot: int) -> None:
+        pass
+
+    def __getattr__(self, name):
+        return getattr(self._engine, name)
+
+
+class Conversation:
+    """One sequence whose cache is kept between calls, so that a prompt which goes on from the last call's tokens
+    runs only what is new (the reference keeps a ``KvCache`` between the turns of a chat the same way:
+    ``generate_streaming_resume``, crates/synaptix-models/llm/qwen3/src/pipeline.rs:134-147, generate.rs:248-250).
+
+    ``generate(prompt, ...)`` takes the WHOLE sequence so far (earlier prompts, earlier answers and what is new) and
+    the options of ``LLM.generate``.  The tokens in the cache must be its beginning; here that is checked (the
+    reference trusts the caller)."""
+
+    def __init__(self, llm: "LLM"):
+        self.llm = llm
+        self.slot: Optional[int] = llm.engine.open()
+        self.tokens: List[int] = []          # the tokens whose keys and values the cache holds, in order
+
+    def generate(self, prompt: Sequence[int], **kw) -> List[int]:
+        if self.slot is None:
+            raise ValueError("this conversation is closed")
+        prompt = list(prompt)
+        n = len(self.tokens)
+        if len(prompt) <= n or prompt[:n] != self.tokens:
+            raise ValueError("the prompt must begin with the conversation's tokens so far and bring at least one more "
+                             f"({n} tokens are cached)")
+        # one step at a time (no step launched ahead), so that the cache ends with exactly the tokens that were drawn
+        out = self.llm._generate([prompt], _HeldSlot(self.llm.engine, self.slot), [n], 1, **kw)[0]
+        held = self.llm.engine.cache.slots.length(self.slot)
+        self.tokens = (prompt + out)[:held]     # every token that went through the model: all but the last one drawn
+        return out
+
+    def close(self) -> None:
+        if self.slot is not None:
+            self.llm.engine.close(self.slot)
+            self.slot = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
 
 
 def load_llm(model_dir: str, **kw) -> LLM:

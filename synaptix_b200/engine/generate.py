@@ -65,10 +65,11 @@ class GenerationStats:
 
 
 class _Live:
-    __slots__ = ("request", "slot", "prompt", "out")
+    __slots__ = ("request", "slot", "prompt", "out", "feed")
 
-    def __init__(self, request, slot, prompt):
+    def __init__(self, request, slot, prompt, cached=0):
         self.request, self.slot, self.prompt, self.out = request, slot, prompt, []
+        self.feed = prompt[cached:] if cached else prompt       # what the prompt step runs: the cache holds the rest already
 
 
 def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, max_tokens: int, max_seqs: int,
@@ -103,17 +104,17 @@ def _run_prompts(engine, live, portion: int):
     in the order of ``live``.  ``portion`` 0: all prompts whole, in one step.  Otherwise (the reference's
     ``prefill_batch``, generate.rs:255-271) in steps of at most ``portion`` tokens a sequence, which bounds a step's
     activations whatever the prompts' lengths; a sequence's logits come from the step that holds its last token."""
-    if portion <= 0 or all(len(s.prompt) <= portion for s in live):
-        return engine.step([Entry(s.slot, s.prompt, [len(s.prompt) - 1]) for s in live], keep=False)
+    if portion <= 0 or all(len(s.feed) <= portion for s in live):
+        return engine.step([Entry(s.slot, s.feed, [len(s.feed) - 1]) for s in live], keep=False)
     rows = [None] * len(live)
     off = 0
-    longest = max(len(s.prompt) for s in live)
+    longest = max(len(s.feed) for s in live)
     while off < longest:
-        part = [(i, s) for i, s in enumerate(live) if len(s.prompt) > off]
+        part = [(i, s) for i, s in enumerate(live) if len(s.feed) > off]
         entries, ends = [], []
         for i, s in part:
-            piece = s.prompt[off:off + portion]
-            last = off + len(piece) == len(s.prompt)
+            piece = s.feed[off:off + portion]
+            last = off + len(piece) == len(s.feed)
             entries.append(Entry(s.slot, piece, [len(piece) - 1] if last else []))
             if last:
                 ends.append(i)
@@ -129,16 +130,21 @@ def _run_prompts(engine, live, portion: int):
 
 def run_generation(engine, sample: Callable, prompts: Sequence[Sequence[int]], options: GenerationOptions,
                    on_token: Optional[Callable[[int, int], None]] = None,
-                   clock: Callable[[], float] = time.perf_counter):
+                   clock: Callable[[], float] = time.perf_counter, cached: Optional[Sequence[int]] = None):
     """Generate for every prompt; returns ``(results, stats)`` in the prompts' order.
 
     ``sample(logits, request_index, step, contexts) -> list of ints`` draws one token per row.
     ``on_token(request_index, token)`` is called for every token as it is produced.
+    ``cached[i]``: so many leading tokens of prompt ``i`` are in the cache of the slot that ``engine.open()`` will
+    return for it (a sequence that goes on from an earlier call, as the reference's ``generate_streaming_resume``
+    starts its prompt at ``kv.seq_len``, generate.rs:248-250); the prompt step runs the rest, at least one token.
     """
     prompts = [list(p) for p in prompts]
     for i, p in enumerate(prompts):
         if not p:
             raise ValueError(f"request {i}: the prompt is empty")
+        if cached is not None and not (0 <= cached[i] < len(p)):
+            raise ValueError(f"request {i}: {cached[i]} cached tokens for a prompt of {len(p)}: at least one token must run")
     results: List[Optional[GenerationResult]] = [None] * len(prompts)
     stats = GenerationStats()
     if options.max_new_tokens <= 0:
@@ -170,14 +176,14 @@ def run_generation(engine, sample: Callable, prompts: Sequence[Sequence[int]], o
     for batch in plan_batches([len(p) for p in prompts], options.max_new_tokens, engine.max_tokens,
                               engine.max_seqs, options.max_batch_size):
         stats.batches += 1
-        live = [_Live(i, engine.open(), prompts[i]) for i in batch]
+        live = [_Live(i, engine.open(), prompts[i], cached[i] if cached is not None else 0) for i in batch]
         t0 = clock()
         logits = _run_prompts(engine, live, options.prefill_batch)
         toks = sample(logits, [s.request for s in live], [0] * len(live),
                       [s.prompt for s in live] if need_ctx else None)
         engine.check_kernels()            # the host has waited for the prompt step: did all of it run?
         stats.prefill_ms += (clock() - t0) * 1e3
-        stats.prompt_tokens += sum(len(s.prompt) for s in live)
+        stats.prompt_tokens += sum(len(s.feed) for s in live)
         live = [s for s, t in zip(live, toks) if take(s, int(t))]
 
         t0 = clock()

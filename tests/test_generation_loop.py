@@ -271,3 +271,14 @@ def test_a_token_callback_that_returns_false_ends_its_sequence():
     assert [r.finish_reason for r in results] == ["length", "cancelled", "length"]
     assert sorted(eng.closed) == sorted(eng.opened) and eng.slots.n_live == 0
     assert (1, 22) in seen and (1, 23) not in seen
+
+
+def test_a_prompt_whose_beginning_is_cached_runs_only_the_rest():
+    """``cached``: a sequence that goes on from an earlier call (the reference's resume, generate.rs:248-250)."""
+    sample = lambda logits, *a: list(logits)
+    eng = CounterEngine()
+    results, stats = run_generation(eng, sample, [[1, 2, 3, 4, 5], [7, 8]], GenerationOptions(max_new_tokens=2), cached=[3, 0])
+    assert sorted(n for _, n in eng.steps[0]) == [2, 2] and stats.prompt_tokens == 4
+    assert [r.tokens for r in results] == [[6, 7], [9, 10]] and [r.prompt_tokens for r in results] == [5, 2]
+    with pytest.raises(ValueError):
+        run_generation(CounterEngine(), sample, [[1, 2, 3]], GenerationOptions(max_new_tokens=2), cached=[3])

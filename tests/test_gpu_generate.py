@@ -170,3 +170,39 @@ def test_prompts_in_portions_generate_the_same_tokens():
     want = [P.greedy_generate(cfg, W, p, 5) for p in prompts]
     assert llm.generate(prompts, max_new_tokens=5, eos_token_ids=[], prefill_batch=50) == want
     assert llm.generate(prompts, max_new_tokens=5, eos_token_ids=[]) == want
+
+
+def test_a_conversation_keeps_its_cache_between_calls():
+    """``LLM.conversation()``: the second and third call run only the new tokens of their prompts and draw what a
+    fresh generation from the whole prompt draws (float32, greedy: the plain implementation's tokens)."""
+    import synaptix_b200
+    cfg, W = oracle("B")
+    llm = synaptix_b200.LLM(folder("B"), compute_dtype="f32", max_tokens=1024)
+    turns = [random_tokens(389, n, 1500 + n) for n in (70, 9, 31)]
+    with llm.conversation() as conv:
+        seq = []
+        for k, new in enumerate(turns):
+            seq = seq + new
+            out = conv.generate(seq, max_new_tokens=6, eos_token_ids=[])
+            assert out == P.greedy_generate(cfg, W, seq, 6), f"turn {k}"
+            assert llm.last_stats.prompt_tokens == len(new) + (1 if k else 0)     # + the last token drawn in the turn before
+            seq = seq + out
+            assert conv.tokens == seq[:-1]
+        with pytest.raises(ValueError):
+            conv.generate(seq[:-3], max_new_tokens=2)           # nothing new
+        with pytest.raises(ValueError):
+            conv.generate([1] + seq[1:] + [5], max_new_tokens=2)  # other tokens than the cache holds
+        # a stop token ends a turn; the conversation goes on after it
+        stop = P.greedy_generate(cfg, W, seq + [3], 4)[1]
+        out = conv.generate(seq + [3], max_new_tokens=4, eos_token_ids=[stop])
+        assert out[-1] == stop and len(out) <= 2
+        seq = seq + [3] + out
+        assert conv.generate(seq + [8], max_new_tokens=3, eos_token_ids=[]) == P.greedy_generate(cfg, W, seq + [8], 3)
+    assert llm.engine.cache.slots.n_live == 0
+    # other requests run beside an open conversation
+    conv = llm.conversation()
+    a = conv.generate(turns[0], max_new_tokens=3, eos_token_ids=[])
+    assert llm.generate([turns[1], turns[2]], max_new_tokens=3, eos_token_ids=[]) == [P.greedy_generate(cfg, W, t, 3) for t in turns[1:]]
+    assert conv.generate(turns[0] + a + [4], max_new_tokens=3, eos_token_ids=[]) == P.greedy_generate(cfg, W, turns[0] + a + [4], 3)
+    conv.close()
+    assert llm.engine.cache.slots.n_live == 0
