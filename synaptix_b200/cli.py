@@ -36,6 +36,25 @@ def _dtype_arg(s: str) -> str:
     return table[s.lower()]
 
 
+_ATTN = {"auto": None, "flash-decode": None, "flash_decode": None, "decode": None,
+         "fa2": False, "flash2": False, "flash-attn-2": False, "fa4": True, "flash4": True, "flash-attn-4": True}
+_ATTN_HELP = ("attention backend, the reference's names (synaptix-core/src/backend/attn.rs:47-56): auto (default); "
+              "fa4: prompt attention on the tcgen05 tensor cores; fa2: on mma.sync tiles; flash-decode: accepted, equals "
+              "auto here (single-token steps always run the split-KV decode kernel)")
+
+
+def _set_attn(name) -> None:
+    """``--attn``: which prompt-attention kernel runs (an option of this process, ``ops.set_options(attn_tc=...)``)."""
+    if name is None:
+        return
+    key = name.strip().lower()
+    if key not in _ATTN:
+        raise SystemExit(f"unknown --attn {name!r}: use auto, flash-decode, fa2 or fa4")
+    if _ATTN[key] is not None:
+        from . import ops
+        ops.set_options(attn_tc=_ATTN[key])
+
+
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="synaptix_b200", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -60,6 +79,7 @@ def build_parser() -> argparse.ArgumentParser:
                      help="run the prompt in portions of N tokens (0: the whole prompt in one step)")
     run.add_argument("--max-seq", type=int, default=None,
                      help="cache capacity per sequence; default prompt + max-tokens")
+    run.add_argument("--attn", default=None, help=_ATTN_HELP)
     run.add_argument("--compute-dtype", default="bf16", help="bf16 or f32 (f32: everything in true 32-bit)")
     run.add_argument("--no-graph", action="store_true", help="do not replay decode steps as CUDA graphs")
     run.add_argument("--nvtx", action="store_true", help="name every step for a profiler's timeline (NVTX ranges)")
@@ -74,6 +94,7 @@ def build_parser() -> argparse.ArgumentParser:
     bench.add_argument("--batch-size", type=int, default=1)
     bench.add_argument("--warmup", type=int, default=3)
     bench.add_argument("--device", default="cuda")
+    bench.add_argument("--attn", default=None, help=_ATTN_HELP)
     bench.add_argument("--dtype", default="bf16")
 
     rnd = sub.add_parser("random", help="write a model folder with seeded random weights")
@@ -95,6 +116,7 @@ def _device(s: str) -> str:
 
 def cmd_run(a) -> int:
     from .api import LLM
+    _set_attn(a.attn)
     prompts: List[List[int]] = []
     if a.prompt_file:
         with open(a.prompt_file) as f:
@@ -136,6 +158,7 @@ def cmd_run(a) -> int:
 
 def cmd_bench(a) -> int:
     from .api import LLM
+    _set_attn(a.attn)
     n_prompt = a.prompt_tokens or 32
     B = a.batch_size
     llm = LLM(a.model, compute_dtype=_dtype_arg(a.dtype), device=_device(a.device),

@@ -1,0 +1,34 @@
+"""The command line's options: the reference's names and defaults where it has them
+(crates/synaptix-cli/src/bin/synaptix.rs:49-135, `Run` and `Bench`)."""
+import pytest
+
+from synaptix_b200 import cli, ops
+
+
+def test_run_and_bench_take_the_references_options_with_its_defaults():
+    p = cli.build_parser()
+    a = p.parse_args(["run", "MODEL"])
+    assert (a.prompt, a.max_tokens, a.temperature, a.seed, a.device, a.max_seq, a.attn) == ("", 128, 1.0, 0, "cuda", None, None)
+    assert (a.prompt_file, a.no_graph, a.warmup, a.prefill_batch) == (None, False, False, 0)
+    a = p.parse_args(["run", "MODEL", "5 17 3", "--max-tokens", "9", "--temperature", "0", "--top-k", "40", "--top-p", "0.9",
+                      "--min-p", "0.05", "--repetition-penalty", "1.1", "--seed", "7", "--max-seq", "512", "--attn", "fa2",
+                      "--compute-dtype", "f32", "--no-graph", "--warmup", "--prefill-batch", "256"])
+    assert (a.max_tokens, a.top_k, a.top_p, a.min_p, a.repetition_penalty, a.prefill_batch) == (9, 40, 0.9, 0.05, 1.1, 256)
+    b = p.parse_args(["bench", "MODEL"])
+    assert (b.n_tokens, b.prompt_tokens, b.batch_size, b.warmup, b.device, b.attn) == (128, 0, 1, 3, "cuda", None)
+
+
+def test_attn_names_choose_the_prompt_attention_kernel():
+    was = ops.OPTIONS.attn_tc
+    try:
+        for name, want in (("fa2", False), ("fa4", True), ("flash-attn-2", False), ("FA4", True)):
+            cli._set_attn(name)
+            assert ops.OPTIONS.attn_tc is want
+        ops.set_options(attn_tc=False)
+        for name in (None, "auto", "flash-decode", "decode"):       # leave the choice as it is
+            cli._set_attn(name)
+            assert ops.OPTIONS.attn_tc is False
+        with pytest.raises(SystemExit):
+            cli._set_attn("fa3")
+    finally:
+        ops.set_options(attn_tc=was)
