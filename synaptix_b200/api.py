@@ -131,22 +131,40 @@ class Conversation:
     ``generate_streaming_resume``, crates/synaptix-models/llm/qwen3/src/pipeline.rs:134-147, generate.rs:248-250).
 
     ``generate(prompt, ...)`` takes the WHOLE sequence so far (earlier prompts, earlier answers and what is new) and
-    the options of ``LLM.generate``.  The tokens in the cache must be its beginning; here that is checked (the
-    reference trusts the caller)."""
+    the options of ``LLM.generate``.  If the cached tokens are the prompt's beginning only the rest runs; otherwise
+    the cache is dropped and the whole prompt runs (``reusable`` / ``invalidate``, as the reference's
+    ``LlmKvSession``, crates/synaptix/src/facade/llm.rs:515-590)."""
 
     def __init__(self, llm: "LLM"):
         self.llm = llm
         self.slot: Optional[int] = llm.engine.open()
         self.tokens: List[int] = []          # the tokens whose keys and values the cache holds, in order
 
+    @property
+    def cached_tokens(self) -> int:
+        return len(self.tokens)
+
+    def reusable(self, prompt: Sequence[int]) -> int:
+        """How many tokens of ``prompt`` the cache holds already: all cached tokens, if they are the prompt's beginning
+        and the prompt brings at least one more (its last token always runs: the first logits come from it); else 0."""
+        n = len(self.tokens)
+        return n if 0 < n < len(prompt) and list(prompt[:n]) == self.tokens else 0
+
+    def invalidate(self) -> None:
+        """Forget the cached tokens (the slot's pages go back; the sequence starts anew)."""
+        if self.slot is None:
+            raise ValueError("this conversation is closed")
+        self.llm.engine.close(self.slot)
+        self.slot = self.llm.engine.open()
+        self.tokens = []
+
     def generate(self, prompt: Sequence[int], **kw) -> List[int]:
         if self.slot is None:
             raise ValueError("this conversation is closed")
         prompt = list(prompt)
-        n = len(self.tokens)
-        if len(prompt) <= n or prompt[:n] != self.tokens:
-            raise ValueError("the prompt must begin with the conversation's tokens so far and bring at least one more "
-                             f"({n} tokens are cached)")
+        n = self.reusable(prompt)
+        if n == 0 and self.tokens:
+            self.invalidate()
         # one step at a time (no step launched ahead), so that the cache ends with exactly the tokens that were drawn
         out = self.llm._generate([prompt], _HeldSlot(self.llm.engine, self.slot), [n], 1, **kw)[0]
         held = self.llm.engine.cache.slots.length(self.slot)

@@ -188,10 +188,14 @@ def test_a_conversation_keeps_its_cache_between_calls():
             assert llm.last_stats.prompt_tokens == len(new) + (1 if k else 0)     # + the last token drawn in the turn before
             seq = seq + out
             assert conv.tokens == seq[:-1]
-        with pytest.raises(ValueError):
-            conv.generate(seq[:-3], max_new_tokens=2)           # nothing new
-        with pytest.raises(ValueError):
-            conv.generate([1] + seq[1:] + [5], max_new_tokens=2)  # other tokens than the cache holds
+        assert conv.cached_tokens == len(seq) - 1 and conv.reusable(seq + [1]) == len(seq) - 1
+        assert conv.reusable(seq[:-3]) == 0 and conv.reusable([1] + seq[1:] + [5]) == 0
+        # a prompt that does not go on from the cached tokens: the cache is dropped and the whole prompt runs
+        other = [1] + seq[1:40]
+        assert conv.generate(other, max_new_tokens=3, eos_token_ids=[]) == P.greedy_generate(cfg, W, other, 3)
+        assert llm.last_stats.prompt_tokens == len(other)
+        seq = other + conv.generate(other, max_new_tokens=3, eos_token_ids=[])     # nothing new either: whole again
+        assert llm.last_stats.prompt_tokens == len(other)
         # a stop token ends a turn; the conversation goes on after it
         stop = P.greedy_generate(cfg, W, seq + [3], 4)[1]
         out = conv.generate(seq + [3], max_new_tokens=4, eos_token_ids=[stop])
