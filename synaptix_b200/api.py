@@ -54,6 +54,19 @@ class LLM:
     def config(self):
         return self.model.config
 
+    @property
+    def vocab_size(self) -> int:
+        return self.model.vocab_size
+
+    @property
+    def device(self):
+        return self.engine.device
+
+    @property
+    def kv_bytes_per_token(self) -> int:
+        """Bytes of cache a token takes over all layers (as the reference's ``Llm::kv_bytes_per_token``)."""
+        return self.engine.cache.kv_bytes_per_token
+
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64, temperature: float = 0.0,
                  top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, repetition_penalty: float = 1.0,
                  repeat_last_n: int = 0, presence_penalty: float = 0.0, frequency_penalty: float = 0.0,

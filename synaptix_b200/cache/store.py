@@ -121,6 +121,12 @@ class Cache:
             windows = [r.window for r in kv_keys]
         self.slots = SequenceSlots(self.max_seqs, pools, windows)
 
+    @property
+    def kv_bytes_per_token(self) -> int:
+        """Bytes of keys and values one cached token takes over all layers (the reference's figure of that name,
+        crates/synaptix-models/llm/common/src/model.rs:932-954): 147,456 for the Qwen3-4B shape in bfloat16."""
+        return sum(2 * k.shape[0] * k.shape[2] * k.shape[4] * k.element_size() for k in self._k)
+
     # -- views ------------------------------------------------------------
     @property
     def n_block_tables(self) -> int:

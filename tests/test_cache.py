@@ -129,6 +129,7 @@ def test_cache_groups_requests_and_resets_state():
     c = Cache(reqs, max_tokens=200, max_seqs=3, dtype=torch.float32, device="cpu")
     assert c.n_pages == 5 and c.max_tokens == 256      # 4 pages to hand out + the never-used page 0
     assert len(c.kv_groups) == 2 and c.n_block_tables == 2
+    assert c.kv_bytes_per_token == 3 * 2 * 2 * 16 * 4               # three layers of keys and values, 2 heads of 16 floats
     v0, v1, v2 = c.view(0), c.view(1), c.view(2)
     assert v0.group == v2.group == 0 and v1.group == 1 and v1.window == 8
     assert v0.k.shape == (5, 2, PAGE_TOKENS, 16)
