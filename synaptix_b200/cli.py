@@ -97,6 +97,11 @@ def build_parser() -> argparse.ArgumentParser:
     bench.add_argument("--attn", default=None, help=_ATTN_HELP)
     bench.add_argument("--dtype", default="bf16")
 
+    ins = sub.add_parser("inspect", help="list the tensors of a safetensors file, or of a model folder with what its configuration says")
+    ins.add_argument("file", help="a .safetensors file, or a folder with config.json and model.safetensors")
+    ins.add_argument("-v", "--verbose", action="store_true", help="bytes of every tensor too")
+    ins.add_argument("-f", "--filter", default=None, help="only tensors whose name contains this")
+
     rnd = sub.add_parser("random", help="write a model folder with seeded random weights")
     rnd.add_argument("config", help="a config.json (or a folder holding one)")
     rnd.add_argument("out_dir")
@@ -156,6 +161,53 @@ def cmd_run(a) -> int:
     return 0
 
 
+def cmd_inspect(a) -> int:
+    """As the reference's ``inspect`` for safetensors (crates/synaptix-cli/src/commands/inspect.rs:66-93): every
+    tensor with its dtype and shape, how many were shown, and the total of bytes.  For a model folder first what the
+    configuration gives: the architecture, its sizes, the cache's bytes a token.  Needs no GPU."""
+    import os
+    from .weights.safetensors_io import SafetensorsFile
+    path = a.file
+    if os.path.isdir(path):
+        from .config import load_config
+        cfg = load_config(path)
+        d = cfg.to_dict()
+        print(f"=== model folder: {path} ===")
+        print(f"  architecture: {(d.get('architectures') or ['?'])[0]} ({d.get('model_type', '?')})")
+        for k in ("num_hidden_layers", "hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
+                  "intermediate_size", "vocab_size", "rope_theta", "rms_norm_eps", "tie_word_embeddings",
+                  "max_position_embeddings"):
+            if k in d:
+                print(f"  {k}: {d[k]}")
+        if all(k in d for k in ("num_hidden_layers", "num_key_value_heads", "head_dim")):
+            print(f"  cache, bfloat16: {2 * d['num_hidden_layers'] * d['num_key_value_heads'] * d['head_dim'] * 2} bytes a token")
+        print()
+        path = os.path.join(path, "model.safetensors")
+    f = SafetensorsFile(path)
+    print(f"=== SafeTensors: {path} ===")
+    print(f"  total tensors: {len(f.tensors)}")
+    print()
+    shown = total_bytes = params = 0
+    for name, info in f.tensors.items():
+        total_bytes += info.end - info.begin
+        n = 1
+        for x in info.shape:
+            n *= x
+        params += n
+        if a.filter is not None and a.filter not in name:
+            continue
+        shape = ",".join(str(x) for x in info.shape)
+        if a.verbose:
+            print(f"  {name} dtype={info.dtype} shape=[{shape}] bytes={info.end - info.begin}")
+        else:
+            print(f"  {name:<60} {info.dtype} [{shape}]")
+        shown += 1
+    print()
+    print(f"  shown {shown} of {len(f.tensors)} tensors, {params} elements, total {total_bytes} bytes "
+          f"({total_bytes / 1024.0 / 1024.0:.2f} MB)")
+    return 0
+
+
 def cmd_bench(a) -> int:
     from .api import LLM
     _set_attn(a.attn)
@@ -192,4 +244,4 @@ def cmd_random(a) -> int:
 
 def main(argv=None) -> int:
     a = build_parser().parse_args(argv)
-    return {"run": cmd_run, "bench": cmd_bench, "random": cmd_random}[a.command](a)
+    return {"run": cmd_run, "bench": cmd_bench, "random": cmd_random, "inspect": cmd_inspect}[a.command](a)

@@ -32,3 +32,19 @@ def test_attn_names_choose_the_prompt_attention_kernel():
             cli._set_attn("fa3")
     finally:
         ops.set_options(attn_tc=was)
+
+
+def test_inspect_lists_a_model_folder(tmp_path, capsys):
+    """``inspect`` (the reference has the command for safetensors files, commands/inspect.rs:66-93), on the CPU."""
+    import tiny
+    folder = tiny.make_folder("A", str(tmp_path / "a"))
+    assert cli.main(["inspect", folder]) == 0
+    out = capsys.readouterr().out
+    assert "architecture: Qwen3ForCausalLM (qwen3)" in out and "hidden_size: 64" in out
+    assert "cache, bfloat16: 256 bytes a token" in out                    # 2 layers x 2 kv heads x 16 x (K and V) x 2 bytes
+    assert "model.layers.1.self_attn.q_norm.weight" in out and "model.embed_tokens.weight" in out
+    n = 2 * 11 + 2                                                         # 11 tensors a layer, embedding and final norm (tied head)
+    assert f"shown {n} of {n} tensors" in out
+    assert cli.main(["inspect", folder + "/model.safetensors", "-f", "layers.0.mlp", "-v"]) == 0
+    out = capsys.readouterr().out
+    assert f"shown 3 of {n} tensors" in out and "bytes=" in out and "layers.1" not in out.split("total tensors")[1].split("shown")[0]
