@@ -45,3 +45,15 @@ def test_which_products_add_themselves_into_the_residual_stream():
     assert not ops.residual_product_fusable(8, 2560, 4096, torch.float32)
     with ops.options(fused_residual=False):
         assert not ops.residual_product_fusable(8, 2560, 4096, BF)
+
+
+def test_the_tile_product_splits_uniformly_only_a_handful_of_tiles():
+    """``plan_splits`` (the two-kernel form of the tcgen05 product): one row of tiles that leaves SMs idle, or up to a
+    dozen tiles; several rows of more tiles run whole (or cut by the persistent kernel)."""
+    from synaptix_b200.ops.gemm_tc import plan_splits
+    assert plan_splits(64, 2560, 4096, 148) > 1            # 10 tiles of 256 columns
+    assert plan_splits(200, 1000, 3072, 148) > 1           # 8 tiles in two rows
+    assert plan_splits(512, 2560, 4096, 148) == 1          # 40 tiles in four rows
+    assert plan_splits(256, 6144, 2560, 148) == 1
+    assert plan_splits(2048, 2560, 4096, 148) == 1         # more tiles than three quarters of the SMs
+    assert plan_splits(64, 151936, 2560, 148) == 1
