@@ -172,13 +172,15 @@ def test_prompts_in_portions_generate_the_same_tokens():
     assert llm.generate(prompts, max_new_tokens=5, eos_token_ids=[]) == want
 
 
-def test_a_conversation_keeps_its_cache_between_calls():
+@pytest.mark.parametrize("name", ["B", "W"])
+def test_a_conversation_keeps_its_cache_between_calls(name):
     """``LLM.conversation()``: the second and third call run only the new tokens of their prompts and draw what a
-    fresh generation from the whole prompt draws (float32, greedy: the plain implementation's tokens)."""
+    fresh generation from the whole prompt draws (float32, greedy: the plain implementation's tokens).  W has layers
+    with a window of 24 keys, whose pages are given back while the conversation goes on."""
     import synaptix_b200
-    cfg, W = oracle("B")
-    llm = synaptix_b200.LLM(folder("B"), compute_dtype="f32", max_tokens=1024)
-    turns = [random_tokens(389, n, 1500 + n) for n in (70, 9, 31)]
+    cfg, W = oracle(name)
+    llm = synaptix_b200.LLM(folder(name), compute_dtype="f32", max_tokens=1024)
+    turns = [random_tokens(cfg["vocab_size"], n, 1500 + n) for n in (70, 9, 31)]
     with llm.conversation() as conv:
         seq = []
         for k, new in enumerate(turns):
