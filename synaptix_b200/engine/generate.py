@@ -173,8 +173,12 @@ def run_generation(engine, sample: Callable, prompts: Sequence[Sequence[int]], o
             return False
         return True
 
-    for batch in plan_batches([len(p) for p in prompts], options.max_new_tokens, engine.max_tokens,
-                              engine.max_seqs, options.max_batch_size):
+    # what the cache can still take: all of it, unless sequences of other callers are open (a conversation beside this
+    # call); a sequence that goes on brings its own pages along
+    room_tokens = getattr(engine, "free_tokens", engine.max_tokens) if cached is None else engine.max_tokens
+    room_seqs = getattr(engine, "free_seqs", engine.max_seqs) if cached is None else engine.max_seqs
+    for batch in plan_batches([len(p) for p in prompts], options.max_new_tokens, room_tokens,
+                              max(1, room_seqs), options.max_batch_size):
         stats.batches += 1
         live = [_Live(i, engine.open(), prompts[i], cached[i] if cached is not None else 0) for i in batch]
         t0 = clock()

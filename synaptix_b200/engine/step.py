@@ -273,6 +273,15 @@ class Engine:
         return self.cache.max_seqs
 
     @property
+    def free_tokens(self) -> int:
+        """Tokens the pages hold that no open sequence has: what new sequences can still take."""
+        return min(pool.n_free for pool in self.cache.slots.pools) * PAGE_TOKENS
+
+    @property
+    def free_seqs(self) -> int:
+        return self.cache.max_seqs - self.cache.slots.n_live
+
+    @property
     def h2d_bytes(self) -> int:
         """Bytes of step index arrays uploaded from pinned host memory so far."""
         return self._staging.bytes_uploaded

@@ -210,5 +210,9 @@ def test_a_conversation_keeps_its_cache_between_calls(name):
     a = conv.generate(turns[0], max_new_tokens=3, eos_token_ids=[])
     assert llm.generate([turns[1], turns[2]], max_new_tokens=3, eos_token_ids=[]) == [P.greedy_generate(cfg, W, t, 3) for t in turns[1:]]
     assert conv.generate(turns[0] + a + [4], max_new_tokens=3, eos_token_ids=[]) == P.greedy_generate(cfg, W, turns[0] + a + [4], 3)
+    # requests that would fill the whole cache are cut into batches around what the conversation holds
+    many = [random_tokens(cfg["vocab_size"], 100, 1600 + i) for i in range(8)]           # 8 x 2 pages = the 16 pages of the cache
+    assert llm.generate(many, max_new_tokens=3, eos_token_ids=[]) == [P.greedy_generate(cfg, W, p, 3) for p in many]
+    assert llm.last_stats.batches == 2
     conv.close()
     assert llm.engine.cache.slots.n_live == 0
