@@ -10,9 +10,7 @@ from __future__ import annotations
 
 from typing import Callable, List, Optional, Sequence, Tuple
 
-import torch
-
-from .engine.generate import GenerationOptions, GenerationResult, GenerationStats, run_generation
+from .engine.generate import GenerationOptions, GenerationStats, run_generation
 from .engine.step import Engine
 from .models import load_model
 from .sampling import Sampler, SamplingParams

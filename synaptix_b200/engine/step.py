@@ -28,7 +28,7 @@ import numpy as np
 import torch
 
 from .. import ops
-from ..cache import PAGE_TOKENS, Cache, CacheFull, SlotError, pages_for
+from ..cache import PAGE_TOKENS, Cache, pages_for
 from ..csrc.build import KernelsUnavailable
 from ..parts.base import StepContext
 

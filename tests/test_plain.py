@@ -1,6 +1,5 @@
 """The plain implementation checked against itself and against first principles (CPU)."""
 import math
-import tempfile
 
 import numpy as np
 import pytest
