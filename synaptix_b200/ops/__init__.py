@@ -85,9 +85,21 @@ WS_FEW_ROWS_MIN_ELEMENTS = 15_000_000
 PROLOGUE_NORM_MAX_ROWS = 1
 
 
+_STREAM_KERNEL = {}
+
+
 def _weight_stream_kernel(M: int, N: int, K: int, x_dtype, w_dtype) -> Optional[str]:
     """Which weight-streaming product takes ``M <= 160`` rows against ``w[N, K]``: ``"skinny"`` (mma.sync, up to 16
-    rows), ``"ws"`` (tcgen05, up to 160 rows and 32,768 outputs) or ``None``."""
+    rows), ``"ws"`` (tcgen05, up to 160 rows and 32,768 outputs) or ``None``.  (Remembered per shape: a step asks
+    several times per product, and a prompt step of a few dozen tokens is bound by the host.)"""
+    key = (M, N, K, x_dtype, w_dtype, OPTIONS.gemm_ws)
+    kind = _STREAM_KERNEL.get(key, 0)
+    if kind == 0:
+        kind = _STREAM_KERNEL[key] = _pick_weight_stream_kernel(M, N, K, x_dtype, w_dtype)
+    return kind
+
+
+def _pick_weight_stream_kernel(M: int, N: int, K: int, x_dtype, w_dtype) -> Optional[str]:
     skinny = skinny_supported(M, N, K, x_dtype, w_dtype)
     ws = OPTIONS.gemm_ws and N <= WS_MAX_OUT and M <= WS_MAX_ROWS and ws_supported(M, N, K, x_dtype, w_dtype)
     if skinny and ws:
