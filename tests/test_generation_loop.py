@@ -282,3 +282,13 @@ def test_a_prompt_whose_beginning_is_cached_runs_only_the_rest():
     assert [r.tokens for r in results] == [[6, 7], [9, 10]] and [r.prompt_tokens for r in results] == [5, 2]
     with pytest.raises(ValueError):
         run_generation(CounterEngine(), sample, [[1, 2, 3]], GenerationOptions(max_new_tokens=2), cached=[3])
+
+
+def test_cached_tokens_and_portions_together():
+    """A prompt whose beginning is cached, run in portions: the portions are cut from what is left to run."""
+    sample = lambda logits, *a: list(logits)
+    eng = CounterEngine()
+    prompt = list(range(100, 112))                                   # 12 tokens, 5 of them cached: 7 run, in 3 + 3 + 1
+    results, stats = run_generation(eng, sample, [prompt], GenerationOptions(max_new_tokens=2, prefill_batch=3), cached=[5])
+    assert [n for st in eng.steps[:3] for _, n in st] == [3, 3, 1] and stats.prompt_tokens == 7
+    assert results[0].tokens == [112, 113]
